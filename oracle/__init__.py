@@ -1,0 +1,298 @@
+"""TEST INFRASTRUCTURE ONLY -- numpy/ctypes front end of the CPU oracle (`mimir_oracle.cpp`).
+
+Only the test-suite, the smoke check and the benchmark's CPU-baseline leg may import this package; the
+product (`mimir_b200`) never does.  The derived operators below are built on the generic
+`map_reduce_post` interpreter exactly the way the reference derives them (MimIR
+`src/mim/plug/tensor/tensor.mim`: `product_2d` 1422, `dot_product_impl` 1367-1411, `reduce` 1151-1157,
+`binary_ax` 1162-1167, `softmax` 1172-1176, `transpose` via access maps 1459) so that a mistake in a
+derivation shows up against the reference's own known answers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_ref", "libmimir_oracle.so")
+
+I32, I64, F32, F64, BF16 = 0, 1, 2, 3, 4
+_NP2DT = {np.dtype(np.int32): I32, np.dtype(np.int64): I64, np.dtype(np.float32): F32, np.dtype(np.float64): F64}
+_DT2NP = {I32: np.int32, I64: np.int64, F32: np.float32, F64: np.float64, BF16: np.uint16}
+
+# combiner / epilogue ids (keep in step with mimir_oracle.cpp)
+F_ADD_I32, F_MULADD_I32, F_MIX_I32_I64, F_ADD_F32, F_MULADD_F32, F_FMAX_F32, F_SUBEXP_F32, F_DIV_F32 = range(8)
+F_ADD2_F32, F_FIRST_F32, F_MULADD_F64, F_ADD_F64, F_FMIN_F32, F_MUL2_F32, F_FIRST_I32 = range(8, 15)
+P_ID, P_CONV_ADD_I64, P_ADD_PLUS1_I32, P_BIAS_RELU_F32, P_BIAS_TANH_F32, P_BIAS_F32, P_F64_TO_F32 = range(7)
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the committed Makefile (g++, a second or two)."""
+    src = os.path.join(_HERE, "mimir_oracle.cpp")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    return _SO
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        _lib.mo_map_reduce_post.restype = C.c_int
+    return _lib
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _i64(xs) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(list(xs), dtype=np.int64).reshape(-1))
+
+
+def to_bf16(x: np.ndarray) -> np.ndarray:
+    """f32 -> bf16 bit pattern (uint16), round to nearest even."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty(x.shape, dtype=np.uint16)
+    lib().mo_f32_to_bf16(_p(x), _p(y), C.c_int64(x.size))
+    return y
+
+
+def from_bf16(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    y = np.empty(x.shape, dtype=np.float32)
+    lib().mo_bf16_to_f32(_p(x), _p(y), C.c_int64(x.size))
+    return y
+
+
+# ---------------------------------------------------------------------------------------------
+# access maps: dense matrices of shape [results, n_loops + 1]; last column is the constant
+# ---------------------------------------------------------------------------------------------
+def proj_map(n_loops: int, subs) -> np.ndarray:
+    """`proj_map subs` (tensor.mim:196-203): result j reads loop variable subs[j]."""
+    subs = list(subs)
+    m = np.zeros((len(subs), n_loops + 1), dtype=np.int64)
+    for j, s in enumerate(subs):
+        m[j, s] = 1
+    return m
+
+
+def id_map(n: int) -> np.ndarray:
+    return proj_map(n, range(n))
+
+
+def map_reduce_post(So, Sr, f, init, post, map_out, maps, ins, post_maps=(), post_ins=(), out_dtype=None,
+                    in_dtypes=None, post_dtypes=None) -> np.ndarray:
+    """The one real op (tensor.mim:159-169).  `init` is a numpy scalar of the accumulator type."""
+    So, Sr = [int(s) for s in So], [int(s) for s in Sr]
+    Ro, Rn = len(So), len(Sr)
+    ins = [np.ascontiguousarray(a) for a in ins]
+    post_ins = [np.ascontiguousarray(a) for a in post_ins]
+    in_dt = list(in_dtypes) if in_dtypes else [_NP2DT[a.dtype] for a in ins]
+    p_dt = list(post_dtypes) if post_dtypes else [_NP2DT[a.dtype] for a in post_ins]
+    init = np.asarray(init)
+    acc_dt = _NP2DT[init.dtype]
+    if out_dtype is None:
+        out_dtype = acc_dt
+    init_bits = int(np.frombuffer(init.tobytes().ljust(8, b"\0"), dtype=np.int64)[0])
+    out = np.zeros(So if So else (), dtype=_DT2NP[out_dtype])
+
+    def pack(arrs, mps, n):
+        ranks = np.asarray([a.ndim for a in arrs], dtype=np.int32)
+        shapes = _i64(s for a in arrs for s in a.shape)
+        for a, m in zip(arrs, mps):
+            assert np.asarray(m).shape == (a.ndim, n + 1), (np.asarray(m).shape, a.ndim, n)
+        flat = _i64(v for m in mps for v in np.asarray(m, dtype=np.int64).reshape(-1))
+        ptrs = (C.c_void_p * max(1, len(arrs)))(*[a.ctypes.data for a in arrs])
+        return ranks, shapes, flat, ptrs
+
+    ir, ish, imp, iptr = pack(ins, maps, Rn)
+    pr, psh, pmp, pptr = pack(post_ins, post_maps, Ro)
+    idt = np.asarray(in_dt + [0], dtype=np.int32)
+    pdt = np.asarray(p_dt + [0], dtype=np.int32)
+    mo = _i64(np.asarray(map_out, dtype=np.int64).reshape(-1))
+    assert np.asarray(map_out).shape == (Ro, Rn + 1)
+    rc = lib().mo_map_reduce_post(
+        C.c_int(Ro), C.c_int(Rn), _p(_i64(Sr + [0])), _p(_i64(So + [0])),
+        C.c_int(len(ins)), iptr, _p(idt), _p(ir), _p(ish), _p(imp),
+        C.c_int(len(post_ins)), pptr, _p(pdt), _p(pr), _p(psh), _p(pmp),
+        _p(mo), C.c_int(f), C.c_int64(init_bits), C.c_int(post), C.c_int(out_dtype), _p(out))
+    if rc != 0:
+        raise ValueError(f"map_reduce_post: access outside a buffer or bad ranks (code {rc})")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# derived ops, as the reference derives them
+# ---------------------------------------------------------------------------------------------
+def product_2d(a: np.ndarray, b: np.ndarray, *, b_transposed: bool = False, mode: str = "f32",
+               post=P_ID, post_in=None) -> np.ndarray:
+    """`product_2d R (a, b)` = dot_product_impl with loops (m, l, k): maps (0,2) and (2,1) (tensor.mim:1422).
+    `b_transposed`: `b` is stored [l, k] and read through `transpose_2d` -- the map (1,2) of the stored tensor.
+    An epilogue input (bias [l]) is read at output coordinate 1 (fuse_epilogue, fuse.cpp:408-534)."""
+    m, k = a.shape
+    l = b.shape[0] if b_transposed else b.shape[1]
+    maps = [proj_map(3, (0, 2)), proj_map(3, (1, 2) if b_transposed else (2, 1))]
+    if a.dtype == np.int32:
+        f, init = F_MULADD_I32, np.int32(0)
+    elif mode == "f64":
+        f, init = F_MULADD_F64, np.float64(0)
+    else:
+        f, init = F_MULADD_F32, np.float32(0)
+    pm, pi = ([proj_map(2, (1,))], [post_in]) if post_in is not None else ([], [])
+    return map_reduce_post((m, l), (m, l, k), f, init, post, proj_map(3, (0, 1)), maps, [a, b], pm, pi)
+
+
+def reduce(x: np.ndarray, ax: int, monoid: str = "sum", mode: str = "f32") -> np.ndarray:
+    """`reduce (g, init) ax x` (tensor.mim:1151-1157): output axes lead, `ax` is the trailing loop."""
+    r = x.ndim
+    so = [s for i, s in enumerate(x.shape) if i != ax]
+    sr = so + [x.shape[ax]]
+    subs = [j if j < ax else (r - 1 if j == ax else j - 1) for j in range(r)]
+    if x.dtype == np.int32:
+        f, init = F_ADD_I32, np.int32(0)
+    elif monoid == "sum":
+        f, init = (F_ADD_F64, np.float64(0)) if mode == "f64" else (F_ADD_F32, np.float32(0))
+    elif monoid == "max":
+        f, init = F_FMAX_F32, np.float32(-np.inf)
+    else:
+        f, init = F_FMIN_F32, np.float32(np.inf)
+    return map_reduce_post(so, sr, f, init, P_ID, proj_map(r, range(r - 1)), [proj_map(r, subs)], [x])
+
+
+def binary_ax(app: int, ax: int, x: np.ndarray, y: np.ndarray) -> np.ndarray:
+    """`binary_ax app ax (x, y)` (tensor.mim:1162-1167): y lacks axis ax and is broadcast along it."""
+    r = x.ndim
+    subs = [i if i < ax else i + 1 for i in range(r - 1)]
+    return map_reduce_post(x.shape, x.shape, app, np.float32(0), P_ID, id_map(r), [id_map(r), proj_map(r, subs)],
+                           [x, y])
+
+
+def softmax(x: np.ndarray, ax: int) -> np.ndarray:
+    """The four map_reduce ops of the `softmax` lam (tensor.mim:1172-1176)."""
+    mx = reduce(x, ax, "max")
+    e = binary_ax(F_SUBEXP_F32, ax, x, mx)
+    return binary_ax(F_DIV_F32, ax, e, reduce(e, ax, "sum"))
+
+
+def transpose_2d(x: np.ndarray) -> np.ndarray:
+    f, init = (F_FIRST_I32, np.int32(0)) if x.dtype == np.int32 else (F_FIRST_F32, np.float32(0))
+    return map_reduce_post(x.shape[::-1], x.shape[::-1], f, init, P_ID, id_map(2), [proj_map(2, (1, 0))], [x])
+
+
+def attention_composed(x, wq, wk, wv) -> np.ndarray:
+    """lit/tensor/attn_exec.mim:20-22: softmax(q k^T) v with q,k,v = x wq, x wk, x wv (f32, as lowered)."""
+    q, k, v = product_2d(x, wq), product_2d(x, wk), product_2d(x, wv)
+    return product_2d(softmax(product_2d(q, k, b_transposed=True), 1), v)
+
+
+# ---------------------------------------------------------------------------------------------
+# direct loops (larger sizes; same per-cell fold order)
+# ---------------------------------------------------------------------------------------------
+def _rows(rows):
+    if rows is None:
+        return None, 0
+    r = _i64(rows)
+    return r, r.size
+
+
+def gemm(a, b, *, b_nk=False, bf16=False) -> np.ndarray:
+    """As lowered: f32 accumulator, ascending k.  bf16=True: inputs are uint16 bf16 bit patterns."""
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    m, k = a.shape
+    n = b.shape[0] if b_nk else b.shape[1]
+    c = np.empty((m, n), dtype=np.float32)
+    fn = lib().mo_gemm_bf16 if bf16 else lib().mo_gemm_f32
+    fn(_p(a), _p(b), _p(c), C.c_int64(m), C.c_int64(n), C.c_int64(k), C.c_int(int(b_nk)))
+    return c
+
+
+def gemm_truth(a, b, *, b_nk=False, bf16=False, rows=None) -> np.ndarray:
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    m, k = a.shape
+    n = b.shape[0] if b_nk else b.shape[1]
+    r, nr = _rows(rows)
+    c = np.empty((nr or m, n), dtype=np.float64)
+    fn = lib().mo_gemm_truth_bf16 if bf16 else lib().mo_gemm_truth_f32
+    fn(_p(a), _p(b), _p(c), C.c_int64(m), C.c_int64(n), C.c_int64(k), C.c_int(int(b_nk)),
+       _p(r) if nr else None, C.c_int64(nr))
+    return c
+
+
+_MONOID = {"sum": 0, "max": 1, "min": 2}
+
+
+def reduce_axis(x, ax: int, monoid="sum", truth=False) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    outer = int(np.prod(x.shape[:ax], dtype=np.int64))
+    inner = int(np.prod(x.shape[ax + 1:], dtype=np.int64))
+    shape = x.shape[:ax] + x.shape[ax + 1:]
+    out = np.empty(shape, dtype=np.float64 if truth else np.float32)
+    fn = lib().mo_reduce_truth if truth else lib().mo_reduce_f32
+    fn(_p(x), _p(out), C.c_int64(outer), C.c_int64(x.shape[ax]), C.c_int64(inner), C.c_int(_MONOID[monoid]))
+    return out
+
+
+def softmax_rows(x, truth=False) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty(x.shape, dtype=np.float64 if truth else np.float32)
+    fn = lib().mo_softmax_rows_truth if truth else lib().mo_softmax_rows_f32
+    fn(_p(x), _p(y), C.c_int64(x.shape[0]), C.c_int64(x.shape[1]))
+    return y
+
+
+def rmsnorm_rows(x, gamma, eps, truth=False) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    gamma = np.ascontiguousarray(gamma, dtype=np.float32)
+    y = np.empty(x.shape, dtype=np.float64 if truth else np.float32)
+    if truth:
+        lib().mo_rmsnorm_rows_truth(_p(x), _p(gamma), _p(y), C.c_int64(x.shape[0]), C.c_int64(x.shape[1]),
+                                    C.c_double(eps))
+    else:
+        lib().mo_rmsnorm_rows_f32(_p(x), _p(gamma), _p(y), C.c_int64(x.shape[0]), C.c_int64(x.shape[1]),
+                                  C.c_float(eps))
+    return y
+
+
+def attention(q, k, v, *, scale=1.0, causal=False, bf16=False, truth=True, heads=None) -> np.ndarray:
+    """q,k,v: [BH, S, D].  truth: f64 (the reference driver's check); else f32 as lowered (all heads)."""
+    q, k, v = (np.ascontiguousarray(t) for t in (q, k, v))
+    bh, s, d = q.shape
+    if truth:
+        h, nh = _rows(heads)
+        o = np.empty((nh or bh, s, d), dtype=np.float64)
+        fn = lib().mo_attn_truth_bf16 if bf16 else lib().mo_attn_truth_f32
+        fn(_p(q), _p(k), _p(v), _p(o), C.c_int64(bh), C.c_int64(s), C.c_int64(d), C.c_double(scale),
+           C.c_int(int(causal)), _p(h) if nh else None, C.c_int64(nh))
+    else:
+        o = np.empty((bh, s, d), dtype=np.float32)
+        fn = lib().mo_attn_bf16 if bf16 else lib().mo_attn_f32
+        fn(_p(q), _p(k), _p(v), _p(o), C.c_int64(bh), C.c_int64(s), C.c_int64(d), C.c_float(scale),
+           C.c_int(int(causal)))
+    return o
+
+
+def mlp_gated_truth(x, w1, w3, w2, rows=None) -> np.ndarray:
+    """bf16 bit-pattern inputs; x [M,K], w1/w3 [K,F], w2 [F,N]; returns f64 [rows or M, N]."""
+    x, w1, w3, w2 = (np.ascontiguousarray(t, dtype=np.uint16) for t in (x, w1, w3, w2))
+    m, k = x.shape
+    f = w1.shape[1]
+    n = w2.shape[1]
+    r, nr = _rows(rows)
+    y = np.empty((nr or m, n), dtype=np.float64)
+    lib().mo_mlp_truth_bf16(_p(x), _p(w1), _p(w3), _p(w2), _p(y), C.c_int64(m), C.c_int64(k), C.c_int64(f),
+                            C.c_int64(n), _p(r) if nr else None, C.c_int64(nr))
+    return y
+
+
+def normalised_error(got, want) -> float:
+    """max|got - want| / max|want| per tensor -- the parity metric every report states."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    denom = float(np.max(np.abs(want))) or 1.0
+    return float(np.max(np.abs(got - want))) / denom
