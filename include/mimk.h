@@ -1,0 +1,193 @@
+/* mimk.h -- C ABI of the B200 (sm_100a) kernel library behind MimIR's `tensor` plugin.
+ *
+ * Every entry point is what a lowered `tensor.*` / `btensor.map_reduce_post` call binds to once the
+ * `gpu.lower_btensor_map_reduce` phase emits launcher calls instead of one-thread-per-cell NVPTX kernels.
+ * The "replaces" notes give the reference interface (paths inside the MimIR project) each one stands in for.
+ *
+ * Conventions (from the reference's run-time ABI, lit/tensor/hlo_aux.cpp:19-23, lit/tensor/fc_aux.cpp:10-14):
+ *   - a tensor is a bare pointer to a dense row-major buffer; shapes travel as int64_t;
+ *   - unless a name contains `_host_`, every pointer is a DEVICE pointer valid on the current CUDA device and
+ *     the call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the default stream);
+ *   - every call returns an int status (0 = ok) instead of aborting, so emitted code can pipe it to
+ *     `mim_cu_check(int)` (src/mim/plug/nvptx/rt/mim_cuda_rt.c:16-21) exactly like a CUresult;
+ *   - nothing here falls back to the CPU: without a usable sm_100 device every compute call fails with
+ *     MIMK_E_NO_DEVICE.
+ */
+#ifndef MIMK_H_
+#define MIMK_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MIMK_ABI_VERSION 1
+
+/* ---- element types (math.F32 / math.BF16, src/mim/plug/math/math.mim:26,34; I32/I64 of the core plugin) ---- */
+enum { MIMK_F32 = 0, MIMK_BF16 = 1, MIMK_I32 = 2, MIMK_I64 = 3 };
+
+/* ---- status codes ---- */
+enum {
+    MIMK_OK = 0,
+    MIMK_E_ARG = 1,         /* null pointer, negative extent, unknown enum value */
+    MIMK_E_SHAPE = 2,       /* extents inconsistent with each other */
+    MIMK_E_ALIGN = 3,       /* a pointer or leading dimension misses the alignment the kernel needs */
+    MIMK_E_DTYPE = 4,       /* this dtype combination has no kernel */
+    MIMK_E_CUDA = 5,        /* a CUDA runtime/driver call failed; see mimk_last_cuda_error() */
+    MIMK_E_NO_DEVICE = 6,   /* no CUDA device, or not compute capability 10.x */
+    MIMK_E_DEVICE_WAIT = 7, /* a bounded wait inside a kernel expired (reported by mimk_device_status) */
+    MIMK_E_UNSUPPORTED = 8, /* well-formed request outside what the kernels cover */
+    MIMK_E_WORKSPACE = 9,   /* scratch buffer missing or too small */
+};
+
+/* Human-readable name of a status code. Never NULL. */
+const char* mimk_status_str(int status);
+/* MIMK_ABI_VERSION the library was built with (cf. Plugin::version, include/mim/plugin.h:159). */
+int mimk_abi_version(void);
+/* cudaError_t of the most recent failed CUDA call on this host thread (0 if none). */
+int mimk_last_cuda_error(void);
+/* MIMK_OK iff the current device can run the kernels (compute capability 10.x). */
+int mimk_device_check(void);
+/* Synchronises `stream` and returns MIMK_E_DEVICE_WAIT if any kernel since the last call gave up on a bounded
+ * wait (its results are then undefined), MIMK_OK otherwise. Clears the flag. */
+int mimk_device_status(void* stream);
+
+/* ---- reduction monoids: the (g, init) pairs handed to `reduce` / `pool_fun`
+ *      (src/mim/plug/tensor/tensor.mim:1139-1157): sum = (arith.add, 0), max = (extrema.fmax, -inf), ... ---- */
+enum { MIMK_SUM = 0, MIMK_MAX = 1, MIMK_MIN = 2 };
+
+/* ---- epilogues: what `fuse_tensor` sinks into the `post` slot of a reducing map_reduce_post
+ *      (src/mim/plug/tensor/phase/fuse.cpp:408-534); `row` operands are epilogue inputs read at output
+ *      coordinate 1 (a bias broadcast over rows), `full` operands at identity coordinates. ---- */
+enum {
+    MIMK_POST_ID = 0,
+    MIMK_POST_BIAS = 1,      /* acc + row[n] */
+    MIMK_POST_BIAS_RELU = 2, /* fmax(0, acc + row[n])            lit/tensor/fc_exec.mim:27-31 */
+    MIMK_POST_BIAS_TANH = 3, /* tanh(acc + row[n])               lit/tensor/hlo_exec.mim */
+    MIMK_POST_RELU = 4,      /* fmax(0, acc) */
+    MIMK_POST_SILU = 5,      /* acc * slf(acc)                    math.slf, src/mim/plug/math/math.mim:283-284 */
+    MIMK_POST_ADD_FULL = 6,  /* acc + full[m,n] */
+};
+
+/* ---- right-operand layouts of the dot family ---- */
+enum {
+    MIMK_B_KN = 0, /* B stored row-major [K,N]:  product_2d (a, b)                    tensor.mim:510-513 */
+    MIMK_B_NK = 1, /* B stored row-major [N,K]:  product_2d (a, transpose_2d w), the read-through of
+                      fuse.cpp:542-589 -- "column-major B" */
+};
+
+/* C[b,m,n] = post(sum_k A[b,m,k] * B[b,k,n]).
+ * Replaces: tensor.product_2d / tensor.bmm / 2-D tensor.dot_product lowered through dot_product_impl
+ * (src/mim/plug/tensor/tensor.mim:404-407, 480-486, 510-513, 1367-1423) and the kernel that
+ * gpu::phase::LowerMapReduce::build_kernel generates for them (src/mim/plug/gpu/phase/lower_map_reduce.cpp:148-265).
+ * in_dtype F32: f32 accumulation in ascending k per cell. in_dtype BF16: f32 accumulation on the tensor cores.
+ * out_dtype F32 or BF16 (round to nearest even). batch strides are in elements; 0 re-uses the operand. */
+typedef struct mimk_gemm_desc {
+    int64_t batch, m, n, k;
+    const void* a;
+    const void* b;
+    void* c;
+    int64_t stride_a, stride_b, stride_c;
+    int32_t in_dtype, out_dtype, b_layout, post;
+    const void* post_row;  /* f32 [n], or NULL */
+    const void* post_full; /* out_dtype [m,n] per batch, or NULL */
+} mimk_gemm_desc;
+int mimk_gemm(const mimk_gemm_desc* desc, void* stream);
+
+/* out[o,i] = fold_a g(x[o,a,i]) over the middle axis of a [outer, len, inner] view; inner == 1 is a row reduce.
+ * Replaces: tensor.reduce (tensor.mim:1151-1157) lowered by gpu.lower_btensor_map_reduce. dtype F32 (x and out). */
+int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner, int monoid,
+                void* stream);
+
+/* y = softmax(x) along the middle axis of a [outer, len, inner] view, in one pass over HBM.
+ * Replaces: the four map_reduce_post ops the `softmax` lam expands to (tensor.mim:1172-1176).
+ * x F32 (or BF16), y F32 or BF16; statistics in f32. */
+int mimk_softmax(const void* x, void* y, int in_dtype, int out_dtype, int64_t outer, int64_t len, int64_t inner,
+                 void* stream);
+
+/* y[r,c] = x[r,c] * rrt(mean_c(x[r,:]^2) + eps) * gamma[c].
+ * Replaces: the reduce + binary_ax + math.rrt chain (tensor.mim:1151-1167, math.mim:297-298). gamma F32. */
+int mimk_rmsnorm(const void* x, const void* gamma, void* y, int in_dtype, int out_dtype, int64_t rows, int64_t cols,
+                 float eps, void* stream);
+
+/* y = rmsnorm(softmax_rows(x)) fused into one pass (the chained reading of "row softmax + RMSNorm"). */
+int mimk_softmax_rmsnorm(const void* x, const void* gamma, void* y, int in_dtype, int out_dtype, int64_t rows,
+                         int64_t cols, float eps, void* stream);
+
+/* ---- elementwise: tensor.unary / tensor.binary / binary_ax (tensor.mim:361-394, 1162-1167) ---- */
+enum {
+    MIMK_OP_ADD = 0, MIMK_OP_SUB = 1, MIMK_OP_MUL = 2, MIMK_OP_DIV = 3, MIMK_OP_MAX = 4, MIMK_OP_MIN = 5,
+    MIMK_OP_SUBEXP = 6, /* exp(x - y): the softmax producer, tensor.mim:1175 */
+    /* unary (y operand ignored) */
+    MIMK_OP_RELU = 16, MIMK_OP_TANH = 17, MIMK_OP_EXP = 18, MIMK_OP_SILU = 19, MIMK_OP_NEG = 20, MIMK_OP_COPY = 21,
+};
+/* out[o,a,i] = op(x[o,a,i], y[...]) over a [outer, len, inner] view of x (F32).
+ * y_mode 0: y has x's shape (tensor.binary); 1: y is [outer, inner], broadcast along the middle axis
+ * (binary_ax); 2: y is [len*inner], broadcast over `outer` (a bias row); 3: unary, y unused. */
+int mimk_map(int op, const void* x, const void* y, void* out, int out_dtype, int64_t outer, int64_t len,
+             int64_t inner, int y_mode, void* stream);
+
+/* O[h,i,:] = softmax_j(scale * Q[h,i,:].K[h,j,:] (+ causal mask j <= i + seq_k - seq_q)) V[h,j,:].
+ * Replaces: the composed program `softmax (q * transpose_2d k) * v` (lit/tensor/attn_exec.mim:20-22), seven
+ * map_reduce_post ops with a materialised score matrix; scale, mask and batching are extensions.
+ * q,o: [batch_heads, seq_q, head_dim]; k,v: [batch_heads, seq_k, head_dim]; dtype F32 or BF16 (o same dtype);
+ * lse (optional, f32 [batch_heads, seq_q]) receives log-sum-exp of the scaled scores. */
+typedef struct mimk_attn_desc {
+    int64_t batch_heads, seq_q, seq_k, head_dim;
+    const void* q;
+    const void* k;
+    const void* v;
+    void* o;
+    float* lse;
+    float scale;
+    int32_t causal, dtype;
+} mimk_attn_desc;
+int mimk_attn_fwd(const mimk_attn_desc* desc, void* stream);
+
+/* Y = (silu(X W1) * (X W3)) W2 with the gated product H kept in `dtype`.
+ * Replaces: two product_2d + math.slf + binary mul (epilogue-fused into one contraction) + product_2d.
+ * x [m,k]; w1,w3 [k,f] (b_layout KN) or [f,k] (NK); w2 [f,n] (KN) or [n,f] (NK); y [m,n].
+ * h is scratch for the [m,f] intermediate (dtype elements); NULL lets the library use its own cached buffer. */
+typedef struct mimk_mlp_desc {
+    int64_t m, k, f, n;
+    const void* x;
+    const void* w1;
+    const void* w3;
+    const void* w2;
+    void* y;
+    void* h;
+    int32_t dtype, b_layout;
+} mimk_mlp_desc;
+int mimk_mlp_gated(const mimk_mlp_desc* desc, void* stream);
+
+/* ---- host-buffer forms -------------------------------------------------------------------------------
+ * Same operators with HOST pointers: inputs are copied to the device, the kernel runs, the result is copied
+ * back and the call returns when the result is in host memory.
+ * Replaces: the per-operation wrapper gpu.lower_btensor_map_reduce emits around its kernel -- gpu.buf_alloc_copy
+ * for every input and epilogue input, gpu.alloc.block for the output, gpu.launch, gpu.buf_copy_to_host, gpu.free
+ * (src/mim/plug/gpu/phase/lower_map_reduce.cpp:111-126, 267-297, 317-395), i.e. the run-time ABI
+ * `extern "C" T* f(T* in0, ...)` of an emitted tensor function (lit/tensor/hlo_aux.cpp:19-23).
+ * Differences in mechanism only: device buffers come from a cached per-device arena instead of cuMemAlloc/cuMemFree
+ * per call, copies are asynchronous on private streams, and row-wise operators stream the matrix through the device
+ * in row blocks so that upload, kernel and download overlap. Copies run at full speed only from page-locked host
+ * memory (mimk_host_register or any cudaHostAlloc/cudaHostRegister'd buffer); pageable memory works but is slower. */
+enum { MIMK_ROWS_SOFTMAX = 0, MIMK_ROWS_RMSNORM = 1, MIMK_ROWS_SOFTMAX_RMSNORM = 2 };
+int mimk_host_rows(int kind, const void* x, const void* gamma, void* y, int in_dtype, int out_dtype, int64_t rows,
+                   int64_t cols, float eps);
+/* desc holds host pointers (a, b, c, post_row, post_full). */
+int mimk_host_gemm(const mimk_gemm_desc* desc);
+/* desc holds host pointers (q, k, v, o, lse). */
+int mimk_host_attn_fwd(const mimk_attn_desc* desc);
+/* desc holds host pointers (x, w1, w3, w2, y); h is ignored. */
+int mimk_host_mlp_gated(const mimk_mlp_desc* desc);
+/* Page-lock / unlock a host range so that the copies above are asynchronous DMA. */
+int mimk_host_register(void* ptr, uint64_t bytes);
+int mimk_host_unregister(void* ptr);
+/* Release the cached device arena of the current device (it is otherwise kept until process exit). */
+int mimk_host_release(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIMK_H_ */

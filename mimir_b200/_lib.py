@@ -1,0 +1,105 @@
+"""ctypes binding of libmimk.so -- the C ABI declared in include/mimk.h.
+
+The library is loaded from this directory (built in-tree by `mimir_b200.build`).  There is no fallback: if it is
+missing, importing fails, and if no sm_100 device is present every compute call raises MimkError.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmimk.so")
+
+F32, BF16, I32, I64 = 0, 1, 2, 3
+SUM, MAX, MIN = 0, 1, 2
+POST_ID, POST_BIAS, POST_BIAS_RELU, POST_BIAS_TANH, POST_RELU, POST_SILU, POST_ADD_FULL = range(7)
+B_KN, B_NK = 0, 1
+OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MAX, OP_MIN, OP_SUBEXP = range(7)
+OP_RELU, OP_TANH, OP_EXP, OP_SILU, OP_NEG, OP_COPY = range(16, 22)
+E_DEVICE_WAIT = 7
+ROWS_SOFTMAX, ROWS_RMSNORM, ROWS_SOFTMAX_RMSNORM = 0, 1, 2
+
+# every symbol include/mimk.h declares
+SYMBOLS = (
+    "mimk_status_str", "mimk_abi_version", "mimk_last_cuda_error", "mimk_device_check", "mimk_device_status",
+    "mimk_gemm", "mimk_reduce", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map",
+    "mimk_attn_fwd", "mimk_mlp_gated",
+    "mimk_host_rows", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_register",
+    "mimk_host_unregister", "mimk_host_release",
+)
+
+
+class MimkError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().mimk_status_str(status).decode()
+        if status == 5:
+            msg += f" (cudaError {lib().mimk_last_cuda_error()})"
+        super().__init__(f"{where}: {msg} [status {status}]")
+
+
+class GemmDesc(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int64), ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p),
+        ("stride_a", C.c_int64), ("stride_b", C.c_int64), ("stride_c", C.c_int64),
+        ("in_dtype", C.c_int32), ("out_dtype", C.c_int32), ("b_layout", C.c_int32), ("post", C.c_int32),
+        ("post_row", C.c_void_p), ("post_full", C.c_void_p),
+    ]
+
+
+class AttnDesc(C.Structure):
+    _fields_ = [
+        ("batch_heads", C.c_int64), ("seq_q", C.c_int64), ("seq_k", C.c_int64), ("head_dim", C.c_int64),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("scale", C.c_float), ("causal", C.c_int32), ("dtype", C.c_int32),
+    ]
+
+
+class MlpDesc(C.Structure):
+    _fields_ = [
+        ("m", C.c_int64), ("k", C.c_int64), ("f", C.c_int64), ("n", C.c_int64),
+        ("x", C.c_void_p), ("w1", C.c_void_p), ("w3", C.c_void_p), ("w2", C.c_void_p), ("y", C.c_void_p),
+        ("h", C.c_void_p), ("dtype", C.c_int32), ("b_layout", C.c_int32),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m mimir_b200.build` (there is no fallback path)")
+        L = C.CDLL(LIB_PATH)
+        L.mimk_status_str.restype = C.c_char_p
+        L.mimk_status_str.argtypes = [C.c_int]
+        i64, vp, ci, cf = C.c_int64, C.c_void_p, C.c_int, C.c_float
+        L.mimk_device_status.argtypes = [vp]
+        L.mimk_gemm.argtypes = [C.POINTER(GemmDesc), vp]
+        L.mimk_reduce.argtypes = [vp, vp, ci, i64, i64, i64, ci, vp]
+        L.mimk_softmax.argtypes = [vp, vp, ci, ci, i64, i64, i64, vp]
+        L.mimk_rmsnorm.argtypes = [vp, vp, vp, ci, ci, i64, i64, cf, vp]
+        L.mimk_softmax_rmsnorm.argtypes = [vp, vp, vp, ci, ci, i64, i64, cf, vp]
+        L.mimk_map.argtypes = [ci, vp, vp, vp, ci, i64, i64, i64, ci, vp]
+        L.mimk_attn_fwd.argtypes = [C.POINTER(AttnDesc), vp]
+        L.mimk_mlp_gated.argtypes = [C.POINTER(MlpDesc), vp]
+        L.mimk_host_rows.argtypes = [ci, vp, vp, vp, ci, ci, i64, i64, cf]
+        L.mimk_host_gemm.argtypes = [C.POINTER(GemmDesc)]
+        L.mimk_host_attn_fwd.argtypes = [C.POINTER(AttnDesc)]
+        L.mimk_host_mlp_gated.argtypes = [C.POINTER(MlpDesc)]
+        L.mimk_host_register.argtypes = [vp, C.c_uint64]
+        L.mimk_host_unregister.argtypes = [vp]
+        for name in SYMBOLS:
+            fn = getattr(L, name)
+            if name != "mimk_status_str":
+                fn.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        raise MimkError(status, where)

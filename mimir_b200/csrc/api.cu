@@ -1,0 +1,185 @@
+// C-ABI entry points that only validate and dispatch, plus the per-device state of the library.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace mimk {
+
+static thread_local int g_last_cuda_error = 0;
+
+int note_cuda_error(cudaError_t e) {
+    if (e == cudaSuccess) return MIMK_OK;
+    g_last_cuda_error = int(e);
+    return MIMK_E_CUDA;
+}
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+DeviceInfo g_devices[MAX_DEVICES];
+bool g_device_ready[MAX_DEVICES];
+std::mutex g_mutex;
+}  // namespace
+
+DeviceInfo* device_info(int* status) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        cudaGetLastError();
+        *status = MIMK_E_NO_DEVICE;
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceInfo& d = g_devices[dev];
+    if (!g_device_ready[dev]) {
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+            cudaGetLastError();
+            *status = MIMK_E_NO_DEVICE;
+            return nullptr;
+        }
+        if (prop.major != 10) {  // the kernels are built for sm_100a only
+            *status = MIMK_E_NO_DEVICE;
+            return nullptr;
+        }
+        d.device   = dev;
+        d.sm_count = prop.multiProcessorCount;
+        d.cc_major = prop.major;
+        int* host  = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void**>(&host), 64, cudaHostAllocMapped) != cudaSuccess ||
+            cudaHostGetDevicePointer(reinterpret_cast<void**>(&d.status_dev), host, 0) != cudaSuccess) {
+            *status = note_cuda_error(cudaGetLastError());
+            return nullptr;
+        }
+        *host              = 0;
+        d.status_host      = host;
+        g_device_ready[dev] = true;
+    }
+    return &d;
+}
+
+int get_scratch(size_t bytes, void** out) {
+    int st        = MIMK_OK;
+    DeviceInfo* d = device_info(&st);
+    if (!d) return st;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (d->scratch_bytes < bytes) {
+        if (d->scratch) {
+            // work queued on any stream may still use the old buffer
+            MIMK_CUDA_TRY(cudaDeviceSynchronize());
+            MIMK_CUDA_TRY(cudaFree(d->scratch));
+            d->scratch       = nullptr;
+            d->scratch_bytes = 0;
+        }
+        size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+        MIMK_CUDA_TRY(cudaMalloc(&d->scratch, want));
+        d->scratch_bytes = want;
+    }
+    *out = d->scratch;
+    return MIMK_OK;
+}
+
+}  // namespace mimk
+
+using namespace mimk;
+
+extern "C" const char* mimk_status_str(int status) {
+    switch (status) {
+        case MIMK_OK: return "ok";
+        case MIMK_E_ARG: return "invalid argument";
+        case MIMK_E_SHAPE: return "inconsistent shape";
+        case MIMK_E_ALIGN: return "misaligned pointer or extent";
+        case MIMK_E_DTYPE: return "unsupported element type combination";
+        case MIMK_E_CUDA: return "CUDA call failed";
+        case MIMK_E_NO_DEVICE: return "no usable sm_100 device";
+        case MIMK_E_DEVICE_WAIT: return "bounded device-side wait expired";
+        case MIMK_E_UNSUPPORTED: return "unsupported configuration";
+        case MIMK_E_WORKSPACE: return "scratch buffer missing or too small";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int mimk_abi_version(void) { return MIMK_ABI_VERSION; }
+extern "C" int mimk_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int mimk_device_check(void) {
+    int st = MIMK_OK;
+    return device_info(&st) ? MIMK_OK : st;
+}
+
+extern "C" int mimk_device_status(void* stream) {
+    int st        = MIMK_OK;
+    DeviceInfo* d = device_info(&st);
+    if (!d) return st;
+    MIMK_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    const int flag = *d->status_host;
+    *d->status_host = 0;
+    return flag ? MIMK_E_DEVICE_WAIT : MIMK_OK;
+}
+
+static int check_gemm(const mimk_gemm_desc* d) {
+    if (!d) return MIMK_E_ARG;
+    if (d->batch < 0 || d->m < 0 || d->n < 0 || d->k < 0) return MIMK_E_ARG;
+    if (d->in_dtype != MIMK_F32 && d->in_dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    if (d->out_dtype != MIMK_F32 && d->out_dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    if (d->b_layout != MIMK_B_KN && d->b_layout != MIMK_B_NK) return MIMK_E_ARG;
+    if (d->post < MIMK_POST_ID || d->post > MIMK_POST_ADD_FULL) return MIMK_E_ARG;
+    if (d->stride_a < 0 || d->stride_b < 0 || d->stride_c < 0) return MIMK_E_ARG;
+    const bool needs_row  = d->post == MIMK_POST_BIAS || d->post == MIMK_POST_BIAS_RELU || d->post == MIMK_POST_BIAS_TANH;
+    const bool needs_full = d->post == MIMK_POST_ADD_FULL;
+    if (needs_row && !d->post_row) return MIMK_E_ARG;
+    if (needs_full && !d->post_full) return MIMK_E_ARG;
+    if (d->batch > 1 && d->stride_c < d->m * d->n) return MIMK_E_SHAPE;  // output batches must not overlap
+    return MIMK_OK;
+}
+
+extern "C" int mimk_gemm(const mimk_gemm_desc* d, void* stream) {
+    MIMK_TRY(check_gemm(d));
+    int st = MIMK_OK;
+    if (!device_info(&st)) return st;
+    if (d->batch == 0 || d->m == 0 || d->n == 0) return MIMK_OK;
+    if (!d->c || (d->k > 0 && (!d->a || !d->b))) return MIMK_E_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (gemm_tc_supported(*d)) return gemm_tc(*d, s, 0, nullptr);
+    return gemm_simt(*d, s);
+}
+
+extern "C" int mimk_attn_fwd(const mimk_attn_desc* d, void* stream) {
+    if (!d) return MIMK_E_ARG;
+    if (d->batch_heads < 0 || d->seq_q < 0 || d->seq_k < 0 || d->head_dim < 0) return MIMK_E_ARG;
+    if (d->dtype != MIMK_F32 && d->dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    int st = MIMK_OK;
+    if (!device_info(&st)) return st;
+    if (d->batch_heads == 0 || d->seq_q == 0 || d->head_dim == 0) return MIMK_OK;
+    if (!d->q || !d->o || (d->seq_k > 0 && (!d->k || !d->v))) return MIMK_E_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (attn_tc_supported(*d)) return attn_tc(*d, s);
+    return attn_simt(*d, s);
+}
+
+extern "C" int mimk_mlp_gated(const mimk_mlp_desc* d, void* stream) {
+    if (!d) return MIMK_E_ARG;
+    if (d->m < 0 || d->k < 0 || d->f < 0 || d->n < 0) return MIMK_E_ARG;
+    if (d->dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    if (d->b_layout != MIMK_B_KN && d->b_layout != MIMK_B_NK) return MIMK_E_ARG;
+    int st = MIMK_OK;
+    if (!device_info(&st)) return st;
+    if (d->m == 0 || d->n == 0) return MIMK_OK;
+    if (!d->x || !d->w1 || !d->w3 || !d->w2 || !d->y) return MIMK_E_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    void* h        = d->h;
+    if (!h) MIMK_TRY(get_scratch(size_t(d->m) * size_t(d->f) * 2, &h));
+    // stage 1: H = silu(X W1) * (X W3), both contractions in one kernel with two accumulators
+    mimk_gemm_desc g1 = {};
+    g1.batch = 1, g1.m = d->m, g1.n = d->f, g1.k = d->k;
+    g1.a = d->x, g1.b = d->w1, g1.c = h;
+    g1.in_dtype = MIMK_BF16, g1.out_dtype = MIMK_BF16, g1.b_layout = d->b_layout, g1.post = MIMK_POST_ID;
+    if (!gemm_tc_supported(g1)) return MIMK_E_UNSUPPORTED;
+    MIMK_TRY(gemm_tc(g1, s, 1, d->w3));
+    // stage 2: Y = H W2
+    mimk_gemm_desc g2 = {};
+    g2.batch = 1, g2.m = d->m, g2.n = d->n, g2.k = d->f;
+    g2.a = h, g2.b = d->w2, g2.c = d->y;
+    g2.in_dtype = MIMK_BF16, g2.out_dtype = MIMK_BF16, g2.b_layout = d->b_layout, g2.post = MIMK_POST_ID;
+    if (gemm_tc_supported(g2)) return gemm_tc(g2, s, 0, nullptr);
+    return gemm_simt(g2, s);
+}

@@ -1,0 +1,90 @@
+// Shared host/device helpers of the mimk kernel library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mimk.h"
+
+namespace mimk {
+
+// ---- host side ------------------------------------------------------------------------------------
+// Records a failed CUDA call for mimk_last_cuda_error() and maps it to MIMK_E_CUDA.
+int note_cuda_error(cudaError_t e);
+#define MIMK_CUDA_TRY(expr)                                        \
+    do {                                                           \
+        cudaError_t mimk_e_ = (expr);                              \
+        if (mimk_e_ != cudaSuccess) return note_cuda_error(mimk_e_); \
+    } while (0)
+#define MIMK_TRY(expr)                    \
+    do {                                  \
+        int mimk_s_ = (expr);             \
+        if (mimk_s_ != MIMK_OK) return mimk_s_; \
+    } while (0)
+
+inline int launch_status() { return note_cuda_error(cudaGetLastError()); }
+
+struct DeviceInfo {
+    int device = -1;
+    int sm_count = 0;
+    int cc_major = 0;
+    int* status_dev = nullptr;   // device-visible alias of the pinned status word
+    volatile int* status_host = nullptr;
+    void* scratch = nullptr;     // cached scratch buffer (grown on demand)
+    size_t scratch_bytes = 0;
+};
+// Per-device lazily created state; returns nullptr (and sets *status) when the device is unusable.
+DeviceInfo* device_info(int* status);
+// A scratch buffer of at least `bytes` on the current device, cached across calls (grows, never shrinks).
+int get_scratch(size_t bytes, void** out);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t dtype_size(int dt) { return dt == MIMK_BF16 ? 2 : (dt == MIMK_I64 ? 8 : 4); }
+
+// kernels implemented in the other translation units
+int gemm_simt(const mimk_gemm_desc& d, cudaStream_t s);
+int gemm_tc_supported(const mimk_gemm_desc& d);
+int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2);
+int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
+int attn_tc_supported(const mimk_attn_desc& d);
+int attn_tc(const mimk_attn_desc& d, cudaStream_t s);
+
+// ---- device side ----------------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Epilogue `post(acc, row, full)`.
+__device__ __forceinline__ float apply_post(int post, float acc, float row, float full) {
+    switch (post) {
+        case MIMK_POST_BIAS: return acc + row;
+        case MIMK_POST_BIAS_RELU: return fmaxf(0.f, acc + row);
+        case MIMK_POST_BIAS_TANH: return tanhf(acc + row);
+        case MIMK_POST_RELU: return fmaxf(0.f, acc);
+        case MIMK_POST_SILU: return acc / (1.f + __expf(-acc));
+        case MIMK_POST_ADD_FULL: return acc + full;
+        default: return acc;
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+#endif
+
+}  // namespace mimk

@@ -1,0 +1,387 @@
+// bf16 contraction on the 5th-generation tensor cores (tcgen05), f32 accumulators in tensor memory.
+//
+// This is `dot_product_impl` (MimIR src/mim/plug/tensor/tensor.mim:1367-1411) for bf16 operands: the fold
+// `acc = add(acc, mul(a, b))` of `dot_general_fun` (tensor.mim:1332) with To = F32 and Tis = (BF16, BF16),
+// followed by the `post` epilogue slot that `fuse_tensor` fills (src/mim/plug/tensor/phase/fuse.cpp:408-534).
+// Both right-operand layouts of the reference exist: B stored [K,N] (`dot_schedule`, tensor.mim:989) is an
+// MN-major operand, B stored [N,K] read through transpose_2d (`dot_schedule_kvec`, tensor.mim:1015) is K-major.
+//
+// Structure: one persistent CTA per SM walks output tiles of 128 x 256 (or 128 x 128 twice for the gated form).
+//   warp 0       TMA producer: A and B tiles of 64 k-columns into a ring of 128-byte-swizzled shared memory stages
+//   warp 1       MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) and commits stage/accumulator barriers
+//   warps 2..5   epilogue: tcgen05.ld the f32 accumulator (one row per thread), apply `post`, store
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
+// Every mbarrier wait is bounded; on expiry the CTA records MIMK_E_DEVICE_WAIT and unwinds (frees TMEM, exits).
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace mimk {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128, BK = 64, STAGES = 4;
+constexpr int ACC_COLS = 256;                  // TMEM columns per accumulator buffer
+constexpr int A_BYTES  = BM * BK * 2;          // 16 KiB
+constexpr int B_BYTES  = ACC_COLS * BK * 2;    // 32 KiB: one 256-row tile or two 128-row tiles
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;
+
+struct Bars {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256;
+static_assert(sizeof(Bars) <= 256, "barrier block too large");
+
+struct Params {
+    int64_t M, N, K;
+    void* C;
+    const float* post_row;
+    const void* post_full;
+    int post;
+    int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t& tm, int64_t& tn) {
+    const int64_t per_group = GROUP_M * tiles_n;
+    const int64_t group     = tile / per_group;
+    const int64_t first_m   = group * GROUP_M;
+    const int64_t gsize     = (tiles_m - first_m) < GROUP_M ? (tiles_m - first_m) : GROUP_M;
+    const int64_t in_group  = tile % per_group;
+    tm                      = first_m + in_group % gsize;
+    tn                      = in_group / gsize;
+}
+
+// BN: output-tile width per B operand (256 plain, 128 gated). B_MN: B stored [K,N] (N contiguous).
+template <int BN, bool B_MN, bool GATED, class TOut>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmB2, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr  = smem_u32(smem_raw);
+    const uint32_t tile_base = (raw_addr + 1023u) & ~1023u;
+    Bars* bars               = reinterpret_cast<Bars*>(smem_raw + (tile_base - raw_addr) + STAGES * STAGE_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+    const int64_t num_tiles = tiles_m * tiles_n;
+    const int num_kb        = int((p.K + BK - 1) / BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars->acc_full[b]), 1);
+            mbar_init(smem_u32(&bars->acc_empty[b]), 128);
+        }
+        bars->abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        if (GATED) tma_prefetch_desc(&tmB2);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&bars->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int64_t tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int m0 = int(tm * BM), n0 = int(tn * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag))) break;
+                    const uint32_t full = smem_u32(&bars->full[stage]);
+                    const uint32_t sa   = tile_base + stage * STAGE_BYTES;
+                    const uint32_t sb   = sa + A_BYTES;
+                    mbar_expect_tx(full, A_BYTES + (GATED ? 2 : 1) * BN * BK * 2);
+                    tma_load_2d(sa, &tmA, kb * BK, m0, full);
+                    if (!B_MN) {
+                        tma_load_2d(sb, &tmB, kb * BK, n0, full);
+                        if (GATED) tma_load_2d(sb + BN * BK * 2, &tmB2, kb * BK, n0, full);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) {
+                            tma_load_2d(sb + j * (BK * 128), &tmB, n0 + j * 64, kb * BK, full);
+                            if (GATED) tma_load_2d(sb + BN * BK * 2 + j * (BK * 128), &tmB2, n0 + j * 64, kb * BK, full);
+                        }
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = idesc_bf16_f32(BM, BN, 0, B_MN ? 1 : 0);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (!(ok = mbar_wait(smem_u32(&bars->acc_empty[acc]), acc_phase ^ 1u, abort_flag))) break;
+                tc_fence_after();
+                const uint32_t d0 = tmem_base + acc * ACC_COLS;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag))) break;
+                    tc_fence_after();
+                    const uint32_t sa = tile_base + stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = smem_desc_sw128(sa + k * 32, 16, 1024);
+                        const uint32_t boff = B_MN ? k * 2048 : k * 32;
+                        const uint32_t lead = B_MN ? BK * 128 : 16;
+                        const uint64_t bd   = smem_desc_sw128(sb + boff, lead, 1024);
+                        const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                        mma_f16_ss(d0, ad, bd, idesc, accum);
+                        if (GATED) {
+                            const uint64_t bd2 = smem_desc_sw128(sb + BN * BK * 2 + boff, lead, 1024);
+                            mma_f16_ss(d0 + BN, ad, bd2, idesc, accum);
+                        }
+                    }
+                    mma_commit(smem_u32(&bars->empty[stage]));
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                mma_commit(smem_u32(&bars->acc_full[acc]));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) are this warp's
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        TOut* C = static_cast<TOut*>(p.C);
+        const TOut* post_full = static_cast<const TOut*>(p.post_full);
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int64_t tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int64_t row = tm * BM + quarter * 32 + lane;
+            const int64_t n0  = tn * BN;
+            if (!(ok = mbar_wait(smem_u32(&bars->acc_full[acc]), acc_phase, abort_flag))) break;
+            tc_fence_after();
+            const uint32_t t0 = tmem_base + acc * ACC_COLS + (uint32_t(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                float v[32];
+                tmem_ld_32x32(t0 + c, r);
+                if (GATED) {
+                    uint32_t u[32];
+                    tmem_ld_32x32(t0 + BN + c, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = __uint_as_float(r[i]);
+                        v[i]          = (g / (1.f + __expf(-g))) * __uint_as_float(u[i]);
+                    }
+                } else {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                }
+                if (c + 32 >= BN) {
+                    // last read of this accumulator buffer: hand it back before the stores
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+                }
+                if (row < p.M) {
+                    const int64_t col0 = n0 + c;
+                    if (p.post != MIMK_POST_ID) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int64_t col = col0 + i;
+                            if (col < p.N) {
+                                const float rowv = p.post_row ? __ldg(p.post_row + col) : 0.f;
+                                const float full = post_full ? float(post_full[row * p.N + col]) : 0.f;
+                                v[i]             = apply_post(p.post, v[i], rowv, full);
+                            }
+                        }
+                    }
+                    TOut* dst = C + row * p.N + col0;
+                    if (sizeof(TOut) == 2) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            if (col0 + i < p.N) {  // N % 8 == 0: an 8-column group is all in or all out
+                                uint4 q;
+                                q.x = pack_bf16x2(v[i], v[i + 1]);
+                                q.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                                q.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                                q.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst) + i) = q;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            if (col0 + i < p.N)
+                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + i) =
+                                    make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        }
+                    }
+                }
+            }
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_flag) *p.status = MIMK_E_DEVICE_WAIT;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+template <int BN, bool B_MN, bool GATED, class TOut>
+int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int sm_count,
+           cudaStream_t s) {
+    auto kern = gemm_tc_kernel<BN, B_MN, GATED, TOut>;
+    static bool configured = false;  // per template instance
+    if (!configured) {
+        MIMK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    const int grid      = int(tiles < sm_count ? tiles : sm_count);
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tA, tB, tB2, p);
+    return launch_status();
+}
+
+}  // namespace
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                      uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MIMK_E_CUDA;
+    cuuint64_t dims[2]    = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2]     = {box_inner, box_outer};
+    cuuint32_t estr[2]    = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MIMK_OK : MIMK_E_CUDA;
+}
+
+int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t mid, uint64_t outer,
+                      uint64_t mid_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_mid) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MIMK_E_CUDA;
+    cuuint64_t dims[3]    = {inner, mid, outer};
+    cuuint64_t strides[2] = {mid_stride_bytes, outer_stride_bytes};
+    cuuint32_t box[3]     = {box_inner, box_mid, 1};
+    cuuint32_t estr[3]    = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MIMK_OK : MIMK_E_CUDA;
+}
+
+int gemm_tc_supported(const mimk_gemm_desc& d) {
+    if (d.in_dtype != MIMK_BF16) return 0;
+    if (d.k <= 0 || d.k % 8 != 0 || d.n % 8 != 0) return 0;  // TMA: 16-byte strides; epilogue: 16-byte stores
+    if (d.m >= (int64_t(1) << 31) || d.n >= (int64_t(1) << 31) || d.k >= (int64_t(1) << 31)) return 0;
+    if (!aligned16(d.a) || !aligned16(d.b) || !aligned16(d.c)) return 0;
+    if (d.post_full && !aligned16(d.post_full)) return 0;
+    if (d.batch > 64) return 0;  // one launch per batch entry; larger batches take the CUDA-core kernel
+    if (d.batch > 1 && (d.stride_a % 8 || d.stride_b % 8 || d.stride_c % 8)) return 0;
+    return 1;
+}
+
+int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2) {
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    const bool b_mn = d.b_layout == MIMK_B_KN;
+    const int bn    = gated ? 128 : 256;
+    const size_t out_size = d.out_dtype == MIMK_BF16 ? 2 : 4;
+    for (int64_t b = 0; b < d.batch; ++b) {
+        const uint8_t* A  = static_cast<const uint8_t*>(d.a) + size_t(b * d.stride_a) * 2;
+        const uint8_t* B  = static_cast<const uint8_t*>(d.b) + size_t(b * d.stride_b) * 2;
+        const uint8_t* B2 = b2 ? static_cast<const uint8_t*>(b2) + size_t(b * d.stride_b) * 2 : B;
+        CUtensorMap tA, tB, tB2;
+        MIMK_TRY(make_tmap_bf16_2d(&tA, A, uint64_t(d.k), uint64_t(d.m), uint64_t(d.k) * 2, BK, BM));
+        if (b_mn) {
+            MIMK_TRY(make_tmap_bf16_2d(&tB, B, uint64_t(d.n), uint64_t(d.k), uint64_t(d.n) * 2, 64, BK));
+            MIMK_TRY(make_tmap_bf16_2d(&tB2, B2, uint64_t(d.n), uint64_t(d.k), uint64_t(d.n) * 2, 64, BK));
+        } else {
+            MIMK_TRY(make_tmap_bf16_2d(&tB, B, uint64_t(d.k), uint64_t(d.n), uint64_t(d.k) * 2, BK, uint32_t(bn)));
+            MIMK_TRY(make_tmap_bf16_2d(&tB2, B2, uint64_t(d.k), uint64_t(d.n), uint64_t(d.k) * 2, BK, uint32_t(bn)));
+        }
+        Params p;
+        p.M = d.m, p.N = d.n, p.K = d.k;
+        p.C         = static_cast<uint8_t*>(d.c) + size_t(b * d.stride_c) * out_size;
+        p.post_row  = static_cast<const float*>(d.post_row);
+        p.post_full = d.post_full ? static_cast<const uint8_t*>(d.post_full) + size_t(b * d.stride_c) * out_size : nullptr;
+        p.post      = d.post;
+        p.status    = dev->status_dev;
+        int rc;
+        if (gated) {
+            if (d.out_dtype != MIMK_BF16) return MIMK_E_DTYPE;
+            rc = b_mn ? launch<128, true, true, __nv_bfloat16>(tA, tB, tB2, p, dev->sm_count, s)
+                      : launch<128, false, true, __nv_bfloat16>(tA, tB, tB2, p, dev->sm_count, s);
+        } else if (d.out_dtype == MIMK_BF16) {
+            rc = b_mn ? launch<256, true, false, __nv_bfloat16>(tA, tB, tB2, p, dev->sm_count, s)
+                      : launch<256, false, false, __nv_bfloat16>(tA, tB, tB2, p, dev->sm_count, s);
+        } else {
+            rc = b_mn ? launch<256, true, false, float>(tA, tB, tB2, p, dev->sm_count, s)
+                      : launch<256, false, false, float>(tA, tB, tB2, p, dev->sm_count, s);
+        }
+        MIMK_TRY(rc);
+    }
+    return MIMK_OK;
+}
+
+}  // namespace mimk

@@ -1,0 +1,465 @@
+// Bandwidth-bound kernels: reduce, softmax, RMSNorm, elementwise maps.
+//
+// These are the `map_reduce_post` instances with a short reduction per output cell (MimIR
+// src/mim/plug/tensor/tensor.mim:1151-1176). The reference's GPU lowering gives each output cell one thread
+// that walks its reduction sequentially (src/mim/plug/gpu/phase/lower_map_reduce.cpp:198-260) and runs softmax
+// as four kernels; here a row lives in the registers of one CTA, is read from HBM once with 128-bit loads,
+// reduced with warp shuffles, and written once.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace mimk {
+namespace {
+
+enum { ROWS_SOFTMAX = 0, ROWS_RMSNORM = 1, ROWS_SOFTMAX_RMSNORM = 2 };
+
+struct SumOp {
+    __device__ float operator()(float a, float b) const { return a + b; }
+    __device__ static float ident() { return 0.f; }
+};
+struct MaxOp {
+    __device__ float operator()(float a, float b) const { return fmaxf(a, b); }
+    __device__ static float ident() { return -CUDART_INF_F; }
+};
+struct MinOp {
+    __device__ float operator()(float a, float b) const { return fminf(a, b); }
+    __device__ static float ident() { return CUDART_INF_F; }
+};
+
+template <class Op>
+__device__ __forceinline__ float warp_reduce(float v, Op op) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Every warp ends up with the block-wide result; `red` (32 floats of shared memory) is free again on return.
+template <int THREADS, class Op>
+__device__ __forceinline__ float block_reduce(float v, float* red, Op op) {
+    v = warp_reduce(v, op);
+    if (THREADS == 32) return v;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float r = (l < THREADS / 32) ? red[l] : Op::ident();
+    r       = warp_reduce(r, op);
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ float4 load4(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    uint2 u = __ldcs(reinterpret_cast<const uint2*>(p));
+    float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.x));
+    float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    uint2 u;
+    u.x = pack_bf16x2(v.x, v.y);
+    u.y = pack_bf16x2(v.z, v.w);
+    __stcs(reinterpret_cast<uint2*>(p), u);
+}
+
+// One CTA per row (grid-stride over rows); a thread keeps NV float4 of the row in registers.
+// Requires cols % 4 == 0, cols <= THREADS * NV * 4 and 16-byte (f32) / 8-byte (bf16) aligned rows.
+template <int MODE, int THREADS, int NV, class TIn, class TOut>
+__global__ void __launch_bounds__(THREADS) rows_in_regs_kernel(const TIn* __restrict__ x, const float* __restrict__ gamma,
+                                                              TOut* __restrict__ y, int64_t rows, int cols, float eps) {
+    __shared__ float red[32];
+    const int nvec = cols >> 2;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const TIn* xr = x + row * cols;
+        float4 v[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = i * THREADS + threadIdx.x;
+            if (idx < nvec) v[i] = load4(xr + 4 * idx);
+        }
+        if (MODE == ROWS_SOFTMAX || MODE == ROWS_SOFTMAX_RMSNORM) {
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (i * THREADS + threadIdx.x < nvec)
+                    mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+            mx        = block_reduce<THREADS>(mx, red, MaxOp());
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (i * THREADS + threadIdx.x < nvec) {
+                    v[i].x = expf(v[i].x - mx);
+                    v[i].y = expf(v[i].y - mx);
+                    v[i].z = expf(v[i].z - mx);
+                    v[i].w = expf(v[i].w - mx);
+                    sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+                }
+            sum             = block_reduce<THREADS>(sum, red, SumOp());
+            const float inv = 1.f / sum;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                v[i].x *= inv;
+                v[i].y *= inv;
+                v[i].z *= inv;
+                v[i].w *= inv;
+            }
+        }
+        if (MODE == ROWS_RMSNORM || MODE == ROWS_SOFTMAX_RMSNORM) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (i * THREADS + threadIdx.x < nvec)
+                    ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+            ss              = block_reduce<THREADS>(ss, red, SumOp());
+            const float inv = rsqrtf(ss / float(cols) + eps);
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int idx = i * THREADS + threadIdx.x;
+                if (idx < nvec) {
+                    const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + idx);
+                    v[i].x *= inv * g.x;
+                    v[i].y *= inv * g.y;
+                    v[i].z *= inv * g.z;
+                    v[i].w *= inv * g.w;
+                }
+            }
+        }
+        TOut* yr = y + row * cols;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = i * THREADS + threadIdx.x;
+            if (idx < nvec) store4(yr + 4 * idx, v[i]);
+        }
+    }
+}
+
+__device__ __forceinline__ float ldf(const float* p, int64_t i) { return p[i]; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void stf(float* p, int64_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+// Any length / alignment, inner == 1: one CTA per row, the row is re-read from L2 for each pass.
+template <int MODE, class TIn, class TOut>
+__global__ void __launch_bounds__(256) rows_generic_kernel(const TIn* __restrict__ x, const float* __restrict__ gamma,
+                                                          TOut* __restrict__ y, int64_t rows, int64_t cols, float eps) {
+    __shared__ float red[32];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const TIn* xr = x + row * cols;
+        TOut* yr      = y + row * cols;
+        float mx = 0.f, inv_sum = 1.f;
+        if (MODE != ROWS_RMSNORM) {
+            mx = -CUDART_INF_F;
+            for (int64_t c = threadIdx.x; c < cols; c += 256) mx = fmaxf(mx, ldf(xr, c));
+            mx      = block_reduce<256>(mx, red, MaxOp());
+            float s = 0.f;
+            for (int64_t c = threadIdx.x; c < cols; c += 256) s += expf(ldf(xr, c) - mx);
+            inv_sum = 1.f / block_reduce<256>(s, red, SumOp());
+        }
+        float inv_rms = 1.f;
+        if (MODE != ROWS_SOFTMAX) {
+            float ss = 0.f;
+            for (int64_t c = threadIdx.x; c < cols; c += 256) {
+                float v = ldf(xr, c);
+                if (MODE == ROWS_SOFTMAX_RMSNORM) v = expf(v - mx) * inv_sum;
+                ss += v * v;
+            }
+            inv_rms = rsqrtf(block_reduce<256>(ss, red, SumOp()) / float(cols) + eps);
+        }
+        for (int64_t c = threadIdx.x; c < cols; c += 256) {
+            float v = ldf(xr, c);
+            if (MODE != ROWS_RMSNORM) v = expf(v - mx) * inv_sum;
+            if (MODE != ROWS_SOFTMAX) v = v * inv_rms * gamma[c];
+            stf(yr, c, v);
+        }
+    }
+}
+
+// softmax along the middle axis of [outer, len, inner] with inner > 1: one thread per (o, i) column, so that
+// neighbouring threads read neighbouring addresses.
+template <class TIn, class TOut>
+__global__ void softmax_strided_kernel(const TIn* __restrict__ x, TOut* __restrict__ y, int64_t outer, int64_t len,
+                                       int64_t inner) {
+    const int64_t total = outer * inner;
+    for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total; t += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t o = t / inner, i = t % inner;
+        const int64_t base = o * len * inner + i;
+        float mx           = -CUDART_INF_F;
+        for (int64_t a = 0; a < len; ++a) mx = fmaxf(mx, ldf(x, base + a * inner));
+        float s = 0.f;
+        for (int64_t a = 0; a < len; ++a) s += expf(ldf(x, base + a * inner) - mx);
+        const float inv = 1.f / s;
+        for (int64_t a = 0; a < len; ++a) stf(y, base + a * inner, expf(ldf(x, base + a * inner) - mx) * inv);
+    }
+}
+
+// ---- reduce ------------------------------------------------------------------------------------
+template <class Op>
+__global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t rows,
+                                                         int64_t cols, int vec_ok) {
+    __shared__ float red[32];
+    Op op;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* xr = x + row * cols;
+        float acc       = Op::ident();
+        if (vec_ok) {
+            const int64_t nvec = cols >> 2;
+            for (int64_t i = threadIdx.x; i < nvec; i += 256) {
+                float4 v = load4(xr + 4 * i);
+                acc      = op(acc, op(op(v.x, v.y), op(v.z, v.w)));
+            }
+        } else {
+            for (int64_t c = threadIdx.x; c < cols; c += 256) acc = op(acc, xr[c]);
+        }
+        acc = block_reduce<256>(acc, red, op);
+        if (threadIdx.x == 0) out[row] = acc;
+    }
+}
+
+// inner > 1: thread per (o, i) column; blockIdx.y splits the reduced axis into `gridDim.y` slices whose partial
+// results go to `partial` [slice, outer*inner] (or straight to `out` when there is a single slice).
+template <class Op>
+__global__ void reduce_mid_kernel(const float* __restrict__ x, float* __restrict__ dst, int64_t outer, int64_t len,
+                                  int64_t inner, int64_t slice_len) {
+    Op op;
+    const int64_t total = outer * inner;
+    const int64_t a0    = int64_t(blockIdx.y) * slice_len;
+    const int64_t a1    = a0 + slice_len < len ? a0 + slice_len : len;
+    for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total; t += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t o = t / inner, i = t % inner;
+        const float* p = x + o * len * inner + i;
+        float acc      = Op::ident();
+        for (int64_t a = a0; a < a1; ++a) acc = op(acc, p[a * inner]);
+        dst[int64_t(blockIdx.y) * total + t] = acc;
+    }
+}
+template <class Op>
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t total,
+                                       int slices) {
+    Op op;
+    for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total; t += int64_t(gridDim.x) * blockDim.x) {
+        float acc = Op::ident();
+        for (int s = 0; s < slices; ++s) acc = op(acc, partial[int64_t(s) * total + t]);
+        out[t] = acc;
+    }
+}
+
+// ---- elementwise -------------------------------------------------------------------------------
+__device__ __forceinline__ float apply_op(int op, float a, float b) {
+    switch (op) {
+        case MIMK_OP_ADD: return a + b;
+        case MIMK_OP_SUB: return a - b;
+        case MIMK_OP_MUL: return a * b;
+        case MIMK_OP_DIV: return a / b;
+        case MIMK_OP_MAX: return fmaxf(a, b);
+        case MIMK_OP_MIN: return fminf(a, b);
+        case MIMK_OP_SUBEXP: return expf(a - b);
+        case MIMK_OP_RELU: return fmaxf(0.f, a);
+        case MIMK_OP_TANH: return tanhf(a);
+        case MIMK_OP_EXP: return expf(a);
+        case MIMK_OP_SILU: return a / (1.f + expf(-a));
+        case MIMK_OP_NEG: return -a;
+        default: return a;
+    }
+}
+template <class TOut>
+__global__ void map_kernel(int op, const float* __restrict__ x, const float* __restrict__ y, TOut* __restrict__ out,
+                           int64_t outer, int64_t len, int64_t inner, int y_mode) {
+    const int64_t total = outer * len * inner;
+    for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total; t += int64_t(gridDim.x) * blockDim.x) {
+        float b = 0.f;
+        if (y_mode == 0) {
+            b = y[t];
+        } else if (y_mode == 1) {
+            const int64_t o = t / (len * inner), i = t % inner;
+            b = y[o * inner + i];
+        } else if (y_mode == 2) {
+            b = y[t % (len * inner)];
+        }
+        stf(out, t, apply_op(op, x[t], b));
+    }
+}
+
+int grid_for(int64_t work_items, int threads, int sm_count, int ctas_per_sm) {
+    int64_t blocks = (work_items + threads - 1) / threads;
+    int64_t cap    = int64_t(sm_count) * ctas_per_sm;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return int(blocks);
+}
+
+template <int MODE, class TIn, class TOut>
+int launch_rows(const TIn* x, const float* gamma, TOut* y, int64_t rows, int64_t cols, float eps, cudaStream_t s,
+                const DeviceInfo& dev) {
+    const bool in_align  = (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(TIn))) == 0;
+    const bool out_align = (reinterpret_cast<uintptr_t>(y) % (4 * sizeof(TOut))) == 0;
+    const bool g_align   = MODE == ROWS_SOFTMAX || aligned16(gamma);
+    const bool vec       = cols % 4 == 0 && in_align && out_align && g_align && cols <= 32768;
+#define MIMK_ROWS_CASE(THREADS, NV, PER_SM)                                                                   \
+    if (vec && cols <= THREADS * NV * 4) {                                                                    \
+        int grid = int(rows < int64_t(dev.sm_count) * PER_SM ? rows : int64_t(dev.sm_count) * PER_SM);        \
+        rows_in_regs_kernel<MODE, THREADS, NV, TIn, TOut><<<grid, THREADS, 0, s>>>(x, gamma, y, rows, int(cols), eps); \
+        return launch_status();                                                                               \
+    }
+    MIMK_ROWS_CASE(32, 1, 32)
+    MIMK_ROWS_CASE(32, 4, 32)
+    MIMK_ROWS_CASE(128, 4, 16)
+    MIMK_ROWS_CASE(256, 4, 8)
+    MIMK_ROWS_CASE(256, 8, 4)
+    MIMK_ROWS_CASE(512, 8, 2)
+    MIMK_ROWS_CASE(1024, 8, 1)
+#undef MIMK_ROWS_CASE
+    int grid = int(rows < int64_t(dev.sm_count) * 8 ? rows : int64_t(dev.sm_count) * 8);
+    rows_generic_kernel<MODE, TIn, TOut><<<grid, 256, 0, s>>>(x, gamma, y, rows, cols, eps);
+    return launch_status();
+}
+
+template <int MODE>
+int dispatch_rows(const void* x, const float* gamma, void* y, int in_dtype, int out_dtype, int64_t rows, int64_t cols,
+                  float eps, cudaStream_t s, const DeviceInfo& dev) {
+    if (in_dtype == MIMK_F32 && out_dtype == MIMK_F32)
+        return launch_rows<MODE>(static_cast<const float*>(x), gamma, static_cast<float*>(y), rows, cols, eps, s, dev);
+    if (in_dtype == MIMK_F32 && out_dtype == MIMK_BF16)
+        return launch_rows<MODE>(static_cast<const float*>(x), gamma, static_cast<__nv_bfloat16*>(y), rows, cols, eps, s,
+                                 dev);
+    if (in_dtype == MIMK_BF16 && out_dtype == MIMK_BF16)
+        return launch_rows<MODE>(static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(y), rows, cols,
+                                 eps, s, dev);
+    if (in_dtype == MIMK_BF16 && out_dtype == MIMK_F32)
+        return launch_rows<MODE>(static_cast<const __nv_bfloat16*>(x), gamma, static_cast<float*>(y), rows, cols, eps, s,
+                                 dev);
+    return MIMK_E_DTYPE;
+}
+
+template <class Op>
+int reduce_impl(const float* x, float* out, int64_t outer, int64_t len, int64_t inner, cudaStream_t s,
+                const DeviceInfo& dev) {
+    if (inner == 1) {
+        const int vec_ok = (len % 4 == 0) && aligned16(x);
+        int grid         = int(outer < int64_t(dev.sm_count) * 8 ? outer : int64_t(dev.sm_count) * 8);
+        reduce_rows_kernel<Op><<<grid, 256, 0, s>>>(x, out, outer, len, vec_ok);
+        return launch_status();
+    }
+    const int64_t total = outer * inner;
+    const int threads   = 256;
+    int gx              = grid_for(total, threads, dev.sm_count, 8);
+    // Split the reduced axis when the columns alone cannot fill the machine.
+    int slices = 1;
+    if (int64_t(gx) < 2 * dev.sm_count && len >= 256) {
+        int64_t want = (4LL * dev.sm_count + gx - 1) / gx;
+        int64_t maxs = len / 64;
+        slices       = int(want < maxs ? want : maxs);
+        if (slices < 1) slices = 1;
+        if (slices > 1024) slices = 1024;
+    }
+    if (slices == 1) {
+        reduce_mid_kernel<Op><<<dim3(gx, 1), threads, 0, s>>>(x, out, outer, len, inner, len);
+        return launch_status();
+    }
+    const int64_t slice_len = (len + slices - 1) / slices;
+    slices                  = int((len + slice_len - 1) / slice_len);
+    void* scratch           = nullptr;
+    MIMK_TRY(get_scratch(size_t(slices) * size_t(total) * sizeof(float), &scratch));
+    reduce_mid_kernel<Op><<<dim3(gx, slices), threads, 0, s>>>(x, static_cast<float*>(scratch), outer, len, inner,
+                                                              slice_len);
+    MIMK_TRY(launch_status());
+    reduce_partials_kernel<Op><<<gx, threads, 0, s>>>(static_cast<const float*>(scratch), out, total, slices);
+    return launch_status();
+}
+
+}  // namespace
+}  // namespace mimk
+
+using namespace mimk;
+
+extern "C" int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner, int monoid,
+                           void* stream) {
+    if (outer < 0 || len < 0 || inner < 0) return MIMK_E_ARG;
+    if (dtype != MIMK_F32) return MIMK_E_DTYPE;
+    if (monoid < MIMK_SUM || monoid > MIMK_MIN) return MIMK_E_ARG;
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    if (outer * inner == 0) return MIMK_OK;
+    if (!x || !out) return MIMK_E_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float* xf = static_cast<const float*>(x);
+    float* of       = static_cast<float*>(out);
+    switch (monoid) {
+        case MIMK_SUM: return reduce_impl<SumOp>(xf, of, outer, len, inner, s, *dev);
+        case MIMK_MAX: return reduce_impl<MaxOp>(xf, of, outer, len, inner, s, *dev);
+        default: return reduce_impl<MinOp>(xf, of, outer, len, inner, s, *dev);
+    }
+}
+
+extern "C" int mimk_softmax(const void* x, void* y, int in_dtype, int out_dtype, int64_t outer, int64_t len,
+                            int64_t inner, void* stream) {
+    if (outer < 0 || len < 0 || inner < 0) return MIMK_E_ARG;
+    if ((in_dtype != MIMK_F32 && in_dtype != MIMK_BF16) || (out_dtype != MIMK_F32 && out_dtype != MIMK_BF16))
+        return MIMK_E_DTYPE;
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    if (outer * len * inner == 0) return MIMK_OK;
+    if (!x || !y) return MIMK_E_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (inner == 1) return dispatch_rows<ROWS_SOFTMAX>(x, nullptr, y, in_dtype, out_dtype, outer, len, 0.f, s, *dev);
+    if (in_dtype != MIMK_F32) return MIMK_E_DTYPE;
+    int grid = grid_for(outer * inner, 128, dev->sm_count, 16);
+    if (out_dtype == MIMK_F32)
+        softmax_strided_kernel<<<grid, 128, 0, s>>>(static_cast<const float*>(x), static_cast<float*>(y), outer, len, inner);
+    else
+        softmax_strided_kernel<<<grid, 128, 0, s>>>(static_cast<const float*>(x), static_cast<__nv_bfloat16*>(y), outer,
+                                                    len, inner);
+    return launch_status();
+}
+
+extern "C" int mimk_rmsnorm(const void* x, const void* gamma, void* y, int in_dtype, int out_dtype, int64_t rows,
+                            int64_t cols, float eps, void* stream) {
+    if (rows < 0 || cols < 0) return MIMK_E_ARG;
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    if (rows * cols == 0) return MIMK_OK;
+    if (!x || !y || !gamma) return MIMK_E_ARG;
+    return dispatch_rows<ROWS_RMSNORM>(x, static_cast<const float*>(gamma), y, in_dtype, out_dtype, rows, cols, eps,
+                                       static_cast<cudaStream_t>(stream), *dev);
+}
+
+extern "C" int mimk_softmax_rmsnorm(const void* x, const void* gamma, void* y, int in_dtype, int out_dtype, int64_t rows,
+                                    int64_t cols, float eps, void* stream) {
+    if (rows < 0 || cols < 0) return MIMK_E_ARG;
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    if (rows * cols == 0) return MIMK_OK;
+    if (!x || !y || !gamma) return MIMK_E_ARG;
+    return dispatch_rows<ROWS_SOFTMAX_RMSNORM>(x, static_cast<const float*>(gamma), y, in_dtype, out_dtype, rows, cols, eps,
+                                               static_cast<cudaStream_t>(stream), *dev);
+}
+
+extern "C" int mimk_map(int op, const void* x, const void* y, void* out, int out_dtype, int64_t outer, int64_t len,
+                        int64_t inner, int y_mode, void* stream) {
+    if (outer < 0 || len < 0 || inner < 0 || y_mode < 0 || y_mode > 3) return MIMK_E_ARG;
+    const bool unary = op >= MIMK_OP_RELU && op <= MIMK_OP_COPY;
+    const bool binary = op >= MIMK_OP_ADD && op <= MIMK_OP_SUBEXP;
+    if (!unary && !binary) return MIMK_E_ARG;
+    if (binary && y_mode == 3) return MIMK_E_ARG;
+    if (out_dtype != MIMK_F32 && out_dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    const int64_t total = outer * len * inner;
+    if (total == 0) return MIMK_OK;
+    if (!x || !out || (binary && !y)) return MIMK_E_ARG;
+    if (unary) y_mode = 3;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int grid       = grid_for(total, 256, dev->sm_count, 8);
+    if (out_dtype == MIMK_F32)
+        map_kernel<<<grid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),
+                                        static_cast<float*>(out), outer, len, inner, y_mode);
+    else
+        map_kernel<<<grid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),
+                                        static_cast<__nv_bfloat16*>(out), outer, len, inner, y_mode);
+    return launch_status();
+}

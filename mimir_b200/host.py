@@ -1,0 +1,102 @@
+"""Host-buffer form of the operators: CPU tensors in, CPU tensors out, the device in between.
+
+This is the call a program lowered by the reference's GPU path makes today -- every operation uploads its inputs,
+launches, and downloads its result (MimIR src/mim/plug/gpu/phase/lower_map_reduce.cpp:317-395) -- served by the
+`mimk_host_*` entry points of include/mimk.h.  Pass pinned tensors (`tensor.pin_memory()`) for full copy speed.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+from .tensor import _DT, _POST, _b_layout
+
+
+def _cpu(*ts):
+    for t in ts:
+        if t is not None and t.is_cuda:
+            raise ValueError("mimir_b200.host takes host tensors; use mimir_b200.tensor for device tensors")
+
+
+def _rows(kind, x, gamma, eps, out, out_dtype):
+    _cpu(x, gamma, out)
+    x = x.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // max(cols, 1)
+    if out is None:
+        out = torch.empty(x.shape, dtype=out_dtype or x.dtype)
+    if gamma is not None:
+        gamma = gamma.to(torch.float32).contiguous()
+        if gamma.numel() != cols:
+            raise ValueError("gamma extent must equal the last extent of x")
+    L.check(L.lib().mimk_host_rows(kind, x.data_ptr(), gamma.data_ptr() if gamma is not None else None, out.data_ptr(),
+                                   _DT[x.dtype], _DT[out.dtype], rows, cols, float(eps)), "host_rows")
+    return out
+
+
+def softmax_rows(x, *, out=None, out_dtype=None):
+    return _rows(L.ROWS_SOFTMAX, x, None, 0.0, out, out_dtype)
+
+
+def rmsnorm(x, gamma, eps, *, out=None, out_dtype=None):
+    return _rows(L.ROWS_RMSNORM, x, gamma, eps, out, out_dtype)
+
+
+def softmax_rmsnorm(x, gamma, eps, *, out=None, out_dtype=None):
+    return _rows(L.ROWS_SOFTMAX_RMSNORM, x, gamma, eps, out, out_dtype)
+
+
+def product_2d(a, b, *, post=None, bias=None, out=None, out_dtype=None):
+    _cpu(a, b, bias, out)
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+        raise ValueError("contracting dims don't match")
+    a = a.contiguous()
+    b_store, layout = _b_layout(b)
+    m, k = a.shape
+    n = b.shape[1]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or a.dtype)
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+    d = L.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, m, n, k
+    d.a, d.b, d.c = a.data_ptr(), b_store.data_ptr(), out.data_ptr()
+    d.stride_c = m * n
+    d.in_dtype, d.out_dtype, d.b_layout, d.post = _DT[a.dtype], _DT[out.dtype], layout, _POST[post]
+    d.post_row = bias.data_ptr() if bias is not None else None
+    L.check(L.lib().mimk_host_gemm(C.byref(d)), "host product_2d")
+    return out
+
+
+def attention(q, k, v, *, scale=1.0, causal=False, out=None):
+    _cpu(q, k, v, out)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if out is None:
+        out = torch.empty_like(q)
+    d = L.AttnDesc()
+    bh = q.numel() // (q.shape[-1] * q.shape[-2])
+    d.batch_heads, d.seq_q, d.seq_k, d.head_dim = bh, q.shape[-2], k.shape[-2], q.shape[-1]
+    d.q, d.k, d.v, d.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    d.scale, d.causal, d.dtype = float(scale), int(causal), _DT[q.dtype]
+    L.check(L.lib().mimk_host_attn_fwd(C.byref(d)), "host attention")
+    return out
+
+
+def mlp_gated(x, w1, w3, w2, *, out=None):
+    _cpu(x, w1, w3, w2, out)
+    x = x.contiguous()
+    w1s, lay = _b_layout(w1)
+    w3s, _ = _b_layout(w3)
+    w2s, _ = _b_layout(w2)
+    m, k = x.shape
+    f, n = w1.shape[1], w2.shape[1]
+    if out is None:
+        out = torch.empty((m, n), dtype=x.dtype)
+    d = L.MlpDesc()
+    d.m, d.k, d.f, d.n = m, k, f, n
+    d.x, d.w1, d.w3, d.w2, d.y = x.data_ptr(), w1s.data_ptr(), w3s.data_ptr(), w2s.data_ptr(), out.data_ptr()
+    d.dtype, d.b_layout = _DT[x.dtype], lay
+    L.check(L.lib().mimk_host_mlp_gated(C.byref(d)), "host mlp_gated")
+    return out

@@ -1,0 +1,248 @@
+"""Host-side mirror of the reference's `tensor` plugin operators, on CUDA torch tensors.
+
+Names and argument meaning follow MimIR's src/mim/plug/tensor/tensor.mim (product_2d 510-513, bmm 404-407,
+transpose_2d, reduce 1151-1157, binary_ax 1162-1167, softmax 1172-1176, unary/binary 361-394); a dense row-major
+tensor is what `tensor.Tensor r s T` bufferises to (tensor.mim:48-50, buffer/phase/lower_ptr.cpp:16-20).
+torch is used for device memory and streams only; every operator is one call into the C ABI (include/mimk.h).
+Shape errors the reference reports at compile time ("contracting dims don't match", tensor.mim:1393) are raised
+as ValueError before anything is launched; kernel-side failures raise MimkError.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib as L
+
+_DT = {torch.float32: L.F32, torch.bfloat16: L.BF16}
+_MONOID = {"sum": L.SUM, "add": L.SUM, "max": L.MAX, "fmax": L.MAX, "min": L.MIN, "fmin": L.MIN}
+_POST = {None: L.POST_ID, "id": L.POST_ID, "bias": L.POST_BIAS, "bias_relu": L.POST_BIAS_RELU,
+         "bias_tanh": L.POST_BIAS_TANH, "relu": L.POST_RELU, "silu": L.POST_SILU, "add": L.POST_ADD_FULL}
+_BINOP = {"add": L.OP_ADD, "sub": L.OP_SUB, "mul": L.OP_MUL, "div": L.OP_DIV, "max": L.OP_MAX, "min": L.OP_MIN,
+          "subexp": L.OP_SUBEXP}
+_UNOP = {"relu": L.OP_RELU, "tanh": L.OP_TANH, "exp": L.OP_EXP, "silu": L.OP_SILU, "neg": L.OP_NEG, "copy": L.OP_COPY}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported element type {t.dtype}") from None
+
+
+def _dev(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("mimir_b200.tensor operates on CUDA tensors only (there is no CPU path)")
+
+
+def device_status() -> None:
+    """Synchronise the current stream and raise if a kernel gave up on a bounded wait."""
+    L.check(L.lib().mimk_device_status(_stream()), "device_status")
+
+
+def transpose_2d(t: torch.Tensor) -> torch.Tensor:
+    """A read-through view: consumers absorb it into their access maps (fuse.cpp:542-589), nothing is copied."""
+    if t.dim() != 2:
+        raise ValueError("transpose_2d expects a rank-2 tensor")
+    return t.t()
+
+
+def _b_layout(b: torch.Tensor):
+    """Row-major [K,N] -> KN; a transpose_2d view of a row-major [N,K] tensor -> NK (no copy either way)."""
+    if b.is_contiguous():
+        return b, L.B_KN
+    if b.transpose(-1, -2).is_contiguous():
+        return b.transpose(-1, -2), L.B_NK
+    return b.contiguous(), L.B_KN
+
+
+def _gemm(a, b_store, layout, batch, m, n, k, sa, sb, out, post, bias, full):
+    d = L.GemmDesc()
+    d.batch, d.m, d.n, d.k = batch, m, n, k
+    d.a, d.b, d.c = a.data_ptr(), b_store.data_ptr(), out.data_ptr()
+    d.stride_a, d.stride_b, d.stride_c = sa, sb, m * n
+    d.in_dtype, d.out_dtype, d.b_layout, d.post = _dt(a), _dt(out), layout, _POST[post]
+    d.post_row = bias.data_ptr() if bias is not None else None
+    d.post_full = full.data_ptr() if full is not None else None
+    L.check(L.lib().mimk_gemm(C.byref(d), _stream()), "product_2d")
+
+
+def product_2d(a: torch.Tensor, b: torch.Tensor, *, post=None, bias=None, full=None, out_dtype=None) -> torch.Tensor:
+    """C[m,l] = post(sum_k a[m,k] * b[k,l]).  `b` may be a transpose_2d view of a [l,k] tensor."""
+    _dev(a, b, bias, full)
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("product_2d expects rank-2 tensors")
+    if a.shape[1] != b.shape[0]:
+        raise ValueError("contracting dims don't match")
+    if a.dtype != b.dtype:
+        raise TypeError("product_2d: both operands share the ring's element type")
+    a = a.contiguous()
+    b_store, layout = _b_layout(b)
+    m, k = a.shape
+    n = b.shape[1]
+    out = torch.empty((m, n), dtype=out_dtype or a.dtype, device=a.device)
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+        if bias.numel() != n:
+            raise ValueError("bias extent must equal the output's last extent")
+    if full is not None:
+        full = full.to(out.dtype).contiguous()
+        if tuple(full.shape) != (m, n):
+            raise ValueError("epilogue operand must have the output's shape")
+    _gemm(a, b_store, layout, 1, m, n, k, 0, 0, out, post, bias, full)
+    return out
+
+
+def bmm(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
+    """C[B,m,n] = sum_k a[B,m,k] * b[B,k,n] (tensor.mim:404-407, batching axis 0)."""
+    _dev(a, b)
+    if a.dim() != 3 or b.dim() != 3:
+        raise ValueError("bmm expects rank-3 tensors")
+    if a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
+        raise ValueError("contracting dims don't match")
+    a = a.contiguous()
+    b_store, layout = _b_layout(b)
+    bt, m, k = a.shape
+    n = b.shape[2]
+    out = torch.empty((bt, m, n), dtype=out_dtype or a.dtype, device=a.device)
+    _gemm(a, b_store, layout, bt, m, n, k, m * k, k * n, out, None, None, None)
+    return out
+
+
+def _view3(x: torch.Tensor, ax: int):
+    ax = ax % x.dim()
+    outer = math.prod(x.shape[:ax])
+    inner = math.prod(x.shape[ax + 1:])
+    return ax, outer, x.shape[ax], inner
+
+
+def reduce(monoid: str, ax: int, x: torch.Tensor) -> torch.Tensor:
+    """`reduce (g, init) ax x`: folds axis `ax` away; monoid names the (g, init) pair (sum/max/min)."""
+    _dev(x)
+    x = x.contiguous()
+    ax, outer, ln, inner = _view3(x, ax)
+    out = torch.empty(x.shape[:ax] + x.shape[ax + 1:], dtype=x.dtype, device=x.device)
+    L.check(L.lib().mimk_reduce(x.data_ptr(), out.data_ptr(), _dt(x), outer, ln, inner, _MONOID[monoid], _stream()),
+            "reduce")
+    return out
+
+
+def softmax(ax: int, x: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
+    """`softmax m ax x`: exp(x - max) / sum exp(x - max) along `ax`, one pass over memory."""
+    _dev(x)
+    x = x.contiguous()
+    ax, outer, ln, inner = _view3(x, ax)
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    L.check(L.lib().mimk_softmax(x.data_ptr(), out.data_ptr(), _dt(x), _dt(out), outer, ln, inner, _stream()), "softmax")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, *, out_dtype=None) -> torch.Tensor:
+    """y = x * rrt(mean(x^2, last axis) + eps) * gamma."""
+    _dev(x, gamma)
+    x = x.contiguous()
+    cols = x.shape[-1]
+    if gamma.numel() != cols:
+        raise ValueError("gamma extent must equal the last extent of x")
+    gamma = gamma.to(torch.float32).contiguous()
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    L.check(L.lib().mimk_rmsnorm(x.data_ptr(), gamma.data_ptr(), out.data_ptr(), _dt(x), _dt(out), x.numel() // max(cols, 1),
+                                 cols, eps, _stream()), "rmsnorm")
+    return out
+
+
+def softmax_rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, *, out_dtype=None) -> torch.Tensor:
+    """rmsnorm(softmax(x, last axis)) in one kernel."""
+    _dev(x, gamma)
+    x = x.contiguous()
+    cols = x.shape[-1]
+    if gamma.numel() != cols:
+        raise ValueError("gamma extent must equal the last extent of x")
+    gamma = gamma.to(torch.float32).contiguous()
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    L.check(L.lib().mimk_softmax_rmsnorm(x.data_ptr(), gamma.data_ptr(), out.data_ptr(), _dt(x), _dt(out),
+                                         x.numel() // max(cols, 1), cols, eps, _stream()), "softmax_rmsnorm")
+    return out
+
+
+def unary(op: str, x: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
+    _dev(x)
+    x = x.contiguous()
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    L.check(L.lib().mimk_map(_UNOP[op], x.data_ptr(), None, out.data_ptr(), _dt(out), 1, x.numel(), 1, 3, _stream()),
+            "unary")
+    return out
+
+
+def binary(op: str, x: torch.Tensor, y: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
+    _dev(x, y)
+    if x.shape != y.shape:
+        raise ValueError("binary expects operands of one shape")
+    x, y = x.contiguous(), y.contiguous()
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    L.check(L.lib().mimk_map(_BINOP[op], x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(out), 1, x.numel(), 1, 0,
+                             _stream()), "binary")
+    return out
+
+
+def binary_ax(op: str, ax: int, x: torch.Tensor, y: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
+    """`binary_ax app ax (x, y)`: y lacks axis `ax` of x and is broadcast along it."""
+    _dev(x, y)
+    x, y = x.contiguous(), y.contiguous()
+    ax, outer, ln, inner = _view3(x, ax)
+    if tuple(y.shape) != tuple(x.shape[:ax] + x.shape[ax + 1:]):
+        raise ValueError("binary_ax: y must have x's shape without axis ax")
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    L.check(L.lib().mimk_map(_BINOP[op], x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(out), outer, ln, inner, 1,
+                             _stream()), "binary_ax")
+    return out
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float = 1.0, causal: bool = False,
+              return_lse: bool = False):
+    """softmax(scale * q k^T [+ causal mask]) v over the trailing [seq, head_dim] axes; leading axes are batch x head.
+    With scale = 1 and causal = False on rank-2 tensors this is lit/tensor/attn_exec.mim:22."""
+    _dev(q, k, v)
+    if q.shape[:-2] != k.shape[:-2] or k.shape != v.shape or q.shape[-1] != k.shape[-1]:
+        raise ValueError("contracting dims don't match")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    bh = math.prod(q.shape[:-2])
+    o = torch.empty_like(q)
+    lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device) if return_lse else None
+    d = L.AttnDesc()
+    d.batch_heads, d.seq_q, d.seq_k, d.head_dim = bh, q.shape[-2], k.shape[-2], q.shape[-1]
+    d.q, d.k, d.v, d.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    d.lse = lse.data_ptr() if lse is not None else None
+    d.scale, d.causal, d.dtype = float(scale), int(causal), _dt(q)
+    L.check(L.lib().mimk_attn_fwd(C.byref(d), _stream()), "attention")
+    return (o, lse) if return_lse else o
+
+
+def mlp_gated(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor, *, h: torch.Tensor | None = None):
+    """(silu(x w1) * (x w3)) w2, bf16; weights row-major [in, out] or transpose_2d views of [out, in]."""
+    _dev(x, w1, w3, w2, h)
+    if x.shape[1] != w1.shape[0] or w1.shape != w3.shape or w1.shape[1] != w2.shape[0]:
+        raise ValueError("contracting dims don't match")
+    x = x.contiguous()
+    w1s, lay1 = _b_layout(w1)
+    w3s, lay3 = _b_layout(w3)
+    w2s, lay2 = _b_layout(w2)
+    if not (lay1 == lay3 == lay2):
+        raise ValueError("mlp_gated: the three weights must share one storage layout")
+    m, k = x.shape
+    f, n = w1.shape[1], w2.shape[1]
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    d = L.MlpDesc()
+    d.m, d.k, d.f, d.n = m, k, f, n
+    d.x, d.w1, d.w3, d.w2, d.y = x.data_ptr(), w1s.data_ptr(), w3s.data_ptr(), w2s.data_ptr(), y.data_ptr()
+    d.h = h.data_ptr() if h is not None else None
+    d.dtype, d.b_layout = _dt(x), lay1
+    L.check(L.lib().mimk_mlp_gated(C.byref(d), _stream()), "mlp_gated")
+    return y

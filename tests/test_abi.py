@@ -1,0 +1,86 @@
+"""CPU-only checks of the drop-in boundary: the library loads, exports every symbol include/mimk.h declares,
+and validates arguments before touching a device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+import __graft_entry__ as entry
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    entry.build()
+    from mimir_b200 import _lib
+    return _lib
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "mimk.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mimk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 13
+    L = lib.lib()
+    for n in names:
+        assert hasattr(L, n), n
+    assert sorted(lib.SYMBOLS) == names
+
+
+def test_abi_version_and_status_strings(lib):
+    L = lib.lib()
+    assert L.mimk_abi_version() == 1
+    assert L.mimk_status_str(0) == b"ok"
+    for code in range(1, 10):
+        s = L.mimk_status_str(code)
+        assert s and s != b"unknown status"
+    assert L.mimk_status_str(1234) == b"unknown status"
+
+
+def test_argument_validation_needs_no_device(lib):
+    L = lib.lib()
+    assert L.mimk_gemm(None, None) == 1
+    d = lib.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, -4, 4, 4
+    assert L.mimk_gemm(C.byref(d), None) == 1          # negative extent
+    d.m = 4
+    d.in_dtype = 7
+    assert L.mimk_gemm(C.byref(d), None) == 4          # dtype
+    d.in_dtype, d.out_dtype, d.post = lib.F32, lib.F32, lib.POST_BIAS
+    assert L.mimk_gemm(C.byref(d), None) == 1          # bias epilogue without its operand
+    assert L.mimk_attn_fwd(None, None) == 1
+    assert L.mimk_mlp_gated(None, None) == 1
+    assert L.mimk_reduce(None, None, lib.F32, -1, 4, 1, lib.SUM, None) == 1
+    assert L.mimk_reduce(None, None, lib.BF16, 1, 4, 1, lib.SUM, None) == 4
+    assert L.mimk_map(99, None, None, None, lib.F32, 1, 1, 1, 0, None) == 1
+
+
+def test_no_cpu_fallback_without_device(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    L = lib.lib()
+    assert L.mimk_device_check() == 6                   # MIMK_E_NO_DEVICE
+    d = lib.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, 4, 4, 4
+    d.in_dtype, d.out_dtype = lib.F32, lib.F32
+    assert L.mimk_gemm(C.byref(d), None) == 6
+    with pytest.raises(ValueError):
+        from mimir_b200 import tensor as T
+        T.product_2d(torch.zeros(2, 2), torch.zeros(2, 2))
+
+
+def test_host_shape_errors_mirror_the_reference(lib):
+    # the reference's refly.check message for mismatching contractions (tensor.mim:1393)
+    import torch
+    from mimir_b200 import tensor as T
+    if not torch.cuda.is_available():
+        pytest.skip("shape checks run after the device check")
+    with pytest.raises(ValueError, match="contracting dims don't match"):
+        T.product_2d(torch.zeros(2, 3, device="cuda"), torch.zeros(4, 2, device="cuda"))

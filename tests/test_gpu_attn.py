@@ -1,0 +1,63 @@
+"""GPU parity: attention forward against the oracle's f64 routine (the reference driver's check)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as mo
+from tests.util import TOL_BF16, TOL_F32, bits, f64, nerr, randn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T():
+    from mimir_b200 import tensor
+    return tensor
+
+
+@pytest.mark.parametrize("bh,sq,sk,d", [(1, 4, 4, 8), (2, 64, 64, 8), (3, 33, 70, 40), (2, 128, 128, 64)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_f32(T, bh, sq, sk, d, causal):
+    if causal and sq != sk:
+        pytest.skip("the oracle's mask is defined for square scores")
+    q, k, v = randn((bh, sq, d), 1), randn((bh, sk, d), 2), randn((bh, sk, d), 3)
+    scale = 1.0 / d ** 0.5
+    o, lse = T.attention(q, k, v, scale=scale, causal=causal, return_lse=True)
+    if sq == sk:
+        want = mo.attention(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), scale=scale, causal=causal)
+    else:
+        s = np.einsum("hid,hjd->hij", f64(q), f64(k)) * scale
+        p = np.exp(s - s.max(-1, keepdims=True))
+        want = (p / p.sum(-1, keepdims=True)) @ f64(v)
+    assert nerr(f64(o), want) <= TOL_F32
+    s = np.einsum("hid,hjd->hij", f64(q), f64(k)) * scale
+    if causal:
+        s = np.where(np.tril(np.ones((sq, sk), bool)), s, -np.inf)
+    want_lse = np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1)
+    assert np.abs(lse.cpu().numpy() - want_lse).max() < 1e-4
+
+
+@pytest.mark.parametrize("bh,s,d", [(2, 128, 128), (2, 256, 128), (3, 384, 128), (1, 1024, 128), (2, 200, 128),
+                                    (2, 512, 64)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_bf16(T, bh, s, d, causal):
+    q, k, v = (randn((bh, s, d), 10 + i, 1.0, torch.bfloat16) for i in range(3))
+    scale = 1.0 / d ** 0.5
+    o = T.attention(q, k, v, scale=scale, causal=causal)
+    T.device_status()
+    want = mo.attention(bits(q), bits(k), bits(v), scale=scale, causal=causal, bf16=True)
+    assert nerr(f64(o), want) <= TOL_BF16
+
+
+def test_attention_config_c4_heads(T):
+    # batch=4, heads=32, seqlen=4096, head_dim=128, causal: every head computed, three checked against the oracle
+    q, k, v = (randn((4, 32, 4096, 128), 1240 + i, 1.0, torch.bfloat16) for i in range(3))
+    scale = 1.0 / 128 ** 0.5
+    o = T.attention(q, k, v, scale=scale, causal=True)
+    T.device_status()
+    heads = [0, 77, 127]
+    qf, kf, vf = (t.reshape(128, 4096, 128) for t in (q, k, v))
+    want = mo.attention(bits(qf[heads]), bits(kf[heads]), bits(vf[heads]), scale=scale, causal=True, bf16=True)
+    assert nerr(f64(o.reshape(128, 4096, 128)[heads]), want) <= TOL_BF16
+    # first query row attends to one key only: O[0] = V[0] exactly
+    assert torch.equal(o[..., 0, :], v[..., 0, :])

@@ -1,0 +1,205 @@
+"""GPU parity: the dot family (f32 CUDA-core path, bf16 tcgen05 path, epilogues, gated MLP) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as mo
+from tests.util import TOL_BF16, TOL_F32, bits, f64, nerr, randn, uniform
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T():
+    from mimir_b200 import tensor
+    return tensor
+
+
+def test_config_c1_f32_256(T):
+    a, b = uniform((256, 256), 1234), uniform((256, 256), 1235)
+    c = T.product_2d(a, b)
+    an, bn = a.cpu().numpy(), b.cpu().numpy()
+    assert nerr(f64(c), mo.gemm_truth(an, bn)) <= TOL_F32
+    assert nerr(f64(c), mo.gemm(an, bn)) <= TOL_F32
+
+
+@pytest.mark.parametrize("M,K,N", [(6, 40, 8), (5, 33, 7)])
+def test_fc_exec_fixture(T, M, K, N):
+    # lit/tensor/fc_aux.cpp:16-42 -- relu(x W^T + b), W stored [N,K], bias/relu fused into `post`
+    x = ((torch.arange(M * K) % 13).float() / 13.0 - 0.4).reshape(M, K).cuda()
+    w = (((7 * torch.arange(N * K)) % 11).float() / 11.0 - 0.5).reshape(N, K).cuda()
+    bias = ((torch.arange(N) % 5).float() / 5.0 - 0.4).cuda()
+    out = T.product_2d(x, T.transpose_2d(w), post="bias_relu", bias=bias)
+    s = x.double().cpu().numpy() @ w.double().cpu().numpy().T
+    ref = np.maximum((s + bias.cpu().numpy()).astype(np.float32), 0)
+    assert (np.abs(ref - out.cpu().numpy()) <= 1e-4 + 1e-4 * np.abs(ref)).all()
+
+
+def test_attn_exec_fixture_composed_on_device(T):
+    # lit/tensor/attn_exec.mim:20-22 op by op: three product_2d, scores through transpose_2d, softmax, product_2d
+    for N in (4, 64):
+        D = 8
+        x = ((torch.arange(N * D) % 13).float() / 13.0 - 0.4).reshape(N, D).cuda()
+        j = torch.arange(D * D)
+        wq = (((7 * j) % 11).float() / 11.0 - 0.5).reshape(D, D).cuda()
+        wk = (((5 * j) % 9).float() / 9.0 - 0.5).reshape(D, D).cuda()
+        wv = (((3 * j) % 7).float() / 7.0 - 0.5).reshape(D, D).cuda()
+        q, k, v = T.product_2d(x, wq), T.product_2d(x, wk), T.product_2d(x, wv)
+        out = T.product_2d(T.softmax(1, T.product_2d(q, T.transpose_2d(k))), v)
+        xd = x.double().cpu().numpy()
+        qd, kd, vd = (xd @ w.double().cpu().numpy() for w in (wq, wk, wv))
+        s = qd @ kd.T
+        p = np.exp(s - s.max(1, keepdims=True))
+        ref = (p / p.sum(1, keepdims=True)) @ vd
+        assert (np.abs(ref - out.cpu().numpy()) <= 1e-4 + 1e-4 * np.abs(ref)).all()
+        fused = T.attention(q, k, v)
+        assert (np.abs(ref - fused.cpu().numpy()) <= 1e-4 + 1e-4 * np.abs(ref)).all()
+
+
+def test_hlo_mlp_fixture(T):
+    # lit/tensor/hlo_aux.cpp:41-84 -- tanh MLP 128/784/1024/10 with bias+tanh epilogues, rel <= 1e-3
+    B, IN, H, OUT = 128, 784, 1024, 10
+
+    def init(n):
+        return ((torch.arange(n) % 100).float() / 100.0).cuda()
+
+    w0, b0, w1, b1 = init(IN * H).reshape(IN, H), init(H), init(H * H).reshape(H, H), init(H)
+    w2, b2, x = init(H * OUT).reshape(H, OUT), init(OUT), init(B * IN).reshape(B, IN)
+    h0 = T.product_2d(x, w0, post="bias_tanh", bias=b0)
+    h1 = T.product_2d(h0, w1, post="bias_tanh", bias=b1)
+    out = T.reduce("max", 1, T.product_2d(h1, w2, post="bias", bias=b2))
+    d0 = np.tanh(x.double().cpu().numpy() @ w0.double().cpu().numpy() + b0.cpu().numpy())
+    d1 = np.tanh(d0 @ w1.double().cpu().numpy() + b1.cpu().numpy())
+    ref = (d1 @ w2.double().cpu().numpy() + b2.cpu().numpy()).max(axis=1)
+    rel = np.abs(ref - out.cpu().numpy()) / (np.abs(ref) + 1e-6)
+    assert rel.max() <= 1e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (17, 19, 23), (64, 64, 64), (130, 70, 257), (256, 512, 100)])
+@pytest.mark.parametrize("nk", [False, True])
+def test_f32_shapes(T, M, N, K, nk):
+    a = uniform((M, K), M * 7 + K)
+    b = uniform((N, K) if nk else (K, N), N * 3 + K)
+    c = T.product_2d(a, T.transpose_2d(b) if nk else b)
+    want = mo.gemm_truth(a.cpu().numpy(), b.cpu().numpy(), b_nk=nk)
+    assert nerr(f64(c), want) <= TOL_F32
+
+
+def test_bmm_f32(T):
+    a, b = uniform((5, 33, 20), 1), uniform((5, 20, 17), 2)
+    c = T.bmm(a, b)
+    for i in range(5):
+        assert nerr(f64(c[i]), mo.gemm_truth(a[i].cpu().numpy(), b[i].cpu().numpy())) <= TOL_F32
+
+
+# ------------------------------------------------------------------ tensor-core path
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 512), (384, 264, 200), (100, 72, 136),
+                                   (1000, 1000, 1000), (2048, 2048, 2048)])
+@pytest.mark.parametrize("nk", [True, False])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_bf16_tensor_core(T, M, N, K, nk, out_dtype):
+    a = randn((M, K), 100 + M, 0.5, torch.bfloat16)
+    b = randn((N, K) if nk else (K, N), 200 + N, 0.5, torch.bfloat16)
+    c = T.product_2d(a, T.transpose_2d(b) if nk else b, out_dtype=out_dtype)
+    T.device_status()
+    rows = None if M * N * K <= 300 * 300 * 300 else sorted(set(np.random.default_rng(M).integers(0, M, 48).tolist() + [0, M - 1]))
+    want = mo.gemm_truth(bits(a), bits(b), b_nk=nk, bf16=True, rows=rows)
+    got = f64(c) if rows is None else f64(c[rows])
+    tol = TOL_BF16 if out_dtype == torch.bfloat16 else 1e-4   # f32 store: only the accumulation order differs
+    assert nerr(got, want) <= tol
+
+
+def test_bf16_structured_identity(T):
+    # B = identity picks columns of A exactly: any layout/descriptor mistake shows up as a permutation
+    M, K = 256, 256
+    a = randn((M, K), 3, 1.0, torch.bfloat16)
+    eye = torch.eye(K, dtype=torch.bfloat16, device="cuda")
+    for b in (eye, T.transpose_2d(eye.clone())):
+        c = T.product_2d(a, b)
+        T.device_status()
+        assert torch.equal(c, a)
+    # a single one in B at (k0, n0) moves column k0 of A to column n0 of C
+    for nk in (False, True):
+        b = torch.zeros((K, K), dtype=torch.bfloat16, device="cuda")
+        b[37, 201] = 1
+        bb = T.transpose_2d(b.t().contiguous()) if nk else b
+        c = T.product_2d(a, bb)
+        want = torch.zeros_like(a)
+        want[:, 201] = a[:, 37]
+        assert torch.equal(c, want)
+
+
+def test_bf16_epilogues(T):
+    M, N, K = 256, 320, 192
+    a = randn((M, K), 1, 0.3, torch.bfloat16)
+    w = randn((N, K), 2, 0.3, torch.bfloat16)
+    bias = uniform((N,), 3)
+    res = randn((M, N), 4, 1.0, torch.bfloat16)
+    acc = mo.gemm_truth(bits(a), bits(w), b_nk=True, bf16=True)
+    bn = bias.cpu().numpy().astype(np.float64)
+    cases = {
+        "bias": acc + bn, "bias_relu": np.maximum(acc + bn, 0), "bias_tanh": np.tanh(acc + bn),
+        "relu": np.maximum(acc, 0), "silu": acc / (1 + np.exp(-acc)),
+    }
+    for post, want in cases.items():
+        c = T.product_2d(a, T.transpose_2d(w), post=post, bias=bias if "bias" in post else None, out_dtype=torch.float32)
+        assert nerr(f64(c), want) <= 1e-4, post
+    c = T.product_2d(a, T.transpose_2d(w), post="add", full=res)
+    assert nerr(f64(c), acc + f64(res)) <= TOL_BF16
+
+
+def test_bf16_linearity_and_checksum_full_size(T):
+    # config C3's shape: C.1 = A.(B.1) and row samples against the oracle
+    n = 8192
+    a = randn((n, n), 1236, 0.02, torch.bfloat16)
+    b = randn((n, n), 1237, 0.02, torch.bfloat16)   # stored [N,K]
+    c = T.product_2d(a, T.transpose_2d(b), out_dtype=torch.float32)
+    T.device_status()
+    ones = torch.ones(n, dtype=torch.float64, device="cuda")
+    lhs = c.double() @ ones
+    rhs = a.double() @ (b.double() @ ones)          # B^T 1 for B stored [N,K] is the row sums of... (b^T)1 = b.sum(0)
+    rhs = a.double() @ b.double().sum(dim=0)
+    assert (lhs - rhs).abs().max() / rhs.abs().max() < 1e-3
+    rows = [0, 127, 128, 4095, 8191]
+    want = mo.gemm_truth(bits(a), bits(b), b_nk=True, bf16=True, rows=rows)
+    assert nerr(f64(c[rows]), want) <= 1e-4
+    cb = T.product_2d(a, T.transpose_2d(b))
+    assert nerr(f64(cb[rows]), want) <= TOL_BF16
+
+
+def test_bmm_bf16(T):
+    a = randn((3, 128, 64), 5, 0.5, torch.bfloat16)
+    b = randn((3, 64, 256), 6, 0.5, torch.bfloat16)
+    c = T.bmm(a, b, out_dtype=torch.float32)
+    T.device_status()
+    for i in range(3):
+        assert nerr(f64(c[i]), mo.gemm_truth(bits(a[i]), bits(b[i]), bf16=True)) <= 1e-4
+
+
+@pytest.mark.parametrize("nk", [False, True])
+def test_mlp_gated(T, nk):
+    M, K, F, N = 256, 192, 384, 128
+    x = randn((M, K), 1, 1.0, torch.bfloat16)
+    w1 = randn((K, F), 2, 0.05, torch.bfloat16)
+    w3 = randn((K, F), 3, 0.05, torch.bfloat16)
+    w2 = randn((F, N), 4, 0.05, torch.bfloat16)
+    if nk:
+        y = T.mlp_gated(x, T.transpose_2d(w1.t().contiguous()), T.transpose_2d(w3.t().contiguous()),
+                        T.transpose_2d(w2.t().contiguous()))
+    else:
+        y = T.mlp_gated(x, w1, w3, w2)
+    T.device_status()
+    want = mo.mlp_gated_truth(bits(x), bits(w1), bits(w3), bits(w2))
+    assert nerr(f64(y), want) <= TOL_BF16
+
+
+def test_zero_extents(T):
+    a = torch.empty((0, 8), device="cuda")
+    b = torch.empty((8, 4), device="cuda")
+    assert T.product_2d(a, b).shape == (0, 4)
+    # K = 0: the fold never runs, every cell is the ring's zero (tensor.mim:1332 with init = R#_0)
+    c = T.product_2d(torch.empty((3, 0), device="cuda"), torch.empty((0, 5), device="cuda"))
+    assert torch.equal(c, torch.zeros(3, 5, device="cuda"))
+    cb = T.product_2d(torch.empty((8, 0), device="cuda", dtype=torch.bfloat16),
+                      torch.empty((0, 8), device="cuda", dtype=torch.bfloat16))
+    assert torch.equal(cb, torch.zeros(8, 8, device="cuda", dtype=torch.bfloat16))

@@ -1,0 +1,145 @@
+"""GPU parity: reduce / softmax / RMSNorm / elementwise against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as mo
+from tests.util import TOL_BF16, TOL_F32, f64, nerr, randn, uniform
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T():
+    from mimir_b200 import tensor
+    return tensor
+
+
+def test_reduce_exec_fixture(T):
+    # lit/tensor/reduce_exec.mim:19-43 on the device
+    x = torch.arange(24, dtype=torch.float32).reshape(2, 3, 4).cuda()
+    xn = x.cpu().numpy()
+    for ax in range(3):
+        assert np.abs(T.reduce("sum", ax, x).cpu().numpy() - mo.reduce(xn, ax)).max() < 1e-5
+    p = T.softmax(1, x)
+    assert np.abs(T.reduce("sum", 1, p).cpu().numpy() - 1.0).max() < 1e-5
+    peak = 1.0 / (1.0 + np.exp(-4.0) + np.exp(-8.0))
+    assert abs(float(p[1, 2, 3]) - peak) < 1e-5
+    total = T.reduce("sum", 0, T.reduce("sum", 0, T.reduce("sum", 0, x)))
+    assert abs(float(total) - 276.0) < 1e-5
+    assert nerr(p.cpu().numpy(), mo.softmax(xn, 1)) < TOL_F32
+
+
+@pytest.mark.parametrize("rows,cols", [(3, 4), (7, 33), (64, 128), (33, 1000), (16, 4096), (8, 8192), (4, 16384),
+                                       (2, 32768), (2, 40000), (5, 8190)])
+def test_softmax_rows_f32(T, rows, cols):
+    x = randn((rows, cols), 11 + cols)
+    y = T.softmax(1, x)
+    want = mo.softmax_rows(x.cpu().numpy(), truth=True)
+    assert nerr(f64(y), want) < TOL_F32
+    # as-lowered f32 oracle: same ops, different summation order
+    assert nerr(f64(y), mo.softmax_rows(x.cpu().numpy())) < TOL_F32
+
+
+@pytest.mark.parametrize("rows,cols", [(16, 8192), (9, 1024), (5, 100)])
+def test_softmax_and_rmsnorm_to_bf16(T, rows, cols):
+    x = randn((rows, cols), 5)
+    gamma = uniform((cols,), 6, 0.5, 1.5)
+    y = T.softmax(1, x, out_dtype=torch.bfloat16)
+    assert y.dtype == torch.bfloat16
+    want = mo.softmax_rows(x.cpu().numpy(), truth=True)
+    assert nerr(f64(y), want) < TOL_BF16
+    # the stored value is the f32 result rounded to nearest even: compare bit patterns with the f32 kernel
+    y32 = T.softmax(1, x)
+    assert torch.equal(y, y32.to(torch.bfloat16))
+    z = T.rmsnorm(x, gamma, 1e-6, out_dtype=torch.bfloat16)
+    wz = mo.rmsnorm_rows(x.cpu().numpy(), gamma.cpu().numpy(), 1e-6, truth=True)
+    assert nerr(f64(z), wz) < TOL_BF16
+    z32 = T.rmsnorm(x, gamma, 1e-6)
+    assert nerr(f64(z32), wz) < TOL_F32
+    assert torch.equal(z, z32.to(torch.bfloat16))
+
+
+def test_softmax_rmsnorm_chain(T):
+    x = randn((12, 2048), 21)
+    gamma = uniform((2048,), 22, 0.5, 1.5)
+    fused = T.softmax_rmsnorm(x, gamma, 1e-6)
+    p = mo.softmax_rows(x.cpu().numpy(), truth=True)
+    want = p / np.sqrt((p * p).mean(axis=1, keepdims=True) + 1e-6) * gamma.cpu().numpy().astype(np.float64)
+    assert nerr(f64(fused), want) < TOL_F32
+    x2 = randn((3, 1001), 23)      # generic (unaligned) kernel
+    g2 = uniform((1001,), 24, 0.5, 1.5)
+    p2 = mo.softmax_rows(x2.cpu().numpy(), truth=True)
+    w2 = p2 / np.sqrt((p2 * p2).mean(axis=1, keepdims=True) + 1e-6) * g2.cpu().numpy().astype(np.float64)
+    assert nerr(f64(T.softmax_rmsnorm(x2, g2, 1e-6)), w2) < TOL_F32
+
+
+def test_softmax_bf16_input(T):
+    x = randn((6, 512), 31, dtype=torch.bfloat16)
+    y = T.softmax(1, x)
+    want = mo.softmax_rows(x.float().cpu().numpy(), truth=True)
+    assert nerr(f64(y), want) < TOL_BF16
+
+
+@pytest.mark.parametrize("shape,ax", [((5, 7, 9), 0), ((5, 7, 9), 1), ((5, 7, 9), 2), ((1, 5000, 64), 1),
+                                      ((300, 4096), 1), ((2048, 130), 0), ((3, 1), 1)])
+@pytest.mark.parametrize("monoid", ["sum", "max", "min"])
+def test_reduce_axes(T, shape, ax, monoid):
+    x = randn(shape, 41 + ax)
+    got = T.reduce(monoid, ax, x)
+    want = mo.reduce_axis(x.cpu().numpy(), ax, monoid, truth=True)
+    assert got.shape == want.shape
+    if monoid == "sum":
+        # error of an f32 sum, relative to the largest partial magnitude
+        scale = np.abs(x.cpu().numpy().astype(np.float64)).sum(axis=ax).max()
+        assert np.abs(f64(got) - want).max() <= 1e-6 * scale + 1e-6
+    else:
+        assert np.array_equal(got.cpu().numpy().astype(np.float64), want)
+
+
+def test_softmax_middle_axis(T):
+    x = randn((4, 37, 6), 51)
+    got = T.softmax(1, x)
+    assert nerr(f64(got), mo.softmax(x.cpu().numpy(), 1)) < TOL_F32
+
+
+def test_elementwise_and_binary_ax(T):
+    x = randn((6, 10, 4), 61)
+    y = randn((6, 10, 4), 62)
+    xn, yn = x.cpu().numpy(), y.cpu().numpy()
+    assert np.allclose(T.binary("add", x, y).cpu().numpy(), xn + yn, rtol=0, atol=0)
+    assert np.allclose(T.binary("mul", x, y).cpu().numpy(), xn * yn, rtol=0, atol=0)
+    assert np.allclose(T.unary("relu", x).cpu().numpy(), np.maximum(xn, 0), rtol=0, atol=0)
+    assert np.allclose(T.unary("tanh", x).cpu().numpy(), np.tanh(xn), rtol=1e-6, atol=1e-6)
+    mx = T.reduce("max", 1, x)
+    e = T.binary_ax("subexp", 1, x, mx)
+    want = mo.binary_ax(mo.F_SUBEXP_F32, 1, xn, mx.cpu().numpy())
+    assert nerr(e.cpu().numpy(), want) < TOL_F32
+    # the reference's own four-op softmax, run op by op on the device, equals the fused kernel
+    s = T.binary_ax("div", 1, e, T.reduce("sum", 1, e))
+    assert nerr(f64(s), f64(T.softmax(1, x))) < TOL_F32
+
+
+def test_empty_and_degenerate(T):
+    e = torch.empty((0, 16), device="cuda")
+    assert T.softmax(1, e).shape == (0, 16)
+    assert T.reduce("sum", 1, e).shape == (0,)
+    one = randn((4, 1), 71)
+    assert torch.equal(T.softmax(1, one), torch.ones_like(one))
+    z = T.reduce("sum", 1, torch.empty((3, 0), device="cuda"))
+    assert torch.equal(z, torch.zeros(3, device="cuda"))
+    m = T.reduce("max", 1, torch.empty((3, 0), device="cuda"))
+    assert torch.isinf(m).all() and (m < 0).all()
+
+
+def test_full_size_softmax_properties(T):
+    # the bench workload's shape: rows sum to one, argmax preserved, idempotent statistics
+    x = randn((16384, 8192), 81)
+    y = T.softmax(1, x, out_dtype=torch.bfloat16)
+    sums = y.float().sum(dim=1)
+    assert (sums - 1).abs().max() < 2e-2
+    assert torch.equal(y.float().argmax(dim=1), x.argmax(dim=1)) or \
+        (y.float().max(dim=1).values == y.float().gather(1, x.argmax(dim=1, keepdim=True)).squeeze(1)).all()
+    rows = [0, 1, 8191, 16383]
+    want = mo.softmax_rows(x[rows].cpu().numpy(), truth=True)
+    assert nerr(f64(y[rows]), want) < TOL_BF16
