@@ -381,7 +381,7 @@ extern "C" int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, i
     DeviceInfo* dev = device_info(&st);
     if (!dev) return st;
     if (outer * inner == 0) return MIMK_OK;
-    if (!x || !out) return MIMK_E_ARG;
+    if (!out || (len > 0 && !x)) return MIMK_E_ARG;  // len == 0: every cell is the monoid's identity, x is not read
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const float* xf = static_cast<const float*>(x);
     float* of       = static_cast<float*>(out);
