@@ -100,6 +100,23 @@ int mimk_gemm(const mimk_gemm_desc* desc, void* stream);
 int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner, int monoid,
                 void* stream);
 
+/* mimk_reduce for callers that must not have the library allocate: same arguments, same results, but no
+ * cudaMalloc / cudaFree / cudaHostAlloc is ever issued, on any call. (No counterpart in the reference, whose
+ * generated wrappers allocate per operation.) Two kinds of caller need this: an embedder that plans all device
+ * memory itself -- a fixed memory budget, or an allocator of its own that a hidden cudaMalloc would bypass -- and
+ * a latency-critical loop that cannot take the device-wide synchronisation an allocation may imply.
+ * Where mimk_reduce keeps the partial results of a split reduction in a cached allocation, this entry point keeps
+ * them in a fixed 1 MiB array inside the library image (MIMK_REDUCE_STATIC_BYTES; every GPU that loads the library
+ * holds it until the process exits). A call whose plan needs more partials than fit returns MIMK_E_WORKSPACE and
+ * launches nothing; on a 148-SM B200 no plan exceeds about 0.9 MiB.
+ * The first call on each device resolves the array's device address (with that device current) and reads two
+ * device attributes; make that first call before any stream capture begins. All calls on a device share the one
+ * array, so two calls whose kernels may overlap on the GPU (different streams, no dependency between them) race
+ * on it: order them. Nothing needs zeroing between calls -- each call overwrites every partial it later reads. */
+#define MIMK_REDUCE_STATIC_BYTES (1u << 20)
+int mimk_reduce_static(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner, int monoid,
+                       void* stream);
+
 /* y = softmax(x) along the middle axis of a [outer, len, inner] view, in one pass over HBM.
  * Replaces: the four map_reduce_post ops the `softmax` lam expands to (tensor.mim:1172-1176).
  * x F32 (or BF16), y F32 or BF16; statistics in f32. */

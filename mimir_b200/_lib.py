@@ -23,7 +23,7 @@ ROWS_SOFTMAX, ROWS_RMSNORM, ROWS_SOFTMAX_RMSNORM = 0, 1, 2
 # every symbol include/mimk.h declares
 SYMBOLS = (
     "mimk_status_str", "mimk_abi_version", "mimk_last_cuda_error", "mimk_device_check", "mimk_device_status",
-    "mimk_gemm", "mimk_reduce", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map",
+    "mimk_gemm", "mimk_reduce", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map",
     "mimk_attn_fwd", "mimk_mlp_gated",
     "mimk_host_rows", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_register",
     "mimk_host_unregister", "mimk_host_release",
@@ -80,6 +80,7 @@ def lib() -> C.CDLL:
         L.mimk_device_status.argtypes = [vp]
         L.mimk_gemm.argtypes = [C.POINTER(GemmDesc), vp]
         L.mimk_reduce.argtypes = [vp, vp, ci, i64, i64, i64, ci, vp]
+        L.mimk_reduce_static.argtypes = [vp, vp, ci, i64, i64, i64, ci, vp]
         L.mimk_softmax.argtypes = [vp, vp, ci, ci, i64, i64, i64, vp]
         L.mimk_rmsnorm.argtypes = [vp, vp, vp, ci, ci, i64, i64, cf, vp]
         L.mimk_softmax_rmsnorm.argtypes = [vp, vp, vp, ci, ci, i64, i64, cf, vp]

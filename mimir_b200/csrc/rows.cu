@@ -7,7 +7,14 @@
 // reduced with warp shuffles, and written once.
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
+
+// Home of the partial results of mimk_reduce_static's split-axis reduction (instead of the library's cached
+// cudaMalloc'd scratch). Every GPU that loads the library holds these bytes until the process exits.
+constexpr size_t STATIC_PARTIALS = MIMK_REDUCE_STATIC_BYTES / sizeof(float);  // 262144 floats = 1 MiB
+static __device__ __align__(256) float g_static_partials[STATIC_PARTIALS];
 
 namespace mimk {
 namespace {
@@ -367,6 +374,79 @@ int reduce_impl(const float* x, float* out, int64_t outer, int64_t len, int64_t 
     return launch_status();
 }
 
+
+// ---- reduce without any allocation ------------------------------------------------------------------
+
+struct StaticSetup {
+    bool ready = false;
+    float* partials = nullptr;  // device address of g_static_partials on this device
+    int sm_count = 0;
+};
+StaticSetup g_static_setup[64];
+std::mutex g_static_mutex;
+
+// Once per device, with that device current: resolve the array's device address. In host code the name
+// `g_static_partials` is only a stand-in handle for the symbol, never a pointer a kernel may be given.
+int static_setup(StaticSetup** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return MIMK_E_NO_DEVICE;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticSetup& st = g_static_setup[dev];
+    if (!st.ready) {
+        int major = 0, sms = 0;
+        MIMK_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10) return MIMK_E_NO_DEVICE;
+        MIMK_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        float* ptr = nullptr;
+        MIMK_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_partials));
+        if (!ptr) return MIMK_E_CUDA;
+        st.partials = ptr;
+        st.sm_count = sms;
+        st.ready    = true;
+    }
+    *out = &st;
+    return MIMK_OK;
+}
+
+// Same plan and kernels as reduce_impl (kept in step with it by hand so that both give identical bits); only the
+// home of the partial results differs. Nothing needs clearing: every partial that the second kernel reads is
+// written by the first kernel of the same call.
+template <class Op>
+int reduce_static_impl(const float* x, float* out, int64_t outer, int64_t len, int64_t inner, cudaStream_t s,
+                       const StaticSetup& st) {
+    if (inner == 1) {
+        const int vec_ok = (len % 4 == 0) && aligned16(x);
+        int grid         = int(outer < int64_t(st.sm_count) * 8 ? outer : int64_t(st.sm_count) * 8);
+        reduce_rows_kernel<Op><<<grid, 256, 0, s>>>(x, out, outer, len, vec_ok);
+        return launch_status();
+    }
+    const int64_t total = outer * inner;
+    const int threads   = 256;
+    int gx              = grid_for(total, threads, st.sm_count, 8);
+    int slices          = 1;
+    if (int64_t(gx) < 2 * st.sm_count && len >= 256) {
+        int64_t want = (4LL * st.sm_count + gx - 1) / gx;
+        int64_t maxs = len / 64;
+        slices       = int(want < maxs ? want : maxs);
+        if (slices < 1) slices = 1;
+        if (slices > 1024) slices = 1024;
+    }
+    if (slices == 1) {
+        reduce_mid_kernel<Op><<<dim3(gx, 1), threads, 0, s>>>(x, out, outer, len, inner, len);
+        return launch_status();
+    }
+    const int64_t slice_len = (len + slices - 1) / slices;
+    slices                  = int((len + slice_len - 1) / slice_len);
+    if (size_t(slices) * size_t(total) > STATIC_PARTIALS) return MIMK_E_WORKSPACE;
+    reduce_mid_kernel<Op><<<dim3(gx, slices), threads, 0, s>>>(x, st.partials, outer, len, inner, slice_len);
+    MIMK_TRY(launch_status());
+    reduce_partials_kernel<Op><<<gx, threads, 0, s>>>(st.partials, out, total, slices);
+    return launch_status();
+}
+
 }  // namespace
 }  // namespace mimk
 
@@ -389,6 +469,25 @@ extern "C" int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, i
         case MIMK_SUM: return reduce_impl<SumOp>(xf, of, outer, len, inner, s, *dev);
         case MIMK_MAX: return reduce_impl<MaxOp>(xf, of, outer, len, inner, s, *dev);
         default: return reduce_impl<MinOp>(xf, of, outer, len, inner, s, *dev);
+    }
+}
+
+extern "C" int mimk_reduce_static(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner,
+                                  int monoid, void* stream) {
+    if (outer < 0 || len < 0 || inner < 0) return MIMK_E_ARG;
+    if (dtype != MIMK_F32) return MIMK_E_DTYPE;
+    if (monoid < MIMK_SUM || monoid > MIMK_MIN) return MIMK_E_ARG;
+    StaticSetup* st = nullptr;
+    MIMK_TRY(static_setup(&st));
+    if (outer * inner == 0) return MIMK_OK;
+    if (!out || (len > 0 && !x)) return MIMK_E_ARG;
+    cudaStream_t s  = static_cast<cudaStream_t>(stream);
+    const float* xf = static_cast<const float*>(x);
+    float* of       = static_cast<float*>(out);
+    switch (monoid) {
+        case MIMK_SUM: return reduce_static_impl<SumOp>(xf, of, outer, len, inner, s, *st);
+        case MIMK_MAX: return reduce_static_impl<MaxOp>(xf, of, outer, len, inner, s, *st);
+        default: return reduce_static_impl<MinOp>(xf, of, outer, len, inner, s, *st);
     }
 }
 
