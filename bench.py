@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--workload", default="rows", choices=["rows", "gemm", "attn", "mlp", "matmul_f32"])
     ap.add_argument("--no-extras", action="store_true", help="skip the short runs of the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     return ap.parse_args()
 
 
@@ -449,28 +450,31 @@ def run_ours(args):
     peak = pk["hbm"] if w.bound == "hbm" else pk["tensor"]
 
     # end to end through the host-buffer entry points: pinned host inputs in, host result out, every step
-    w.e2e_setup()
-    w.e2e_step()
-    e2e_steps = max(1, min(K, 5))
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    te = time.perf_counter()
-    sink = 0.0
-    for _ in range(e2e_steps):
-        sink += w.e2e_step()
-    e2e_s = time.perf_counter() - te
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_val = w.units * e2e_steps * world / e2e_s / (1e9 if w.unit == "GB/s" else 1e12)
+    e2e = None
+    if not args.no_e2e:
+        w.e2e_setup()
+        w.e2e_step()
+        e2e_steps = max(1, min(K, 5))
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        te = time.perf_counter()
+        sink = 0.0
+        for _ in range(e2e_steps):
+            sink += w.e2e_step()
+        e2e_s = time.perf_counter() - te
+        if world > 1:
+            t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        e2e_val = w.units * e2e_steps * world / e2e_s / (1e9 if w.unit == "GB/s" else 1e12)
+        e2e = {"value": e2e_val, "unit": w.unit, "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
+               "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3, "sink": sink}
 
     line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
             "data": "synthetic", "config": w.config, "clocks": clocks,
-            "e2e": {"value": e2e_val, "unit": w.unit, "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
-                    "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3, "sink": sink},
+            "e2e": e2e,
             "gpu_launches": K * w.launches_per_step,
             "roofline": {"bound": w.bound, "kernel": w.kernel, "achieved": achieved, "peak": peak,
                          "unit": "GB/s" if w.bound == "hbm" else "TFLOP/s", "frac": achieved / peak,

@@ -1,6 +1,370 @@
-// placeholder until the tensor-core attention kernel lands
+// Attention forward on the 5th-generation tensor cores: O = softmax(scale * Q K^T [+ causal mask]) V, bf16 in/out,
+// f32 scores, statistics and accumulation, head_dim 128.
+//
+// The reference computes this as the composed program `softmax (q * transpose_2d k) * v` (MimIR
+// lit/tensor/attn_exec.mim:20-22): two contractions around the four-op softmax (tensor.mim:1172-1176) with the whole
+// score matrix in memory. Here the score tile never leaves the SM:
+//
+//   one CTA owns two query tiles of 128 rows of one (batch, head) and walks the key/value tiles of 128 keys
+//   warp 0        TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled shared memory)
+//   warp 1        MMA issuer (one thread): S_t = Q_t K^T  (tcgen05.mma, M128 N128 K16 x 8, both operands in shared
+//                 memory) and O_t += P_t V (A operand = P_t in tensor memory, B operand = V as an MN-major tile)
+//   warps 4..7    softmax of query tile 0, one thread per row: tcgen05.ld the f32 scores, running max / sum in
+//   warps 8..11   softmax of query tile 1   registers, exp2 with the scale folded in, P written back over S in
+//                 tensor memory as bf16 (tcgen05.st); O is rescaled in tensor memory only when the running max
+//                 has grown by more than 2^8 since the last rescale
+//   TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 f32 columns each; P_t aliases the first 64 columns of S_t.
+// While one tile's warps do their exponentials the tensor core works on the other tile.
+// Every mbarrier wait is bounded; on expiry the CTA records MIMK_E_DEVICE_WAIT and unwinds.
+#include <math_constants.h>
+
 #include "common.cuh"
+#include "sm100.cuh"
+
 namespace mimk {
-int attn_tc_supported(const mimk_attn_desc&) { return 0; }
-int attn_tc(const mimk_attn_desc&, cudaStream_t) { return MIMK_E_UNSUPPORTED; }
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int TILE_BYTES = 128 * 128 * 2;  // a [128 x 128] bf16 tile = two swizzle atoms of [128 x 64]
+constexpr int ATOM_BYTES = TILE_BYTES / 2;
+constexpr int KV_STAGES = 2;
+constexpr int NUM_THREADS = 384;
+constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+
+struct Bars {
+    uint64_t q_full;
+    uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
+    uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
+    uint64_t s_full[2], p_full[2], o_full[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+constexpr int SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + 1024 + 256;
+static_assert(sizeof(Bars) <= 256, "barrier block too large");
+
+struct Params {
+    int64_t Sq, Sk, BH;
+    __nv_bfloat16* O;
+    float* lse;
+    float scale_log2;  // scale * log2(e)
+    int causal;
+    int* status;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void tmem_st_32x32_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base     = (raw_addr + 1023u) & ~1023u;
+    const uint32_t sQ = base, sK = base + 2 * TILE_BYTES, sV = sK + KV_STAGES * TILE_BYTES;
+    Bars* bars = reinterpret_cast<Bars*>(smem_raw + (base - raw_addr) + (2 + 2 * KV_STAGES) * TILE_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y;
+    const int pair = int(gridDim.x) - 1 - int(blockIdx.x);  // longest (latest) query tiles first
+    int64_t q0[2];
+    int n_kv[2];
+    const int kv_tiles = int((p.Sk + BKV - 1) / BKV);
+    for (int t = 0; t < 2; ++t) {
+        q0[t] = int64_t(pair) * 2 * BQ + t * BQ;
+        if (q0[t] >= p.Sq) {
+            n_kv[t] = 0;
+        } else if (p.causal) {
+            const int diag = int(q0[t] / BKV) + 1;
+            n_kv[t]        = diag < kv_tiles ? diag : kv_tiles;
+        } else {
+            n_kv[t] = kv_tiles;
+        }
+    }
+    const int n_max = n_kv[0] > n_kv[1] ? n_kv[0] : n_kv[1];
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars->q_full), 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(smem_u32(&bars->k_full[s]), 1);
+            mbar_init(smem_u32(&bars->k_empty[s]), 1);
+            mbar_init(smem_u32(&bars->v_full[s]), 1);
+            mbar_init(smem_u32(&bars->v_empty[s]), 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(smem_u32(&bars->s_full[t]), 1);
+            mbar_init(smem_u32(&bars->p_full[t]), 128);
+            mbar_init(smem_u32(&bars->o_full[t]), 1);
+        }
+        bars->abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&bars->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0 && n_max > 0) {
+            const uint32_t qf = smem_u32(&bars->q_full);
+            mbar_expect_tx(qf, (n_kv[1] > 0 ? 2 : 1) * TILE_BYTES);
+            for (int t = 0; t < 2; ++t)
+                if (n_kv[t] > 0) {
+                    tma_load_3d(sQ + t * TILE_BYTES, &tmQ, 0, int(q0[t]), head, qf);
+                    tma_load_3d(sQ + t * TILE_BYTES + ATOM_BYTES, &tmQ, 64, int(q0[t]), head, qf);
+                }
+            bool ok = true;
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int s = j % KV_STAGES;
+                const uint32_t ph = (j / KV_STAGES) & 1;
+                if (!(ok = mbar_wait(smem_u32(&bars->k_empty[s]), ph ^ 1u, abort_flag))) break;
+                const uint32_t kf = smem_u32(&bars->k_full[s]);
+                mbar_expect_tx(kf, TILE_BYTES);
+                tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, j * BKV, head, kf);
+                tma_load_3d(sK + s * TILE_BYTES + ATOM_BYTES, &tmK, 64, j * BKV, head, kf);
+                if (!(ok = mbar_wait(smem_u32(&bars->v_empty[s]), ph ^ 1u, abort_flag))) break;
+                const uint32_t vf = smem_u32(&bars->v_full[s]);
+                mbar_expect_tx(vf, TILE_BYTES);
+                tma_load_3d(sV + s * TILE_BYTES, &tmV, 0, j * BKV, head, vf);
+                tma_load_3d(sV + s * TILE_BYTES + ATOM_BYTES, &tmV, 64, j * BKV, head, vf);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && n_max > 0) {
+            const uint32_t idesc_qk = idesc_bf16_f32(BQ, BKV, 0, 0);
+            const uint32_t idesc_pv = idesc_bf16_f32(BQ, HD, 0, 1);
+            bool ok = true;
+            // S_t = Q_t K_j^T: 8 k-steps of 16 over head_dim; atom = k-step / 4, 32 bytes per step inside an atom
+            auto issue_qk = [&](int t, int j) {
+                const uint32_t qa = sQ + t * TILE_BYTES, kb = sK + (j % KV_STAGES) * TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * ATOM_BYTES + (k & 3) * 32;
+                    mma_f16_ss(tmem_base + t * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(kb + off, 16, 1024),
+                               idesc_qk, k > 0 ? 1u : 0u);
+                }
+                mma_commit(smem_u32(&bars->s_full[t]));
+            };
+            // O_t (+)= P_t V_j: 8 k-steps of 16 keys; P from tensor memory (8 columns of packed bf16 pairs per step),
+            // V as an MN-major operand: 16 key rows = 2048 bytes per step, the two 64-wide halves of head_dim are
+            // ATOM_BYTES apart
+            auto issue_pv = [&](int t, int j) {
+                const uint32_t vb = sV + (j % KV_STAGES) * TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k)
+                    mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+                               smem_desc_sw128(vb + k * 2048, ATOM_BYTES, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+            };
+            ok = mbar_wait(smem_u32(&bars->q_full), 0, abort_flag);
+            if (ok) ok = mbar_wait(smem_u32(&bars->k_full[0]), 0, abort_flag);
+            if (ok) {
+                tc_fence_after();
+                for (int t = 0; t < 2; ++t)
+                    if (n_kv[t] > 0) issue_qk(t, 0);
+                mma_commit(smem_u32(&bars->k_empty[0]));
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int s = j % KV_STAGES, s1 = (j + 1) % KV_STAGES;
+                const uint32_t ph = (j / KV_STAGES) & 1, ph1 = ((j + 1) / KV_STAGES) & 1;
+                bool v_ready = false, k_ready = false;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (j >= n_kv[t]) continue;
+                    if (!(ok = mbar_wait(smem_u32(&bars->p_full[t]), j & 1, abort_flag))) break;
+                    if (!v_ready) {
+                        if (!(ok = mbar_wait(smem_u32(&bars->v_full[s]), ph, abort_flag))) break;
+                        v_ready = true;
+                    }
+                    tc_fence_after();
+                    issue_pv(t, j);
+                    if (j + 1 == n_kv[t]) mma_commit(smem_u32(&bars->o_full[t]));
+                    if (j + 1 < n_kv[t]) {
+                        if (!k_ready) {
+                            if (!(ok = mbar_wait(smem_u32(&bars->k_full[s1]), ph1, abort_flag))) break;
+                            k_ready = true;
+                            tc_fence_after();
+                        }
+                        issue_qk(t, j + 1);
+                    }
+                }
+                if (!ok) break;
+                mma_commit(smem_u32(&bars->v_empty[s]));
+                if (k_ready) mma_commit(smem_u32(&bars->k_empty[s1]));
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- softmax + output, one thread per query row ----------------
+        const int t = (warp - 4) >> 2;
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const int64_t qi = q0[t] + row_in_tile;
+        const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
+        const uint32_t tS = tmem_base + t * 128 + lane_sel, tO = tmem_base + 256 + t * 128 + lane_sel;
+        float m_used = -CUDART_INF_F, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kv[t] && ok; ++j) {
+            if (!(ok = mbar_wait(smem_u32(&bars->s_full[t]), j & 1, abort_flag))) break;
+            tc_fence_after();
+            const int64_t k0 = int64_t(j) * BKV;
+            const bool need_mask = (p.causal && k0 + BKV - 1 > q0[t]) || (k0 + BKV > p.Sk);
+            int64_t limit = p.Sk;  // keys >= limit are masked for this row
+            if (p.causal && qi + 1 < limit) limit = qi + 1;
+            // pass 1: row maximum of the scaled scores
+            float mx = -CUDART_INF_F;
+#pragma unroll 1
+            for (int c = 0; c < BKV; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tS + c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float v = __uint_as_float(r[i]) * p.scale_log2;
+                    if (need_mask && k0 + c + i >= limit) v = -CUDART_INF_F;
+                    mx = fmaxf(mx, v);
+                }
+            }
+            if (j == 0) {
+                m_used = mx;
+            } else if (mx > m_used + RESCALE_THRESHOLD) {
+                // the previous O_t += P_t V has completed: its commit precedes the one that released S_t
+                const float alpha = fast_exp2(m_used - mx);
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tO + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_st_32x32_x32(tO + c, r);
+                }
+                l *= alpha;
+                m_used = mx;
+            }
+            // pass 2: p = exp2(s - m), row sum, P as bf16 over the first 64 columns of S_t
+#pragma unroll 1
+            for (int c = 0; c < BKV; c += 32) {
+                uint32_t r[32], pk[16];
+                tmem_ld_32x32(tS + c, r);
+                tmem_ld_wait();
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float a = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_used));
+                    float b = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_used));
+                    if (need_mask) {
+                        if (k0 + c + i >= limit) a = 0.f;
+                        if (k0 + c + i + 1 >= limit) b = 0.f;
+                    }
+                    sum += a + b;
+                    pk[i >> 1] = pack_bf16x2(a, b);
+                }
+                l += sum;
+                tmem_st_32x32_x16(tS + (c >> 1), pk);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bars->p_full[t]));
+        }
+        if (ok && n_kv[t] > 0) ok = mbar_wait(smem_u32(&bars->o_full[t]), 0, abort_flag);
+        if (ok && n_kv[t] > 0) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = p.O + (int64_t(head) * p.Sq + qi) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tO + c, r);
+                tmem_ld_wait();
+                if (qi < p.Sq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 q;
+                        q.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        q.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        q.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        q.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + i) = q;
+                    }
+                }
+            }
+            if (p.lse && qi < p.Sq)
+                p.lse[int64_t(head) * p.Sq + qi] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_flag) *p.status = MIMK_E_DEVICE_WAIT;
+}
+
+}  // namespace
+
+int attn_tc_supported(const mimk_attn_desc& d) {
+    if (d.dtype != MIMK_BF16 || d.head_dim != HD) return 0;
+    if (d.seq_k <= 0 || d.seq_q <= 0) return 0;
+    if (d.causal && d.seq_q != d.seq_k) return 0;
+    if (d.batch_heads > 65535 || d.seq_q >= (int64_t(1) << 31) || d.seq_k >= (int64_t(1) << 31)) return 0;
+    if (!aligned16(d.q) || !aligned16(d.k) || !aligned16(d.v) || !aligned16(d.o)) return 0;
+    if (!(d.scale > 0.f)) return 0;
+    return 1;
+}
+
+int attn_tc(const mimk_attn_desc& d, cudaStream_t s) {
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    CUtensorMap tQ, tK, tV;
+    const uint64_t row = HD * 2;
+    MIMK_TRY(make_tmap_bf16_3d(&tQ, d.q, HD, uint64_t(d.seq_q), uint64_t(d.batch_heads), row, uint64_t(d.seq_q) * row, 64, BQ));
+    MIMK_TRY(make_tmap_bf16_3d(&tK, d.k, HD, uint64_t(d.seq_k), uint64_t(d.batch_heads), row, uint64_t(d.seq_k) * row, 64, BKV));
+    MIMK_TRY(make_tmap_bf16_3d(&tV, d.v, HD, uint64_t(d.seq_k), uint64_t(d.batch_heads), row, uint64_t(d.seq_k) * row, 64, BKV));
+    static bool configured = false;
+    if (!configured) {
+        MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    Params p;
+    p.Sq = d.seq_q, p.Sk = d.seq_k, p.BH = d.batch_heads;
+    p.O          = static_cast<__nv_bfloat16*>(d.o);
+    p.lse        = d.lse;
+    p.scale_log2 = d.scale * 1.4426950408889634f;
+    p.causal     = d.causal;
+    p.status     = dev->status_dev;
+    dim3 grid((unsigned)((d.seq_q + 2 * BQ - 1) / (2 * BQ)), (unsigned)d.batch_heads);
+    attn_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, p);
+    return launch_status();
+}
+
 }  // namespace mimk

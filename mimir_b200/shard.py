@@ -1,0 +1,89 @@
+"""Sharding of the hot-path operators over the GPUs of one node (one process per GPU, torch.distributed).
+
+Each sharded configuration is independent on its output, so the data path needs no collective:
+  * contraction C = A B: rank g owns a contiguous slab of B's columns (rows of the stored [N,K] tensor) and
+    computes C[:, slab]; A is replicated;
+  * attention: rank g owns a contiguous range of batch x head;
+  * row-wise operators: rank g owns a contiguous block of rows.
+A collective appears only when every rank needs the whole result: `gather_columns` / `gather_rows` all-gather the
+shards (NCCL over NVLink on GPUs; the same code runs on gloo for CPU tests).  The reference has no multi-device
+support at all (device 0 is hard-coded, MimIR src/mim/plug/nvptx/phase/nvptx.cpp:186-204).
+"""
+from __future__ import annotations
+
+from typing import Callable, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def split_range(n: int, rank: int, world: int) -> Tuple[int, int]:
+    """[lo, hi) of `n` units for `rank`: contiguous, sizes differ by at most one, earlier ranks take the extra."""
+    if world <= 0 or not (0 <= rank < world) or n < 0:
+        raise ValueError("split_range: need 0 <= rank < world and n >= 0")
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def _world():
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+def gather_rows(local: torch.Tensor, total_rows: int) -> torch.Tensor:
+    """All-gather row blocks (split_range order) into the full [total_rows, ...] tensor on every rank.
+    Uneven blocks are padded to the largest one for the collective and trimmed afterwards."""
+    rank, world = _world()
+    if world == 1:
+        return local
+    spans = [split_range(total_rows, r, world) for r in range(world)]
+    biggest = max(hi - lo for lo, hi in spans)
+    tail = tuple(local.shape[1:])
+    send = local.contiguous()
+    if send.shape[0] != biggest:
+        pad = torch.zeros((biggest,) + tail, dtype=local.dtype, device=local.device)
+        pad[: send.shape[0]] = send
+        send = pad
+    recv = torch.empty((world * biggest,) + tail, dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(recv, send)
+    if biggest * world == total_rows:
+        return recv
+    return torch.cat([recv[r * biggest: r * biggest + (hi - lo)] for r, (lo, hi) in enumerate(spans)], dim=0)
+
+
+def gather_columns(local: torch.Tensor, total_cols: int) -> torch.Tensor:
+    """All-gather column slabs C[:, lo:hi] into the full [M, total_cols] tensor on every rank."""
+    rank, world = _world()
+    if world == 1:
+        return local
+    return gather_rows(local.t().contiguous(), total_cols).t().contiguous()
+
+
+def sharded_product_2d(a: torch.Tensor, b_nk: torch.Tensor, compute: Callable, gather: bool = False):
+    """C = a . b_nk^T with b_nk stored [N, K]: this rank's slab of B rows -> its columns of C.
+    `compute(a, b_slab)` returns a . b_slab^T (mimir_b200.tensor.product_2d with a transpose_2d view on the GPU)."""
+    rank, world = _world()
+    n = b_nk.shape[0]
+    lo, hi = split_range(n, rank, world)
+    c_local = compute(a, b_nk[lo:hi])
+    return gather_columns(c_local, n) if gather else (c_local, (lo, hi))
+
+
+def sharded_heads(q, k, v, compute: Callable, gather: bool = False):
+    """Attention over this rank's range of the leading (batch x head) axis."""
+    rank, world = _world()
+    bh = q.shape[0]
+    lo, hi = split_range(bh, rank, world)
+    o_local = compute(q[lo:hi], k[lo:hi], v[lo:hi])
+    return gather_rows(o_local, bh) if gather else (o_local, (lo, hi))
+
+
+def sharded_rows(x, compute: Callable, gather: bool = False):
+    """A row-wise operator over this rank's block of rows."""
+    rank, world = _world()
+    rows = x.shape[0]
+    lo, hi = split_range(rows, rank, world)
+    y_local = compute(x[lo:hi])
+    return gather_rows(y_local, rows) if gather else (y_local, (lo, hi))
