@@ -73,7 +73,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 // One CTA per row (grid-stride over rows); a thread keeps NV float4 of the row in registers.
 // Requires cols % 4 == 0, cols <= THREADS * NV * 4 and 16-byte (f32) / 8-byte (bf16) aligned rows.
 template <int MODE, int THREADS, int NV, class TIn, class TOut>
-__global__ void __launch_bounds__(THREADS) rows_in_regs_kernel(const TIn* __restrict__ x, const float* __restrict__ gamma,
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS) rows_in_regs_kernel(const TIn* __restrict__ x, const float* __restrict__ gamma,
                                                               TOut* __restrict__ y, int64_t rows, int cols, float eps) {
     __shared__ float red[32];
     const int nvec = cols >> 2;
