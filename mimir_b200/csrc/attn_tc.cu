@@ -6,17 +6,20 @@
 // score matrix in memory. Here the score tile never leaves the SM:
 //
 //   one CTA owns two query tiles of 128 rows of one (batch, head) and walks the key/value tiles of 128 keys
-//   warp 0        TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled shared memory)
-//   warp 1        MMA issuer (one thread): S_t = Q_t K^T  (tcgen05.mma, M128 N128 K16 x 8, both operands in shared
+//   warps 0..3    softmax of query tile 0, one thread per row: tcgen05.ld the 128 f32 scores of the row into
+//   warps 4..7    softmax of query tile 1   registers, running max / sum, exp2 with the scale folded in, P written
+//                 back over S in tensor memory as bf16 (tcgen05.st); O is rescaled in tensor memory only when the
+//                 running max has grown by more than 2^8 since the last rescale
+//   (registers are moved from the third warpgroup to the two softmax warpgroups with setmaxnreg: 216 vs 64 per thread)
+//   warp 8        TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled shared memory)
+//   warp 9        MMA issuer (one thread): S_t = Q_t K^T  (tcgen05.mma, M128 N128 K16 x 8, both operands in shared
 //                 memory) and O_t += P_t V (A operand = P_t in tensor memory, B operand = V as an MN-major tile)
-//   warps 4..7    softmax of query tile 0, one thread per row: tcgen05.ld the f32 scores, running max / sum in
-//   warps 8..11   softmax of query tile 1   registers, exp2 with the scale folded in, P written back over S in
-//                 tensor memory as bf16 (tcgen05.st); O is rescaled in tensor memory only when the running max
-//                 has grown by more than 2^8 since the last rescale
 //   TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 f32 columns each; P_t aliases the first 64 columns of S_t.
 // While one tile's warps do their exponentials the tensor core works on the other tile.
 // Every mbarrier wait is bounded; on expiry the CTA records MIMK_E_DEVICE_WAIT and unwinds.
 #include <math_constants.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -31,7 +34,14 @@ constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;  // a [128 x 128] bf16 tile = two swizzle atoms of [128 x 64]
 constexpr int ATOM_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
-constexpr int NUM_THREADS = 384;
+constexpr int NUM_THREADS = 384;  // three warpgroups: softmax tile 0, softmax tile 1, {producer, MMA, two idle warps}
+constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
+// setmaxnreg moves registers between warpgroups inside what the CTA got at launch (168 per thread under
+// __launch_bounds__(384, 1)). An increase that the pool cannot satisfy would block for ever, so the budget is checked
+// here: two softmax warpgroups and the producer/MMA warpgroup must fit in 168 * 384 registers.
+constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 216, OTHER_REGS = 64;
+static_assert(2 * 128 * SOFTMAX_REGS + 128 * OTHER_REGS <= LAUNCH_REGS * NUM_THREADS, "setmaxnreg budget exceeds the CTA's registers");
+static_assert(SOFTMAX_REGS % 8 == 0 && OTHER_REGS % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 struct Bars {
@@ -60,6 +70,70 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// ---- packed f32x2 arithmetic (one instruction for two floats) ----
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2_rd(uint64_t a, uint64_t b) {  // round towards -inf
+    uint64_t d;
+    asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// 2^x for two values x <= 8 on the FMA pipe instead of the special-function unit: split x into floor and fraction
+// with a round-down add of 1.5 * 2^23, evaluate a cubic minimax polynomial of 2^frac on [0,1) (relative error 8.8e-5,
+// far below the bf16 rounding P receives), and add floor(x) into the exponent field.
+__device__ __forceinline__ void poly_exp2_x2(float xa, float xb, float& ea, float& eb) {
+    const uint64_t x    = pack2(fmaxf(xa, -127.f), fmaxf(xb, -127.f));
+    const uint64_t xf   = add2_rd(x, pack2(12582912.f, 12582912.f));
+    const uint64_t fl   = add2(xf, pack2(-12582912.f, -12582912.f));
+    const uint64_t frac = fma2(fl, pack2(-1.f, -1.f), x);
+    uint64_t pf = fma2(pack2(0.077119089663028717041015625f, 0.077119089663028717041015625f), frac,
+                       pack2(0.227564394474029541015625f, 0.227564394474029541015625f));
+    pf          = fma2(pf, frac, pack2(0.695146143436431884765625f, 0.695146143436431884765625f));
+    pf          = fma2(pf, frac, pack2(1.0f, 1.0f));
+    float pa, pb, fa, fb;
+    unpack2(pf, pa, pb);
+    unpack2(xf, fa, fb);
+    ea = __int_as_float(__float_as_int(pa) + (__float_as_int(fa) << 23));
+    eb = __int_as_float(__float_as_int(pb) + (__float_as_int(fb) << 23));
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 32 lanes x 32 columns into r[0..31] (a slice of a larger register array)
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_32x32_x32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -72,6 +146,8 @@ __device__ __forceinline__ void tmem_st_32x32_x32(uint32_t taddr, const uint32_t
         : "memory");
 }
 
+// EMU: how many of every four PAIRS of exponentials go to the polynomial instead of the special-function unit.
+template <int EMU>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const Params p) {
@@ -120,7 +196,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
     }
-    if (warp == 1) {
+    if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&bars->tmem_base), 512);
         tmem_relinquish();
     }
@@ -129,7 +205,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
-    if (warp == 0) {
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
+      if (warp == PRODUCER_WARP) {
         // ---------------- TMA producer ----------------
         if (lane == 0 && n_max > 0) {
             const uint32_t qf = smem_u32(&bars->q_full);
@@ -155,7 +233,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 tma_load_3d(sV + s * TILE_BYTES + ATOM_BYTES, &tmV, 64, j * BKV, head, vf);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == MMA_WARP) {
         // ---------------- MMA issuer ----------------
         if (lane == 0 && n_max > 0) {
             const uint32_t idesc_qk = idesc_bf16_f32(BQ, BKV, 0, 0);
@@ -218,9 +296,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 if (k_ready) mma_commit(smem_u32(&bars->k_empty[s1]));
             }
         }
-    } else if (warp >= 4) {
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SOFTMAX_REGS));
         // ---------------- softmax + output, one thread per query row ----------------
-        const int t = (warp - 4) >> 2;
+        const int t = warp >> 2;
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
         const int64_t qi = q0[t] + row_in_tile;
@@ -235,20 +315,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const bool need_mask = (p.causal && k0 + BKV - 1 > q0[t]) || (k0 + BKV > p.Sk);
             int64_t limit = p.Sk;  // keys >= limit are masked for this row
             if (p.causal && qi + 1 < limit) limit = qi + 1;
-            // pass 1: row maximum of the scaled scores
-            float mx = -CUDART_INF_F;
-#pragma unroll 1
-            for (int c = 0; c < BKV; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(tS + c, r);
-                tmem_ld_wait();
+            // the whole score row (128 f32) in registers: one round trip to tensor memory
+            uint32_t r[BKV];
+            tmem_ld_32x32(tS, r);
+            tmem_ld_32x32(tS + 32, r + 32);
+            tmem_ld_32x32(tS + 64, r + 64);
+            tmem_ld_32x32(tS + 96, r + 96);
+            tmem_ld_wait();
+            if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = __uint_as_float(r[i]) * p.scale_log2;
-                    if (need_mask && k0 + c + i >= limit) v = -CUDART_INF_F;
-                    mx = fmaxf(mx, v);
-                }
+                for (int i = 0; i < BKV; ++i)
+                    if (k0 + i >= limit) r[i] = 0xff800000u;  // -inf: exp2 gives 0
             }
+            // four independent chains of three-input maxima, then one join
+            float mx4[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                mx4[c] = max3(__uint_as_float(r[32 * c]), __uint_as_float(r[32 * c + 1]), __uint_as_float(r[32 * c + 2]));
+#pragma unroll
+                for (int i = 3; i + 1 < 32; i += 2)
+                    mx4[c] = max3(mx4[c], __uint_as_float(r[32 * c + i]), __uint_as_float(r[32 * c + i + 1]));
+                mx4[c] = fmaxf(mx4[c], __uint_as_float(r[32 * c + 31]));
+            }
+            float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * p.scale_log2;  // scale > 0: max commutes with it
             if (j == 0) {
                 m_used = mx;
             } else if (mx > m_used + RESCALE_THRESHOLD) {
@@ -256,36 +345,41 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 const float alpha = fast_exp2(m_used - mx);
 #pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tO + c, r);
+                    uint32_t o[32];
+                    tmem_ld_32x32(tO + c, o);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st_32x32_x32(tO + c, r);
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_32x32_x32(tO + c, o);
                 }
                 l *= alpha;
                 m_used = mx;
             }
-            // pass 2: p = exp2(s - m), row sum, P as bf16 over the first 64 columns of S_t
-#pragma unroll 1
+            // p = exp2(s * scale - m), row sum, P as bf16 over the first 64 columns of S_t
+            const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2), neg_m = pack2(-m_used, -m_used);
+            uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+#pragma unroll
             for (int c = 0; c < BKV; c += 32) {
-                uint32_t r[32], pk[16];
-                tmem_ld_32x32(tS + c, r);
-                tmem_ld_wait();
-                float sum = 0.f;
+                uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float a = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_used));
-                    float b = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_used));
-                    if (need_mask) {
-                        if (k0 + c + i >= limit) a = 0.f;
-                        if (k0 + c + i + 1 >= limit) b = 0.f;
+                    float xa, xb, a, b;
+                    unpack2(fma2(pack2(__uint_as_float(r[c + i]), __uint_as_float(r[c + i + 1])), sl2, neg_m), xa, xb);
+                    if (((i >> 1) & 3) < EMU) {
+                        poly_exp2_x2(xa, xb, a, b);
+                    } else {
+                        a = fast_exp2(xa);
+                        b = fast_exp2(xb);
                     }
-                    sum += a + b;
-                    pk[i >> 1] = pack_bf16x2(a, b);
+                    sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(a, b));
+                    pk[i >> 1]         = pack_bf16x2(a, b);
                 }
-                l += sum;
                 tmem_st_32x32_x16(tS + (c >> 1), pk);
+            }
+            {
+                float s0, s1;
+                unpack2(add2(sum2[0], sum2[1]), s0, s1);
+                l += s0 + s1;
             }
             tmem_st_wait();
             tc_fence_before();
@@ -321,7 +415,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ---------------- teardown ----------------
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == MMA_WARP) {
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
@@ -350,10 +444,15 @@ int attn_tc(const mimk_attn_desc& d, cudaStream_t s) {
     MIMK_TRY(make_tmap_bf16_3d(&tQ, d.q, HD, uint64_t(d.seq_q), uint64_t(d.batch_heads), row, uint64_t(d.seq_q) * row, 64, BQ));
     MIMK_TRY(make_tmap_bf16_3d(&tK, d.k, HD, uint64_t(d.seq_k), uint64_t(d.batch_heads), row, uint64_t(d.seq_k) * row, 64, BKV));
     MIMK_TRY(make_tmap_bf16_3d(&tV, d.v, HD, uint64_t(d.seq_k), uint64_t(d.batch_heads), row, uint64_t(d.seq_k) * row, 64, BKV));
-    static bool configured = false;
-    if (!configured) {
-        MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured = true;
+    // exponentials sent to the FMA-pipe polynomial, out of every four (MIMK_ATTN_EMU=0..2 overrides for experiments)
+    static int emu = -1;
+    if (emu < 0) {
+        const char* e = getenv("MIMK_ATTN_EMU");
+        emu           = e ? atoi(e) : 0;
+        if (emu < 0 || emu > 2) emu = 0;
+        MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     }
     Params p;
     p.Sq = d.seq_q, p.Sk = d.seq_k, p.BH = d.batch_heads;
@@ -363,7 +462,12 @@ int attn_tc(const mimk_attn_desc& d, cudaStream_t s) {
     p.causal     = d.causal;
     p.status     = dev->status_dev;
     dim3 grid((unsigned)((d.seq_q + 2 * BQ - 1) / (2 * BQ)), (unsigned)d.batch_heads);
-    attn_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, p);
+    if (emu == 0)
+        attn_tc_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, p);
+    else if (emu == 1)
+        attn_tc_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, p);
+    else
+        attn_tc_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, p);
     return launch_status();
 }
 
