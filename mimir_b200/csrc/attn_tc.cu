@@ -10,7 +10,7 @@
 //   warps 4..7    softmax of query tile 1   registers, running max / sum, exp2 with the scale folded in, P written
 //                 back over S in tensor memory as bf16 (tcgen05.st); O is rescaled in tensor memory only when the
 //                 running max has grown by more than 2^8 since the last rescale
-//   (registers are moved from the third warpgroup to the two softmax warpgroups with setmaxnreg: 216 vs 64 per thread)
+//   (registers are moved from the third warpgroup to the two softmax warpgroups with setmaxnreg: 208 vs 88 per thread)
 //   warp 8        TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled shared memory)
 //   warp 9        MMA issuer (one thread): S_t = Q_t K^T  (tcgen05.mma, M128 N128 K16 x 8, both operands in shared
 //                 memory) and O_t += P_t V (A operand = P_t in tensor memory, B operand = V as an MN-major tile)
@@ -39,7 +39,7 @@ constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
 // setmaxnreg moves registers between warpgroups inside what the CTA got at launch (168 per thread under
 // __launch_bounds__(384, 1)). An increase that the pool cannot satisfy would block for ever, so the budget is checked
 // here: two softmax warpgroups and the producer/MMA warpgroup must fit in 168 * 384 registers.
-constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 216, OTHER_REGS = 64;
+constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 208, OTHER_REGS = 88;
 static_assert(2 * 128 * SOFTMAX_REGS + 128 * OTHER_REGS <= LAUNCH_REGS * NUM_THREADS, "setmaxnreg budget exceeds the CTA's registers");
 static_assert(SOFTMAX_REGS % 8 == 0 && OTHER_REGS % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
@@ -48,7 +48,7 @@ struct Bars {
     uint64_t q_full;
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
     uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-    uint64_t s_full[2], p_full[2], o_full[2];
+    uint64_t s_full[2], p_half[2], p_full[2], o_full[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -63,6 +63,19 @@ struct Params {
     int causal;
     int* status;
 };
+
+#ifdef MIMK_TRACE
+// Bring-up aid (not built into the library): SM-clock timestamps of one CTA's hand-offs.
+__device__ long long g_trace[3][64][8];
+#define MIMK_TR(role, iter, ev)                                                            \
+    do {                                                                                   \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (iter) < 64) g_trace[role][iter][ev] = clock64(); \
+    } while (0)
+#else
+#define MIMK_TR(role, iter, ev) \
+    do {                        \
+    } while (0)
+#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -159,8 +172,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     volatile int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // grid = (query-tile pairs, heads), handed out x-fastest: the CTAs resident at any moment belong to a few heads and
+    // share those heads' K/V through L2 (ordering by head first was measured 10-20 % slower: every CTA then streams
+    // its own K/V from HBM). Within a head the longest pair (the last one under a causal mask) goes first.
     const int head = blockIdx.y;
-    const int pair = int(gridDim.x) - 1 - int(blockIdx.x);  // longest (latest) query tiles first
+    const int pair = int(gridDim.x) - 1 - int(blockIdx.x);
     int64_t q0[2];
     int n_kv[2];
     const int kv_tiles = int((p.Sk + BKV - 1) / BKV);
@@ -187,6 +203,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(smem_u32(&bars->s_full[t]), 1);
+            mbar_init(smem_u32(&bars->p_half[t]), 128);
             mbar_init(smem_u32(&bars->p_full[t]), 128);
             mbar_init(smem_u32(&bars->o_full[t]), 1);
         }
@@ -239,26 +256,31 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const uint32_t idesc_qk = idesc_bf16_f32(BQ, BKV, 0, 0);
             const uint32_t idesc_pv = idesc_bf16_f32(BQ, HD, 0, 1);
             bool ok = true;
+            // Descriptors are built once; a k-step only adds a byte offset (>> 4) to the start-address field.
+            // (consecutive tiles / stages are TILE_BYTES apart, i.e. TILE_BYTES >> 4 in the start-address field)
+            static_assert(KV_STAGES == 2, "stage selection below assumes two stages");
+            const uint64_t dQ0 = smem_desc_sw128(sQ, 16, 1024), dK0 = smem_desc_sw128(sK, 16, 1024);
+            const uint64_t dV0 = smem_desc_sw128(sV, ATOM_BYTES, 1024);
+            constexpr uint64_t TILE_STEP = uint64_t(TILE_BYTES >> 4);
             // S_t = Q_t K_j^T: 8 k-steps of 16 over head_dim; atom = k-step / 4, 32 bytes per step inside an atom
             auto issue_qk = [&](int t, int j) {
-                const uint32_t qa = sQ + t * TILE_BYTES, kb = sK + (j % KV_STAGES) * TILE_BYTES;
+                const uint64_t qa = dQ0 + (t ? TILE_STEP : 0), kb = dK0 + ((j & 1) ? TILE_STEP : 0);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k >> 2) * ATOM_BYTES + (k & 3) * 32;
-                    mma_f16_ss(tmem_base + t * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(kb + off, 16, 1024),
-                               idesc_qk, k > 0 ? 1u : 0u);
+                    const uint64_t off = uint64_t(((k >> 2) * ATOM_BYTES + (k & 3) * 32) >> 4);
+                    mma_f16_ss(tmem_base + t * 128, qa + off, kb + off, idesc_qk, k > 0 ? 1u : 0u);
                 }
                 mma_commit(smem_u32(&bars->s_full[t]));
             };
-            // O_t (+)= P_t V_j: 8 k-steps of 16 keys; P from tensor memory (8 columns of packed bf16 pairs per step),
-            // V as an MN-major operand: 16 key rows = 2048 bytes per step, the two 64-wide halves of head_dim are
-            // ATOM_BYTES apart
-            auto issue_pv = [&](int t, int j) {
-                const uint32_t vb = sV + (j % KV_STAGES) * TILE_BYTES;
+            // O_t (+)= P_t V_j, k-steps [k0, k1) of 16 keys each; P from tensor memory (8 columns of packed bf16 pairs
+            // per step), V as an MN-major operand: 16 key rows = 2048 bytes per step, the two 64-wide halves of
+            // head_dim are ATOM_BYTES apart
+            auto issue_pv = [&](int t, int j, int k0, int k1) {
+                const uint64_t vb = dV0 + ((j & 1) ? TILE_STEP : 0);
 #pragma unroll
-                for (int k = 0; k < BKV / 16; ++k)
-                    mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
-                               smem_desc_sw128(vb + k * 2048, ATOM_BYTES, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                for (int k = k0; k < k1; ++k)
+                    mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, vb + uint64_t((k * 2048) >> 4), idesc_pv,
+                               (j > 0 || k > 0) ? 1u : 0u);
             };
             ok = mbar_wait(smem_u32(&bars->q_full), 0, abort_flag);
             if (ok) ok = mbar_wait(smem_u32(&bars->k_full[0]), 0, abort_flag);
@@ -274,13 +296,19 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 bool v_ready = false, k_ready = false;
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j >= n_kv[t]) continue;
-                    if (!(ok = mbar_wait(smem_u32(&bars->p_full[t]), j & 1, abort_flag))) break;
+                    // the first 64 keys of P_t are ready before the rest: start O_t += P_t V on them
+                    if (!(ok = mbar_wait(smem_u32(&bars->p_half[t]), j & 1, abort_flag))) break;
                     if (!v_ready) {
                         if (!(ok = mbar_wait(smem_u32(&bars->v_full[s]), ph, abort_flag))) break;
                         v_ready = true;
                     }
                     tc_fence_after();
-                    issue_pv(t, j);
+                    MIMK_TR(2, j, t * 4 + 0);
+                    issue_pv(t, j, 0, 4);
+                    if (!(ok = mbar_wait(smem_u32(&bars->p_full[t]), j & 1, abort_flag))) break;
+                    tc_fence_after();
+                    issue_pv(t, j, 4, 8);
+                    MIMK_TR(2, j, t * 4 + 1);
                     if (j + 1 == n_kv[t]) mma_commit(smem_u32(&bars->o_full[t]));
                     if (j + 1 < n_kv[t]) {
                         if (!k_ready) {
@@ -289,6 +317,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             tc_fence_after();
                         }
                         issue_qk(t, j + 1);
+                        MIMK_TR(2, j, t * 4 + 2);
                     }
                 }
                 if (!ok) break;
@@ -309,8 +338,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         float m_used = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kv[t] && ok; ++j) {
+            if (row_in_tile == 0) MIMK_TR(t, j, 0);
             if (!(ok = mbar_wait(smem_u32(&bars->s_full[t]), j & 1, abort_flag))) break;
             tc_fence_after();
+            if (row_in_tile == 0) MIMK_TR(t, j, 1);
             const int64_t k0 = int64_t(j) * BKV;
             const bool need_mask = (p.causal && k0 + BKV - 1 > q0[t]) || (k0 + BKV > p.Sk);
             int64_t limit = p.Sk;  // keys >= limit are masked for this row
@@ -322,22 +353,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tmem_ld_32x32(tS + 64, r + 64);
             tmem_ld_32x32(tS + 96, r + 96);
             tmem_ld_wait();
+            if (row_in_tile == 0) MIMK_TR(t, j, 2);
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < BKV; ++i)
                     if (k0 + i >= limit) r[i] = 0xff800000u;  // -inf: exp2 gives 0
             }
-            // four independent chains of three-input maxima, then one join
-            float mx4[4];
+            // eight independent chains of three-input maxima, then one join
+            float mx8[8];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                mx4[c] = max3(__uint_as_float(r[32 * c]), __uint_as_float(r[32 * c + 1]), __uint_as_float(r[32 * c + 2]));
+            for (int c = 0; c < 8; ++c) {
+                mx8[c] = max3(__uint_as_float(r[16 * c]), __uint_as_float(r[16 * c + 1]), __uint_as_float(r[16 * c + 2]));
 #pragma unroll
-                for (int i = 3; i + 1 < 32; i += 2)
-                    mx4[c] = max3(mx4[c], __uint_as_float(r[32 * c + i]), __uint_as_float(r[32 * c + i + 1]));
-                mx4[c] = fmaxf(mx4[c], __uint_as_float(r[32 * c + 31]));
+                for (int i = 3; i + 1 < 16; i += 2)
+                    mx8[c] = max3(mx8[c], __uint_as_float(r[16 * c + i]), __uint_as_float(r[16 * c + i + 1]));
+                mx8[c] = fmaxf(mx8[c], __uint_as_float(r[16 * c + 15]));
             }
-            float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * p.scale_log2;  // scale > 0: max commutes with it
+            float mx = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) *
+                       p.scale_log2;  // scale > 0: max commutes with it
             if (j == 0) {
                 m_used = mx;
             } else if (mx > m_used + RESCALE_THRESHOLD) {
@@ -356,6 +389,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 m_used = mx;
             }
             // p = exp2(s * scale - m), row sum, P as bf16 over the first 64 columns of S_t
+            if (row_in_tile == 0) MIMK_TR(t, j, 3);
             const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2), neg_m = pack2(-m_used, -m_used);
             uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
@@ -375,15 +409,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     pk[i >> 1]         = pack_bf16x2(a, b);
                 }
                 tmem_st_32x32_x16(tS + (c >> 1), pk);
+                if (c == 32) {  // keys 0..63 of P_t are stored: let the tensor core start on them
+                    tmem_st_wait();
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&bars->p_half[t]));
+                }
             }
             {
                 float s0, s1;
                 unpack2(add2(sum2[0], sum2[1]), s0, s1);
                 l += s0 + s1;
             }
+            if (row_in_tile == 0) MIMK_TR(t, j, 4);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(smem_u32(&bars->p_full[t]));
+            if (row_in_tile == 0) MIMK_TR(t, j, 5);
         }
         if (ok && n_kv[t] > 0) ok = mbar_wait(smem_u32(&bars->o_full[t]), 0, abort_flag);
         if (ok && n_kv[t] > 0) {
@@ -424,6 +465,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 }
 
 }  // namespace
+
+#ifdef MIMK_TRACE
+extern "C" int mimk_debug_attn_trace(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : 5;
+}
+#endif
 
 int attn_tc_supported(const mimk_attn_desc& d) {
     if (d.dtype != MIMK_BF16 || d.head_dim != HD) return 0;
