@@ -119,6 +119,7 @@ class Workload:
     bound = "hbm"
     kernel = ""
     launches_per_step = 1
+    traffic = None  # dram bytes (read + write) of one launch of the dominant kernel, from the ncu capture in profiles/
 
     def __init__(self, torch, T, H, rank, world):
         self.torch, self.T, self.H, self.rank, self.world = torch, T, H, rank, world
@@ -132,6 +133,7 @@ class Workload:
 class Rows(Workload):
     name, metric, unit, dtype, bound = "row softmax + RMSNorm f32 X[16384,8192] -> bf16", "HBM GB/s (row softmax+RMSNorm)", "GB/s", "f32", "hbm"
     kernel, launches_per_step = "rows_in_regs_kernel<softmax>", 2
+    traffic = 536886016 + 229935360   # profiles/rows_softmax_rmsnorm_c2.md
     R, Cc = 16384, 8192
 
     def setup(self):
@@ -183,6 +185,7 @@ class Rows(Workload):
 class Gemm(Workload):
     name, metric, unit, dtype, bound = "matmul bf16 M=N=K=8192, A row-major, B stored [N,K], f32 accumulate", "TFLOP/s (bf16 GEMM 8192^3)", "TFLOP/s", "bf16", "tensor"
     kernel = "gemm_tc_kernel"
+    traffic = 995304192 + 127100160   # profiles/gemm_tc_bf16_8192_c3.md
     n = 8192
 
     def setup(self):
@@ -224,6 +227,7 @@ class Gemm(Workload):
 class Attn(Workload):
     name, metric, unit, dtype, bound = "causal attention fwd bf16 batch*heads=128 seq=4096 head_dim=128", "TFLOP/s (causal attention fwd)", "TFLOP/s", "bf16", "tensor"
     kernel = "attn_tc_kernel"
+    traffic = 402804736 + 117293312   # profiles/attn_tc_causal_c4.md
     BH, S, D = 128, 4096, 128
 
     def setup(self):
@@ -478,7 +482,7 @@ def run_ours(args):
             "gpu_launches": K * w.launches_per_step,
             "roofline": {"bound": w.bound, "kernel": w.kernel, "achieved": achieved, "peak": peak,
                          "unit": "GB/s" if w.bound == "hbm" else "TFLOP/s", "frac": achieved / peak,
-                         "peak_source": pk["source"], "avg_launch_ms": dom_ms, "traffic": None}}
+                         "peak_source": pk["source"], "avg_launch_ms": dom_ms, "traffic": w.traffic}}
 
     if rank == 0 and world == 1 and not args.no_cpu:
         import numpy as np

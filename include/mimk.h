@@ -178,6 +178,64 @@ typedef struct mimk_mlp_desc {
 } mimk_mlp_desc;
 int mimk_mlp_gated(const mimk_mlp_desc* desc, void* stream);
 
+/* ---- the generic operation ------------------------------------------------------------------------------
+ * out[map_out(o)] = post(fold_r f(acc, (in_i[maps_i(o, r)])_i), (post_in_j[post_maps_j(map_out(o))])_j)
+ * over the loop vector (o..., r...) with bounds `sr`: the leading `ro` loops are the output loops, the trailing
+ * `rn - ro` loops are folded, ascending, per output cell (classic nest order).
+ * Replaces: btensor.map_reduce_post itself (src/mim/plug/btensor/btensor.mim:102-115; decoder struct MapRedPost,
+ * include/mim/plug/btensor/btensor.h:20-52) for every instance the specialised entry points above do not take --
+ * strip-mined / interchanged domains, packed outputs, transposes, slices, broadcasts, convolutions, mixed element
+ * types. One thread per output cell walks its reduction, like the kernel gpu::phase::LowerMapReduce::build_kernel
+ * generates (src/mim/plug/gpu/phase/lower_map_reduce.cpp:148-265), but with the access maps as data.
+ * An access map is a matrix: result j = sum_l coef[j][l] * loop[l] + coef[j][n_loops], in wrap-around int64
+ * (include/mim/plug/affine/phase/lower_index.h:14-20); buffers are row-major. Every access is bounds-checked on the
+ * host against the loop bounds before launch (MIMK_E_SHAPE), so a wrong map never reads outside a buffer. */
+#define MIMK_MRP_MAX_LOOPS 8
+#define MIMK_MRP_MAX_RANK 6
+#define MIMK_MRP_MAX_INPUTS 4
+enum { /* combiners f(acc, ins) */
+    MIMK_F_ADD = 0,     /* acc + a                      pool_fun add          */
+    MIMK_F_MULADD = 1,  /* acc + a * b                  dot_general_fun, tensor.mim:1332 */
+    MIMK_F_MAX = 2, MIMK_F_MIN = 3,
+    MIMK_F_FIRST = 4,   /* a (acc ignored): copy-style ops, tensor_copy, tensor.mim:1074 */
+    MIMK_F_SUBEXP = 5,  /* exp(a - b)  */
+    MIMK_F_DIV = 6, MIMK_F_ADD2 = 7, MIMK_F_MUL2 = 8, /* a / b, a + b, a * b (acc ignored): binary / binary_ax */
+    MIMK_F_MIX = 9,     /* acc + a + (acc type)b         lit/btensor/map_reduce_post.mim:17-18 */
+};
+enum { /* epilogues post(acc, post_ins) */
+    MIMK_P_ID = 0,
+    MIMK_P_ADD = 1,       /* widen(acc) + p0 (unsigned widening when the output type is wider)  map_reduce_post.mim:19-20 */
+    MIMK_P_ADD_PLUS1 = 2, /* acc + p0 + 1                                                 lit/buffer/exec_epilogue.mim:33 */
+    MIMK_P_ADD_RELU = 3,  /* fmax(0, acc + p0) */
+    MIMK_P_ADD_TANH = 4,  /* tanh(acc + p0) */
+    MIMK_P_RELU = 5, MIMK_P_SILU = 6,
+};
+typedef struct mimk_affine_map {
+    int32_t rows; /* number of results (the rank of the tensor it indexes) */
+    int32_t pad_;
+    int64_t coef[MIMK_MRP_MAX_RANK][MIMK_MRP_MAX_LOOPS + 1];
+} mimk_affine_map;
+typedef struct mimk_mrp_desc {
+    int32_t ro, rn;                   /* output loops, all loops (rn >= ro) */
+    int64_t sr[MIMK_MRP_MAX_LOOPS];   /* loop bounds */
+    int64_t so[MIMK_MRP_MAX_RANK];    /* shape of the result (rank ro) */
+    int32_t nis, nps;                 /* inputs, epilogue inputs */
+    const void* in[MIMK_MRP_MAX_INPUTS];
+    int32_t in_dtype[MIMK_MRP_MAX_INPUTS];
+    int64_t in_shape[MIMK_MRP_MAX_INPUTS][MIMK_MRP_MAX_RANK];
+    mimk_affine_map in_map[MIMK_MRP_MAX_INPUTS];   /* over the rn loop variables */
+    const void* post_in[MIMK_MRP_MAX_INPUTS];
+    int32_t post_dtype[MIMK_MRP_MAX_INPUTS];
+    int64_t post_shape[MIMK_MRP_MAX_INPUTS][MIMK_MRP_MAX_RANK];
+    mimk_affine_map post_map[MIMK_MRP_MAX_INPUTS]; /* over the ro write coordinates */
+    mimk_affine_map map_out;                       /* over the rn loop variables (reduction slots read 0) */
+    int32_t comb, post;
+    int32_t acc_dtype, out_dtype;     /* F32, I32 or I64 accumulators; out additionally BF16 */
+    int64_t init_bits;                /* the accumulator's initial value, as raw bits (low bytes) */
+    void* out;
+} mimk_mrp_desc;
+int mimk_map_reduce_post(const mimk_mrp_desc* desc, void* stream);
+
 /* ---- host-buffer forms -------------------------------------------------------------------------------
  * Same operators with HOST pointers: inputs are copied to the device, the kernel runs, the result is copied
  * back and the call returns when the result is in host memory.

@@ -24,7 +24,7 @@ ROWS_SOFTMAX, ROWS_RMSNORM, ROWS_SOFTMAX_RMSNORM = 0, 1, 2
 SYMBOLS = (
     "mimk_status_str", "mimk_abi_version", "mimk_last_cuda_error", "mimk_device_check", "mimk_device_status",
     "mimk_gemm", "mimk_reduce", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map",
-    "mimk_attn_fwd", "mimk_mlp_gated",
+    "mimk_attn_fwd", "mimk_mlp_gated", "mimk_map_reduce_post",
     "mimk_host_rows", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_register",
     "mimk_host_unregister", "mimk_host_release",
 )
@@ -65,6 +65,30 @@ class MlpDesc(C.Structure):
     ]
 
 
+MRP_MAX_LOOPS, MRP_MAX_RANK, MRP_MAX_INPUTS = 8, 6, 4
+F_ADD, F_MULADD, F_MAX, F_MIN, F_FIRST, F_SUBEXP, F_DIV, F_ADD2, F_MUL2, F_MIX = range(10)
+P_ID, P_ADD, P_ADD_PLUS1, P_ADD_RELU, P_ADD_TANH, P_RELU, P_SILU = range(7)
+
+
+class AffineMap(C.Structure):
+    _fields_ = [("rows", C.c_int32), ("pad_", C.c_int32), ("coef", (C.c_int64 * (MRP_MAX_LOOPS + 1)) * MRP_MAX_RANK)]
+
+
+class MrpDesc(C.Structure):
+    _fields_ = [
+        ("ro", C.c_int32), ("rn", C.c_int32),
+        ("sr", C.c_int64 * MRP_MAX_LOOPS), ("so", C.c_int64 * MRP_MAX_RANK),
+        ("nis", C.c_int32), ("nps", C.c_int32),
+        ("in_", C.c_void_p * MRP_MAX_INPUTS), ("in_dtype", C.c_int32 * MRP_MAX_INPUTS),
+        ("in_shape", (C.c_int64 * MRP_MAX_RANK) * MRP_MAX_INPUTS), ("in_map", AffineMap * MRP_MAX_INPUTS),
+        ("post_in", C.c_void_p * MRP_MAX_INPUTS), ("post_dtype", C.c_int32 * MRP_MAX_INPUTS),
+        ("post_shape", (C.c_int64 * MRP_MAX_RANK) * MRP_MAX_INPUTS), ("post_map", AffineMap * MRP_MAX_INPUTS),
+        ("map_out", AffineMap),
+        ("comb", C.c_int32), ("post", C.c_int32), ("acc_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("init_bits", C.c_int64), ("out", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -87,6 +111,7 @@ def lib() -> C.CDLL:
         L.mimk_map.argtypes = [ci, vp, vp, vp, ci, i64, i64, i64, ci, vp]
         L.mimk_attn_fwd.argtypes = [C.POINTER(AttnDesc), vp]
         L.mimk_mlp_gated.argtypes = [C.POINTER(MlpDesc), vp]
+        L.mimk_map_reduce_post.argtypes = [C.POINTER(MrpDesc), vp]
         L.mimk_host_rows.argtypes = [ci, vp, vp, vp, ci, ci, i64, i64, cf]
         L.mimk_host_gemm.argtypes = [C.POINTER(GemmDesc)]
         L.mimk_host_attn_fwd.argtypes = [C.POINTER(AttnDesc)]

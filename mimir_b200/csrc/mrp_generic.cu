@@ -1,0 +1,228 @@
+// The generic `map_reduce_post`: every instance the specialised kernels do not take.
+//
+// Semantics follow the reference's value-world lowering (MimIR src/mim/plug/tensor/phase/lower_map_reduce.cpp:93-206):
+// output loops over the leading Ro bounds of Sr, the accumulator seeded with `init`, the trailing loops folded in
+// ascending order with the combiner, `post` applied once per cell with the epilogue inputs read at the write
+// coordinates, the result stored at `map_out` of the output loop vector (reduction slots 0). The launch shape is the
+// reference GPU lowering's (one thread per output cell, lower_map_reduce.cpp:132-139, 198-206); what differs is that
+// maps, combiner and epilogue are data, not generated code, and that the host proves every access in range first.
+#include "common.cuh"
+
+namespace mimk {
+namespace {
+
+struct Val {
+    long long i;
+    float f;
+};
+
+__device__ __forceinline__ Val load_val(const void* p, int dt, long long off) {
+    Val v;
+    v.i = 0;
+    v.f = 0.f;
+    switch (dt) {
+        case MIMK_F32: v.f = static_cast<const float*>(p)[off]; break;
+        case MIMK_BF16: v.f = __bfloat162float(static_cast<const __nv_bfloat16*>(p)[off]); break;
+        case MIMK_I32: v.i = static_cast<const int*>(p)[off]; break;
+        default: v.i = static_cast<const long long*>(p)[off]; break;
+    }
+    return v;
+}
+
+__device__ __forceinline__ long long wrap(long long x, int dt) { return dt == MIMK_I32 ? (long long)(int)x : x; }
+
+__device__ __forceinline__ Val combine(int id, int acc_dt, Val acc, const Val* in) {
+    Val r = acc;
+    if (acc_dt == MIMK_F32) {
+        switch (id) {
+            case MIMK_F_ADD: r.f = acc.f + in[0].f; break;
+            case MIMK_F_MULADD: r.f = fmaf(in[0].f, in[1].f, acc.f); break;
+            case MIMK_F_MAX: r.f = fmaxf(acc.f, in[0].f); break;
+            case MIMK_F_MIN: r.f = fminf(acc.f, in[0].f); break;
+            case MIMK_F_FIRST: r.f = in[0].f; break;
+            case MIMK_F_SUBEXP: r.f = expf(in[0].f - in[1].f); break;
+            case MIMK_F_DIV: r.f = in[0].f / in[1].f; break;
+            case MIMK_F_ADD2: r.f = in[0].f + in[1].f; break;
+            case MIMK_F_MUL2: r.f = in[0].f * in[1].f; break;
+            default: break;
+        }
+    } else {
+        unsigned long long a = (unsigned long long)acc.i, x = (unsigned long long)in[0].i, y = (unsigned long long)in[1].i;
+        switch (id) {
+            case MIMK_F_ADD: a = a + x; break;
+            case MIMK_F_MULADD: a = a + x * y; break;
+            case MIMK_F_MAX: a = (unsigned long long)(acc.i > in[0].i ? acc.i : in[0].i); break;
+            case MIMK_F_MIN: a = (unsigned long long)(acc.i < in[0].i ? acc.i : in[0].i); break;
+            case MIMK_F_FIRST: a = x; break;
+            case MIMK_F_ADD2: a = x + y; break;
+            case MIMK_F_MUL2: a = x * y; break;
+            case MIMK_F_MIX: a = a + x + y; break;
+            default: break;
+        }
+        r.i = wrap((long long)a, acc_dt);
+    }
+    return r;
+}
+
+__device__ __forceinline__ void store_post(int post, int acc_dt, int out_dt, Val acc, Val p0, void* out, long long off) {
+    if (acc_dt == MIMK_F32) {
+        float v = acc.f;
+        switch (post) {
+            case MIMK_P_ADD: v = acc.f + p0.f; break;
+            case MIMK_P_ADD_PLUS1: v = acc.f + p0.f + 1.f; break;
+            case MIMK_P_ADD_RELU: v = fmaxf(0.f, acc.f + p0.f); break;
+            case MIMK_P_ADD_TANH: v = tanhf(acc.f + p0.f); break;
+            case MIMK_P_RELU: v = fmaxf(0.f, acc.f); break;
+            case MIMK_P_SILU: v = acc.f / (1.f + expf(-acc.f)); break;
+            default: break;
+        }
+        if (out_dt == MIMK_BF16)
+            static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(v);
+        else
+            static_cast<float*>(out)[off] = v;
+    } else {
+        // unsigned widening of a 32-bit accumulator into a 64-bit result (core.conv.u), then the epilogue
+        unsigned long long a = acc_dt == MIMK_I32 && out_dt == MIMK_I64 ? (unsigned long long)(unsigned int)acc.i
+                                                                       : (unsigned long long)acc.i;
+        switch (post) {
+            case MIMK_P_ADD: a = a + (unsigned long long)p0.i; break;
+            case MIMK_P_ADD_PLUS1: a = a + (unsigned long long)p0.i + 1ull; break;
+            case MIMK_P_RELU: a = (long long)a > 0 ? a : 0ull; break;
+            default: break;
+        }
+        if (out_dt == MIMK_I32)
+            static_cast<int*>(out)[off] = (int)a;
+        else
+            static_cast<long long*>(out)[off] = (long long)a;
+    }
+}
+
+__device__ __forceinline__ long long map_offset(const mimk_affine_map& m, int n, const long long* loop, const int64_t* shape) {
+    unsigned long long off = 0;
+    for (int j = 0; j < m.rows; ++j) {
+        unsigned long long v = (unsigned long long)m.coef[j][n];
+        for (int l = 0; l < n; ++l) v += (unsigned long long)m.coef[j][l] * (unsigned long long)loop[l];
+        off = off * (unsigned long long)shape[j] + v;
+    }
+    return (long long)off;
+}
+
+__global__ void __launch_bounds__(256) mrp_generic_kernel(const __grid_constant__ mimk_mrp_desc d, long long n_out,
+                                                         long long n_red) {
+    for (long long o = blockIdx.x * (long long)blockDim.x + threadIdx.x; o < n_out; o += (long long)gridDim.x * blockDim.x) {
+        long long loop[MIMK_MRP_MAX_LOOPS];
+        long long rem = o;
+        for (int l = d.ro - 1; l >= 0; --l) {
+            loop[l] = rem % d.sr[l];
+            rem /= d.sr[l];
+        }
+        Val acc;
+        acc.i = d.acc_dtype == MIMK_I32 ? (long long)(int)d.init_bits : d.init_bits;
+        acc.f = __int_as_float((int)d.init_bits);
+        for (long long r = 0; r < n_red; ++r) {
+            long long rr = r;
+            for (int l = d.rn - 1; l >= d.ro; --l) {
+                loop[l] = rr % d.sr[l];
+                rr /= d.sr[l];
+            }
+            Val in[MIMK_MRP_MAX_INPUTS];
+            for (int i = 0; i < d.nis; ++i)
+                in[i] = load_val(d.in[i], d.in_dtype[i], map_offset(d.in_map[i], d.rn, loop, d.in_shape[i]));
+            for (int i = d.nis; i < 2; ++i) in[i].i = 0, in[i].f = 0.f;
+            acc = combine(d.comb, d.acc_dtype, acc, in);
+        }
+        for (int l = d.ro; l < d.rn; ++l) loop[l] = 0;
+        long long wc[MIMK_MRP_MAX_RANK];
+        for (int j = 0; j < d.ro; ++j) {
+            unsigned long long v = (unsigned long long)d.map_out.coef[j][d.rn];
+            for (int l = 0; l < d.rn; ++l) v += (unsigned long long)d.map_out.coef[j][l] * (unsigned long long)loop[l];
+            wc[j] = (long long)v;
+        }
+        Val p0;
+        p0.i = 0, p0.f = 0.f;
+        if (d.nps > 0) p0 = load_val(d.post_in[0], d.post_dtype[0], map_offset(d.post_map[0], d.ro, wc, d.post_shape[0]));
+        unsigned long long woff = 0;
+        for (int j = 0; j < d.ro; ++j) woff = woff * (unsigned long long)d.so[j] + (unsigned long long)wc[j];
+        store_post(d.post, d.acc_dtype, d.out_dtype, acc, p0, d.out, (long long)woff);
+    }
+}
+
+// Range of an affine form over the box 0 <= loop[l] < bound[l]: every result coordinate must stay in [0, extent).
+bool map_in_range(const mimk_affine_map& m, int n, const int64_t* bounds, const int64_t* shape) {
+    for (int j = 0; j < m.rows; ++j) {
+        __int128 lo = m.coef[j][n], hi = m.coef[j][n];
+        for (int l = 0; l < n; ++l) {
+            const __int128 c = m.coef[j][l];
+            const __int128 span = c * (__int128)(bounds[l] - 1);
+            if (span < 0) lo += span; else hi += span;
+        }
+        if (lo < 0 || hi >= (__int128)shape[j]) return false;
+    }
+    return true;
+}
+
+bool dtype_ok(int dt) { return dt == MIMK_F32 || dt == MIMK_BF16 || dt == MIMK_I32 || dt == MIMK_I64; }
+
+}  // namespace
+}  // namespace mimk
+
+using namespace mimk;
+
+extern "C" int mimk_map_reduce_post(const mimk_mrp_desc* d, void* stream) {
+    if (!d) return MIMK_E_ARG;
+    if (d->ro < 0 || d->rn < d->ro || d->rn > MIMK_MRP_MAX_LOOPS || d->ro > MIMK_MRP_MAX_RANK) return MIMK_E_ARG;
+    if (d->nis < 0 || d->nis > MIMK_MRP_MAX_INPUTS || d->nps < 0 || d->nps > 1) return MIMK_E_ARG;
+    if (d->comb < MIMK_F_ADD || d->comb > MIMK_F_MIX || d->post < MIMK_P_ID || d->post > MIMK_P_SILU) return MIMK_E_ARG;
+    if (d->acc_dtype != MIMK_F32 && d->acc_dtype != MIMK_I32 && d->acc_dtype != MIMK_I64) return MIMK_E_DTYPE;
+    const bool facc = d->acc_dtype == MIMK_F32;
+    if (facc ? (d->out_dtype != MIMK_F32 && d->out_dtype != MIMK_BF16) : (d->out_dtype != MIMK_I32 && d->out_dtype != MIMK_I64))
+        return MIMK_E_DTYPE;
+    const int need = (d->comb == MIMK_F_MULADD || d->comb == MIMK_F_SUBEXP || d->comb == MIMK_F_DIV || d->comb == MIMK_F_ADD2 ||
+                      d->comb == MIMK_F_MUL2 || d->comb == MIMK_F_MIX) ? 2 : 1;
+    if (d->nis != need) return MIMK_E_ARG;
+    if (!facc && (d->comb == MIMK_F_SUBEXP || d->comb == MIMK_F_DIV)) return MIMK_E_DTYPE;
+    if (facc && d->comb == MIMK_F_MIX) return MIMK_E_DTYPE;
+    const bool post_needs = d->post >= MIMK_P_ADD && d->post <= MIMK_P_ADD_TANH;
+    if (post_needs != (d->nps == 1)) return MIMK_E_ARG;
+    if (!facc && (d->post == MIMK_P_ADD_RELU || d->post == MIMK_P_ADD_TANH || d->post == MIMK_P_SILU)) return MIMK_E_DTYPE;
+    long long n_out = 1, n_red = 1;
+    for (int l = 0; l < d->rn; ++l) {
+        if (d->sr[l] < 0) return MIMK_E_ARG;
+        if (l < d->ro) n_out *= d->sr[l]; else n_red *= d->sr[l];
+    }
+    for (int j = 0; j < d->ro; ++j)
+        if (d->so[j] < 0) return MIMK_E_ARG;
+    for (int i = 0; i < d->nis; ++i) {
+        if (!dtype_ok(d->in_dtype[i]) || d->in_map[i].rows < 0 || d->in_map[i].rows > MIMK_MRP_MAX_RANK) return MIMK_E_ARG;
+        if ((d->in_dtype[i] == MIMK_F32 || d->in_dtype[i] == MIMK_BF16) != facc) return MIMK_E_DTYPE;
+    }
+    if (d->nps == 1) {
+        if (!dtype_ok(d->post_dtype[0]) || d->post_map[0].rows < 0 || d->post_map[0].rows > MIMK_MRP_MAX_RANK) return MIMK_E_ARG;
+        if ((d->post_dtype[0] == MIMK_F32 || d->post_dtype[0] == MIMK_BF16) != facc) return MIMK_E_DTYPE;
+    }
+    if (d->map_out.rows != d->ro) return MIMK_E_SHAPE;
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    if (n_out == 0) return MIMK_OK;
+    if (!d->out) return MIMK_E_ARG;
+    // Prove every access in range over the whole iteration box before anything is launched.
+    int64_t out_bounds[MIMK_MRP_MAX_LOOPS];
+    for (int l = 0; l < d->rn; ++l) out_bounds[l] = l < d->ro ? d->sr[l] : 1;  // reduction slots are 0 at write-back
+    if (!map_in_range(d->map_out, d->rn, out_bounds, d->so)) return MIMK_E_SHAPE;
+    if (n_red > 0)
+        for (int i = 0; i < d->nis; ++i) {
+            if (!d->in[i]) return MIMK_E_ARG;
+            if (!map_in_range(d->in_map[i], d->rn, d->sr, d->in_shape[i])) return MIMK_E_SHAPE;
+        }
+    if (d->nps == 1) {
+        if (!d->post_in[0]) return MIMK_E_ARG;
+        // the epilogue input is read at the write coordinates, which range over the result's shape
+        if (!map_in_range(d->post_map[0], d->ro, d->so, d->post_shape[0])) return MIMK_E_SHAPE;
+    }
+    long long blocks = (n_out + 255) / 256;
+    const long long cap = (long long)dev->sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    mrp_generic_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(*d, n_out, n_red);
+    return launch_status();
+}

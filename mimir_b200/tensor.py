@@ -16,7 +16,8 @@ import torch
 
 from . import _lib as L
 
-_DT = {torch.float32: L.F32, torch.bfloat16: L.BF16}
+_DT = {torch.float32: L.F32, torch.bfloat16: L.BF16, torch.int32: L.I32, torch.int64: L.I64}
+_TORCH = {v: k for k, v in _DT.items()}
 _MONOID = {"sum": L.SUM, "add": L.SUM, "max": L.MAX, "fmax": L.MAX, "min": L.MIN, "fmin": L.MIN}
 _POST = {None: L.POST_ID, "id": L.POST_ID, "bias": L.POST_BIAS, "bias_relu": L.POST_BIAS_RELU,
          "bias_tanh": L.POST_BIAS_TANH, "relu": L.POST_RELU, "silu": L.POST_SILU, "add": L.POST_ADD_FULL}
@@ -246,3 +247,87 @@ def mlp_gated(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Ten
     d.dtype, d.b_layout = _dt(x), lay1
     L.check(L.lib().mimk_mlp_gated(C.byref(d), _stream()), "mlp_gated")
     return y
+
+
+# ------------------------------------------------------------------------------------------------ the generic op
+def proj_map(n_loops: int, subs):
+    """`proj_map subs`: result j reads loop variable subs[j] (tensor.mim:196-203), as a coefficient matrix."""
+    subs = list(subs)
+    m = [[0] * (n_loops + 1) for _ in subs]
+    for j, s in enumerate(subs):
+        m[j][s] = 1
+    return m
+
+
+def id_map(n: int):
+    return proj_map(n, range(n))
+
+
+def _fill_map(dst, m, n_loops):
+    rows = len(m)
+    if rows > L.MRP_MAX_RANK:
+        raise ValueError("access map has too many results")
+    dst.rows = rows
+    for j, row in enumerate(m):
+        row = [int(v) for v in row]
+        if len(row) != n_loops + 1:
+            raise ValueError("access map row must have n_loops + 1 coefficients (the last one is the constant)")
+        for l in range(n_loops):
+            dst.coef[j][l] = row[l]
+        dst.coef[j][n_loops] = row[n_loops]
+
+
+def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_maps=(), post_ins=(), *,
+                    acc_dtype=None, out_dtype=None) -> torch.Tensor:
+    """`map_reduce_post` itself (tensor.mim:159-169): combiner / epilogue by id (mimir_b200._lib.F_*, P_*), access
+    maps as coefficient matrices [results][n_loops + 1].  `init` is a Python number of the accumulator type."""
+    _dev(*ins, *post_ins)
+    So, Sr = [int(v) for v in So], [int(v) for v in Sr]
+    ro, rn = len(So), len(Sr)
+    if rn > L.MRP_MAX_LOOPS or ro > L.MRP_MAX_RANK or len(ins) > L.MRP_MAX_INPUTS or len(post_ins) > 1:
+        raise ValueError("map_reduce_post: too many loops, axes or inputs for the generic kernel")
+    ins = [t.contiguous() for t in ins]
+    post_ins = [t.contiguous() for t in post_ins]
+    if acc_dtype is None:
+        acc_dtype = torch.float32 if (ins and ins[0].dtype in (torch.float32, torch.bfloat16)) or not ins and isinstance(init, float) else (ins[0].dtype if ins else torch.int32)
+    if out_dtype is None:
+        out_dtype = acc_dtype
+    dev = ins[0].device if ins else (post_ins[0].device if post_ins else torch.device("cuda"))
+    out = torch.zeros(So, dtype=out_dtype, device=dev)
+    d = L.MrpDesc()
+    d.ro, d.rn, d.nis, d.nps = ro, rn, len(ins), len(post_ins)
+    for i, v in enumerate(Sr):
+        d.sr[i] = v
+    for i, v in enumerate(So):
+        d.so[i] = v
+    for i, (t, m) in enumerate(zip(ins, maps)):
+        if t.dim() > L.MRP_MAX_RANK:
+            raise ValueError("input rank too large for the generic kernel")
+        d.in_[i] = t.data_ptr()
+        d.in_dtype[i] = _dt(t)
+        for j, v in enumerate(t.shape):
+            d.in_shape[i][j] = v
+        if len(m) != t.dim():
+            raise ValueError("access map must have one result per input axis")
+        _fill_map(d.in_map[i], m, rn)
+    for i, (t, m) in enumerate(zip(post_ins, post_maps)):
+        d.post_in[i] = t.data_ptr()
+        d.post_dtype[i] = _dt(t)
+        for j, v in enumerate(t.shape):
+            d.post_shape[i][j] = v
+        if len(m) != t.dim():
+            raise ValueError("epilogue access map must have one result per epilogue-input axis")
+        _fill_map(d.post_map[i], m, ro)
+    if len(map_out) != ro:
+        raise ValueError("map_out must have one result per output axis")
+    _fill_map(d.map_out, map_out, rn)
+    d.comb, d.post = f, post
+    d.acc_dtype, d.out_dtype = _DT[acc_dtype], _DT[out_dtype]
+    if acc_dtype == torch.float32:
+        import struct
+        d.init_bits = struct.unpack("<i", struct.pack("<f", float(init)))[0]
+    else:
+        d.init_bits = int(init)
+    d.out = out.data_ptr()
+    L.check(L.lib().mimk_map_reduce_post(C.byref(d), _stream()), "map_reduce_post")
+    return out

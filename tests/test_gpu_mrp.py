@@ -1,0 +1,142 @@
+"""GPU parity of the generic `map_reduce_post` kernel: the reference's integer known answers (bit exact) and
+seeded comparisons with the oracle's interpreter on the same descriptors."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T():
+    from mimir_b200 import tensor
+    return tensor
+
+
+@pytest.fixture(scope="module")
+def L():
+    from mimir_b200 import _lib
+    return _lib
+
+
+def cu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_exec_map_reduce_42_and_epilogue_46(T, L):
+    t = cu((np.arange(12, dtype=np.int32) + 1).reshape(3, 4))
+    out = T.map_reduce_post((3,), (3, 4), L.F_ADD, 0, L.P_ID, T.proj_map(2, (0,)), [T.id_map(2)], [t])
+    assert out.tolist() == [10, 26, 42]                      # lit/buffer/exec_map_reduce.mim
+    tt = cu(np.array([[1, 5, 9], [2, 6, 10], [3, 7, 11], [4, 8, 12]], dtype=np.int32))
+    bias = cu(np.array([1, 2, 3], dtype=np.int32))
+    out = T.map_reduce_post((3,), (3, 4), L.F_ADD, 0, L.P_ADD_PLUS1, T.proj_map(2, (0,)), [T.proj_map(2, (1, 0))], [tt],
+                            [T.id_map(1)], [bias])
+    assert out.tolist() == [12, 29, 46]                      # lit/buffer/exec_epilogue.mim
+
+
+def test_exec_interchange_ktile_tile(T, L):
+    a = cu((np.arange(6, dtype=np.int32) + 1).reshape(2, 3))
+    b = cu(np.add.outer(np.arange(3), np.arange(4)).astype(np.int32))
+    mm = lambda a, b, m, l, k: T.map_reduce_post((m, l), (m, l, k), L.F_MULADD, 0, L.P_ID, T.proj_map(3, (0, 1)),
+                                                 [T.proj_map(3, (0, 2)), T.proj_map(3, (2, 1))], [a, b])
+    assert int(mm(a, b, 2, 4, 3)[1, 2]) == 47                # lit/buffer/exec_interchange.mim
+    ones, twos = cu(np.ones((2, 4), np.int32)), cu(np.full((4, 2), 2, np.int32))
+    assert int(mm(ones, twos, 2, 2, 4)[1, 1]) == 8           # lit/buffer/exec_ktile.mim
+    # lit/buffer/exec_tile.mim: loops (io, jo, ii, ji, ko, ki), packed output (io, ii, jo, ji); C_packed[0,1,1,0] = 80
+    a = cu(np.repeat(np.arange(1, 5, dtype=np.int32)[:, None], 8, axis=1))
+    b = cu(np.repeat(np.array([[1, 3, 5, 7]], dtype=np.int32), 8, axis=0))
+    ma = [[2, 0, 1, 0, 0, 0, 0], [0, 0, 0, 0, 4, 1, 0]]
+    mb = [[0, 0, 0, 0, 4, 1, 0], [0, 2, 0, 1, 0, 0, 0]]
+    out = T.map_reduce_post((2, 2, 2, 2), (2, 2, 2, 2, 2, 4), L.F_MULADD, 0, L.P_ID, T.proj_map(6, (0, 2, 1, 3)), [ma, mb],
+                            [a, b])
+    assert int(out[0, 1, 1, 0]) == 80
+    assert np.array_equal(out.reshape(4, 4).cpu().numpy(), a.cpu().numpy() @ b.cpu().numpy())
+
+
+def test_exec_conv_63(T, L):
+    def conv(cin):
+        x, w = cu(np.ones((2, cin, 4, 4), np.int32)), cu(np.ones((2, cin, 3, 3), np.int32))
+        mi = [[0] * 8 for _ in range(4)]
+        mi[0][0] = 1; mi[1][4] = 1; mi[2][2] = 1; mi[2][5] = 1; mi[3][3] = 1; mi[3][6] = 1
+        return T.map_reduce_post((2, 2, 2, 2), (2, 2, 2, 2, cin, 3, 3), L.F_MULADD, 0, L.P_ID, T.proj_map(7, (0, 1, 2, 3)),
+                                 [mi, T.proj_map(7, (1, 4, 5, 6))], [x, w])
+    assert int(conv(3)[1, 1, 1, 1]) + int(conv(4)[0, 1, 0, 1]) == 63   # lit/buffer/exec_conv.mim
+
+
+def test_heterogeneous_166_365(T, L):
+    # lit/btensor/map_reduce_post.mim:22-36 -- I32 and I64 inputs, I32 accumulator, I64 epilogue input and result
+    a = cu(np.array([[[1, 2, 3]], [[4, 5, 6]]], dtype=np.int32))
+    b = cu(np.array([[[10, 20, 30]], [[40, 50, 60]]], dtype=np.int64))
+    p = cu(np.array([[100], [200]], dtype=np.int64))
+    out = T.map_reduce_post((2, 1), (2, 1, 3), L.F_MIX, 0, L.P_ADD, T.proj_map(3, (0, 1)), [T.id_map(3), T.id_map(3)],
+                            [a, b], [T.id_map(2)], [p], acc_dtype=torch.int32, out_dtype=torch.int64)
+    assert out.reshape(-1).tolist() == [166, 365]
+
+
+def test_int32_wraps_like_the_oracle(T, L):
+    rng = np.random.default_rng(0)
+    a = rng.integers(-2**31, 2**31 - 1, (5, 9), dtype=np.int64).astype(np.int32)
+    b = rng.integers(-2**31, 2**31 - 1, (9, 4), dtype=np.int64).astype(np.int32)
+    got = T.map_reduce_post((5, 4), (5, 4, 9), L.F_MULADD, 0, L.P_ID, T.proj_map(3, (0, 1)),
+                            [T.proj_map(3, (0, 2)), T.proj_map(3, (2, 1))], [cu(a), cu(b)])
+    assert np.array_equal(got.cpu().numpy(), mo.product_2d(a, b))
+
+
+def test_float_instances_match_the_interpreter(T, L):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((6, 7, 5)).astype(np.float32)
+    # reduce over the middle axis: output loops (0, 2), reduction loop 1
+    got = T.map_reduce_post((6, 5), (6, 5, 7), L.F_ADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, (0, 2, 1))],
+                            [cu(x)])
+    assert np.array_equal(got.cpu().numpy(), mo.reduce(x, 1))        # same ascending fold order: same bits
+    mx = T.map_reduce_post((6, 5), (6, 5, 7), L.F_MAX, float("-inf"), L.P_ID, T.proj_map(3, (0, 1)),
+                           [T.proj_map(3, (0, 2, 1))], [cu(x)])
+    assert np.array_equal(mx.cpu().numpy(), mo.reduce(x, 1, "max"))
+    # binary_ax exp(x - max) with y broadcast along axis 1
+    e = T.map_reduce_post((6, 7, 5), (6, 7, 5), L.F_SUBEXP, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.proj_map(3, (0, 2))],
+                          [cu(x), mx])
+    want = mo.binary_ax(mo.F_SUBEXP_F32, 1, x, mo.reduce(x, 1, "max"))
+    assert np.allclose(e.cpu().numpy(), want, rtol=2e-6, atol=0)
+    # transposed copy, flipped copy (negative coefficient + constant), strided slice, broadcast
+    t2 = rng.standard_normal((4, 9)).astype(np.float32)
+    tr = T.map_reduce_post((9, 4), (9, 4), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, (1, 0))], [cu(t2)])
+    assert np.array_equal(tr.cpu().numpy(), t2.T)
+    fl = T.map_reduce_post((4, 9), (4, 9), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [[[-1, 0, 3], [0, -1, 8]]], [cu(t2)])
+    assert np.array_equal(fl.cpu().numpy(), t2[::-1, ::-1])
+    sl = T.map_reduce_post((2, 4), (2, 4), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [[[2, 0, 1], [0, 2, 0]]], [cu(t2)])
+    assert np.array_equal(sl.cpu().numpy(), t2[1::2, 0:8:2])
+    bc = T.map_reduce_post((3, 9), (3, 9), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [[[0, 1, 0]]], [cu(t2[0])])
+    assert np.array_equal(bc.cpu().numpy(), np.broadcast_to(t2[0], (3, 9)))
+
+
+def test_fc_fixture_through_the_generic_kernel(T, L):
+    # lit/tensor/fc_aux.cpp with the bias+relu epilogue in the `post` slot and W read through its transpose
+    M, K, N = 5, 33, 7
+    x = ((np.arange(M * K) % 13).astype(np.float32) / np.float32(13.0) - np.float32(0.4)).reshape(M, K)
+    w = (((7 * np.arange(N * K)) % 11).astype(np.float32) / np.float32(11.0) - np.float32(0.5)).reshape(N, K)
+    bias = ((np.arange(N) % 5).astype(np.float32) / np.float32(5.0) - np.float32(0.4))
+    got = T.map_reduce_post((M, N), (M, N, K), L.F_MULADD, 0.0, L.P_ADD_RELU, T.proj_map(3, (0, 1)),
+                            [T.proj_map(3, (0, 2)), T.proj_map(3, (1, 2))], [cu(x), cu(w)], [T.proj_map(2, (1,))], [cu(bias)])
+    ref = np.maximum((x.astype(np.float64) @ w.astype(np.float64).T + bias).astype(np.float32), 0)
+    assert (np.abs(ref - got.cpu().numpy()) <= 1e-4 + 1e-4 * np.abs(ref)).all()
+    # and it agrees with the specialised contraction kernel
+    spec = T.product_2d(cu(x), T.transpose_2d(cu(w)), post="bias_relu", bias=cu(bias))
+    assert np.allclose(spec.cpu().numpy(), got.cpu().numpy(), rtol=1e-6, atol=1e-6)
+
+
+def test_out_of_range_maps_are_refused(T, L):
+    from mimir_b200 import MimkError
+    t = cu(np.zeros((3, 4), np.float32))
+    with pytest.raises(MimkError) as e:   # reads column 4 of a 4-column tensor
+        T.map_reduce_post((3, 4), (3, 4), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [[[1, 0, 0], [0, 1, 1]]], [t])
+    assert e.value.status == 2
+    with pytest.raises(MimkError) as e:   # writes outside the result
+        T.map_reduce_post((3, 3), (3, 4), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.id_map(2)], [t])
+    assert e.value.status == 2
+    # zero-sized output, dynamic-bound style empty reduction
+    out = T.map_reduce_post((0, 4), (0, 4), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.id_map(2)], [cu(np.zeros((0, 4), np.float32))])
+    assert out.shape == (0, 4)
+    out = T.map_reduce_post((3,), (3, 0), L.F_ADD, 0.0, L.P_ID, T.proj_map(2, (0,)), [T.id_map(2)], [cu(np.zeros((3, 0), np.float32))])
+    assert out.tolist() == [0.0, 0.0, 0.0]
