@@ -1,4 +1,5 @@
 // C-ABI entry points that only validate and dispatch, plus the per-device state of the library.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -82,6 +83,21 @@ int get_scratch(size_t bytes, void** out) {
 
 using namespace mimk;
 
+namespace mimk {
+// The paired-SM kernel when the problem has enough 256-row tiles, else the one-CTA kernel.
+// MIMK_GEMM_2CTA=0 forces the one-CTA kernel, =2 the paired one whenever it can run (for A/B measurements).
+int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2) {
+    static int allow_pair = -1;
+    if (allow_pair < 0) {
+        const char* e = getenv("MIMK_GEMM_2CTA");
+        allow_pair    = (e && e[0] == '0') ? 0 : ((e && e[0] == '2') ? 2 : 1);
+    }
+    if (allow_pair == 2 && gemm_tc_supported(d)) return gemm_tc2(d, s, gated, b2);
+    if (allow_pair && gemm_tc2_supported(d, gated)) return gemm_tc2(d, s, gated, b2);
+    return gemm_tc(d, s, gated, b2);
+}
+}  // namespace mimk
+
 extern "C" const char* mimk_status_str(int status) {
     switch (status) {
         case MIMK_OK: return "ok";
@@ -139,7 +155,7 @@ extern "C" int mimk_gemm(const mimk_gemm_desc* d, void* stream) {
     if (d->batch == 0 || d->m == 0 || d->n == 0) return MIMK_OK;
     if (!d->c || (d->k > 0 && (!d->a || !d->b))) return MIMK_E_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (gemm_tc_supported(*d)) return gemm_tc(*d, s, 0, nullptr);
+    if (gemm_tc_supported(*d)) return gemm_tc_any(*d, s, 0, nullptr);
     return gemm_simt(*d, s);
 }
 
@@ -174,12 +190,12 @@ extern "C" int mimk_mlp_gated(const mimk_mlp_desc* d, void* stream) {
     g1.a = d->x, g1.b = d->w1, g1.c = h;
     g1.in_dtype = MIMK_BF16, g1.out_dtype = MIMK_BF16, g1.b_layout = d->b_layout, g1.post = MIMK_POST_ID;
     if (!gemm_tc_supported(g1)) return MIMK_E_UNSUPPORTED;
-    MIMK_TRY(gemm_tc(g1, s, 1, d->w3));
+    MIMK_TRY(gemm_tc_any(g1, s, 1, d->w3));
     // stage 2: Y = H W2
     mimk_gemm_desc g2 = {};
     g2.batch = 1, g2.m = d->m, g2.n = d->n, g2.k = d->f;
     g2.a = h, g2.b = d->w2, g2.c = d->y;
     g2.in_dtype = MIMK_BF16, g2.out_dtype = MIMK_BF16, g2.b_layout = d->b_layout, g2.post = MIMK_POST_ID;
-    if (gemm_tc_supported(g2)) return gemm_tc(g2, s, 0, nullptr);
+    if (gemm_tc_supported(g2)) return gemm_tc_any(g2, s, 0, nullptr);
     return gemm_simt(g2, s);
 }

@@ -135,7 +135,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = idesc_bf16_f32(BM, BN, 0, B_MN ? 1 : 0);
+            const uint32_t idesc = idesc_bf16_f32(BM, GATED ? 2 * BN : BN, 0, B_MN ? 1 : 0);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -154,11 +154,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const uint32_t lead = B_MN ? BK * 128 : 16;
                         const uint64_t bd   = smem_desc_sw128(sb + boff, lead, 1024);
                         const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                        // gated: the two 128-row B tiles lie back to back in shared memory and are issued as one 256-row
+                        // operand, so one instruction feeds both accumulators (columns [0,128) gate, [128,256) up)
                         mma_f16_ss(d0, ad, bd, idesc, accum);
-                        if (GATED) {
-                            const uint64_t bd2 = smem_desc_sw128(sb + BN * BK * 2 + boff, lead, 1024);
-                            mma_f16_ss(d0 + BN, ad, bd2, idesc, accum);
-                        }
                     }
                     mma_commit(smem_u32(&bars->empty[stage]));
                     if (++stage == STAGES) {
