@@ -250,6 +250,10 @@ int mimk_map_reduce_post(const mimk_mrp_desc* desc, void* stream);
 enum { MIMK_ROWS_SOFTMAX = 0, MIMK_ROWS_RMSNORM = 1, MIMK_ROWS_SOFTMAX_RMSNORM = 2 };
 int mimk_host_rows(int kind, const void* x, const void* gamma, void* y, int in_dtype, int out_dtype, int64_t rows,
                    int64_t cols, float eps);
+/* softmax(x) and rmsnorm(x) of the same matrix from ONE upload of x: two consumers of one tensor, which the reference's
+ * per-operation wrappers would upload twice (lower_map_reduce.cpp:111-122 runs once per operation). */
+int mimk_host_rows_pair(const void* x, const void* gamma, void* y_softmax, void* y_rmsnorm, int in_dtype, int out_dtype,
+                        int64_t rows, int64_t cols, float eps);
 /* desc holds host pointers (a, b, c, post_row, post_full). */
 int mimk_host_gemm(const mimk_gemm_desc* desc);
 /* desc holds host pointers (q, k, v, o, lse). */

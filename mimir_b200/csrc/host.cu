@@ -87,16 +87,19 @@ extern "C" int mimk_host_release(void) {
     return MIMK_OK;
 }
 
-extern "C" int mimk_host_rows(int kind, const void* x, const void* gamma, void* y, int in_dtype, int out_dtype,
-                              int64_t rows, int64_t cols, float eps) {
-    if (kind < MIMK_ROWS_SOFTMAX || kind > MIMK_ROWS_SOFTMAX_RMSNORM || rows < 0 || cols < 0) return MIMK_E_ARG;
+namespace {
+// kind 0..2: one result `y`; kind 3: softmax into `y` and RMSNorm into `y2` from ONE upload of x.
+int host_rows_impl(int kind, const void* x, const void* gamma, void* y, void* y2, int in_dtype, int out_dtype,
+                   int64_t rows, int64_t cols, float eps) {
+    const bool both = kind == 3;
+    if ((!both && (kind < MIMK_ROWS_SOFTMAX || kind > MIMK_ROWS_SOFTMAX_RMSNORM)) || rows < 0 || cols < 0) return MIMK_E_ARG;
     if ((in_dtype != MIMK_F32 && in_dtype != MIMK_BF16) || (out_dtype != MIMK_F32 && out_dtype != MIMK_BF16))
         return MIMK_E_DTYPE;
     std::lock_guard<std::mutex> lock(g_host_mutex);
     HostCtx* c = nullptr;
     MIMK_TRY(get_ctx(&c));
     if (rows * cols == 0) return MIMK_OK;
-    if (!x || !y || (kind != MIMK_ROWS_SOFTMAX && !gamma)) return MIMK_E_ARG;
+    if (!x || !y || (both && !y2) || (kind != MIMK_ROWS_SOFTMAX && !gamma)) return MIMK_E_ARG;
     const size_t in_row = size_t(cols) * dtype_size(in_dtype), out_row = size_t(cols) * dtype_size(out_dtype);
     // Row blocks of about 32 MiB of input: small enough to overlap, large enough to fill the machine.
     int64_t block_rows = int64_t((size_t(32) << 20) / in_row);
@@ -105,9 +108,11 @@ extern "C" int mimk_host_rows(int kind, const void* x, const void* gamma, void* 
     if (block_rows > rows) block_rows = rows;
     const int64_t nblocks = (rows + block_rows - 1) / block_rows;
     const int slots       = nblocks < 3 ? int(nblocks) : 3;  // ring of device buffers
-    const size_t in_slot = round256(size_t(block_rows) * in_row), out_slot = round256(size_t(block_rows) * out_row);
-    const size_t g_bytes = round256(size_t(cols) * 4);
-    uint8_t* base        = nullptr;
+    const size_t in_slot  = round256(size_t(block_rows) * in_row);
+    const size_t out_one  = round256(size_t(block_rows) * out_row);
+    const size_t out_slot = (both ? 2 : 1) * out_one;
+    const size_t g_bytes  = round256(size_t(cols) * 4);
+    uint8_t* base         = nullptr;
     MIMK_TRY(arena(*c, g_bytes + size_t(slots) * (in_slot + out_slot), &base));
     float* d_gamma = reinterpret_cast<float*>(base);
     if (kind != MIMK_ROWS_SOFTMAX) MIMK_CUDA_TRY(cudaMemcpyAsync(d_gamma, gamma, size_t(cols) * 4, cudaMemcpyHostToDevice, c->up));
@@ -122,18 +127,18 @@ extern "C" int mimk_host_rows(int kind, const void* x, const void* gamma, void* 
         if (b >= slots) MIMK_CUDA_TRY(cudaStreamWaitEvent(c->up, c->drained[int((b - slots) % HostCtx::MAX_EVENTS)], 0));
         MIMK_CUDA_TRY(cudaMemcpyAsync(d_in, static_cast<const uint8_t*>(x) + size_t(r0) * in_row, size_t(nr) * in_row,
                                       cudaMemcpyHostToDevice, c->up));
-        int rc;
-        if (kind == MIMK_ROWS_SOFTMAX)
-            rc = mimk_softmax(d_in, d_out, in_dtype, out_dtype, nr, cols, 1, c->up);
-        else if (kind == MIMK_ROWS_RMSNORM)
-            rc = mimk_rmsnorm(d_in, d_gamma, d_out, in_dtype, out_dtype, nr, cols, eps, c->up);
-        else
-            rc = mimk_softmax_rmsnorm(d_in, d_gamma, d_out, in_dtype, out_dtype, nr, cols, eps, c->up);
-        MIMK_TRY(rc);
+        if (kind == MIMK_ROWS_SOFTMAX || both) MIMK_TRY(mimk_softmax(d_in, d_out, in_dtype, out_dtype, nr, cols, 1, c->up));
+        if (kind == MIMK_ROWS_RMSNORM) MIMK_TRY(mimk_rmsnorm(d_in, d_gamma, d_out, in_dtype, out_dtype, nr, cols, eps, c->up));
+        if (both) MIMK_TRY(mimk_rmsnorm(d_in, d_gamma, d_out + out_one, in_dtype, out_dtype, nr, cols, eps, c->up));
+        if (kind == MIMK_ROWS_SOFTMAX_RMSNORM)
+            MIMK_TRY(mimk_softmax_rmsnorm(d_in, d_gamma, d_out, in_dtype, out_dtype, nr, cols, eps, c->up));
         MIMK_CUDA_TRY(cudaEventRecord(c->computed[ev], c->up));
         MIMK_CUDA_TRY(cudaStreamWaitEvent(c->down, c->computed[ev], 0));
         MIMK_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(y) + size_t(r0) * out_row, d_out, size_t(nr) * out_row,
                                       cudaMemcpyDeviceToHost, c->down));
+        if (both)
+            MIMK_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(y2) + size_t(r0) * out_row, d_out + out_one, size_t(nr) * out_row,
+                                          cudaMemcpyDeviceToHost, c->down));
         MIMK_CUDA_TRY(cudaEventRecord(c->drained[ev], c->down));
         // keep at most MAX_EVENTS blocks in flight so that an event is never re-recorded while still awaited
         if (b + 1 >= HostCtx::MAX_EVENTS) MIMK_CUDA_TRY(cudaEventSynchronize(c->drained[int((b + 1) % HostCtx::MAX_EVENTS)]));
@@ -141,6 +146,18 @@ extern "C" int mimk_host_rows(int kind, const void* x, const void* gamma, void* 
     MIMK_CUDA_TRY(cudaStreamSynchronize(c->down));
     MIMK_CUDA_TRY(cudaStreamSynchronize(c->up));
     return MIMK_OK;
+}
+}  // namespace
+
+extern "C" int mimk_host_rows(int kind, const void* x, const void* gamma, void* y, int in_dtype, int out_dtype,
+                              int64_t rows, int64_t cols, float eps) {
+    if (kind == 3) return MIMK_E_ARG;
+    return host_rows_impl(kind, x, gamma, y, nullptr, in_dtype, out_dtype, rows, cols, eps);
+}
+
+extern "C" int mimk_host_rows_pair(const void* x, const void* gamma, void* y_softmax, void* y_rmsnorm, int in_dtype,
+                                   int out_dtype, int64_t rows, int64_t cols, float eps) {
+    return host_rows_impl(3, x, gamma, y_softmax, y_rmsnorm, in_dtype, out_dtype, rows, cols, eps);
 }
 
 extern "C" int mimk_host_gemm(const mimk_gemm_desc* h) {

@@ -48,6 +48,26 @@ def softmax_rmsnorm(x, gamma, eps, *, out=None, out_dtype=None):
     return _rows(L.ROWS_SOFTMAX_RMSNORM, x, gamma, eps, out, out_dtype)
 
 
+def softmax_and_rmsnorm(x, gamma, eps, *, out_softmax=None, out_rmsnorm=None, out_dtype=None):
+    """softmax(x) and rmsnorm(x) along the last axis from one upload of x; returns (softmax, rmsnorm)."""
+    _cpu(x, gamma, out_softmax, out_rmsnorm)
+    x = x.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // max(cols, 1)
+    gamma = gamma.to(torch.float32).contiguous()
+    if gamma.numel() != cols:
+        raise ValueError("gamma extent must equal the last extent of x")
+    if out_softmax is None:
+        out_softmax = torch.empty(x.shape, dtype=out_dtype or x.dtype)
+    if out_rmsnorm is None:
+        out_rmsnorm = torch.empty(x.shape, dtype=out_softmax.dtype)
+    if out_softmax.dtype != out_rmsnorm.dtype:
+        raise TypeError("both results share one element type")
+    L.check(L.lib().mimk_host_rows_pair(x.data_ptr(), gamma.data_ptr(), out_softmax.data_ptr(), out_rmsnorm.data_ptr(),
+                                        _DT[x.dtype], _DT[out_softmax.dtype], rows, cols, float(eps)), "host_rows_pair")
+    return out_softmax, out_rmsnorm
+
+
 def product_2d(a, b, *, post=None, bias=None, out=None, out_dtype=None):
     _cpu(a, b, bias, out)
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:

@@ -32,6 +32,8 @@ def test_host_rows(H, rows, cols, pinned):
     assert (y.float().sum(1) - 1).abs().max() < 2e-2
     z = H.rmsnorm(x, gamma, 1e-6)
     assert nerr(z[sel].double().numpy(), mo.rmsnorm_rows(x[sel].numpy(), gamma.numpy(), 1e-6, truth=True)) < TOL_F32
+    ys, yr = H.softmax_and_rmsnorm(x, gamma, 1e-6, out_dtype=torch.bfloat16)
+    assert torch.equal(ys, y) and torch.equal(yr, H.rmsnorm(x, gamma, 1e-6, out_dtype=torch.bfloat16))
     # the device-resident path gives the same bits
     from mimir_b200 import tensor as T
     assert torch.equal(T.softmax(1, x.cuda(), out_dtype=torch.bfloat16).cpu(), y)
