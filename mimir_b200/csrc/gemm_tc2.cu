@@ -30,7 +30,7 @@ constexpr int A_BYTES  = BM * BK * 2;
 constexpr int B_BYTES  = 128 * BK * 2;   // this CTA's half of the B tile(s)
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
-constexpr int GROUP_M = 16;      // pair-tiles (256 rows) per raster group
+constexpr int GROUP_M = 8;       // pair-tiles (256 rows) per raster group: A of a group (32 MiB at K = 8192) stays in L2
 
 struct Bars {
     uint64_t full[STAGES];
