@@ -331,3 +331,196 @@ def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_ma
     d.out = out.data_ptr()
     L.check(L.lib().mimk_map_reduce_post(C.byref(d), _stream()), "map_reduce_post")
     return out
+
+
+# ------------------------------------------------------------------------------------------------ the rest of the op surface
+# Every operator below is ONE `map_reduce_post` with the access maps the reference's `_impl` lams build
+# (tensor.mim:1086-1134, 1182-1327, 1367-1411, 1443-1468), run by the generic kernel.
+def _copy_fn(t):
+    return L.F_FIRST, (0.0 if t.dtype in (torch.float32, torch.bfloat16) else 0)
+
+
+def transpose(x: torch.Tensor, perm) -> torch.Tensor:
+    """`transpose perm x`: out[o] = x[o[inv perm]] -- output axis i is input axis perm[i] (tensor.mim:1459)."""
+    perm = [int(p) for p in perm]
+    r = x.dim()
+    if sorted(perm) != list(range(r)):
+        raise ValueError("transpose: perm must be a permutation of the axes")
+    so = [x.shape[p] for p in perm]
+    inv = [perm.index(i) for i in range(r)]
+    f, init = _copy_fn(x)
+    return map_reduce_post(so, so, f, init, L.P_ID, id_map(r), [proj_map(r, inv)], [x], acc_dtype=_acc(x), out_dtype=x.dtype)
+
+
+def _acc(t):
+    return torch.float32 if t.dtype in (torch.float32, torch.bfloat16) else t.dtype
+
+
+def flip(x: torch.Tensor) -> torch.Tensor:
+    """`flip x`: every axis reversed, read map (s - 1) - o (tensor.mim:1094-1101)."""
+    r = x.dim()
+    m = [[0] * (r + 1) for _ in range(r)]
+    for d in range(r):
+        m[d][d] = -1
+        m[d][r] = x.shape[d] - 1
+    f, init = _copy_fn(x)
+    return map_reduce_post(x.shape, x.shape, f, init, L.P_ID, id_map(r), [m], [x], acc_dtype=_acc(x), out_dtype=x.dtype)
+
+
+def slice_(x: torch.Tensor, start, stride, shape) -> torch.Tensor:
+    """`slice`: out[o] = x[start + o * stride] with the given result shape."""
+    r = x.dim()
+    m = [[0] * (r + 1) for _ in range(r)]
+    for d in range(r):
+        m[d][d] = int(stride[d])
+        m[d][r] = int(start[d])
+    f, init = _copy_fn(x)
+    return map_reduce_post(list(shape), list(shape), f, init, L.P_ID, id_map(r), [m], [x], acc_dtype=_acc(x), out_dtype=x.dtype)
+
+
+def broadcast_in_dim(x: torch.Tensor, shape, index) -> torch.Tensor:
+    """`broadcast_in_dim`: input axis i reads output loop index[i], or 0 where its extent is 1 (bid_map, tensor.mim:1080-1089)."""
+    shape = [int(s) for s in shape]
+    ro = len(shape)
+    m = [[0] * (ro + 1) for _ in range(x.dim())]
+    for i, o in enumerate(index):
+        if x.shape[i] != 1:
+            if x.shape[i] != shape[o]:
+                raise ValueError("broadcast_in_dim: extents must match or be 1")
+            m[i][int(o)] = 1
+    f, init = _copy_fn(x)
+    return map_reduce_post(shape, shape, f, init, L.P_ID, id_map(ro), [m], [x], acc_dtype=_acc(x), out_dtype=x.dtype)
+
+
+def pad(x: torch.Tensor, lo, hi, value=0) -> torch.Tensor:
+    """`pad`: x placed at offset `lo` inside a tensor filled with `value` (edge padding only)."""
+    r = x.dim()
+    shape = [x.shape[d] + int(lo[d]) + int(hi[d]) for d in range(r)]
+    out = torch.full(shape, value, dtype=x.dtype, device=x.device)
+    if x.numel() == 0:
+        return out
+    mo = [[0] * (r + 1) for _ in range(r)]
+    for d in range(r):
+        mo[d][d] = 1
+        mo[d][r] = int(lo[d])
+    f, init = _copy_fn(x)
+    # the copy writes through map_out = o + lo into the pre-filled result
+    d = _mrp_into(out, list(x.shape), f, init, L.P_ID, mo, [id_map(r)], [x])
+    return d
+
+
+def _mrp_into(out, Sr, f, init, post, map_out, maps, ins):
+    """map_reduce_post writing into an existing tensor `out` (destination passing, as btensor does)."""
+    So = list(out.shape)
+    ro, rn = len(So), len(Sr)
+    d = L.MrpDesc()
+    d.ro, d.rn, d.nis, d.nps = ro, rn, len(ins), 0
+    for i, v in enumerate(Sr):
+        d.sr[i] = int(v)
+    for i, v in enumerate(So):
+        d.so[i] = int(v)
+    for i, (t, m) in enumerate(zip(ins, maps)):
+        t = t.contiguous()
+        d.in_[i] = t.data_ptr()
+        d.in_dtype[i] = _dt(t)
+        for j, v in enumerate(t.shape):
+            d.in_shape[i][j] = v
+        _fill_map(d.in_map[i], m, rn)
+    _fill_map(d.map_out, map_out, rn)
+    d.comb, d.post = f, post
+    acc = _acc(out)
+    d.acc_dtype, d.out_dtype = _DT[acc], _dt(out)
+    if acc == torch.float32:
+        import struct
+        d.init_bits = struct.unpack("<i", struct.pack("<f", float(init)))[0]
+    else:
+        d.init_bits = int(init)
+    d.out = out.data_ptr()
+    L.check(L.lib().mimk_map_reduce_post(C.byref(d), _stream()), "map_reduce_post")
+    return out
+
+
+def conv(x: torch.Tensor, w: torch.Tensor, stride=(1, 1), dilation=(1, 1), padding=(0, 0)) -> torch.Tensor:
+    """`conv R (stride, dilation, padding) (input, weight)`: NCHW input, [Cout, Cin, KH, KW] weight (tensor.mim:434-438).
+    Loop vector (n, co, oh, ow, ci, kh, kw); the input is read at (n, ci, oh*s + kh*d, ow*s + kw*d) of the padded tensor
+    (conv_impl, tensor.mim:1254-1282)."""
+    _dev(x, w)
+    n, cin, h, wd = x.shape
+    cout, cin2, kh, kw = w.shape
+    if cin != cin2:
+        raise ValueError("contracting dims don't match")
+    xp = pad(x, (0, 0, padding[0], padding[1]), (0, 0, padding[0], padding[1])) if any(padding) else x
+    oh = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+    ow = (wd + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    mi = [[0] * 8 for _ in range(4)]
+    mi[0][0] = 1
+    mi[1][4] = 1
+    mi[2][2], mi[2][5] = stride[0], dilation[0]
+    mi[3][3], mi[3][6] = stride[1], dilation[1]
+    init = 0.0 if x.dtype in (torch.float32, torch.bfloat16) else 0
+    return map_reduce_post((n, cout, oh, ow), (n, cout, oh, ow, cin, kh, kw), L.F_MULADD, init, L.P_ID,
+                           proj_map(7, (0, 1, 2, 3)), [mi, proj_map(7, (1, 4, 5, 6))], [xp, w], acc_dtype=_acc(x),
+                           out_dtype=x.dtype)
+
+
+def pool(monoid: str, x: torch.Tensor, kernel, stride=None, dilation=(1, 1), padding=(0, 0)) -> torch.Tensor:
+    """`pool (g, init) (kernel, stride, dilation, padding, s_out) input` on NCHW (tensor.mim:499-504); padded cells hold
+    the monoid's identity."""
+    _dev(x)
+    stride = stride or kernel
+    n, c, h, wd = x.shape
+    ident = {"sum": 0.0, "max": float("-inf"), "min": float("inf")}[monoid]
+    comb = {"sum": L.F_ADD, "max": L.F_MAX, "min": L.F_MIN}[monoid]
+    xp = pad(x, (0, 0, padding[0], padding[1]), (0, 0, padding[0], padding[1]), ident) if any(padding) else x
+    oh = (h + 2 * padding[0] - dilation[0] * (kernel[0] - 1) - 1) // stride[0] + 1
+    ow = (wd + 2 * padding[1] - dilation[1] * (kernel[1] - 1) - 1) // stride[1] + 1
+    mi = [[0] * 7 for _ in range(4)]
+    mi[0][0] = 1
+    mi[1][1] = 1
+    mi[2][2], mi[2][4] = stride[0], dilation[0]
+    mi[3][3], mi[3][5] = stride[1], dilation[1]
+    return map_reduce_post((n, c, oh, ow), (n, c, oh, ow, kernel[0], kernel[1]), comb, ident, L.P_ID, proj_map(6, (0, 1, 2, 3)),
+                           [mi], [xp], acc_dtype=torch.float32, out_dtype=x.dtype)
+
+
+def dot_product(a: torch.Tensor, b: torch.Tensor, contract, batch=((), ())) -> torch.Tensor:
+    """`dot_product R (c1, c2, b1, b2) (a, b)` (tensor.mim:480-486): result axes are the batching axes, then a's free
+    axes, then b's (dot_general_shape). Rank-2 products and bmm go to the contraction kernels; any other pattern is one
+    generic map_reduce_post with the subscripts dot_product_impl builds (tensor.mim:1381-1396)."""
+    _dev(a, b)
+    c1, c2 = [int(i) for i in contract[0]], [int(i) for i in contract[1]]
+    b1, b2 = [int(i) for i in batch[0]], [int(i) for i in batch[1]]
+    for i, j in zip(b1, b2):
+        if a.shape[i] != b.shape[j]:
+            raise ValueError("batching dims don't match")
+    for i, j in zip(c1, c2):
+        if a.shape[i] != b.shape[j]:
+            raise ValueError("contracting dims don't match")
+    if a.dim() == 2 and b.dim() == 2 and not b1 and c1 == [1] and c2 == [0]:
+        return product_2d(a, b)
+    if a.dim() == 2 and b.dim() == 2 and not b1 and c1 == [1] and c2 == [1]:
+        return product_2d(a, transpose_2d(b))
+    if a.dim() == 3 and b.dim() == 3 and b1 == [0] and b2 == [0] and c1 == [2] and c2 == [1]:
+        return bmm(a, b)
+    free1 = [i for i in range(a.dim()) if i not in b1 and i not in c1]
+    free2 = [i for i in range(b.dim()) if i not in b2 and i not in c2]
+    so = [a.shape[i] for i in b1] + [a.shape[i] for i in free1] + [b.shape[i] for i in free2]
+    sr = so + [a.shape[i] for i in c1]
+    nb, r_out, n = len(b1), len(so), len(sr)
+
+    def subs(rank, bd, cd, free, off_free):
+        s = []
+        for i in range(rank):
+            if i in bd:
+                s.append(bd.index(i))
+            elif i in cd:
+                s.append(r_out + cd.index(i))
+            else:
+                s.append(off_free + free.index(i))
+        return s
+
+    s1 = subs(a.dim(), b1, c1, free1, nb)
+    s2 = subs(b.dim(), b2, c2, free2, nb + len(free1))
+    init = 0.0 if a.dtype in (torch.float32, torch.bfloat16) else 0
+    return map_reduce_post(so, sr, L.F_MULADD, init, L.P_ID, proj_map(n, range(r_out)), [proj_map(n, s1), proj_map(n, s2)],
+                           [a, b], acc_dtype=_acc(a), out_dtype=a.dtype)

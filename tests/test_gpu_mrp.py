@@ -140,3 +140,35 @@ def test_out_of_range_maps_are_refused(T, L):
     assert out.shape == (0, 4)
     out = T.map_reduce_post((3,), (3, 0), L.F_ADD, 0.0, L.P_ID, T.proj_map(2, (0,)), [T.id_map(2)], [cu(np.zeros((3, 0), np.float32))])
     assert out.tolist() == [0.0, 0.0, 0.0]
+
+
+def test_shape_ops_conv_pool_dot_general(T, L):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((3, 4, 5)).astype(np.float32)
+    assert np.array_equal(T.transpose(cu(x), (2, 0, 1)).cpu().numpy(), x.transpose(2, 0, 1))
+    assert np.array_equal(T.flip(cu(x)).cpu().numpy(), x[::-1, ::-1, ::-1])
+    assert np.array_equal(T.slice_(cu(x), (1, 0, 1), (1, 2, 2), (2, 2, 2)).cpu().numpy(), x[1:3, 0:4:2, 1:5:2])
+    b = rng.standard_normal((1, 5)).astype(np.float32)
+    assert np.array_equal(T.broadcast_in_dim(cu(b), (4, 5), (0, 1)).cpu().numpy(), np.broadcast_to(b, (4, 5)))
+    assert np.array_equal(T.pad(cu(x), (1, 0, 2), (0, 1, 1), 7.0).cpu().numpy(),
+                          np.pad(x, ((1, 0), (0, 1), (2, 1)), constant_values=7.0))
+    # conv: the reference's all-ones fixture (lit/buffer/exec_conv.mim) and a seeded one against torch's own
+    ones = lambda *s: cu(np.ones(s, np.int32))
+    assert int(T.conv(ones(2, 3, 4, 4), ones(2, 3, 3, 3))[1, 1, 1, 1]) + int(T.conv(ones(2, 4, 4, 4), ones(2, 4, 3, 3))[0, 1, 0, 1]) == 63
+    xi = rng.standard_normal((2, 3, 9, 8)).astype(np.float32)
+    w = rng.standard_normal((4, 3, 3, 2)).astype(np.float32)
+    got = T.conv(cu(xi), cu(w), stride=(2, 1), dilation=(1, 2), padding=(1, 1))
+    want = torch.nn.functional.conv2d(torch.from_numpy(xi).double(), torch.from_numpy(w).double(), stride=(2, 1),
+                                      dilation=(1, 2), padding=(1, 1)).numpy()
+    assert got.shape == want.shape and mo.normalised_error(got.cpu().numpy(), want) < 1e-5
+    pm = T.pool("max", cu(xi), (2, 2), padding=(1, 0))
+    wantp = torch.nn.functional.max_pool2d(torch.from_numpy(xi), (2, 2), padding=(1, 0)).numpy()
+    assert np.array_equal(pm.cpu().numpy(), wantp)
+    # dot_general: batch axis 1 of a with axis 0 of b, contraction over two axes
+    a = rng.standard_normal((4, 3, 5, 6)).astype(np.float32)
+    bb = rng.standard_normal((3, 6, 7, 5)).astype(np.float32)
+    got = T.dot_product(cu(a), cu(bb), ((2, 3), (3, 1)), ((1,), (0,)))
+    want = np.einsum("abcd,bdec->bae", a.astype(np.float64), bb.astype(np.float64))
+    assert got.shape == want.shape and mo.normalised_error(got.cpu().numpy(), want) < 1e-5
+    with pytest.raises(ValueError, match="contracting dims don't match"):
+        T.dot_product(cu(a), cu(bb), ((2,), (0,)))
