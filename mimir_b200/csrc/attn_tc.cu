@@ -43,6 +43,7 @@ constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 208, OTHER_REGS = 88;
 static_assert(2 * 128 * SOFTMAX_REGS + 128 * OTHER_REGS <= LAUNCH_REGS * NUM_THREADS, "setmaxnreg budget exceeds the CTA's registers");
 static_assert(SOFTMAX_REGS % 8 == 0 && OTHER_REGS % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+constexpr int HEAD_GROUP = 8;             // heads whose CTAs are interleaved longest-first under a causal mask
 
 struct Bars {
     uint64_t q_full;
@@ -56,7 +57,7 @@ constexpr int SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + 1024 + 256;
 static_assert(sizeof(Bars) <= 256, "barrier block too large");
 
 struct Params {
-    int64_t Sq, Sk, BH;
+    int64_t Sq, Sk, BH, num_pairs, head_group;
     __nv_bfloat16* O;
     float* lse;
     float scale_log2;  // scale * log2(e)
@@ -69,7 +70,7 @@ struct Params {
 __device__ long long g_trace[3][64][8];
 #define MIMK_TR(role, iter, ev)                                                            \
     do {                                                                                   \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && (iter) < 64) g_trace[role][iter][ev] = clock64(); \
+        if (blockIdx.x == 0 && (iter) < 64) g_trace[role][iter][ev] = clock64(); \
     } while (0)
 #else
 #define MIMK_TR(role, iter, ev) \
@@ -172,11 +173,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     volatile int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // grid = (query-tile pairs, heads), handed out x-fastest: the CTAs resident at any moment belong to a few heads and
-    // share those heads' K/V through L2 (ordering by head first was measured 10-20 % slower: every CTA then streams
-    // its own K/V from HBM). Within a head the longest pair (the last one under a causal mask) goes first.
-    const int head = blockIdx.y;
-    const int pair = int(gridDim.x) - 1 - int(blockIdx.x);
+    // CTAs are handed out in blockIdx order. Heads are taken in groups; inside a group all heads' longest query-tile
+    // pair (the last one under a causal mask) comes first, then all second-longest, and so on. Longest-first keeps
+    // the tail of a causal launch short, while the CTAs of one head still run close together in time and share its
+    // K/V tiles through L2. Measured at batch*heads 128, seq 4096: causal 1027 / 1072 / 1050 / 951 TFLOP/s for groups
+    // of 1 / 8 / 32 / 128 heads; without a mask all CTAs are equally long and a group of 1 is best (1244 vs 1230 at 8).
+    int head, pair;
+    {
+        const int64_t HG = p.head_group;
+        const int64_t per_group = HG * p.num_pairs;
+        const int64_t g = blockIdx.x / per_group, r = blockIdx.x % per_group;
+        const int64_t gsz = (p.BH - g * HG) < HG ? (p.BH - g * HG) : HG;
+        // the last group may be smaller: its CTAs are numbered with its own size
+        const int64_t rr = blockIdx.x - g * per_group;
+        pair = int(p.num_pairs - 1 - rr / gsz);
+        head = int(g * HG + rr % gsz);
+        (void)r;
+    }
     int64_t q0[2];
     int n_kv[2];
     const int kv_tiles = int((p.Sk + BKV - 1) / BKV);
@@ -508,7 +521,18 @@ int attn_tc(const mimk_attn_desc& d, cudaStream_t s) {
     p.scale_log2 = d.scale * 1.4426950408889634f;
     p.causal     = d.causal;
     p.status     = dev->status_dev;
-    dim3 grid((unsigned)((d.seq_q + 2 * BQ - 1) / (2 * BQ)), (unsigned)d.batch_heads);
+    p.num_pairs = (d.seq_q + 2 * BQ - 1) / (2 * BQ);
+    {
+        static int hg = -1;
+        if (hg < 0) {
+            const char* e = getenv("MIMK_ATTN_HEAD_GROUP");
+            hg            = e ? atoi(e) : 0;
+            if (hg < 1) hg = 0;
+        }
+        p.head_group = hg ? hg : (d.causal ? HEAD_GROUP : 1);
+    }
+    if (p.num_pairs * d.batch_heads >= (int64_t(1) << 31)) return MIMK_E_UNSUPPORTED;
+    dim3 grid((unsigned)(p.num_pairs * d.batch_heads));
     if (emu == 0)
         attn_tc_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, p);
     else if (emu == 1)
