@@ -160,7 +160,7 @@ __device__ __forceinline__ void tmem_st_32x32_x32(uint32_t taddr, const uint32_t
         : "memory");
 }
 
-// EMU: how many of every four PAIRS of exponentials go to the polynomial instead of the special-function unit.
+// EMU: how many of every eight PAIRS of exponentials go to the polynomial instead of the special-function unit.
 template <int EMU>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -412,7 +412,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 for (int i = 0; i < 32; i += 2) {
                     float xa, xb, a, b;
                     unpack2(fma2(pack2(__uint_as_float(r[c + i]), __uint_as_float(r[c + i + 1])), sl2, neg_m), xa, xb);
-                    if (((i >> 1) & 3) < EMU) {
+                    if (((i >> 1) & 7) < EMU) {
                         poly_exp2_x2(xa, xb, a, b);
                     } else {
                         a = fast_exp2(xa);
@@ -421,12 +421,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(a, b));
                     pk[i >> 1]         = pack_bf16x2(a, b);
                 }
-                tmem_st_32x32_x16(tS + (c >> 1), pk);
-                if (c == 32) {  // keys 0..63 of P_t are stored: let the tensor core start on them
+                if (c == 64) {
+                    // keys 0..63 of P_t were stored a whole chunk of exponentials ago, so this wait does not stall:
+                    // let the tensor core start on them
                     tmem_st_wait();
                     tc_fence_before();
                     mbar_arrive(smem_u32(&bars->p_half[t]));
                 }
+                tmem_st_32x32_x16(tS + (c >> 1), pk);
             }
             {
                 float s0, s1;
@@ -504,7 +506,7 @@ int attn_tc(const mimk_attn_desc& d, cudaStream_t s) {
     MIMK_TRY(make_tmap_bf16_3d(&tQ, d.q, HD, uint64_t(d.seq_q), uint64_t(d.batch_heads), row, uint64_t(d.seq_q) * row, 64, BQ));
     MIMK_TRY(make_tmap_bf16_3d(&tK, d.k, HD, uint64_t(d.seq_k), uint64_t(d.batch_heads), row, uint64_t(d.seq_k) * row, 64, BKV));
     MIMK_TRY(make_tmap_bf16_3d(&tV, d.v, HD, uint64_t(d.seq_k), uint64_t(d.batch_heads), row, uint64_t(d.seq_k) * row, 64, BKV));
-    // exponentials sent to the FMA-pipe polynomial, out of every four (MIMK_ATTN_EMU=0..2 overrides for experiments)
+    // pairs of exponentials sent to the FMA-pipe polynomial, out of every eight (MIMK_ATTN_EMU=0..2 overrides for experiments)
     static int emu = -1;
     if (emu < 0) {
         const char* e = getenv("MIMK_ATTN_EMU");
