@@ -53,6 +53,12 @@ int mimk_device_check(void);
  * wait (its results are then undefined), MIMK_OK otherwise. Clears the flag. */
 int mimk_device_status(void* stream);
 
+/* Launches a one-CTA kernel that waits, with a limit of `limit_cycles` SM clocks, on a barrier nothing arrives on, and
+ * then reports exactly like the compute kernels: the status word is set and the kernel returns normally. After it,
+ * mimk_device_status() must answer MIMK_E_DEVICE_WAIT and the context must still be usable. This is how the
+ * failure path (cf. mim_cu_check, src/mim/plug/nvptx/rt/mim_cuda_rt.c:16-21) is tested without faulting a GPU. */
+int mimk_selftest_wait_expiry(int64_t limit_cycles, void* stream);
+
 /* ---- reduction monoids: the (g, init) pairs handed to `reduce` / `pool_fun`
  *      (src/mim/plug/tensor/tensor.mim:1139-1157): sum = (arith.add, 0), max = (extrema.fmax, -inf), ... ---- */
 enum { MIMK_SUM = 0, MIMK_MAX = 1, MIMK_MIN = 2 };

@@ -3,6 +3,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace mimk {
 
@@ -198,4 +199,35 @@ extern "C" int mimk_mlp_gated(const mimk_mlp_desc* d, void* stream) {
     g2.in_dtype = MIMK_BF16, g2.out_dtype = MIMK_BF16, g2.b_layout = d->b_layout, g2.post = MIMK_POST_ID;
     if (gemm_tc_supported(g2)) return gemm_tc_any(g2, s, 0, nullptr);
     return gemm_simt(g2, s);
+}
+
+// ---- self-test of the bounded-wait path --------------------------------------------------------------------------
+namespace mimk {
+namespace {
+// Waits on a barrier that nothing will ever arrive on, with a limit of `limit_cycles`, then reports like the real
+// kernels do: sets the status word and returns normally. No trap, no fault, no endless loop.
+__global__ void wait_expiry_kernel(long long limit_cycles, int* status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(sm100::smem_u32(&bar), 1);
+        abort_flag = 0;
+        sm100::fence_barrier_init();
+    }
+    __syncthreads();
+    volatile int* af = &abort_flag;
+    const bool ok = sm100::mbar_wait_limit(sm100::smem_u32(&bar), 0, af, limit_cycles);
+    __syncthreads();
+    if (threadIdx.x == 0 && (!ok || *af)) *status = MIMK_E_DEVICE_WAIT;
+}
+}  // namespace
+}  // namespace mimk
+
+extern "C" int mimk_selftest_wait_expiry(int64_t limit_cycles, void* stream) {
+    if (limit_cycles < 0 || limit_cycles > 2000000000LL) return MIMK_E_ARG;
+    int st        = MIMK_OK;
+    DeviceInfo* d = device_info(&st);
+    if (!d) return st;
+    wait_expiry_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, d->status_dev);
+    return launch_status();
 }

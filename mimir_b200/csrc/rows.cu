@@ -287,6 +287,33 @@ __global__ void map_kernel(int op, const float* __restrict__ x, const float* __r
     }
 }
 
+// 128-bit form of map_kernel: four consecutive elements per thread. Requires 16-byte aligned x / y / out, a total
+// divisible by 4, and a broadcast operand whose index is constant over the four elements (y_mode 1 with inner == 1 and
+// len % 4 == 0) or runs with them (y_mode 0; y_mode 2 with (len * inner) % 4 == 0).
+template <class TOut>
+__global__ void __launch_bounds__(256) map_vec4_kernel(int op, const float* __restrict__ x, const float* __restrict__ y,
+                                                      TOut* __restrict__ out, int64_t total4, int64_t len, int64_t period4,
+                                                      int y_mode) {
+    for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total4; t += int64_t(gridDim.x) * blockDim.x) {
+        const float4 a = load4(x + 4 * t);
+        float4 b       = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (y_mode == 0) {
+            b = load4(y + 4 * t);
+        } else if (y_mode == 1) {
+            const float v = __ldg(y + (4 * t) / len);
+            b             = make_float4(v, v, v, v);
+        } else if (y_mode == 2) {
+            b = __ldg(reinterpret_cast<const float4*>(y) + (t % period4));
+        }
+        float4 r;
+        r.x = apply_op(op, a.x, b.x);
+        r.y = apply_op(op, a.y, b.y);
+        r.z = apply_op(op, a.z, b.z);
+        r.w = apply_op(op, a.w, b.w);
+        store4(out + 4 * t, r);
+    }
+}
+
 int grid_for(int64_t work_items, int threads, int sm_count, int ctas_per_sm) {
     int64_t blocks = (work_items + threads - 1) / threads;
     int64_t cap    = int64_t(sm_count) * ctas_per_sm;
@@ -553,6 +580,20 @@ extern "C" int mimk_map(int op, const void* x, const void* y, void* out, int out
     if (!x || !out || (binary && !y)) return MIMK_E_ARG;
     if (unary) y_mode = 3;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool out_al = (reinterpret_cast<uintptr_t>(out) % (out_dtype == MIMK_F32 ? 16 : 8)) == 0;
+    const bool y_ok   = y_mode == 3 || (y_mode == 0 && aligned16(y)) || (y_mode == 1 && inner == 1 && len % 4 == 0) ||
+                      (y_mode == 2 && (len * inner) % 4 == 0 && aligned16(y));
+    if (total % 4 == 0 && aligned16(x) && out_al && y_ok) {
+        const int64_t total4 = total / 4, period4 = y_mode == 2 ? (len * inner) / 4 : 1;
+        const int vgrid      = grid_for(total4, 256, dev->sm_count, 8);
+        if (out_dtype == MIMK_F32)
+            map_vec4_kernel<<<vgrid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),
+                                                  static_cast<float*>(out), total4, len, period4, y_mode);
+        else
+            map_vec4_kernel<<<vgrid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),
+                                                  static_cast<__nv_bfloat16*>(out), total4, len, period4, y_mode);
+        return launch_status();
+    }
     int grid       = grid_for(total, 256, dev->sm_count, 8);
     if (out_dtype == MIMK_F32)
         map_kernel<<<grid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),

@@ -39,20 +39,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Returns false when the wait expired or another thread of the CTA already gave up (`*abort_flag != 0`).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     unsigned spins     = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 63u) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
     return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT_CYCLES);
 }
 
 // ---- TMA ----------------------------------------------------------------------------------------

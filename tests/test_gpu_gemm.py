@@ -203,3 +203,21 @@ def test_zero_extents(T):
     cb = T.product_2d(torch.empty((8, 0), device="cuda", dtype=torch.bfloat16),
                       torch.empty((0, 8), device="cuda", dtype=torch.bfloat16))
     assert torch.equal(cb, torch.zeros(8, 8, device="cuda", dtype=torch.bfloat16))
+
+
+def test_mlp_config_c5_full_size_rows(T):
+    # X[8192,4096], W1/W3[4096,14336], W2[14336,4096]: the whole block on the device, two rows against the oracle,
+    # plus linearity in X (the block is positively homogeneous of degree 1 only through the gate, so use additivity
+    # of the second contraction instead: Y is linear in W2)
+    M, K, F, N = 8192, 4096, 14336, 4096
+    x = randn((M, K), 1238, 1.0, torch.bfloat16)
+    w1 = randn((K, F), 1239, 0.02, torch.bfloat16)
+    w3 = randn((K, F), 1240, 0.02, torch.bfloat16)
+    w2 = randn((F, N), 1241, 0.02, torch.bfloat16)
+    y = T.mlp_gated(x, w1, w3, w2)
+    T.device_status()
+    rows = [0, 8191]
+    want = mo.mlp_gated_truth(bits(x[rows]), bits(w1), bits(w3), bits(w2))
+    assert nerr(f64(y[rows]), want) <= TOL_BF16
+    y2 = T.mlp_gated(x, w1, w3, (w2.float() * 2).to(torch.bfloat16))      # doubling W2 is exact in bf16
+    assert torch.equal(y2[rows].float(), (y[rows].float() * 2).to(torch.bfloat16).float())
