@@ -100,6 +100,11 @@ typedef struct mimk_gemm_desc {
     const void* post_full; /* out_dtype [m,n] per batch, or NULL */
 } mimk_gemm_desc;
 int mimk_gemm(const mimk_gemm_desc* desc, void* stream);
+/* The same call with scalar arguments only (batch = 1, no full-shape epilogue operand): emitted code can call it
+ * without building a struct in memory -- an `extern con` with scalar parameters is all the binding needs
+ * (lit/cps/ds_external_cimp.mim:13-20). */
+int mimk_gemm_flat(int64_t m, int64_t n, int64_t k, const void* a, const void* b, void* c, int32_t in_dtype,
+                   int32_t out_dtype, int32_t b_layout, int32_t post, const void* post_row, void* stream);
 
 /* out[o,i] = fold_a g(x[o,a,i]) over the middle axis of a [outer, len, inner] view; inner == 1 is a row reduce.
  * Replaces: tensor.reduce (tensor.mim:1151-1157) lowered by gpu.lower_btensor_map_reduce. dtype F32 (x and out). */

@@ -160,6 +160,16 @@ extern "C" int mimk_gemm(const mimk_gemm_desc* d, void* stream) {
     return gemm_simt(*d, s);
 }
 
+extern "C" int mimk_gemm_flat(int64_t m, int64_t n, int64_t k, const void* a, const void* b, void* c, int32_t in_dtype,
+                              int32_t out_dtype, int32_t b_layout, int32_t post, const void* post_row, void* stream) {
+    mimk_gemm_desc d = {};
+    d.batch = 1, d.m = m, d.n = n, d.k = k;
+    d.a = a, d.b = b, d.c = c;
+    d.in_dtype = in_dtype, d.out_dtype = out_dtype, d.b_layout = b_layout, d.post = post;
+    d.post_row = post_row;
+    return mimk_gemm(&d, stream);
+}
+
 extern "C" int mimk_attn_fwd(const mimk_attn_desc* d, void* stream) {
     if (!d) return MIMK_E_ARG;
     if (d->batch_heads < 0 || d->seq_q < 0 || d->seq_k < 0 || d->head_dim < 0) return MIMK_E_ARG;
