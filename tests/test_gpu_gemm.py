@@ -221,3 +221,14 @@ def test_mlp_config_c5_full_size_rows(T):
     assert nerr(f64(y[rows]), want) <= TOL_BF16
     y2 = T.mlp_gated(x, w1, w3, (w2.float() * 2).to(torch.bfloat16))      # doubling W2 is exact in bf16
     assert torch.equal(y2[rows].float(), (y[rows].float() * 2).to(torch.bfloat16).float())
+
+
+def test_gemm_flat_entry_point(T):
+    # the scalar-argument form emitted code would call: same result as the descriptor form
+    from mimir_b200 import _lib
+    a, b = uniform((40, 24), 1), uniform((24, 56), 2)
+    c = torch.empty((40, 56), device="cuda")
+    st = _lib.lib().mimk_gemm_flat(40, 56, 24, a.data_ptr(), b.data_ptr(), c.data_ptr(), _lib.F32, _lib.F32, _lib.B_KN,
+                                   _lib.POST_ID, None, torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    assert torch.equal(c, T.product_2d(a, b))
