@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--no-extras", action="store_true", help="skip the short runs of the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
+    ap.add_argument("--gather", action="store_true",
+                    help="gemm / attn under torchrun: all-gather every rank's output shard inside the timed step (NCCL)")
     return ap.parse_args()
 
 
@@ -124,6 +126,16 @@ class Workload:
     def __init__(self, torch, T, H, rank, world):
         self.torch, self.T, self.H, self.rank, self.world = torch, T, H, rank, world
 
+    gather = False
+    gathered = None
+
+    def all_gather(self, local):
+        """All-gather the ranks' output shards into one [world, ...] tensor on every rank (NCCL over NVLink)."""
+        import torch.distributed as dist
+        if self.gathered is None:
+            self.gathered = self.torch.empty((self.world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(self.gathered, local)
+
     def gen(self, seed):
         g = self.torch.Generator(device="cuda")
         g.manual_seed(seed + 1000 * self.rank)
@@ -202,6 +214,8 @@ class Gemm(Workload):
         self.c = self.T.product_2d(self.a, self.T.transpose_2d(self.b))
         if ev:
             ev[1].record()
+        if self.gather and self.world > 1:
+            self.all_gather(self.c)
 
     def e2e_setup(self):
         self.ha, self.hb = self.a.cpu().pin_memory(), self.b.cpu().pin_memory()
@@ -243,6 +257,8 @@ class Attn(Workload):
         self.o = self.T.attention(self.q, self.k, self.v, scale=1.0 / self.D ** 0.5, causal=True)
         if ev:
             ev[1].record()
+        if self.gather and self.world > 1:
+            self.all_gather(self.o)
 
     def e2e_setup(self):
         self.hq, self.hk, self.hv = (x.cpu().pin_memory() for x in (self.q, self.k, self.v))
@@ -433,7 +449,10 @@ def run_ours(args):
 
     pk = peaks()
     w = WORKLOADS[args.workload](torch, T, H, rank, world)
+    w.gather = bool(args.gather)
     w.setup()
+    if args.gather:
+        w.config["gather"] = "outputs all-gathered over NCCL inside the step" if world > 1 else "n/a at one GPU"
     # clocks are sampled every 20 ms from the first warm-up step to the end of the timed region: the timed region
     # alone (a few ms) is shorter than one nvidia-smi sampling period
     sampler = ClockSampler(local) if rank == 0 else None
