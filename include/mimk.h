@@ -100,6 +100,22 @@ typedef struct mimk_gemm_desc {
     const void* post_full; /* out_dtype [m,n] per batch, or NULL */
 } mimk_gemm_desc;
 int mimk_gemm(const mimk_gemm_desc* desc, void* stream);
+/* The all-gather of a column-sharded contraction fused into its epilogue. Each GPU computes its column slab
+ * C[:, col_off : col_off + n] and stores every tile directly into `n_dst` copies of the full [m, ldc] matrix -- its own
+ * and its peers' (peer-mapped device pointers, e.g. from CUDA IPC or torch symmetric memory): plain 16-byte stores
+ * over NVLink while the tensor cores work on the next tile, instead of a separate NCCL all-gather afterwards.
+ * `b2` non-NULL selects the gated form, silu(A b) * (A b2) (bf16 out), as in mimk_mlp_gated's first stage.
+ * The caller orders this call before the consumers of the gathered matrix on every GPU (a barrier across ranks after
+ * the kernel has completed). No counterpart in the reference, which has no multi-device support
+ * (src/mim/plug/nvptx/phase/nvptx.cpp:186-204). bf16 inputs only; batch must be 1; no full-shape epilogue operand. */
+#define MIMK_MAX_GATHER 8
+typedef struct mimk_gather_dst {
+    int32_t n_dst;
+    int32_t pad_;
+    void* dst[MIMK_MAX_GATHER];
+    int64_t ldc, col_off; /* in elements */
+} mimk_gather_dst;
+int mimk_gemm_gather(const mimk_gemm_desc* desc, const void* b2, const mimk_gather_dst* dsts, void* stream);
 /* The same call with scalar arguments only (batch = 1, no full-shape epilogue operand): emitted code can call it
  * without building a struct in memory -- an `extern con` with scalar parameters is all the binding needs
  * (lit/cps/ds_external_cimp.mim:13-20). */

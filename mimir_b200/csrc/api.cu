@@ -87,15 +87,15 @@ using namespace mimk;
 namespace mimk {
 // The paired-SM kernel when the problem has enough 256-row tiles, else the one-CTA kernel.
 // MIMK_GEMM_2CTA=0 forces the one-CTA kernel, =2 the paired one whenever it can run (for A/B measurements).
-int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2) {
+int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather) {
     static int allow_pair = -1;
     if (allow_pair < 0) {
         const char* e = getenv("MIMK_GEMM_2CTA");
         allow_pair    = (e && e[0] == '0') ? 0 : ((e && e[0] == '2') ? 2 : 1);
     }
-    if (allow_pair == 2 && gemm_tc_supported(d)) return gemm_tc2(d, s, gated, b2);
-    if (allow_pair && gemm_tc2_supported(d, gated)) return gemm_tc2(d, s, gated, b2);
-    return gemm_tc(d, s, gated, b2);
+    if (allow_pair == 2 && gemm_tc_supported(d)) return gemm_tc2(d, s, gated, b2, gather);
+    if (allow_pair && gemm_tc2_supported(d, gated)) return gemm_tc2(d, s, gated, b2, gather);
+    return gemm_tc(d, s, gated, b2, gather);
 }
 }  // namespace mimk
 
@@ -158,6 +158,25 @@ extern "C" int mimk_gemm(const mimk_gemm_desc* d, void* stream) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (gemm_tc_supported(*d)) return gemm_tc_any(*d, s, 0, nullptr);
     return gemm_simt(*d, s);
+}
+
+extern "C" int mimk_gemm_gather(const mimk_gemm_desc* d, const void* b2, const mimk_gather_dst* g, void* stream) {
+    MIMK_TRY(check_gemm(d));
+    if (!g || g->n_dst < 1 || g->n_dst > MIMK_MAX_GATHER || g->ldc < 0 || g->col_off < 0) return MIMK_E_ARG;
+    if (g->col_off + d->n > g->ldc) return MIMK_E_SHAPE;
+    if (g->ldc % 8 != 0 || g->col_off % 8 != 0) return MIMK_E_ALIGN;  // 16-byte stores into every destination
+    for (int t = 0; t < g->n_dst; ++t)
+        if (!g->dst[t] || !aligned16(g->dst[t])) return MIMK_E_ARG;
+    int st = MIMK_OK;
+    if (!device_info(&st)) return st;
+    if (d->batch != 1 || d->post_full) return MIMK_E_UNSUPPORTED;
+    if (d->m == 0 || d->n == 0) return MIMK_OK;
+    if (!d->a || !d->b) return MIMK_E_ARG;
+    if (b2 && d->out_dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    mimk_gemm_desc dd = *d;
+    dd.c              = g->dst[0];  // only its alignment is looked at; the tiles go to g->dst[*]
+    if (!gemm_tc_supported(dd)) return MIMK_E_UNSUPPORTED;
+    return gemm_tc_any(dd, static_cast<cudaStream_t>(stream), b2 ? 1 : 0, b2, g);
 }
 
 extern "C" int mimk_gemm_flat(int64_t m, int64_t n, int64_t k, const void* a, const void* b, void* c, int32_t in_dtype,

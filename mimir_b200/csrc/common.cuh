@@ -45,10 +45,11 @@ inline size_t dtype_size(int dt) { return dt == MIMK_BF16 ? 2 : (dt == MIMK_I64 
 // kernels implemented in the other translation units
 int gemm_simt(const mimk_gemm_desc& d, cudaStream_t s);
 int gemm_tc_supported(const mimk_gemm_desc& d);
-int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2);
+int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr);
 int gemm_tc2_supported(const mimk_gemm_desc& d, int gated);  // the paired-SM (cta_group::2) form
-int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2);
-int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2);  // picks between the two
+int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr);
+int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
+                const mimk_gather_dst* gather = nullptr);  // picks between the two
 int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_supported(const mimk_attn_desc& d);
 int attn_tc(const mimk_attn_desc& d, cudaStream_t s);

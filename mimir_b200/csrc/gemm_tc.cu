@@ -42,7 +42,12 @@ static_assert(sizeof(Bars) <= 256, "barrier block too large");
 
 struct Params {
     int64_t M, N, K;
-    void* C;
+    // The result tile goes to `n_dst` matrices of leading dimension `ldc`, at column offset `col_off`: one destination
+    // (C itself, ldc = N) for an ordinary call; this GPU's and its peers' copies of a gathered matrix when the all-gather
+    // of a column-sharded contraction is fused into the epilogue (plain stores to peer-mapped addresses over NVLink).
+    void* dst[MIMK_MAX_GATHER];
+    int n_dst;
+    int64_t ldc, col_off;
     const float* post_row;
     const void* post_full;
     int post;
@@ -177,7 +182,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) are this warp's
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        TOut* C = static_cast<TOut*>(p.C);
         const TOut* post_full = static_cast<const TOut*>(p.post_full);
         for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             int64_t tm, tn;
@@ -224,25 +228,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             }
                         }
                     }
-                    TOut* dst = C + row * p.N + col0;
                     if (sizeof(TOut) == 2) {
+                        uint4 q[4];
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
-                            if (col0 + i < p.N) {  // N % 8 == 0: an 8-column group is all in or all out
-                                uint4 q;
-                                q.x = pack_bf16x2(v[i], v[i + 1]);
-                                q.y = pack_bf16x2(v[i + 2], v[i + 3]);
-                                q.z = pack_bf16x2(v[i + 4], v[i + 5]);
-                                q.w = pack_bf16x2(v[i + 6], v[i + 7]);
-                                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst) + i) = q;
-                            }
+                            q[i >> 3].x = pack_bf16x2(v[i], v[i + 1]);
+                            q[i >> 3].y = pack_bf16x2(v[i + 2], v[i + 3]);
+                            q[i >> 3].z = pack_bf16x2(v[i + 4], v[i + 5]);
+                            q[i >> 3].w = pack_bf16x2(v[i + 6], v[i + 7]);
+                        }
+                        for (int t = 0; t < p.n_dst; ++t) {
+                            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.dst[t]) + row * p.ldc + p.col_off + col0;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8)  // N % 8 == 0: an 8-column group is all in or all out
+                                if (col0 + i < p.N) *reinterpret_cast<uint4*>(dst + i) = q[i >> 3];
                         }
                     } else {
+                        for (int t = 0; t < p.n_dst; ++t) {
+                            float* dst = static_cast<float*>(p.dst[t]) + row * p.ldc + p.col_off + col0;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            if (col0 + i < p.N)
-                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + i) =
-                                    make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                            for (int i = 0; i < 32; i += 4)
+                                if (col0 + i < p.N)
+                                    *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                         }
                     }
                 }
@@ -338,7 +345,7 @@ int gemm_tc_supported(const mimk_gemm_desc& d) {
     return 1;
 }
 
-int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2) {
+int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather) {
     int st          = MIMK_OK;
     DeviceInfo* dev = device_info(&st);
     if (!dev) return st;
@@ -360,7 +367,16 @@ int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2) 
         }
         Params p;
         p.M = d.m, p.N = d.n, p.K = d.k;
-        p.C         = static_cast<uint8_t*>(d.c) + size_t(b * d.stride_c) * out_size;
+        if (gather) {
+            if (d.batch != 1) return MIMK_E_UNSUPPORTED;
+            p.n_dst = gather->n_dst;
+            for (int t = 0; t < gather->n_dst; ++t) p.dst[t] = gather->dst[t];
+            p.ldc = gather->ldc, p.col_off = gather->col_off;
+        } else {
+            p.n_dst  = 1;
+            p.dst[0] = static_cast<uint8_t*>(d.c) + size_t(b * d.stride_c) * out_size;
+            p.ldc = d.n, p.col_off = 0;
+        }
         p.post_row  = static_cast<const float*>(d.post_row);
         p.post_full = d.post_full ? static_cast<const uint8_t*>(d.post_full) + size_t(b * d.stride_c) * out_size : nullptr;
         p.post      = d.post;

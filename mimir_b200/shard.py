@@ -87,3 +87,73 @@ def sharded_rows(x, compute: Callable, gather: bool = False):
     lo, hi = split_range(rows, rank, world)
     y_local = compute(x[lo:hi])
     return gather_rows(y_local, rows) if gather else (y_local, (lo, hi))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# All-gather fused into the contraction's epilogue (GPUs of one node, peer memory over NVLink)
+# ---------------------------------------------------------------------------------------------------------------------
+class GatheredMatrix:
+    """A [rows, cols] matrix that every rank holds a full copy of, allocated so that each rank can store into every
+    other rank's copy (torch symmetric memory: peer-mapped device pointers). `local` is this rank's copy."""
+
+    def __init__(self, rows: int, cols: int, dtype=torch.bfloat16, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 destinations (one node)")
+        self.local = symm_mem.empty((rows, cols), dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm_mem.rendezvous(self.local, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.rows, self.cols = rows, cols
+
+    def barrier(self):
+        """Every rank's stores (issued before this call on the current stream) are complete on every rank afterwards."""
+        self.handle.barrier(channel=0, timeout_ms=20000)
+
+
+def gemm_gather(a: torch.Tensor, b: torch.Tensor, out: GatheredMatrix, col_off: int, *, gated_b2: torch.Tensor | None = None):
+    """This rank's column slab of `a . b` (or silu(a . b) * (a . gated_b2)) stored straight into every rank's copy of
+    `out` at columns [col_off, col_off + n): the all-gather happens in the contraction's epilogue.  `b` (and
+    `gated_b2`) may be transpose_2d views of [n, k] tensors.  Call `out.barrier()` before reading `out.local`."""
+    import ctypes as C
+
+    from . import _lib as L
+    from .tensor import _b_layout, _dt, _stream
+    a = a.contiguous()
+    b_store, layout = _b_layout(b)
+    b2_store = None
+    if gated_b2 is not None:
+        b2_store, layout2 = _b_layout(gated_b2)
+        if layout2 != layout:
+            raise ValueError("both right operands must share one storage layout")
+    m, k = a.shape
+    n = b.shape[1]
+    if a.shape[1] != b.shape[0] or m != out.rows or col_off + n > out.cols:
+        raise ValueError("contracting dims don't match")
+    d = L.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, m, n, k
+    d.a, d.b, d.c = a.data_ptr(), b_store.data_ptr(), out.local.data_ptr()
+    d.stride_c = m * n
+    d.in_dtype, d.out_dtype, d.b_layout, d.post = _dt(a), _dt(out.local), layout, L.POST_ID
+    g = L.GatherDst()
+    g.n_dst = out.world
+    for i, ptr in enumerate(out.ptrs):
+        g.dst[i] = ptr
+    g.ldc, g.col_off = out.cols, col_off
+    L.check(L.lib().mimk_gemm_gather(C.byref(d), b2_store.data_ptr() if b2_store is not None else None, C.byref(g),
+                                     _stream()), "gemm_gather")
+
+
+def tp_mlp_gated(x, w1_shard, w3_shard, w2_shard, h: GatheredMatrix):
+    """Tensor-parallel gated MLP: rank g holds columns [g F/G, (g+1) F/G) of W1 and W3 and columns of W2.
+    Stage 1 computes this rank's H slab and scatters it into every rank's H (fused all-gather); after the barrier stage 2
+    multiplies the full H with this rank's W2 columns.  Returns this rank's column slab of Y."""
+    from . import tensor as T
+    rank, world = h.rank, h.world
+    f_local = w1_shard.shape[1]
+    gemm_gather(x, w1_shard, h, rank * f_local, gated_b2=w3_shard)
+    h.barrier()
+    y = T.product_2d(h.local, w2_shard)
+    h.barrier()  # nobody overwrites H (the next call) while a peer still reads it
+    return y

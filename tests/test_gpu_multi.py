@@ -1,0 +1,68 @@
+"""Two-GPU parity of the epilogue-fused all-gather (needs >= 2 CUDA devices; skipped otherwise)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import oracle as mo
+    from mimir_b200 import shard
+    from mimir_b200 import tensor as T
+
+    def bits(t):
+        return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    g = torch.Generator().manual_seed(11)        # the same global tensors on every rank
+    M, K, F, N = 512, 256, 1024, 512
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w1 = (torch.randn(K, F, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    w3 = (torch.randn(K, F, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    w2 = (torch.randn(F, N, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    fl, nl = F // world, N // world
+
+    # plain contraction, column slabs gathered in the epilogue: every rank ends up with the whole product
+    c = shard.GatheredMatrix(M, F)
+    shard.gemm_gather(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), c, rank * fl)
+    c.barrier()
+    want = mo.gemm_truth(bits(x), bits(w1), bf16=True)
+    assert mo.normalised_error(c.local.float().cpu().numpy(), want) <= 2e-2
+    assert torch.equal(c.local, T.product_2d(x, w1))           # same kernel, same bits, whichever rank wrote the slab
+
+    # tensor-parallel gated MLP
+    h = shard.GatheredMatrix(M, F)
+    y = shard.tp_mlp_gated(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), w3[:, rank * fl:(rank + 1) * fl].contiguous(),
+                           w2[:, rank * nl:(rank + 1) * nl].contiguous(), h)
+    T.device_status()
+    wanty = mo.mlp_gated_truth(bits(x), bits(w1), bits(w3), bits(w2))[:, rank * nl:(rank + 1) * nl]
+    assert mo.normalised_error(y.float().cpu().numpy(), wanty) <= 2e-2
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
+
+
+def test_fused_all_gather_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    import __graft_entry__ as entry
+    entry.build()
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
