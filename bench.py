@@ -35,7 +35,9 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="rows", choices=["rows", "gemm", "attn", "mlp", "matmul_f32"])
+    ap.add_argument("--workload", default="rows", choices=["rows", "gemm", "attn", "mlp", "mlp_tp", "matmul_f32"])
+    ap.add_argument("--tp-gather", default="fused", choices=["fused", "nccl"],
+                    help="mlp_tp: all-gather of H fused into the GEMM epilogue (peer stores) or a separate NCCL all-gather")
     ap.add_argument("--no-extras", action="store_true", help="skip the short runs of the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
@@ -325,6 +327,67 @@ class Mlp(Workload):
         return 6 * rows * 4096 * 14336 / dt / 1e12, f"{rows} of 8192 rows through the full block", float(y[0, 0])
 
 
+class MlpTP(Workload):
+    """The C5 block split over the ranks (tensor parallel, STRONG scaling): rank g owns columns [g F/G, (g+1) F/G) of W1
+    and W3 and columns [g N/G, (g+1) N/G) of W2; H is all-gathered between the two stages."""
+    name, metric, unit, dtype, bound = "MLP block bf16 X[8192,4096] W1/W3[4096,14336] W2[14336,4096], tensor parallel", "TFLOP/s (gated MLP block, tensor parallel)", "TFLOP/s", "bf16", "tensor"
+    kernel, launches_per_step = "gemm_tc2_kernel<gated> (+ fused all-gather) + gemm_tc2_kernel", 2
+    scaling = "strong"
+    M, K, F = 8192, 4096, 14336
+    mode = "fused"
+
+    def setup(self):
+        t = self.torch
+        from mimir_b200 import shard
+        self.shard = shard
+        g = t.Generator(device="cuda")
+        g.manual_seed(1238)                       # the same global weights on every rank; each keeps its slab
+        W = self.world
+        self.fl, self.nl = self.F // W, self.K // W
+        self.x = t.randn((self.M, self.K), generator=g, device="cuda").to(t.bfloat16)
+        w1 = (t.randn((self.K, self.F), generator=g, device="cuda") * 0.02).to(t.bfloat16)
+        self.w1 = w1[:, self.rank * self.fl:(self.rank + 1) * self.fl].contiguous()
+        w1 = (t.randn((self.K, self.F), generator=g, device="cuda") * 0.02).to(t.bfloat16)
+        self.w3 = w1[:, self.rank * self.fl:(self.rank + 1) * self.fl].contiguous()
+        w1 = (t.randn((self.F, self.K), generator=g, device="cuda") * 0.02).to(t.bfloat16)
+        self.w2 = w1[:, self.rank * self.nl:(self.rank + 1) * self.nl].contiguous()
+        del w1
+        t.cuda.empty_cache()
+        if W > 1 and self.mode == "fused":
+            self.h = shard.GatheredMatrix(self.M, self.F)
+        else:
+            self.h_local = t.empty((self.M, self.fl), device="cuda", dtype=t.bfloat16)
+        self.units = 3 * 2 * self.M * self.K * self.F // W     # per-rank share: the driver multiplies by world
+        self.dom_units = self.units
+        self.config = {"workload": self.name, "l2": "weights larger than L2", "tp_gather": self.mode if W > 1 else "n/a",
+                       "sharding": "W1/W3 column slabs, H all-gathered, W2 column slabs (outputs stay sharded)"}
+
+    def step(self, ev=None):
+        if ev:
+            ev[0].record()
+        if self.world == 1:
+            self.y = self.T.mlp_gated(self.x, self.w1, self.w3, self.w2, h=self.h_local)
+        elif self.mode == "fused":
+            self.y = self.shard.tp_mlp_gated(self.x, self.w1, self.w3, self.w2, self.h)
+        else:
+            # stage 1 into a local slab (gated contraction with the W2-free path: H slab only), NCCL all-gather, stage 2
+            self.shard.gemm_gather_local(self.x, self.w1, self.w3, self.h_local)
+            h_full = self.shard.gather_columns(self.h_local, self.F)
+            self.y = self.T.product_2d(h_full, self.w2)
+        if ev:
+            ev[1].record()
+
+    def e2e_setup(self):
+        self.h2d = self.d2h = 0
+
+    def e2e_step(self):
+        return 0.0
+
+    @staticmethod
+    def cpu_sample(mo, np, rows=2):
+        return Mlp.cpu_sample(mo, np, rows)
+
+
 class MatmulF32(Workload):
     name, metric, unit, dtype, bound = "matmul f32 256^3", "TFLOP/s (f32 matmul 256^3)", "TFLOP/s", "f32", "tensor"
     kernel = "gemm_simt_kernel"
@@ -367,7 +430,7 @@ class MatmulF32(Workload):
         return 2 * 256 ** 3 / dt / 1e12, "full 256^3, mean of 20 passes", float(c[0, 0])
 
 
-WORKLOADS = {"rows": Rows, "gemm": Gemm, "attn": Attn, "mlp": Mlp, "matmul_f32": MatmulF32}
+WORKLOADS = {"rows": Rows, "gemm": Gemm, "attn": Attn, "mlp": Mlp, "mlp_tp": MlpTP, "matmul_f32": MatmulF32}
 
 
 # ------------------------------------------------------------------------------------------------ arms
@@ -450,6 +513,9 @@ def run_ours(args):
     pk = peaks()
     w = WORKLOADS[args.workload](torch, T, H, rank, world)
     w.gather = bool(args.gather)
+    if args.workload == "mlp_tp":
+        w.mode = args.tp_gather
+        args.no_e2e = True     # the tensor-parallel block has no single-host-buffer form
     w.setup()
     if args.gather:
         w.config["gather"] = "outputs all-gathered over NCCL inside the step" if world > 1 else "n/a at one GPU"
@@ -499,7 +565,7 @@ def run_ours(args):
                "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3, "sink": sink}
 
     line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": getattr(w, "scaling", "weak"), "vs_baseline": None, "dtype": w.dtype,
             "data": "synthetic", "config": w.config, "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": K * w.launches_per_step,
@@ -519,7 +585,7 @@ def run_ours(args):
     if world == 1 and not args.no_extras:
         extras = {}
         for name, cls in WORKLOADS.items():
-            if name == args.workload or name == "matmul_f32":
+            if name == args.workload or name in ("matmul_f32", "mlp_tp"):
                 continue
             w = None
             torch.cuda.empty_cache()

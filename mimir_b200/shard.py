@@ -157,3 +157,25 @@ def tp_mlp_gated(x, w1_shard, w3_shard, w2_shard, h: GatheredMatrix):
     y = T.product_2d(h.local, w2_shard)
     h.barrier()  # nobody overwrites H (the next call) while a peer still reads it
     return y
+
+
+def gemm_gather_local(x, w1_shard, w3_shard, h_local):
+    """Stage 1 of the tensor-parallel MLP into a LOCAL slab (for the variant that all-gathers with NCCL afterwards)."""
+    import ctypes as C
+
+    from . import _lib as L
+    from .tensor import _b_layout, _dt, _stream
+    b_store, layout = _b_layout(w1_shard)
+    b2_store, _ = _b_layout(w3_shard)
+    m, k = x.shape
+    n = w1_shard.shape[1]
+    d = L.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, m, n, k
+    d.a, d.b, d.c = x.data_ptr(), b_store.data_ptr(), h_local.data_ptr()
+    d.stride_c = m * n
+    d.in_dtype, d.out_dtype, d.b_layout, d.post = _dt(x), _dt(h_local), layout, L.POST_ID
+    g = L.GatherDst()
+    g.n_dst = 1
+    g.dst[0] = h_local.data_ptr()
+    g.ldc, g.col_off = n, 0
+    L.check(L.lib().mimk_gemm_gather(C.byref(d), b2_store.data_ptr(), C.byref(g), _stream()), "gemm_gather_local")
