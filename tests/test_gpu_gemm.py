@@ -232,3 +232,36 @@ def test_gemm_flat_entry_point(T):
                                    _lib.POST_ID, None, torch.cuda.current_stream().cuda_stream)
     assert st == 0
     assert torch.equal(c, T.product_2d(a, b))
+
+
+@pytest.mark.parametrize("nk", [True, False])
+def test_paired_sm_kernel_shapes(T, nk):
+    # enough 256-row tiles (>= 74) for the cta_group::2 kernel: ragged M / N / K, both B layouts, f32 store, epilogue
+    M, N, K = 4000, 4104, 520
+    a = randn((M, K), 7, 0.5, torch.bfloat16)
+    b = randn((N, K) if nk else (K, N), 8, 0.5, torch.bfloat16)
+    bias = uniform((N,), 9)
+    c = T.product_2d(a, T.transpose_2d(b) if nk else b, post="bias_relu", bias=bias, out_dtype=torch.float32)
+    T.device_status()
+    rows = [0, 127, 128, 255, 256, 2049, 3999]
+    acc = mo.gemm_truth(bits(a), bits(b), b_nk=nk, bf16=True, rows=rows)
+    want = np.maximum(acc + bias.cpu().numpy().astype(np.float64), 0)
+    assert nerr(f64(c[rows]), want) <= 1e-4
+    # column sums of the un-fused product agree with a . (B 1) -- every tile contributes
+    c0 = T.product_2d(a, T.transpose_2d(b) if nk else b, out_dtype=torch.float32)
+    ones = torch.ones(N, dtype=torch.float64, device="cuda")
+    bsum = (b.double().sum(dim=0) if nk else b.double().sum(dim=1))
+    lhs, rhs = c0.double() @ ones, a.double() @ bsum
+    assert (lhs - rhs).abs().max() / rhs.abs().max() < 1e-3
+
+
+def test_paired_sm_gated_mlp(T):
+    M, K, F, N = 2048, 256, 4096, 512
+    x = randn((M, K), 1, 1.0, torch.bfloat16)
+    w1, w3 = randn((K, F), 2, 0.05, torch.bfloat16), randn((K, F), 3, 0.05, torch.bfloat16)
+    w2 = randn((F, N), 4, 0.05, torch.bfloat16)
+    y = T.mlp_gated(x, w1, w3, w2)
+    T.device_status()
+    rows = [0, 129, 2047]
+    want = mo.mlp_gated_truth(bits(x[rows]), bits(w1), bits(w3), bits(w2))
+    assert nerr(f64(y[rows]), want) <= TOL_BF16
