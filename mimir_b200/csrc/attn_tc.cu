@@ -386,9 +386,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                        p.scale_log2;  // scale > 0: max commutes with it
             if (j == 0) {
                 m_used = mx;
-            } else if (mx > m_used + RESCALE_THRESHOLD) {
-                // the previous O_t += P_t V has completed: its commit precedes the one that released S_t
-                const float alpha = fast_exp2(m_used - mx);
+            } else if (__any_sync(0xffffffffu, mx > m_used + RESCALE_THRESHOLD)) {
+                // tcgen05.ld / tcgen05.st are warp-wide instructions: when ANY row of the warp needs its O rescaled the
+                // whole warp takes this path, rows that do not need it with alpha = 1.
+                // The previous O_t += P_t V has completed: its commit precedes the one that released S_t.
+                const float m_new = (mx > m_used + RESCALE_THRESHOLD) ? mx : m_used;
+                const float alpha = fast_exp2(m_used - m_new);
 #pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
                     uint32_t o[32];
@@ -399,7 +402,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     tmem_st_32x32_x32(tO + c, o);
                 }
                 l *= alpha;
-                m_used = mx;
+                m_used = m_new;
             }
             // p = exp2(s * scale - m), row sum, P as bf16 over the first 64 columns of S_t
             if (row_in_tile == 0) MIMK_TR(t, j, 3);

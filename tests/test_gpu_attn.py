@@ -61,3 +61,41 @@ def test_attention_config_c4_heads(T):
     assert nerr(f64(o.reshape(128, 4096, 128)[heads]), want) <= TOL_BF16
     # first query row attends to one key only: O[0] = V[0] exactly
     assert torch.equal(o[..., 0, :], v[..., 0, :])
+
+
+def test_attention_bf16_rectangular_and_lse(T):
+    # tensor-core kernel: more keys than queries (no mask), and the log-sum-exp output
+    q = randn((2, 200, 128), 31, 1.0, torch.bfloat16)
+    k = randn((2, 520, 128), 32, 1.0, torch.bfloat16)
+    v = randn((2, 520, 128), 33, 1.0, torch.bfloat16)
+    scale = 0.07
+    o, lse = T.attention(q, k, v, scale=scale, causal=False, return_lse=True)
+    T.device_status()
+    s = np.einsum("hid,hjd->hij", f64(q), f64(k)) * scale
+    p = np.exp(s - s.max(-1, keepdims=True))
+    want = (p / p.sum(-1, keepdims=True)) @ f64(v)
+    assert nerr(f64(o), want) <= TOL_BF16
+    want_lse = np.log(p.sum(-1)) + s.max(-1)
+    assert np.abs(lse.cpu().numpy() - want_lse).max() < 2e-3
+    # causal, square, lse
+    q2, k2, v2 = (randn((1, 384, 128), 40 + i, 1.0, torch.bfloat16) for i in range(3))
+    o2, lse2 = T.attention(q2, k2, v2, scale=scale, causal=True, return_lse=True)
+    s2 = np.einsum("hid,hjd->hij", f64(q2), f64(k2)) * scale
+    s2 = np.where(np.tril(np.ones((384, 384), bool)), s2, -np.inf)
+    want2 = np.log(np.exp(s2 - s2.max(-1, keepdims=True)).sum(-1)) + s2.max(-1)
+    assert np.abs(lse2.cpu().numpy() - want2).max() < 2e-3
+
+
+def test_attention_large_score_range(T):
+    # scores spanning hundreds of log2 units exercise the lazy rescale of O (the running max jumps by far more than 2^8)
+    g = torch.Generator().manual_seed(5)
+    q = (torch.randn(1, 512, 128, generator=g) * 4).to(torch.bfloat16).cuda()
+    k = (torch.randn(1, 512, 128, generator=g) * 4).to(torch.bfloat16).cuda()
+    k[:, 300:, :] *= 3          # later keys score much higher: the maximum grows tile after tile
+    v = torch.randn(1, 512, 128, generator=g).to(torch.bfloat16).cuda()
+    for causal in (False, True):
+        o = T.attention(q, k, v, scale=0.25, causal=causal)
+        T.device_status()
+        want = mo.attention(bits(q), bits(k), bits(v), scale=0.25, causal=causal, bf16=True)
+        assert torch.isfinite(o.float()).all()
+        assert nerr(f64(o), want) <= TOL_BF16
