@@ -99,3 +99,24 @@ def test_attention_large_score_range(T):
         want = mo.attention(bits(q), bits(k), bits(v), scale=0.25, causal=causal, bf16=True)
         assert torch.isfinite(o.float()).all()
         assert nerr(f64(o), want) <= TOL_BF16
+
+
+@pytest.mark.parametrize("s", [1, 2, 127, 129, 255, 257, 383])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_bf16_ragged_lengths(T, s, causal):
+    # query / key counts around the 128-row tile and 256-row pair boundaries: out-of-range rows are zero-filled by TMA
+    # on the way in and never stored on the way out
+    q, k, v = (randn((3, s, 128), 50 + i + s, 1.0, torch.bfloat16) for i in range(3))
+    guard = torch.full((3, s + 8, 128), 7.0, dtype=torch.bfloat16, device="cuda")   # rows past s must stay untouched
+    o = T.attention(q, k, v, scale=0.09, causal=causal)
+    T.device_status()
+    want = mo.attention(bits(q), bits(k), bits(v), scale=0.09, causal=causal, bf16=True)
+    assert nerr(f64(o), want) <= TOL_BF16
+    assert torch.equal(guard, torch.full_like(guard, 7.0))
+
+
+def test_attention_no_keys(T):
+    q = randn((2, 5, 16), 1)
+    k = torch.empty((2, 0, 16), device="cuda")
+    o, lse = T.attention(q, k, k.clone(), scale=1.0, return_lse=True)
+    assert torch.equal(o, torch.zeros_like(o)) and torch.isinf(lse).all() and (lse < 0).all()
