@@ -515,9 +515,13 @@ int attn_tc(const mimk_attn_desc& d, cudaStream_t s) {
         const char* e = getenv("MIMK_ATTN_EMU");
         emu           = e ? atoi(e) : 0;
         if (emu < 0 || emu > 2) emu = 0;
+    }
+    static bool configured[64] = {};  // the shared-memory opt-in is a per-device setting
+    if (!configured[dev->device & 63]) {
         MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[dev->device & 63] = true;
     }
     Params p;
     p.Sq = d.seq_q, p.Sk = d.seq_k, p.BH = d.batch_heads;

@@ -293,10 +293,12 @@ template <int BN, bool B_MN, bool GATED, class TOut>
 int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int sm_count,
            cudaStream_t s) {
     auto kern = gemm_tc_kernel<BN, B_MN, GATED, TOut>;
-    static bool configured = false;  // per template instance
-    if (!configured) {
+    static bool configured[64] = {};  // per template instance and device: the attribute is a per-device setting
+    int dev = 0;
+    MIMK_CUDA_TRY(cudaGetDevice(&dev));
+    if (!configured[dev & 63]) {
         MIMK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured = true;
+        configured[dev & 63] = true;
     }
     const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     const int grid      = int(tiles < sm_count ? tiles : sm_count);
