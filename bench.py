@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload rows|gemm|attn|mlp|matmul_f32]
     python bench.py --impl reference ...      # the CPU restatement of the reference's lowering, host cores
 
-Workloads are BASELINE.json's configs with seeded synthetic inputs of the stated shapes and distributions:
+Workloads (seeded synthetic inputs of the stated shapes and distributions):
   rows        X[16384,8192] f32 -> bf16, one step = row softmax + row RMSNorm (two kernels)       HBM GB/s
   gemm        bf16 8192^3, A row-major, B stored [N,K], f32 accumulation, bf16 C                   TFLOP/s
   attn        causal attention forward, batch*heads = 128, seq 4096, head_dim 128, bf16            TFLOP/s
