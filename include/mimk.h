@@ -10,6 +10,9 @@
  *     the call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the default stream);
  *   - every call returns an int status (0 = ok) instead of aborting, so emitted code can pipe it to
  *     `mim_cu_check(int)` (src/mim/plug/nvptx/rt/mim_cuda_rt.c:16-21) exactly like a CUresult;
+ *   - entry points that need scratch beyond their arguments (f32 contractions on the tensor cores, split-axis
+ *     reductions, mimk_mlp_gated without `h`) share one cached per-device buffer: do not run two of them concurrently on
+ *     different streams;
  *   - nothing here falls back to the CPU: without a usable sm_100 device every compute call fails with
  *     MIMK_E_NO_DEVICE.
  */
@@ -87,7 +90,9 @@ enum {
  * Replaces: tensor.product_2d / tensor.bmm / 2-D tensor.dot_product lowered through dot_product_impl
  * (src/mim/plug/tensor/tensor.mim:404-407, 480-486, 510-513, 1367-1423) and the kernel that
  * gpu::phase::LowerMapReduce::build_kernel generates for them (src/mim/plug/gpu/phase/lower_map_reduce.cpp:148-265).
- * in_dtype F32: f32 accumulation in ascending k per cell. in_dtype BF16: f32 accumulation on the tensor cores.
+ * in_dtype F32: f32-grade results -- small or oddly shaped problems fold each cell in ascending k on the CUDA cores,
+ * larger ones run on the tensor cores as three TF32 products per term (head/tail split, about 21 mantissa bits per
+ * product, f32 accumulation). in_dtype BF16: f32 accumulation on the tensor cores.
  * out_dtype F32 or BF16 (round to nearest even). batch strides are in elements; 0 re-uses the operand. */
 typedef struct mimk_gemm_desc {
     int64_t batch, m, n, k;

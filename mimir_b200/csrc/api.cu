@@ -157,6 +157,12 @@ extern "C" int mimk_gemm(const mimk_gemm_desc* d, void* stream) {
     if (!d->c || (d->k > 0 && (!d->a || !d->b))) return MIMK_E_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (gemm_tc_supported(*d)) return gemm_tc_any(*d, s, 0, nullptr);
+    static int f32_tc = -1;  // MIMK_F32_TC=0 keeps f32 contractions on the CUDA cores (for A/B measurements)
+    if (f32_tc < 0) {
+        const char* e = getenv("MIMK_F32_TC");
+        f32_tc        = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (f32_tc && gemm_f32_tc_supported(*d)) return gemm_f32_tc(*d, s);
     return gemm_simt(*d, s);
 }
 

@@ -50,6 +50,8 @@ int gemm_tc2_supported(const mimk_gemm_desc& d, int gated);  // the paired-SM (c
 int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr);
 int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
                 const mimk_gather_dst* gather = nullptr);  // picks between the two
+int gemm_f32_tc_supported(const mimk_gemm_desc& d);  // f32 operands on the tensor cores (3xTF32)
+int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s);
 int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_supported(const mimk_attn_desc& d);
 int attn_tc(const mimk_attn_desc& d, cudaStream_t s);

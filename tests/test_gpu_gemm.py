@@ -265,3 +265,16 @@ def test_paired_sm_gated_mlp(T):
     rows = [0, 129, 2047]
     want = mo.mlp_gated_truth(bits(x[rows]), bits(w1), bits(w3), bits(w2))
     assert nerr(f64(y[rows]), want) <= TOL_BF16
+
+
+@pytest.mark.parametrize("M,N,K,nk", [(512, 512, 8192, True), (384, 640, 4100, False), (1024, 1024, 1024, False)])
+def test_f32_on_tensor_cores_keeps_f32_accuracy(T, M, N, K, nk):
+    # large f32 contractions run as three TF32 products per term with K cut into chunks summed in f32: the error must
+    # stay at the f32 path's tolerance for any K (an unchunked accumulation drifts past 1e-5 around K = 1024)
+    a = uniform((M, K), 70 + K)
+    b = uniform((N, K) if nk else (K, N), 71 + K)
+    c = T.product_2d(a, T.transpose_2d(b) if nk else b, post="bias", bias=uniform((N,), 3))
+    T.device_status()
+    rows = [0, 127, 128, M - 1]
+    want = mo.gemm_truth(a.cpu().numpy(), b.cpu().numpy(), b_nk=nk, rows=rows) + uniform((N,), 3).cpu().numpy().astype(np.float64)
+    assert nerr(f64(c[rows]), want) <= TOL_F32
