@@ -390,7 +390,8 @@ class MlpTP(Workload):
 
 class MatmulF32(Workload):
     name, metric, unit, dtype, bound = "matmul f32 256^3", "TFLOP/s (f32 matmul 256^3)", "TFLOP/s", "f32", "tensor"
-    kernel = "gemm_simt_kernel"
+    kernel = "split_kernel x2 + gemm_f32_tc_kernel (3xTF32)"
+    launches_per_step = 3
 
     def setup(self):
         t = self.torch
