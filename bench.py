@@ -36,7 +36,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="rows", choices=["rows", "gemm", "attn", "mlp", "mlp_tp", "matmul_f32"])
-    ap.add_argument("--tp-gather", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--tp-gather", default="auto", choices=["auto", "fused", "nccl"],
                     help="mlp_tp: all-gather of H fused into the GEMM epilogue (peer stores) or a separate NCCL all-gather")
     ap.add_argument("--no-extras", action="store_true", help="skip the short runs of the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -353,6 +353,8 @@ class MlpTP(Workload):
         self.w2 = w1[:, self.rank * self.nl:(self.rank + 1) * self.nl].contiguous()
         del w1
         t.cuda.empty_cache()
+        if self.mode == "auto":
+            self.mode = "fused" if W == 2 else "nccl"
         if W > 1 and self.mode == "fused":
             self.h = shard.GatheredMatrix(self.M, self.F)
         else:
@@ -368,7 +370,7 @@ class MlpTP(Workload):
         if self.world == 1:
             self.y = self.T.mlp_gated(self.x, self.w1, self.w3, self.w2, h=self.h_local)
         elif self.mode == "fused":
-            self.y = self.shard.tp_mlp_gated(self.x, self.w1, self.w3, self.w2, self.h)
+            self.y = self.shard.tp_mlp_gated(self.x, self.w1, self.w3, self.w2, self.h, gather="fused")
         else:
             # stage 1 into a local slab (gated contraction with the W2-free path: H slab only), NCCL all-gather, stage 2
             self.shard.gemm_gather_local(self.x, self.w1, self.w3, self.h_local)
