@@ -322,6 +322,20 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
     return r == CUDA_SUCCESS ? MIMK_OK : MIMK_E_CUDA;
 }
 
+int make_tmap_2d(CUtensorMap* out, bool f32, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                 uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MIMK_E_CUDA;
+    cuuint64_t dims[2]    = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2]     = {box_inner, box_outer};
+    cuuint32_t estr[2]    = {1, 1};
+    CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MIMK_OK : MIMK_E_CUDA;
+}
+
 int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t mid, uint64_t outer,
                       uint64_t mid_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_mid) {
     EncodeTiledFn fn = encode_fn();

@@ -40,7 +40,13 @@ struct Bars {
     uint32_t tmem_base;
     int abort_flag;
 };
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int OUT_STAGE_BYTES = 4 * 2 * 4096;  // per epilogue warp: two buffers of 32 rows x 128 bytes for the bulk stores
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 1024 + 256;
+
+// One tensor map per destination matrix (this GPU's C, or every rank's copy of a gathered matrix).
+struct OutMaps {
+    CUtensorMap m[MIMK_MAX_GATHER];
+};
 static_assert(sizeof(Bars) <= 256, "barrier block too large");
 
 struct Params {
@@ -108,6 +114,18 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
         : "memory");
 }
 
+// Bulk (TMA) store of a [32 rows x 128 bytes] shared-memory tile to a destination matrix; rows / columns beyond the
+// matrix are clipped by the tensor map. x (in elements) times the element size is a multiple of 128 bytes here.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// at most one earlier group may still be READING its shared-memory source
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t& tm, int64_t& tn) {
     const int64_t per_group = GROUP_M * tiles_n;
     const int64_t group     = tile / per_group;
@@ -122,14 +140,14 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
 template <int BN, bool B_MN, bool GATED, class TOut>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ CUtensorMap tmB2, const Params p) {
+                const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ OutMaps om, const Params p) {
     constexpr int BH = BN / 2;                 // B rows staged by this CTA, per operand
     constexpr int BH_BYTES = BH * BK * 2;
     static_assert((GATED ? 2 : 1) * BH_BYTES == B_BYTES, "stage layout assumes 16 KiB of B per CTA");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr  = smem_u32(smem_raw);
     const uint32_t tile_base = (raw_addr + 1023u) & ~1023u;
-    Bars* bars               = reinterpret_cast<Bars*>(smem_raw + (tile_base - raw_addr) + STAGES * STAGE_BYTES);
+    Bars* bars = reinterpret_cast<Bars*>(smem_raw + (tile_base - raw_addr) + STAGES * STAGE_BYTES + OUT_STAGE_BYTES);
     volatile int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -240,51 +258,60 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else {
         // ---------------- epilogue (warps 2..5, both CTAs) ----------------
+        // Each warp owns 32 rows of the CTA's 128: accumulator -> registers (tcgen05.ld, one row per thread) -> `post`
+        // -> a 128-byte-swizzled [32 x 128 B] tile in shared memory -> one bulk store per destination. Two tiles per warp
+        // alternate, so the stores of one chunk drain while the next chunk is converted. No CTA-wide barrier is involved.
         const int quarter = warp & 3;
-        uint32_t acc = 0, acc_phase = 0;
+        constexpr int CW = 128 / int(sizeof(TOut));  // output columns per 128-byte store row: 64 bf16 or 32 f32
+        const uint32_t out_base = tile_base + STAGES * STAGE_BYTES + quarter * 2 * 4096;
+        uint32_t acc = 0, acc_phase = 0, chunk_no = 0;
         bool ok = true;
         const TOut* post_full = static_cast<const TOut*>(p.post_full);
         for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
             int64_t tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
-            const int64_t row = tm * 2 * BM + int64_t(rank) * BM + quarter * 32 + lane;
-            const int64_t n0  = tn * BN;
+            const int64_t row0 = tm * 2 * BM + int64_t(rank) * BM + quarter * 32;
+            const int64_t row  = row0 + lane;
+            const int64_t n0   = tn * BN;
             if (!(ok = mbar_wait(smem_u32(&bars->acc_full[acc]), acc_phase, abort_flag))) break;
             tc_fence_after();
             const uint32_t t0 = tmem_base + acc * ACC_COLS + (uint32_t(quarter * 32) << 16);
             const uint32_t acc_empty_even = map_to_cta(smem_u32(&bars->acc_empty[acc]), 0);
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32];
-                float v[32];
-                // gated accumulator columns: [gate | up] of the even CTA's B rows, then [gate | up] of the odd CTA's
-                const int gc = GATED ? (c / BH) * 2 * BH + (c % BH) : c;
-                tmem_ld_32x32(t0 + gc, r);
-                if (GATED) {
-                    uint32_t u[32];
-                    tmem_ld_32x32(t0 + gc + BH, u);
-                    tmem_ld_wait();
+            for (int c0 = 0; c0 < BN; c0 += CW, ++chunk_no) {
+                const uint32_t buf = out_base + (chunk_no & 1u) * 4096;
+                if (lane == 0) bulk_wait_read_1();  // the store that last used this buffer has read it
+                __syncwarp();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float g = __uint_as_float(r[i]);
-                        v[i]          = (g / (1.f + __expf(-g))) * __uint_as_float(u[i]);
-                    }
-                } else {
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                }
-                if (c + 32 >= BN) {
-                    // last read of this accumulator buffer: hand it back to the issuer in the even CTA
-                    tc_fence_before();
-                    mbar_arrive_cluster(acc_empty_even);
-                }
-                if (row < p.M) {
-                    const int64_t col0 = n0 + c;
-                    if (p.post != MIMK_POST_ID) {
+                for (int c = c0; c < c0 + CW; c += 32) {
+                    uint32_t r[32];
+                    float v[32];
+                    // gated accumulator columns: [gate | up] of the even CTA's B rows, then [gate | up] of the odd CTA's
+                    const int gc = GATED ? (c / BH) * 2 * BH + (c % BH) : c;
+                    tmem_ld_32x32(t0 + gc, r);
+                    if (GATED) {
+                        uint32_t u[32];
+                        tmem_ld_32x32(t0 + gc + BH, u);
+                        tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const int64_t col = col0 + i;
+                            const float g = __uint_as_float(r[i]);
+                            v[i]          = (g / (1.f + __expf(-g))) * __uint_as_float(u[i]);
+                        }
+                    } else {
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    }
+                    if (c + 32 >= BN) {
+                        // last read of this accumulator buffer: hand it back to the issuer in the even CTA
+                        tc_fence_before();
+                        mbar_arrive_cluster(acc_empty_even);
+                    }
+                    if (p.post != MIMK_POST_ID && row < p.M) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int64_t col = n0 + c + i;
                             if (col < p.N) {
                                 const float rowv = p.post_row ? __ldg(p.post_row + col) : 0.f;
                                 const float full = post_full ? float(post_full[row * p.N + col]) : 0.f;
@@ -292,30 +319,35 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             }
                         }
                     }
+                    // this thread's row of the tile: 16-byte pieces at (piece ^ (row & 7)), the 128-byte swizzle
+                    const uint32_t row_addr = buf + lane * 128;
                     if (sizeof(TOut) == 2) {
-                        uint4 q[4];
+                        const int piece0 = ((c - c0) * 2) >> 4;  // 32 bf16 = 4 pieces
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
-                            q[i >> 3].x = pack_bf16x2(v[i], v[i + 1]);
-                            q[i >> 3].y = pack_bf16x2(v[i + 2], v[i + 3]);
-                            q[i >> 3].z = pack_bf16x2(v[i + 4], v[i + 5]);
-                            q[i >> 3].w = pack_bf16x2(v[i + 6], v[i + 7]);
-                        }
-                        for (int t = 0; t < p.n_dst; ++t) {
-                            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.dst[t]) + row * p.ldc + p.col_off + col0;
-#pragma unroll
-                            for (int i = 0; i < 32; i += 8)  // N % 8 == 0: an 8-column group is all in or all out
-                                if (col0 + i < p.N) *reinterpret_cast<uint4*>(dst + i) = q[i >> 3];
+                            const uint32_t a = row_addr + ((uint32_t(piece0 + (i >> 3)) ^ uint32_t(lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pack_bf16x2(v[i], v[i + 1])),
+                                         "r"(pack_bf16x2(v[i + 2], v[i + 3])), "r"(pack_bf16x2(v[i + 4], v[i + 5])),
+                                         "r"(pack_bf16x2(v[i + 6], v[i + 7]))
+                                         : "memory");
                         }
                     } else {
-                        for (int t = 0; t < p.n_dst; ++t) {
-                            float* dst = static_cast<float*>(p.dst[t]) + row * p.ldc + p.col_off + col0;
 #pragma unroll
-                            for (int i = 0; i < 32; i += 4)
-                                if (col0 + i < p.N)
-                                    *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        for (int i = 0; i < 32; i += 4) {
+                            const uint32_t a = row_addr + ((uint32_t(i >> 2) ^ uint32_t(lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(__float_as_uint(v[i])),
+                                         "r"(__float_as_uint(v[i + 1])), "r"(__float_as_uint(v[i + 2])),
+                                         "r"(__float_as_uint(v[i + 3]))
+                                         : "memory");
                         }
                     }
+                }
+                fence_proxy_async_smem();  // the bulk store reads shared memory through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    if (row0 < p.M && n0 + c0 < p.N)
+                        for (int t = 0; t < p.n_dst; ++t) tma_store_2d(&om.m[t], buf, int(n0 + c0), int(row0));
+                    bulk_commit();
                 }
             }
             if (++acc == 2) {
@@ -323,6 +355,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 acc_phase ^= 1u;
             }
         }
+        if (lane == 0) bulk_wait_all();  // every store has landed before the CTA may exit
     }
 
     // ---------------- teardown ----------------
@@ -339,8 +372,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 template <int BN, bool B_MN, bool GATED, class TOut>
-int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int sm_count,
-           cudaStream_t s) {
+int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const OutMaps& om, const Params& p,
+           int sm_count, cudaStream_t s) {
     auto kern = gemm_tc2_kernel<BN, B_MN, GATED, TOut>;
     static bool configured[64] = {};  // per template instance and device: the attribute is a per-device setting
     int dev = 0;
@@ -352,7 +385,7 @@ int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2,
     const int64_t tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
     const int64_t pairs = sm_count / 2;
     const int grid      = int(2 * (tiles < pairs ? tiles : pairs));
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tA, tB, tB2, p);
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tA, tB, tB2, om, p);
     return launch_status();
 }
 
@@ -402,17 +435,25 @@ int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
         p.post_full = d.post_full ? static_cast<const uint8_t*>(d.post_full) + size_t(b * d.stride_c) * out_size : nullptr;
         p.post      = d.post;
         p.status    = dev->status_dev;
+        // destination maps: [M, N] windows (row pitch ldc) starting at column col_off, boxes of 32 rows x 128 bytes
+        OutMaps om;
+        for (int t = 0; t < p.n_dst; ++t) {
+            const uint8_t* base = static_cast<const uint8_t*>(p.dst[t]) + size_t(p.col_off) * out_size;
+            MIMK_TRY(make_tmap_2d(&om.m[t], d.out_dtype == MIMK_F32, base, uint64_t(d.n), uint64_t(d.m),
+                                  uint64_t(p.ldc) * out_size, uint32_t(128 / out_size), 32));
+        }
+        for (int t = p.n_dst; t < MIMK_MAX_GATHER; ++t) om.m[t] = om.m[0];
         int rc;
         if (gated) {
             if (d.out_dtype != MIMK_BF16) return MIMK_E_DTYPE;
-            rc = b_mn ? launch<128, true, true, __nv_bfloat16>(tA, tB, tB2, p, dev->sm_count, s)
-                      : launch<128, false, true, __nv_bfloat16>(tA, tB, tB2, p, dev->sm_count, s);
+            rc = b_mn ? launch<128, true, true, __nv_bfloat16>(tA, tB, tB2, om, p, dev->sm_count, s)
+                      : launch<128, false, true, __nv_bfloat16>(tA, tB, tB2, om, p, dev->sm_count, s);
         } else if (d.out_dtype == MIMK_BF16) {
-            rc = b_mn ? launch<256, true, false, __nv_bfloat16>(tA, tB, tB2, p, dev->sm_count, s)
-                      : launch<256, false, false, __nv_bfloat16>(tA, tB, tB2, p, dev->sm_count, s);
+            rc = b_mn ? launch<256, true, false, __nv_bfloat16>(tA, tB, tB2, om, p, dev->sm_count, s)
+                      : launch<256, false, false, __nv_bfloat16>(tA, tB, tB2, om, p, dev->sm_count, s);
         } else {
-            rc = b_mn ? launch<256, true, false, float>(tA, tB, tB2, p, dev->sm_count, s)
-                      : launch<256, false, false, float>(tA, tB, tB2, p, dev->sm_count, s);
+            rc = b_mn ? launch<256, true, false, float>(tA, tB, tB2, om, p, dev->sm_count, s)
+                      : launch<256, false, false, float>(tA, tB, tB2, om, p, dev->sm_count, s);
         }
         MIMK_TRY(rc);
     }

@@ -178,6 +178,9 @@ __host__ __device__ __forceinline__ uint32_t idesc_bf16_f32(int m, int n, int a_
 // 2-D bf16 tensor map with 128-byte swizzle. `inner` is the contiguous extent; box_inner must be 64 (128 bytes).
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                       uint32_t box_inner, uint32_t box_outer);
+// 2-D map of bf16 or f32 elements with 128-byte swizzle (box_inner * element size must be 128 bytes).
+int make_tmap_2d(CUtensorMap* out, bool f32, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                 uint32_t box_inner, uint32_t box_outer);
 int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t mid, uint64_t outer,
                       uint64_t mid_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_mid);
 
