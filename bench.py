@@ -354,7 +354,7 @@ class MlpTP(Workload):
         del w1
         t.cuda.empty_cache()
         if self.mode == "auto":
-            self.mode = "fused" if W == 2 else "nccl"
+            self.mode = "fused"
         if W > 1 and self.mode == "fused":
             self.h = shard.GatheredMatrix(self.M, self.F)
         else:
