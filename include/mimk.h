@@ -107,8 +107,9 @@ typedef struct mimk_gemm_desc {
 int mimk_gemm(const mimk_gemm_desc* desc, void* stream);
 /* The all-gather of a column-sharded contraction fused into its epilogue. Each GPU computes its column slab
  * C[:, col_off : col_off + n] and stores every tile directly into `n_dst` copies of the full [m, ldc] matrix -- its own
- * and its peers' (peer-mapped device pointers, e.g. from CUDA IPC or torch symmetric memory): plain 16-byte stores
- * over NVLink while the tensor cores work on the next tile, instead of a separate NCCL all-gather afterwards.
+ * and its peers' (peer-mapped device pointers, e.g. from CUDA IPC or torch symmetric memory): stores over NVLink
+ * (bulk stores from a shared-memory staging tile in the paired-SM kernel, 16-byte stores otherwise) while the tensor
+ * cores work on the next tile, instead of a separate NCCL all-gather afterwards.
  * `b2` non-NULL selects the gated form, silu(A b) * (A b2) (bf16 out), as in mimk_mlp_gated's first stage.
  * The caller orders this call before the consumers of the gathered matrix on every GPU (a barrier across ranks after
  * the kernel has completed). No counterpart in the reference, which has no multi-device support
@@ -267,6 +268,17 @@ typedef struct mimk_mrp_desc {
     void* out;
 } mimk_mrp_desc;
 int mimk_map_reduce_post(const mimk_mrp_desc* desc, void* stream);
+
+/* Which kernel family mimk_map_reduce_post runs a descriptor on. Large floating-point instances whose access maps
+ * spell a contraction over dense matrices (tensor.mim:1381-1396; right operand [K,N] or its transposed read-through
+ * [N,K]; optional batch loop; id / relu / silu / bias / full-addend epilogue), a fold of one axis with (add, 0),
+ * (fmax, -inf) or (fmin, +inf) (tensor.mim:1151-1157), or an elementwise unary / binary / binary_ax instance
+ * (tensor.mim:361-394, 1162-1167) are handed to mimk_gemm, mimk_reduce and mimk_map. These fold in another order than
+ * the ascending per-cell fold, which is why integer instances and instances with fewer than 2^20 combiner
+ * applications always stay on the per-cell kernel. MIMK_MRP_ROUTE=0 in the environment keeps every instance there.
+ * Pure host logic: needs no device. No counterpart in the reference, whose GPU lowering has the one kernel shape. */
+enum { MIMK_ROUTE_GENERIC = 0, MIMK_ROUTE_GEMM = 1, MIMK_ROUTE_REDUCE = 2, MIMK_ROUTE_MAP = 3 };
+int mimk_mrp_classify(const mimk_mrp_desc* desc);
 
 /* ---- host-buffer forms -------------------------------------------------------------------------------
  * Same operators with HOST pointers: inputs are copied to the device, the kernel runs, the result is copied

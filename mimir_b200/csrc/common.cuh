@@ -52,6 +52,8 @@ int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* 
                 const mimk_gather_dst* gather = nullptr);  // picks between the two
 int gemm_f32_tc_supported(const mimk_gemm_desc& d);  // f32 operands on the tensor cores (3xTF32)
 int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s);
+// map_reduce_post instances that are a contraction, an axis fold or an elementwise map go to those kernels (mrp_route.cu)
+bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status);
 int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_supported(const mimk_attn_desc& d);
 int attn_tc(const mimk_attn_desc& d, cudaStream_t s);

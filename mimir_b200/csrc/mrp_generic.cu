@@ -220,6 +220,8 @@ extern "C" int mimk_map_reduce_post(const mimk_mrp_desc* d, void* stream) {
         // the epilogue input is read at the write coordinates, which range over the result's shape
         if (!map_in_range(d->post_map[0], d->ro, d->so, d->post_shape[0])) return MIMK_E_SHAPE;
     }
+    int routed = MIMK_OK;
+    if (n_red > 0 && mrp_try_route(*d, stream, &routed)) return routed;
     long long blocks = (n_out + 255) / 256;
     const long long cap = (long long)dev->sm_count * 8;
     if (blocks > cap) blocks = cap;

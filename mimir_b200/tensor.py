@@ -277,45 +277,33 @@ def _fill_map(dst, m, n_loops):
         dst.coef[j][n_loops] = row[n_loops]
 
 
-def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_maps=(), post_ins=(), *,
-                    acc_dtype=None, out_dtype=None) -> torch.Tensor:
-    """`map_reduce_post` itself (tensor.mim:159-169): combiner / epilogue by id (mimir_b200._lib.F_*, P_*), access
-    maps as coefficient matrices [results][n_loops + 1].  `init` is a Python number of the accumulator type."""
-    _dev(*ins, *post_ins)
-    So, Sr = [int(v) for v in So], [int(v) for v in Sr]
+def _mrp_desc(So, Sr, f, init, post, map_out, maps, in_meta, post_maps, post_meta, acc_dtype, out_dtype, out_ptr):
+    """The C descriptor of one `map_reduce_post`; operands as (pointer, torch dtype, shape) triples."""
     ro, rn = len(So), len(Sr)
-    if rn > L.MRP_MAX_LOOPS or ro > L.MRP_MAX_RANK or len(ins) > L.MRP_MAX_INPUTS or len(post_ins) > 1:
+    if rn > L.MRP_MAX_LOOPS or ro > L.MRP_MAX_RANK or len(in_meta) > L.MRP_MAX_INPUTS or len(post_meta) > 1:
         raise ValueError("map_reduce_post: too many loops, axes or inputs for the generic kernel")
-    ins = [t.contiguous() for t in ins]
-    post_ins = [t.contiguous() for t in post_ins]
-    if acc_dtype is None:
-        acc_dtype = torch.float32 if (ins and ins[0].dtype in (torch.float32, torch.bfloat16)) or not ins and isinstance(init, float) else (ins[0].dtype if ins else torch.int32)
-    if out_dtype is None:
-        out_dtype = acc_dtype
-    dev = ins[0].device if ins else (post_ins[0].device if post_ins else torch.device("cuda"))
-    out = torch.zeros(So, dtype=out_dtype, device=dev)
     d = L.MrpDesc()
-    d.ro, d.rn, d.nis, d.nps = ro, rn, len(ins), len(post_ins)
+    d.ro, d.rn, d.nis, d.nps = ro, rn, len(in_meta), len(post_meta)
     for i, v in enumerate(Sr):
         d.sr[i] = v
     for i, v in enumerate(So):
         d.so[i] = v
-    for i, (t, m) in enumerate(zip(ins, maps)):
-        if t.dim() > L.MRP_MAX_RANK:
+    for i, ((ptr, dt, shape), m) in enumerate(zip(in_meta, maps)):
+        if len(shape) > L.MRP_MAX_RANK:
             raise ValueError("input rank too large for the generic kernel")
-        d.in_[i] = t.data_ptr()
-        d.in_dtype[i] = _dt(t)
-        for j, v in enumerate(t.shape):
+        d.in_[i] = ptr
+        d.in_dtype[i] = _DT[dt]
+        for j, v in enumerate(shape):
             d.in_shape[i][j] = v
-        if len(m) != t.dim():
+        if len(m) != len(shape):
             raise ValueError("access map must have one result per input axis")
         _fill_map(d.in_map[i], m, rn)
-    for i, (t, m) in enumerate(zip(post_ins, post_maps)):
-        d.post_in[i] = t.data_ptr()
-        d.post_dtype[i] = _dt(t)
-        for j, v in enumerate(t.shape):
+    for i, ((ptr, dt, shape), m) in enumerate(zip(post_meta, post_maps)):
+        d.post_in[i] = ptr
+        d.post_dtype[i] = _DT[dt]
+        for j, v in enumerate(shape):
             d.post_shape[i][j] = v
-        if len(m) != t.dim():
+        if len(m) != len(shape):
             raise ValueError("epilogue access map must have one result per epilogue-input axis")
         _fill_map(d.post_map[i], m, ro)
     if len(map_out) != ro:
@@ -328,7 +316,41 @@ def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_ma
         d.init_bits = struct.unpack("<i", struct.pack("<f", float(init)))[0]
     else:
         d.init_bits = int(init)
-    d.out = out.data_ptr()
+    d.out = out_ptr
+    return d
+
+
+ROUTES = {0: "generic", 1: "gemm", 2: "reduce", 3: "map"}
+
+
+def mrp_route(So, Sr, f: int, init, post: int, map_out, maps, in_shapes, in_dtypes, post_maps=(), post_shapes=(),
+              post_dtypes=(), *, acc_dtype=torch.float32, out_dtype=None) -> str:
+    """Which kernel family `map_reduce_post` would run this instance on ("generic", "gemm", "reduce" or "map"), from
+    shapes and dtypes alone -- host logic, no device needed (mimk_mrp_classify)."""
+    So, Sr = [int(v) for v in So], [int(v) for v in Sr]
+    d = _mrp_desc(So, Sr, f, init, post, map_out, maps, [(0, dt, tuple(sh)) for sh, dt in zip(in_shapes, in_dtypes)], post_maps,
+                  [(0, dt, tuple(sh)) for sh, dt in zip(post_shapes, post_dtypes)], acc_dtype, out_dtype or acc_dtype, 0)
+    return ROUTES[L.lib().mimk_mrp_classify(C.byref(d))]
+
+
+def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_maps=(), post_ins=(), *,
+                    acc_dtype=None, out_dtype=None) -> torch.Tensor:
+    """`map_reduce_post` itself (tensor.mim:159-169): combiner / epilogue by id (mimir_b200._lib.F_*, P_*), access
+    maps as coefficient matrices [results][n_loops + 1].  `init` is a Python number of the accumulator type.
+    Large float instances that are a contraction, an axis fold or an elementwise map run on those kernels
+    (see `mrp_route`); everything else on the one-thread-per-cell kernel."""
+    _dev(*ins, *post_ins)
+    So, Sr = [int(v) for v in So], [int(v) for v in Sr]
+    ins = [t.contiguous() for t in ins]
+    post_ins = [t.contiguous() for t in post_ins]
+    if acc_dtype is None:
+        acc_dtype = torch.float32 if (ins and ins[0].dtype in (torch.float32, torch.bfloat16)) or not ins and isinstance(init, float) else (ins[0].dtype if ins else torch.int32)
+    if out_dtype is None:
+        out_dtype = acc_dtype
+    dev = ins[0].device if ins else (post_ins[0].device if post_ins else torch.device("cuda"))
+    out = torch.zeros(So, dtype=out_dtype, device=dev)
+    d = _mrp_desc(So, Sr, f, init, post, map_out, maps, [(t.data_ptr(), t.dtype, tuple(t.shape)) for t in ins], post_maps,
+                  [(t.data_ptr(), t.dtype, tuple(t.shape)) for t in post_ins], acc_dtype, out_dtype, out.data_ptr())
     L.check(L.lib().mimk_map_reduce_post(C.byref(d), _stream()), "map_reduce_post")
     return out
 

@@ -172,3 +172,67 @@ def test_shape_ops_conv_pool_dot_general(T, L):
     assert got.shape == want.shape and mo.normalised_error(got.cpu().numpy(), want) < 1e-5
     with pytest.raises(ValueError, match="contracting dims don't match"):
         T.dot_product(cu(a), cu(bb), ((2,), (0,)))
+
+
+def test_large_float_instances_run_on_the_specialised_kernels(T, L):
+    """Descriptors the recognisers take (contraction, axis fold, elementwise) give what the specialised entry points
+    give -- same kernels, same bits -- and stay within the float tolerance of the f64 truth."""
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 384, 512, 256
+    a = torch.randn(M, K, generator=g).cuda()
+    b = torch.randn(K, N, generator=g).cuda()
+    maps = [T.proj_map(3, (0, 2)), T.proj_map(3, (2, 1))]
+    assert T.mrp_route((M, N), (M, N, K), L.F_MULADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), maps, [a.shape, b.shape],
+                       [a.dtype, b.dtype]) == "gemm"
+    got = T.map_reduce_post((M, N), (M, N, K), L.F_MULADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), maps, [a, b])
+    assert torch.equal(got, T.product_2d(a, b))
+    truth = a.double().cpu().numpy() @ b.double().cpu().numpy()
+    assert mo.normalised_error(got.cpu().numpy(), truth) <= 1e-5
+
+    # bf16, right operand stored [N, K] and read through its transpose, bias + relu in the epilogue, bf16 result
+    ah = a.to(torch.bfloat16)
+    wh = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    bias = torch.randn(N, generator=g).cuda()
+    got = T.map_reduce_post((M, N), (M, N, K), L.F_MULADD, 0.0, L.P_ADD_RELU, T.proj_map(3, (0, 1)),
+                            [T.proj_map(3, (0, 2)), T.proj_map(3, (1, 2))], [ah, wh], [T.proj_map(2, (1,))], [bias],
+                            out_dtype=torch.bfloat16)
+    assert torch.equal(got, T.product_2d(ah, T.transpose_2d(wh), post="bias_relu", bias=bias))
+    truth = np.maximum(ah.double().cpu().numpy() @ wh.double().cpu().numpy().T + bias.double().cpu().numpy(), 0)
+    assert mo.normalised_error(got.float().cpu().numpy(), truth) <= 2e-2
+
+    # batched, batch loop first (bmm, tensor.mim:1416-1417)
+    B = 6
+    ab = torch.randn(B, 128, 192, generator=g).cuda()
+    bb = torch.randn(B, 192, 128, generator=g).cuda()
+    got = T.map_reduce_post((B, 128, 128), (B, 128, 128, 192), L.F_MULADD, 0.0, L.P_ID, T.proj_map(4, (0, 1, 2)),
+                            [T.proj_map(4, (0, 1, 3)), T.proj_map(4, (0, 3, 2))], [ab, bb])
+    assert torch.equal(got, T.bmm(ab, bb))
+    assert mo.normalised_error(got.cpu().numpy(), ab.double().cpu().numpy() @ bb.double().cpu().numpy()) <= 1e-5
+
+    # axis folds of a [96, 160, 128] tensor
+    x = torch.randn(96, 160, 128, generator=g).cuda()
+    xs = list(x.shape)
+    for ax in range(3):
+        out = [s for i, s in enumerate(xs) if i != ax]
+        subs = [0, 1]
+        subs.insert(ax, 2)
+        s = T.map_reduce_post(out, out + [xs[ax]], L.F_ADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, subs)], [x])
+        assert torch.equal(s, T.reduce("sum", ax, x))
+        assert mo.normalised_error(s.cpu().numpy(), x.double().cpu().numpy().sum(axis=ax)) <= 1e-5
+        m = T.map_reduce_post(out, out + [xs[ax]], L.F_MAX, float("-inf"), L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, subs)], [x])
+        assert np.array_equal(m.cpu().numpy(), x.cpu().numpy().max(axis=ax))
+
+    # elementwise: silu; product; exp(x - max) with the maximum broadcast along the middle axis; bias over the leading axes
+    y = torch.randn(96, 160, 128, generator=g).cuda()
+    got = T.map_reduce_post(xs, xs, L.F_FIRST, 0.0, L.P_SILU, T.id_map(3), [T.id_map(3)], [x])
+    assert torch.equal(got, T.unary("silu", x))
+    assert mo.normalised_error(got.cpu().numpy(), (x.double() * torch.sigmoid(x.double())).cpu().numpy()) <= 1e-5
+    got = T.map_reduce_post(xs, xs, L.F_MUL2, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.id_map(3)], [x, y])
+    assert np.array_equal(got.cpu().numpy(), x.cpu().numpy() * y.cpu().numpy())
+    mx = T.reduce("max", 1, x)
+    got = T.map_reduce_post(xs, xs, L.F_SUBEXP, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.proj_map(3, (0, 2))], [x, mx])
+    want = np.exp(x.double().cpu().numpy() - mx.double().cpu().numpy()[:, None, :])
+    assert mo.normalised_error(got.cpu().numpy(), want) <= 1e-5
+    row = torch.randn(160, 128, generator=g).cuda()
+    got = T.map_reduce_post(xs, xs, L.F_ADD2, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.proj_map(3, (1, 2))], [x, row])
+    assert np.array_equal(got.cpu().numpy(), x.cpu().numpy() + row.cpu().numpy()[None])

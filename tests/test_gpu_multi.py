@@ -1,4 +1,4 @@
-"""Two-GPU parity of the epilogue-fused all-gather (needs >= 2 CUDA devices; skipped otherwise)."""
+"""Multi-GPU parity of the epilogue-fused all-gather (needs >= 2 CUDA devices; skipped otherwise)."""
 import os
 import socket
 
@@ -52,6 +52,27 @@ def _worker(rank, world, port, out_dir):
     T.device_status()
     wanty = mo.mlp_gated_truth(bits(x), bits(w1), bits(w3), bits(w2))[:, rank * nl:(rank + 1) * nl]
     assert mo.normalised_error(y.float().cpu().numpy(), wanty) <= 2e-2
+
+    # a slab large enough for the paired-SM kernel (>= 74 tiles of 256 x 256 per rank): its epilogue sends each piece with
+    # one bulk store per destination. The product is checked bit for bit against the one-GPU product of the same operands.
+    M, K, fl, nl = 2560, 256, 2048, 256
+    F, N = fl * world, nl * world
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w1 = (torch.randn(K, F, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    w3 = (torch.randn(K, F, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    w2 = (torch.randn(F, N, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    c = shard.GatheredMatrix(M, F)
+    for _ in range(2):                                         # twice: the second pass overwrites a full buffer
+        shard.gemm_gather(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), c, rank * fl)
+        c.barrier()
+        assert torch.equal(c.local, T.product_2d(x, w1))
+        c.barrier()
+    h = shard.GatheredMatrix(M, F)
+    y = shard.tp_mlp_gated(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), w3[:, rank * fl:(rank + 1) * fl].contiguous(),
+                           w2[:, rank * nl:(rank + 1) * nl].contiguous(), h)
+    T.device_status()
+    whole = T.mlp_gated(x, w1, w3, w2)[:, rank * nl:(rank + 1) * nl].float().cpu().numpy()
+    assert mo.normalised_error(y.float().cpu().numpy(), whole) <= 1e-2
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
@@ -66,3 +87,15 @@ def test_fused_all_gather_two_gpus(tmp_path):
     entry.build()
     mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def test_fused_all_gather_every_gpu(tmp_path):
+    world = torch.cuda.device_count()
+    if world < 4:
+        pytest.skip("needs four or more GPUs")
+    world = 8 if world >= 8 else 4
+    import torch.multiprocessing as mp
+    import __graft_entry__ as entry
+    entry.build()
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == sorted(f"ok{r}" for r in range(world))

@@ -1,0 +1,96 @@
+"""Host-side recognition of `map_reduce_post` instances (mimk_mrp_classify): which descriptors are a contraction,
+an axis fold or an elementwise map -- the shapes the derived ops expand to (tensor.mim:1381-1396, 1151-1167) -- and
+which must stay on the per-cell kernel. Needs no GPU."""
+import pytest
+import torch
+
+import __graft_entry__ as entry
+
+
+@pytest.fixture(scope="module")
+def TL():
+    entry.build()
+    from mimir_b200 import _lib as L
+    from mimir_b200 import tensor as T
+    return T, L
+
+
+F32, BF16, I32 = torch.float32, torch.bfloat16, torch.int32
+NEG_INF = float("-inf")
+
+
+def gemm_route(T, L, M, N, K, *, nk=False, dt=F32, post=None, batch=None, a_batched=True, b_batched=True, **kw):
+    nb = 0 if batch is None else 1
+    n = 3 + nb
+    lead = [batch] if nb else []
+    lm, ln, lk = nb, nb + 1, nb + 2
+    a_map = T.proj_map(n, ([0] if nb and a_batched else []) + [lm, lk])
+    b_map = T.proj_map(n, ([0] if nb and b_batched else []) + ([ln, lk] if nk else [lk, ln]))
+    a_shape = (lead if a_batched else []) + [M, K]
+    b_shape = (lead if b_batched else []) + ([N, K] if nk else [K, N])
+    post = L.P_ID if post is None else post
+    return T.mrp_route(lead + [M, N], lead + [M, N, K], kw.pop("f", L.F_MULADD), kw.pop("init", 0.0), post,
+                       T.proj_map(n, list(range(2 + nb))), [a_map, b_map], [a_shape, b_shape], [dt, dt], **kw)
+
+
+def test_contractions_are_recognised(TL):
+    T, L = TL
+    assert gemm_route(T, L, 256, 256, 256) == "gemm"
+    assert gemm_route(T, L, 512, 384, 128, nk=True, dt=BF16, out_dtype=BF16) == "gemm"
+    assert gemm_route(T, L, 256, 256, 256, post=L.P_RELU) == "gemm"
+    assert gemm_route(T, L, 128, 128, 64, batch=8) == "gemm"
+    assert gemm_route(T, L, 128, 128, 64, batch=8, b_batched=False) == "gemm"     # one right operand for every batch
+    # bias row read at the last write coordinate; full-shape addend at identity
+    assert gemm_route(T, L, 256, 256, 256, post=L.P_ADD_RELU, post_maps=[T.proj_map(2, [1])], post_shapes=[[256]],
+                      post_dtypes=[F32]) == "gemm"
+    assert gemm_route(T, L, 256, 256, 256, post=L.P_ADD, post_maps=[T.id_map(2)], post_shapes=[[256, 256]],
+                      post_dtypes=[F32]) == "gemm"
+
+
+def test_what_is_not_a_dense_contraction_stays_generic(TL):
+    T, L = TL
+    assert gemm_route(T, L, 64, 64, 64) == "generic"                              # small: keeps the ascending fold
+    assert gemm_route(T, L, 256, 256, 256, init=1.0) == "generic"                 # not the ring's zero
+    assert gemm_route(T, L, 256, 256, 256, post=L.P_ADD, post_maps=[T.proj_map(2, [0])], post_shapes=[[256]],
+                      post_dtypes=[F32]) == "generic"                             # bias along rows: no such epilogue
+    # integer contraction: bit-exact wrap-around arithmetic, never re-associated
+    assert gemm_route(T, L, 256, 256, 256, dt=I32, init=0, acc_dtype=I32) == "generic"
+    # left operand read transposed
+    n = 3
+    r = T.mrp_route([256, 256], [256, 256, 256], L.F_MULADD, 0.0, L.P_ID, T.proj_map(n, [0, 1]),
+                    [T.proj_map(n, [2, 0]), T.proj_map(n, [2, 1])], [[256, 256], [256, 256]], [F32, F32])
+    assert r == "generic"
+    # a slice of a larger operand: the buffer is not exactly the loop box
+    r = T.mrp_route([256, 256], [256, 256, 256], L.F_MULADD, 0.0, L.P_ID, T.proj_map(n, [0, 1]),
+                    [T.proj_map(n, [0, 2]), T.proj_map(n, [2, 1])], [[256, 512], [256, 256]], [F32, F32])
+    assert r == "generic"
+    # packed (transposed) output
+    r = T.mrp_route([256, 256], [256, 256, 256], L.F_MULADD, 0.0, L.P_ID, T.proj_map(n, [1, 0]),
+                    [T.proj_map(n, [0, 2]), T.proj_map(n, [2, 1])], [[256, 256], [256, 256]], [F32, F32])
+    assert r == "generic"
+
+
+def test_axis_folds_and_maps(TL):
+    T, L = TL
+    # reduce over each axis of a [64, 128, 256] tensor: loops (o0, o1, r), the folded loop placed at axis `ax`
+    shape = [64, 128, 256]
+    for ax in range(3):
+        out = [s for i, s in enumerate(shape) if i != ax]
+        subs = [0, 1]
+        subs.insert(ax, 2)
+        for f, init in ((L.F_ADD, 0.0), (L.F_MAX, NEG_INF), (L.F_MIN, float("inf"))):
+            r = T.mrp_route(out, out + [shape[ax]], f, init, L.P_ID, T.proj_map(3, [0, 1]), [T.proj_map(3, subs)], [shape], [F32])
+            assert r == "reduce", (ax, f)
+    assert T.mrp_route([2048], [2048, 2048], L.F_MAX, 0.0, L.P_ID, T.proj_map(2, [0]), [T.id_map(2)], [[2048, 2048]], [F32]) == "generic"
+    assert T.mrp_route([2048], [2048, 2048], L.F_ADD, 0, L.P_ID, T.proj_map(2, [0]), [T.id_map(2)], [[2048, 2048]], [I32],
+                       acc_dtype=I32) == "generic"
+    # elementwise: unary, binary, binary_ax (second operand lacks one axis), bias over leading axes
+    big = [1024, 2048]
+    assert T.mrp_route(big, big, L.F_FIRST, 0.0, L.P_SILU, T.id_map(2), [T.id_map(2)], [big], [F32]) == "map"
+    assert T.mrp_route(big, big, L.F_MUL2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [big, big], [F32, F32]) == "map"
+    assert T.mrp_route(big, big, L.F_SUBEXP, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.proj_map(2, [0])], [big, [1024]],
+                       [F32, F32]) == "map"
+    assert T.mrp_route(big, big, L.F_ADD2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.proj_map(2, [1])], [big, [2048]],
+                       [F32, F32]) == "map"
+    # a transposing copy is not an elementwise map over identical layouts
+    assert T.mrp_route([2048, 1024], [2048, 1024], L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0])], [big], [F32]) == "generic"
