@@ -280,6 +280,33 @@ int mimk_map_reduce_post(const mimk_mrp_desc* desc, void* stream);
 enum { MIMK_ROUTE_GENERIC = 0, MIMK_ROUTE_GEMM = 1, MIMK_ROUTE_REDUCE = 2, MIMK_ROUTE_MAP = 3 };
 int mimk_mrp_classify(const mimk_mrp_desc* desc);
 
+/* ---- matrix-chain association ------------------------------------------------------------------------------
+ * In which order to multiply the chain A0 . A1 . ... . A(n-1), matrix i being dims[i] x dims[i+1]; transposed[i] != 0
+ * marks a leaf that is stored [dims[i+1], dims[i]] and read through transpose_2d (NULL: none is).
+ * Replaces: the decision of the tensor.reassoc phase (src/mim/plug/tensor/phase/reassoc.cpp:89-128 cost of one
+ * product, 172-206 the dynamic program, 287-313 the run-time tournament for extents unknown at compile time) -- taken
+ * here when the chain is about to run, with every extent known.
+ * model MIMK_COST_LANES: the reference's price list, vector-lane slots of its CPU schedules; param = vector width
+ * (its `-X tensor:vec-width`, default 8). model MIMK_COST_B200: estimated seconds on one B200 (whole output tiles in
+ * whole waves over 148 SMs against HBM time, plus a launch; a transposed leaf on the left pays a copy); param = the
+ * element type, MIMK_F32 or MIMK_BF16.
+ * mimk_chain_order writes the n-1 products of the cheapest bracketing in an order in which they can be executed (each
+ * one multiplies the results of sub-chains i..s and s+1..j); equal costs keep the lowest split. Under MIMK_COST_B200 a
+ * sub-chain may also be built transposed when that saves a copy; under MIMK_COST_LANES every node is plain, as in the
+ * phase. mimk_chain_cost prices the products it is given (every sub-chain they use must be among them), e.g. the
+ * chain as written, so that a caller can keep that on a tie as the phase does (reassoc.cpp:349-351).
+ * Pure host logic: needs no device. */
+#define MIMK_CHAIN_MAX 64
+enum { MIMK_COST_LANES = 0, MIMK_COST_B200 = 1 };
+typedef struct mimk_chain_split {
+    int32_t i, s, j; /* multiply sub-chain i..s by sub-chain s+1..j */
+    int32_t t;       /* != 0: store the product transposed, i.e. compute (s+1..j)^T . (i..s)^T (reassoc.cpp:224-231) */
+} mimk_chain_split;
+int mimk_chain_order(int32_t n, const int64_t* dims, const int32_t* transposed, int32_t model, int32_t param,
+                     mimk_chain_split* splits, double* cost);
+int mimk_chain_cost(int32_t n, const int64_t* dims, const int32_t* transposed, int32_t model, int32_t param,
+                    const mimk_chain_split* splits, int32_t n_splits, double* cost);
+
 /* ---- host-buffer forms -------------------------------------------------------------------------------
  * Same operators with HOST pointers: inputs are copied to the device, the kernel runs, the result is copied
  * back and the call returns when the result is in host memory.

@@ -278,3 +278,37 @@ def test_f32_on_tensor_cores_keeps_f32_accuracy(T, M, N, K, nk):
     rows = [0, 127, 128, M - 1]
     want = mo.gemm_truth(a.cpu().numpy(), b.cpu().numpy(), b_nk=nk, rows=rows) + uniform((N,), 3).cpu().numpy().astype(np.float64)
     assert nerr(f64(c[rows]), want) <= TOL_F32
+
+
+def test_chain_product_matches_the_chain_as_written():
+    """Whatever association the price list picks (lit/tensor/reassoc.mim's chains, scaled up), the product is the one
+    the chain as written gives, within the float tolerance of the f64 truth."""
+    from mimir_b200 import reassoc as R
+    from mimir_b200 import tensor as T
+    g = torch.Generator().manual_seed(21)
+
+    def rnd(r, c, scale=1.0):
+        return (torch.randn(r, c, generator=g) * scale).cuda()
+    # attention scores (x wq) (x wk)^T as the chain x . wq . wk^T . x^T (reassoc.mim:113-124)
+    x, wq, wk = rnd(640, 96), rnd(96, 96, 0.1), rnd(96, 96, 0.1)
+    mats = [x, wq, T.transpose_2d(wk), T.transpose_2d(x)]
+    truth = (x.double() @ wq.double() @ wk.double().t() @ x.double().t()).cpu().numpy()
+    for model in ("lanes", "b200"):
+        got = R.chain_product(mats, model=model)
+        assert got.shape == (640, 640) and got.is_contiguous()
+        assert mo.normalised_error(got.cpu().numpy(), truth) <= 1e-5
+    written = [(0, 0, 1, False), (2, 2, 3, True), (0, 1, 3, False)]      # the right factor built as x . wk, read transposed
+    got = R.chain_product(mats, written=written, model="lanes")
+    assert mo.normalised_error(got.cpu().numpy(), truth) <= 1e-5
+    # low-rank bottleneck x (U V), bf16: re-associated to (x U) V
+    xb, u, v = rnd(4096, 768).bfloat16(), rnd(768, 8, 0.05).bfloat16(), rnd(8, 768, 0.05).bfloat16()
+    splits, _, moved = R.choose((4096, 768, 8, 768), None, R.right_deep(3), model="b200")
+    assert moved and [s[:3] for s in splits] == [(0, 0, 1), (0, 1, 2)]
+    got = R.chain_product([xb, u, v], written=R.right_deep(3))
+    truth = (xb.double() @ u.double() @ v.double()).cpu().numpy()
+    assert mo.normalised_error(got.float().cpu().numpy(), truth) <= 2e-2
+    # a node built transposed: X . (A^T . B^T)
+    X, A, B = rnd(512, 384, 0.1), rnd(256, 384, 0.1), rnd(128, 256, 0.1)
+    got = R.chain_product([X, T.transpose_2d(A), T.transpose_2d(B)])
+    truth = (X.double() @ A.double().t() @ B.double().t()).cpu().numpy()
+    assert mo.normalised_error(got.cpu().numpy(), truth) <= 1e-5
