@@ -93,8 +93,10 @@ int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* 
         const char* e = getenv("MIMK_GEMM_2CTA");
         allow_pair    = (e && e[0] == '0') ? 0 : ((e && e[0] == '2') ? 2 : 1);
     }
-    if (allow_pair == 2 && gemm_tc_supported(d)) return gemm_tc2(d, s, gated, b2, gather);
-    if (allow_pair && gemm_tc2_supported(d, gated)) return gemm_tc2(d, s, gated, b2, gather);
+    // the paired kernel takes one launch per batch entry; long batches go to the one-CTA kernel, which walks
+    // (batch, tile) pairs in a single launch
+    if (allow_pair == 2 && d.batch <= 64 && gemm_tc_supported(d)) return gemm_tc2(d, s, gated, b2, gather);
+    if (allow_pair && d.batch <= 64 && gemm_tc2_supported(d, gated)) return gemm_tc2(d, s, gated, b2, gather);
     return gemm_tc(d, s, gated, b2, gather);
 }
 }  // namespace mimk

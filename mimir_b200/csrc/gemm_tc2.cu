@@ -116,16 +116,6 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
 
 // Bulk (TMA) store of a [32 rows x 128 bytes] shared-memory tile to a destination matrix; rows / columns beyond the
 // matrix are clipped by the tensor map. x (in elements) times the element size is a multiple of 128 bytes here.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// at most one earlier group may still be READING its shared-memory source
-__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
 __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t& tm, int64_t& tn) {
     const int64_t per_group = GROUP_M * tiles_n;
     const int64_t group     = tile / per_group;

@@ -301,14 +301,38 @@ def test_chain_product_matches_the_chain_as_written():
     got = R.chain_product(mats, written=written, model="lanes")
     assert mo.normalised_error(got.cpu().numpy(), truth) <= 1e-5
     # low-rank bottleneck x (U V), bf16: re-associated to (x U) V
-    xb, u, v = rnd(4096, 768).bfloat16(), rnd(768, 8, 0.05).bfloat16(), rnd(8, 768, 0.05).bfloat16()
-    splits, _, moved = R.choose((4096, 768, 8, 768), None, R.right_deep(3), model="b200")
+    xb, u, v = rnd(65536, 768).bfloat16(), rnd(768, 8, 0.05).bfloat16(), rnd(8, 768, 0.05).bfloat16()
+    splits, _, moved = R.choose((65536, 768, 8, 768), None, R.right_deep(3), model="b200")
     assert moved and [s[:3] for s in splits] == [(0, 0, 1), (0, 1, 2)]
     got = R.chain_product([xb, u, v], written=R.right_deep(3))
-    truth = (xb.double() @ u.double() @ v.double()).cpu().numpy()
-    assert mo.normalised_error(got.float().cpu().numpy(), truth) <= 2e-2
+    truth = (xb[:4096].double() @ u.double() @ v.double()).cpu().numpy()
+    assert mo.normalised_error(got[:4096].float().cpu().numpy(), truth) <= 2e-2
     # a node built transposed: X . (A^T . B^T)
     X, A, B = rnd(512, 384, 0.1), rnd(256, 384, 0.1), rnd(128, 256, 0.1)
     got = R.chain_product([X, T.transpose_2d(A), T.transpose_2d(B)])
     truth = (X.double() @ A.double().t() @ B.double().t()).cpu().numpy()
     assert mo.normalised_error(got.cpu().numpy(), truth) <= 1e-5
+
+
+@pytest.mark.parametrize("nk", [False, True])
+def test_long_batches_run_as_one_launch(T, nk):
+    """96 batch entries with ragged extents (rows and columns that end inside a tile): the batched kernel walks
+    (batch, tile) pairs; every entry must equal the unbatched product of its operands, bit for bit."""
+    B, M, N, K = 96, 200, 264, 72
+    a = randn((B, M, K), 31, 0.5, torch.bfloat16)
+    b = randn((B, N, K) if nk else (B, K, N), 32, 0.5, torch.bfloat16)
+    bv = b.transpose(1, 2) if nk else b
+    c = T.bmm(a, bv)
+    T.device_status()
+    for i in (0, 1, 47, 95):
+        assert torch.equal(c[i], T.product_2d(a[i], bv[i]))
+    want = mo.gemm_truth(bits(a[95]), bits(bv[95].contiguous()), bf16=True)
+    assert nerr(f64(c[95]), want) <= TOL_BF16
+    # one right operand for every entry (batch stride 0), a full-shape addend per entry in the epilogue
+    full = randn((B, M, N), 33, 1.0, torch.bfloat16)
+    out = torch.empty((B, M, N), dtype=torch.bfloat16, device="cuda")
+    b0 = b[0].contiguous()
+    T._gemm(a, b0, 1 if nk else 0, B, M, N, K, M * K, 0, out, "add", None, full)
+    T.device_status()
+    for i in (0, 50, 95):
+        assert torch.equal(out[i], T.product_2d(a[i], bv[0], post="add", full=full[i]))
