@@ -275,9 +275,10 @@ int mimk_map_reduce_post(const mimk_mrp_desc* desc, void* stream);
  * (fmax, -inf) or (fmin, +inf) (tensor.mim:1151-1157), or an elementwise unary / binary / binary_ax instance
  * (tensor.mim:361-394, 1162-1167) are handed to mimk_gemm, mimk_reduce and mimk_map. These fold in another order than
  * the ascending per-cell fold, which is why integer instances and instances with fewer than 2^20 combiner
- * applications always stay on the per-cell kernel. MIMK_MRP_ROUTE=0 in the environment keeps every instance there.
+ * applications always stay on the per-cell kernel. A copy that permutes axes (tensor.transpose, tensor.mim:1443-1468;
+ * any element type, 2^20 elements or more) runs as a tiled copy through shared memory. MIMK_MRP_ROUTE=0 in the environment keeps every instance there.
  * Pure host logic: needs no device. No counterpart in the reference, whose GPU lowering has the one kernel shape. */
-enum { MIMK_ROUTE_GENERIC = 0, MIMK_ROUTE_GEMM = 1, MIMK_ROUTE_REDUCE = 2, MIMK_ROUTE_MAP = 3 };
+enum { MIMK_ROUTE_GENERIC = 0, MIMK_ROUTE_GEMM = 1, MIMK_ROUTE_REDUCE = 2, MIMK_ROUTE_MAP = 3, MIMK_ROUTE_PERMUTE = 4 };
 int mimk_mrp_classify(const mimk_mrp_desc* desc);
 
 /* ---- matrix-chain association ------------------------------------------------------------------------------

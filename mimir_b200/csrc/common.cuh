@@ -54,6 +54,8 @@ int gemm_f32_tc_supported(const mimk_gemm_desc& d);  // f32 operands on the tens
 int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s);
 // map_reduce_post instances that are a contraction, an axis fold or an elementwise map go to those kernels (mrp_route.cu)
 bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status);
+// axis permutation as a tiled copy (permute.cu); perm[j] = the output loop that indexes input axis j
+int permute_copy(const void* in, void* out, int esize, int rank, const int64_t* out_shape, const int* perm, cudaStream_t s);
 int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_supported(const mimk_attn_desc& d);
 int attn_tc(const mimk_attn_desc& d, cudaStream_t s);

@@ -49,6 +49,7 @@ struct Plan {
     // reduce / map
     int64_t outer = 0, len = 0, inner = 0;
     int monoid = 0, op = 0, y_mode = 3;
+    int perm[MIMK_MRP_MAX_RANK] = {};
 };
 
 // Operand `i` as a matrix [..batch, r, c]: its last two results are loops (lr, lc); with a leading batch result (loop 0)
@@ -199,6 +200,24 @@ bool plan_map(const mimk_mrp_desc& d, Plan& p) {
     }
 }
 
+// A copy whose input map permutes the output loops (tensor.transpose): any element type, it moves bits only.
+bool plan_permute(const mimk_mrp_desc& d, Plan& p) {
+    if (d.comb != MIMK_F_FIRST || d.post != MIMK_P_ID || d.nis != 1 || d.nps != 0 || d.rn != d.ro || d.ro < 2) return false;
+    if (d.in_dtype[0] != d.out_dtype || !out_is_identity(d)) return false;
+    const mimk_affine_map& m = d.in_map[0];
+    if (m.rows != d.ro) return false;
+    bool seen[MIMK_MRP_MAX_RANK] = {};
+    for (int j = 0; j < m.rows; ++j) {
+        int l = -1;
+        for (int c = 0; c < d.ro; ++c)
+            if (row_is_loop(m, j, d.rn, c)) { l = c; break; }
+        if (l < 0 || seen[l] || d.in_shape[0][j] != d.sr[l]) return false;
+        seen[l]   = true;
+        p.perm[j] = l;
+    }
+    return p.perm[d.ro - 1] != d.ro - 1;  // the same fastest axis on both sides: the per-cell kernel is coalesced already
+}
+
 // Below this many combiner applications the per-cell kernel is kept: it is launch-bound there anyway, and it keeps
 // the ascending fold of the classic nest bit for bit.
 constexpr long long ROUTE_MIN_WORK = 1ll << 20;
@@ -218,6 +237,7 @@ Plan make_plan(const mimk_mrp_desc& d) {
     if (plan_gemm(d, p)) p.route = MIMK_ROUTE_GEMM;
     else if (plan_reduce(d, p)) p.route = MIMK_ROUTE_REDUCE;
     else if (plan_map(d, p)) p.route = MIMK_ROUTE_MAP;
+    else if (plan_permute(d, p)) p.route = MIMK_ROUTE_PERMUTE;
     return p;
 }
 
@@ -240,6 +260,11 @@ bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status) {
         case MIMK_ROUTE_MAP:
             *status = mimk_map(p.op, d.in[0], d.nis == 2 ? d.in[1] : nullptr, d.out, d.out_dtype, p.outer, p.len, p.inner, p.y_mode, stream);
             return true;
+        case MIMK_ROUTE_PERMUTE: {
+            const int esize = d.out_dtype == MIMK_BF16 ? 2 : d.out_dtype == MIMK_I64 ? 8 : 4;
+            *status = permute_copy(d.in[0], d.out, esize, d.ro, d.sr, p.perm, static_cast<cudaStream_t>(stream));
+            return true;
+        }
         default: return false;
     }
 }

@@ -151,8 +151,9 @@ def tp_mlp_gated(x, w1_shard, w3_shard, w2_shard, h: "GatheredMatrix | None" = N
     Returns this rank's column slab of Y.
     gather = "fused": the H slab is stored straight into every rank's H from the contraction's epilogue (needs `h`);
              "nccl":  a local slab and an NCCL all-gather;
-             "auto":  fused when a GatheredMatrix is supplied, NCCL otherwise. Measured for the 8192 x 4096 x 14336 block on
-                      2 GPUs: 1.02 ms fused (bulk stores from shared memory to every rank's H) / 1.97 ms NCCL."""
+             "auto":  fused when a GatheredMatrix is supplied, NCCL otherwise. Measured for the 8192 x 4096 x 14336 block
+                      (bulk stores from shared memory to every rank's H against a separate NCCL all-gather):
+                      2 GPUs 1.02 / 1.97 ms, 4 GPUs 0.57 / 1.43 ms, 8 GPUs 0.49 / 1.17 ms."""
     from . import tensor as T
     rank, world = _world()
     if gather == "auto":

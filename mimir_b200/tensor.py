@@ -320,7 +320,7 @@ def _mrp_desc(So, Sr, f, init, post, map_out, maps, in_meta, post_maps, post_met
     return d
 
 
-ROUTES = {0: "generic", 1: "gemm", 2: "reduce", 3: "map"}
+ROUTES = {0: "generic", 1: "gemm", 2: "reduce", 3: "map", 4: "permute"}
 
 
 def mrp_route(So, Sr, f: int, init, post: int, map_out, maps, in_shapes, in_dtypes, post_maps=(), post_shapes=(),

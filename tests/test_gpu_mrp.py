@@ -236,3 +236,21 @@ def test_large_float_instances_run_on_the_specialised_kernels(T, L):
     row = torch.randn(160, 128, generator=g).cuda()
     got = T.map_reduce_post(xs, xs, L.F_ADD2, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.proj_map(3, (1, 2))], [x, row])
     assert np.array_equal(got.cpu().numpy(), x.cpu().numpy() + row.cpu().numpy()[None])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int64, torch.int32])
+def test_large_axis_permutations_are_tiled_copies(T, L, dtype):
+    """tensor.transpose of tensors large enough to leave the per-cell kernel: every permutation that moves the fastest
+    axis, with extents that end inside a 32 x 32 tile. A copy: bit exact for every element type."""
+    g = torch.Generator().manual_seed(9)
+    shape = (70, 161, 130)
+    x = torch.randint(-1000, 1000, shape, generator=g).to(dtype).cuda()
+    for perm in ((2, 1, 0), (1, 2, 0), (2, 0, 1), (0, 2, 1)):
+        out_shape = [shape[p] for p in perm]
+        inv = [perm.index(j) for j in range(3)]                  # input axis j is indexed by output loop inv[j]
+        assert T.mrp_route(out_shape, out_shape, L.F_FIRST, 0, L.P_ID, T.id_map(3), [T.proj_map(3, inv)], [shape], [dtype],
+                           acc_dtype=torch.float32 if dtype.is_floating_point else dtype, out_dtype=dtype) == "permute"
+        got = T.transpose(x, perm)
+        assert torch.equal(got, x.permute(perm).contiguous()), perm
+    m = torch.randint(-1000, 1000, (3000, 1111), generator=g).to(dtype).cuda()
+    assert torch.equal(T.transpose(m, (1, 0)), m.t().contiguous())

@@ -92,5 +92,13 @@ def test_axis_folds_and_maps(TL):
                        [F32, F32]) == "map"
     assert T.mrp_route(big, big, L.F_ADD2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.proj_map(2, [1])], [big, [2048]],
                        [F32, F32]) == "map"
-    # a transposing copy is not an elementwise map over identical layouts
-    assert T.mrp_route([2048, 1024], [2048, 1024], L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0])], [big], [F32]) == "generic"
+    # a transposing copy is not an elementwise map over identical layouts: it is a tiled copy, for any element type
+    assert T.mrp_route([2048, 1024], [2048, 1024], L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0])], [big], [F32]) == "permute"
+    assert T.mrp_route([2048, 1024], [2048, 1024], L.F_FIRST, 0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0])], [big], [I32],
+                       acc_dtype=I32) == "permute"
+    # ... unless both sides share their fastest axis (coalesced as it is), the shapes do not match, or it is small
+    assert T.mrp_route([128, 64, 256], [128, 64, 256], L.F_FIRST, 0.0, L.P_ID, T.id_map(3), [T.proj_map(3, [1, 0, 2])],
+                       [[64, 128, 256]], [F32]) == "generic"
+    assert T.mrp_route([2048, 1024], [2048, 1024], L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0])], [[1024, 4096]],
+                       [F32]) == "generic"
+    assert T.mrp_route([64, 32], [64, 32], L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0])], [[32, 64]], [F32]) == "generic"
