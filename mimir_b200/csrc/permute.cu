@@ -1,5 +1,5 @@
 // Axis permutation of a dense tensor (tensor.transpose, MimIR src/mim/plug/tensor/tensor.mim:1443-1468: a copy-style
-// map_reduce_post whose input map is `transpose_map`) as a tiled copy: a 32 x 32 tile over the output's fastest axis
+// map_reduce_post whose input map is `transpose_map`) as a tiled copy: a 64 x 64 tile over the output's fastest axis
 // and the input's fastest axis goes through shared memory, so both the reads and the writes are coalesced. The
 // per-cell kernel reads such an instance with a stride between neighbouring threads.
 #include "common.cuh"
@@ -7,7 +7,7 @@
 namespace mimk {
 namespace {
 
-constexpr int TILE = 32, ROWS = 8;
+constexpr int TILE = 64, ROWS = 4;  // 64 x 64 elements per step, 16 loads in flight per thread
 
 struct PermuteParams {
     int rank;                          // output loops (<= MIMK_MRP_MAX_RANK)

@@ -348,7 +348,9 @@ def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_ma
     if out_dtype is None:
         out_dtype = acc_dtype
     dev = ins[0].device if ins else (post_ins[0].device if post_ins else torch.device("cuda"))
-    out = torch.zeros(So, dtype=out_dtype, device=dev)
+    # a write map that stores loop vector o at o covers the whole result; anything else may leave cells untouched
+    covers = So == Sr[:len(So)] and [list(r) for r in map_out] == [list(r) for r in proj_map(len(Sr), range(len(So)))]
+    out = (torch.empty if covers else torch.zeros)(So, dtype=out_dtype, device=dev)
     d = _mrp_desc(So, Sr, f, init, post, map_out, maps, [(t.data_ptr(), t.dtype, tuple(t.shape)) for t in ins], post_maps,
                   [(t.data_ptr(), t.dtype, tuple(t.shape)) for t in post_ins], acc_dtype, out_dtype, out.data_ptr())
     L.check(L.lib().mimk_map_reduce_post(C.byref(d), _stream()), "map_reduce_post")
