@@ -355,8 +355,11 @@ class MlpTP(Workload):
         t.cuda.empty_cache()
         if self.mode == "auto":
             self.mode = "fused"
+        self.yg = None
         if W > 1 and self.mode == "fused":
             self.h = shard.GatheredMatrix(self.M, self.F)
+            if getattr(self, "gather", False):     # --gather: the whole Y on every rank, gathered in stage 2's epilogue
+                self.yg = shard.GatheredMatrix(self.M, self.K)
         else:
             self.h_local = t.empty((self.M, self.fl), device="cuda", dtype=t.bfloat16)
         self.units = 3 * 2 * self.M * self.K * self.F // W     # per-rank share: the driver multiplies by world
@@ -370,12 +373,14 @@ class MlpTP(Workload):
         if self.world == 1:
             self.y = self.T.mlp_gated(self.x, self.w1, self.w3, self.w2, h=self.h_local)
         elif self.mode == "fused":
-            self.y = self.shard.tp_mlp_gated(self.x, self.w1, self.w3, self.w2, self.h, gather="fused")
+            self.y = self.shard.tp_mlp_gated(self.x, self.w1, self.w3, self.w2, self.h, gather="fused", y=self.yg)
         else:
             # stage 1 into a local slab (gated contraction with the W2-free path: H slab only), NCCL all-gather, stage 2
             self.shard.gemm_gather_local(self.x, self.w1, self.w3, self.h_local)
             h_full = self.shard.gather_columns(self.h_local, self.F)
             self.y = self.T.product_2d(h_full, self.w2)
+            if getattr(self, "gather", False):
+                self.y = self.shard.gather_columns(self.y, self.K)
         if ev:
             ev[1].record()
 

@@ -145,10 +145,13 @@ def gemm_gather(a: torch.Tensor, b: torch.Tensor, out: GatheredMatrix, col_off: 
                                      _stream()), "gemm_gather")
 
 
-def tp_mlp_gated(x, w1_shard, w3_shard, w2_shard, h: "GatheredMatrix | None" = None, gather: str = "auto"):
+def tp_mlp_gated(x, w1_shard, w3_shard, w2_shard, h: "GatheredMatrix | None" = None, gather: str = "auto",
+                 y: "GatheredMatrix | None" = None):
     """Tensor-parallel gated MLP: rank g holds columns [g F/G, (g+1) F/G) of W1 and W3 and a column slab of W2.
     Stage 1 computes this rank's H slab, H is all-gathered, stage 2 multiplies the full H with this rank's W2 columns.
-    Returns this rank's column slab of Y.
+    Returns this rank's column slab of Y -- or, when a GatheredMatrix `y` ([M, N], N = all ranks' W2 columns) is given,
+    the whole Y on every rank: the output all-gather is then fused into the second contraction's epilogue as well
+    (NCCL all-gather of the slabs on the "nccl" path).
     gather = "fused": the H slab is stored straight into every rank's H from the contraction's epilogue (needs `h`);
              "nccl":  a local slab and an NCCL all-gather;
              "auto":  fused when a GatheredMatrix is supplied, NCCL otherwise. Measured for the 8192 x 4096 x 14336 block
@@ -166,12 +169,22 @@ def tp_mlp_gated(x, w1_shard, w3_shard, w2_shard, h: "GatheredMatrix | None" = N
             raise ValueError("the fused all-gather needs a GatheredMatrix for H")
         gemm_gather(x, w1_shard, h, rank * f_local, gated_b2=w3_shard)
         h.barrier()
-        y = T.product_2d(h.local, w2_shard)
-        h.barrier()  # nobody overwrites H (the next call) while a peer still reads it
-        return y
+        if y is None:
+            out = T.product_2d(h.local, w2_shard)
+        else:
+            gemm_gather(h.local, w2_shard, y, rank * w2_shard.shape[1])
+            out = y.local
+        # One barrier after stage 2 on every rank: nobody overwrites H (the next call) while a peer still reads it,
+        # and with a gathered Y every rank's slab has landed everywhere.
+        (h if y is None else y).barrier()
+        return out
     h_local = torch.empty((x.shape[0], f_local), dtype=x.dtype, device=x.device)
     gemm_gather_local(x, w1_shard, w3_shard, h_local)
-    return T.product_2d(gather_columns(h_local, f_local * world), w2_shard)
+    slab = T.product_2d(gather_columns(h_local, f_local * world), w2_shard)
+    if y is None:
+        return slab
+    y.local.copy_(gather_columns(slab, slab.shape[1] * world))
+    return y.local
 
 
 def gemm_gather_local(x, w1_shard, w3_shard, h_local):

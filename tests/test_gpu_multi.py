@@ -71,8 +71,18 @@ def _worker(rank, world, port, out_dir):
     y = shard.tp_mlp_gated(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), w3[:, rank * fl:(rank + 1) * fl].contiguous(),
                            w2[:, rank * nl:(rank + 1) * nl].contiguous(), h)
     T.device_status()
-    whole = T.mlp_gated(x, w1, w3, w2)[:, rank * nl:(rank + 1) * nl].float().cpu().numpy()
+    whole_y = T.mlp_gated(x, w1, w3, w2)
+    whole = whole_y[:, rank * nl:(rank + 1) * nl].float().cpu().numpy()
     assert mo.normalised_error(y.float().cpu().numpy(), whole) <= 1e-2
+    # the output all-gather fused into the second contraction as well: the whole Y on every rank
+    yg = shard.GatheredMatrix(M, N)
+    for mode in ("fused", "nccl"):
+        full = shard.tp_mlp_gated(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), w3[:, rank * fl:(rank + 1) * fl].contiguous(),
+                                  w2[:, rank * nl:(rank + 1) * nl].contiguous(), h, gather=mode, y=yg)
+        T.device_status()
+        assert full.shape == (M, N)
+        assert mo.normalised_error(full.float().cpu().numpy(), whole_y.float().cpu().numpy()) <= 1e-2
+        dist.barrier()
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
