@@ -1,0 +1,92 @@
+// Device helpers shared by the tensor-core attention kernels: exp2 on the special-function unit and on the FMA pipe,
+// packed f32x2 arithmetic, three-input maxima, 32-column tensor-memory loads and stores.
+#pragma once
+#include <cstdint>
+
+namespace mimk {
+namespace attn {
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---- packed f32x2 arithmetic (one instruction for two floats) ----
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2_rd(uint64_t a, uint64_t b) {  // round towards -inf
+    uint64_t d;
+    asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// 2^x for two values x <= 8 on the FMA pipe instead of the special-function unit: split x into floor and fraction
+// with a round-down add of 1.5 * 2^23, evaluate a cubic minimax polynomial of 2^frac on [0,1) (relative error 8.8e-5,
+// far below the bf16 rounding P receives), and add floor(x) into the exponent field.
+__device__ __forceinline__ void poly_exp2_x2(float xa, float xb, float& ea, float& eb) {
+    const uint64_t x    = pack2(fmaxf(xa, -127.f), fmaxf(xb, -127.f));
+    const uint64_t xf   = add2_rd(x, pack2(12582912.f, 12582912.f));
+    const uint64_t fl   = add2(xf, pack2(-12582912.f, -12582912.f));
+    const uint64_t frac = fma2(fl, pack2(-1.f, -1.f), x);
+    uint64_t pf = fma2(pack2(0.077119089663028717041015625f, 0.077119089663028717041015625f), frac,
+                       pack2(0.227564394474029541015625f, 0.227564394474029541015625f));
+    pf          = fma2(pf, frac, pack2(0.695146143436431884765625f, 0.695146143436431884765625f));
+    pf          = fma2(pf, frac, pack2(1.0f, 1.0f));
+    float pa, pb, fa, fb;
+    unpack2(pf, pa, pb);
+    unpack2(xf, fa, fb);
+    ea = __int_as_float(__float_as_int(pa) + (__float_as_int(fa) << 23));
+    eb = __int_as_float(__float_as_int(pb) + (__float_as_int(fb) << 23));
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 32 lanes x 32 columns into r[0..31] (a slice of a larger register array)
+__device__ __forceinline__ void tmem_ld_slice(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x32_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+}  // namespace attn
+}  // namespace mimk

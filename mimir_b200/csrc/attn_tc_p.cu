@@ -1,0 +1,509 @@
+// Attention forward, persistent form of attn_tc.cu: one CTA per SM takes (head, query-tile pair) work items from a
+// global counter until none is left, and the hand-over between items is pipelined.
+//
+// Same program as attn_tc.cu -- `softmax (q * transpose_2d k) * v` (MimIR lit/tensor/attn_exec.mim:20-22) with scale, an
+// optional causal mask and batch x heads -- and the same roles and tensor-memory layout (S0 S1 O0 O1, P over S). What a
+// one-item CTA pays per item and this kernel hides: the CTA launch, barrier and tensor-memory set-up, the load latency
+// of Q and of the first K/V tiles, the pipeline fill and drain. Measured with the one-item kernel at head_dim 128:
+// 5.8 us per item beside 1.84 us per step of 128 keys, i.e. 3.2 steps' worth on items that are 4 to 64 steps long.
+//   producer   fetches the next item as soon as the K/V ring has room: its Q tiles are loaded when the last S = Q K^T
+//              of the previous item has been issued, its first K/V tiles while the previous item's last steps compute
+//   MMA        issues S = Q K^T of the next item's first key tile right behind the previous item's last O += P V; the
+//              first O += P V of an item (which overwrites O_t) waits until the previous item's O_t has been read
+//   softmax    reads the finished O_t into registers, releases it, then normalises and stores from registers
+// Barriers live across items, so every role keeps running counts (K/V tiles, S tiles, P tiles, items per tile) and
+// derives stage and parity from them. Every wait is bounded as in attn_tc.cu.
+#include <math_constants.h>
+
+#include <cstdlib>
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100.cuh"
+#include "attn_common.cuh"
+
+namespace mimk {
+
+using namespace sm100;
+using namespace attn;
+
+namespace {
+
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int TILE_BYTES = 128 * 128 * 2;  // a [128 x 128] bf16 tile = two swizzle atoms of [128 x 64]
+constexpr int ATOM_BYTES = TILE_BYTES / 2;
+constexpr int KV_STAGES = 2;
+constexpr int NUM_THREADS = 384;  // softmax tile 0, softmax tile 1, {producer, MMA, two idle warps}
+constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
+// register budget moved between warpgroups with setmaxnreg; must fit what the CTA got at launch (see attn_tc.cu)
+constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 208, OTHER_REGS = 88;
+static_assert(2 * 128 * SOFTMAX_REGS + 128 * OTHER_REGS <= LAUNCH_REGS * NUM_THREADS, "setmaxnreg budget exceeds the CTA's registers");
+constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+constexpr int WORK_SLOTS = 2;
+
+struct Bars {
+    uint64_t q_full[2], q_empty[2];
+    uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
+    uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
+    uint64_t s_full[2], p_half[2], p_full[2], o_full[2], o_empty[2];
+    uint64_t work_full[WORK_SLOTS], work_empty[WORK_SLOTS];
+    int work_item[WORK_SLOTS];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+constexpr int OUT_STAGE_BYTES = 8 * 4096;  // per softmax warp: 32 rows x 128 bytes of O on their way to a bulk store
+constexpr int SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + OUT_STAGE_BYTES + 1024 + 256;
+static_assert(sizeof(Bars) <= 256, "barrier block too large");
+static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
+
+struct Params {
+    int64_t Sq, Sk;
+    int BH, num_pairs, head_group, num_items;
+    __nv_bfloat16* O;
+    float* lse;
+    float scale_log2;  // scale * log2(e)
+    int causal;
+    int* counter;  // next work item; zeroed before the launch
+    int* status;
+};
+
+// Work counters of launches in flight: a launch takes the next slot and zeroes it in stream order, so launches on
+// different streams do not share one (up to COUNTER_SLOTS of them at a time).
+constexpr int COUNTER_SLOTS = 64;
+__device__ int g_work_counters[COUNTER_SLOTS];
+
+struct Item {
+    int head;
+    int q0[2];
+    int n_kv[2], n_max;
+};
+
+// Items are numbered so that taking them in order is longest-first inside groups of heads (see attn_tc.cu): inside a
+// group all heads' longest query-tile pair comes first, then all second-longest, and so on.
+__device__ __forceinline__ Item decode_item(const Params& p, int item) {
+    Item it;
+    const int HG = p.head_group;
+    const int per_group = HG * p.num_pairs;
+    const int g   = item / per_group;
+    const int gsz = (p.BH - g * HG) < HG ? (p.BH - g * HG) : HG;  // the last group may be smaller
+    const int rr  = item - g * per_group;
+    const int pair = p.num_pairs - 1 - rr / gsz;
+    it.head        = g * HG + rr % gsz;
+    const int kv_tiles = int((p.Sk + BKV - 1) / BKV);
+    for (int t = 0; t < 2; ++t) {
+        it.q0[t] = pair * 2 * BQ + t * BQ;
+        if (it.q0[t] >= p.Sq) {
+            it.n_kv[t] = 0;
+        } else if (p.causal) {
+            const int diag = it.q0[t] / BKV + 1;
+            it.n_kv[t]     = diag < kv_tiles ? diag : kv_tiles;
+        } else {
+            it.n_kv[t] = kv_tiles;
+        }
+    }
+    it.n_max = it.n_kv[0] > it.n_kv[1] ? it.n_kv[0] : it.n_kv[1];
+    return it;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base     = (raw_addr + 1023u) & ~1023u;
+    const uint32_t sQ = base, sK = base + 2 * TILE_BYTES, sV = sK + KV_STAGES * TILE_BYTES;
+    const uint32_t sOut = sV + KV_STAGES * TILE_BYTES;
+    Bars* bars = reinterpret_cast<Bars*>(smem_raw + (base - raw_addr) + (2 + 2 * KV_STAGES) * TILE_BYTES + OUT_STAGE_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+    volatile int* work_item  = bars->work_item;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(smem_u32(&bars->q_full[t]), 1);
+            mbar_init(smem_u32(&bars->q_empty[t]), 1);
+            mbar_init(smem_u32(&bars->s_full[t]), 1);
+            mbar_init(smem_u32(&bars->p_half[t]), 128);
+            mbar_init(smem_u32(&bars->p_full[t]), 128);
+            mbar_init(smem_u32(&bars->o_full[t]), 1);
+            mbar_init(smem_u32(&bars->o_empty[t]), 128);
+        }
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(smem_u32(&bars->k_full[s]), 1);
+            mbar_init(smem_u32(&bars->k_empty[s]), 1);
+            mbar_init(smem_u32(&bars->v_full[s]), 1);
+            mbar_init(smem_u32(&bars->v_empty[s]), 1);
+        }
+        for (int w = 0; w < WORK_SLOTS; ++w) {
+            mbar_init(smem_u32(&bars->work_full[w]), 1);
+            mbar_init(smem_u32(&bars->work_empty[w]), 9);  // the MMA thread and one lane of each softmax warp
+        }
+        bars->abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmO);
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(&bars->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
+      if (warp == PRODUCER_WARP) {
+        // ---------------- work fetch + TMA producer ----------------
+        if (lane == 0) {
+            uint32_t g = 0;              // K/V tiles loaded so far (stage = g % KV_STAGES)
+            uint32_t qc[2] = {0, 0};     // Q tiles loaded so far, per tile slot
+            bool ok = true;
+            for (uint32_t w = 0; ok; ++w) {
+                const uint32_t slot = w % WORK_SLOTS, wph = (w / WORK_SLOTS) & 1u;
+                if (!(ok = mbar_wait(smem_u32(&bars->work_empty[slot]), wph ^ 1u, abort_flag))) break;
+                const int item  = atomicAdd(p.counter, 1);
+                const bool last = item >= p.num_items;
+                work_item[slot] = last ? -1 : item;
+                mbar_arrive(smem_u32(&bars->work_full[slot]));  // release: the slot's content is visible to the waiters
+                if (last) break;
+                const Item it = decode_item(p, item);
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (it.n_kv[t] == 0) continue;
+                    // the previous occupant's last S = Q K^T has been issued and completed
+                    if (!(ok = mbar_wait(smem_u32(&bars->q_empty[t]), (qc[t] & 1u) ^ 1u, abort_flag))) break;
+                    const uint32_t qf = smem_u32(&bars->q_full[t]);
+                    mbar_expect_tx(qf, TILE_BYTES);
+                    tma_load_3d(sQ + t * TILE_BYTES, &tmQ, 0, it.q0[t], it.head, qf);
+                    tma_load_3d(sQ + t * TILE_BYTES + ATOM_BYTES, &tmQ, 64, it.q0[t], it.head, qf);
+                    ++qc[t];
+                }
+                for (int j = 0; j < it.n_max && ok; ++j, ++g) {
+                    const uint32_t s = g % KV_STAGES, ph = (g / KV_STAGES) & 1u;
+                    if (!(ok = mbar_wait(smem_u32(&bars->k_empty[s]), ph ^ 1u, abort_flag))) break;
+                    const uint32_t kf = smem_u32(&bars->k_full[s]);
+                    mbar_expect_tx(kf, TILE_BYTES);
+                    tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, j * BKV, it.head, kf);
+                    tma_load_3d(sK + s * TILE_BYTES + ATOM_BYTES, &tmK, 64, j * BKV, it.head, kf);
+                    if (!(ok = mbar_wait(smem_u32(&bars->v_empty[s]), ph ^ 1u, abort_flag))) break;
+                    const uint32_t vf = smem_u32(&bars->v_full[s]);
+                    mbar_expect_tx(vf, TILE_BYTES);
+                    tma_load_3d(sV + s * TILE_BYTES, &tmV, 0, j * BKV, it.head, vf);
+                    tma_load_3d(sV + s * TILE_BYTES + ATOM_BYTES, &tmV, 64, j * BKV, it.head, vf);
+                }
+            }
+        }
+      } else if (warp == MMA_WARP) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc_qk = idesc_bf16_f32(BQ, BKV, 0, 0);
+            const uint32_t idesc_pv = idesc_bf16_f32(BQ, HD, 0, 1);
+            static_assert(KV_STAGES == 2, "stage selection below assumes two stages");
+            const uint64_t dQ0 = smem_desc_sw128(sQ, 16, 1024), dK0 = smem_desc_sw128(sK, 16, 1024);
+            const uint64_t dV0 = smem_desc_sw128(sV, ATOM_BYTES, 1024);
+            constexpr uint64_t TILE_STEP = uint64_t(TILE_BYTES >> 4);
+            // S_t = Q_t K^T with K in ring stage `stage`: 8 k-steps of 16 over head_dim
+            auto issue_qk = [&](int t, uint32_t stage) {
+                const uint64_t qa = dQ0 + (t ? TILE_STEP : 0), kb = dK0 + (stage ? TILE_STEP : 0);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint64_t off = uint64_t(((k >> 2) * ATOM_BYTES + (k & 3) * 32) >> 4);
+                    mma_f16_ss(tmem_base + t * 128, qa + off, kb + off, idesc_qk, k > 0 ? 1u : 0u);
+                }
+                mma_commit(smem_u32(&bars->s_full[t]));
+            };
+            // O_t (+)= P_t V with V in ring stage `stage`, k-steps [k0, k1) of 16 keys; `first` = first key tile of the item
+            auto issue_pv = [&](int t, uint32_t stage, bool first, int k0, int k1) {
+                const uint64_t vb = dV0 + (stage ? TILE_STEP : 0);
+#pragma unroll
+                for (int k = k0; k < k1; ++k)
+                    mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, vb + uint64_t((k * 2048) >> 4), idesc_pv,
+                               (!first || k > 0) ? 1u : 0u);
+            };
+            uint32_t g = 0;            // K/V tiles consumed so far
+            uint32_t qc[2] = {0, 0};   // items in which tile slot t took part (parity of q_full / o_empty)
+            uint32_t pc[2] = {0, 0};   // P tiles consumed per tile slot (parity of p_half / p_full)
+            bool ok = true;
+            for (uint32_t w = 0; ok; ++w) {
+                const uint32_t slot = w % WORK_SLOTS, wph = (w / WORK_SLOTS) & 1u;
+                if (!(ok = mbar_wait(smem_u32(&bars->work_full[slot]), wph, abort_flag))) break;
+                const int item = work_item[slot];
+                mbar_arrive(smem_u32(&bars->work_empty[slot]));
+                if (item < 0) break;
+                const Item it = decode_item(p, item);
+                if (it.n_max == 0) continue;
+                // first key tile: S_t = Q_t K_0^T for both tiles
+                for (int t = 0; t < 2 && ok; ++t)
+                    if (it.n_kv[t] > 0) ok = mbar_wait(smem_u32(&bars->q_full[t]), qc[t] & 1u, abort_flag);
+                if (ok) ok = mbar_wait(smem_u32(&bars->k_full[g % KV_STAGES]), (g / KV_STAGES) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                for (int t = 0; t < 2; ++t)
+                    if (it.n_kv[t] > 0) {
+                        issue_qk(t, g % KV_STAGES);
+                        if (it.n_kv[t] == 1) mma_commit(smem_u32(&bars->q_empty[t]));  // the item's only S for this tile
+                    }
+                mma_commit(smem_u32(&bars->k_empty[g % KV_STAGES]));
+                for (int j = 0; j < it.n_max && ok; ++j) {
+                    const uint32_t gj = g + uint32_t(j);
+                    const uint32_t s = gj % KV_STAGES, s1 = (gj + 1) % KV_STAGES;
+                    const uint32_t ph = (gj / KV_STAGES) & 1u, ph1 = ((gj + 1) / KV_STAGES) & 1u;
+                    bool v_ready = false, k_ready = false;
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        if (j >= it.n_kv[t]) continue;
+                        // the item's first O_t = P V overwrites O_t: the previous item's result must have been read
+                        if (j == 0 && !(ok = mbar_wait(smem_u32(&bars->o_empty[t]), (qc[t] & 1u) ^ 1u, abort_flag))) break;
+                        // the first 64 keys of P_t are ready before the rest: start O_t += P_t V on them
+                        if (!(ok = mbar_wait(smem_u32(&bars->p_half[t]), pc[t] & 1u, abort_flag))) break;
+                        if (!v_ready) {
+                            if (!(ok = mbar_wait(smem_u32(&bars->v_full[s]), ph, abort_flag))) break;
+                            v_ready = true;
+                        }
+                        tc_fence_after();
+                        issue_pv(t, s, j == 0, 0, 4);
+                        if (!(ok = mbar_wait(smem_u32(&bars->p_full[t]), pc[t] & 1u, abort_flag))) break;
+                        tc_fence_after();
+                        issue_pv(t, s, j == 0, 4, 8);
+                        ++pc[t];
+                        if (j + 1 == it.n_kv[t]) mma_commit(smem_u32(&bars->o_full[t]));
+                        if (j + 1 < it.n_kv[t]) {
+                            if (!k_ready) {
+                                if (!(ok = mbar_wait(smem_u32(&bars->k_full[s1]), ph1, abort_flag))) break;
+                                k_ready = true;
+                                tc_fence_after();
+                            }
+                            issue_qk(t, s1);
+                            // the item's last S for this tile: its Q buffer may be refilled once this has completed
+                            if (j + 2 == it.n_kv[t]) mma_commit(smem_u32(&bars->q_empty[t]));
+                        }
+                    }
+                    if (!ok) break;
+                    mma_commit(smem_u32(&bars->v_empty[s]));
+                    if (k_ready) mma_commit(smem_u32(&bars->k_empty[s1]));
+                }
+                g += uint32_t(it.n_max);
+                for (int t = 0; t < 2; ++t)
+                    if (it.n_kv[t] > 0) ++qc[t];
+            }
+        }
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SOFTMAX_REGS));
+        // ---------------- softmax + output, one thread per query row ----------------
+        const int t = warp >> 2;
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
+        const uint32_t tS = tmem_base + t * 128 + lane_sel, tO = tmem_base + 256 + t * 128 + lane_sel;
+        uint32_t sc = 0;  // S tiles consumed so far by this tile slot (parity of s_full)
+        uint32_t oc = 0;  // items in which this tile slot took part (parity of o_full)
+        bool ok = true;
+        for (uint32_t w = 0; ok; ++w) {
+            const uint32_t slot = w % WORK_SLOTS, wph = (w / WORK_SLOTS) & 1u;
+            if (!(ok = mbar_wait(smem_u32(&bars->work_full[slot]), wph, abort_flag))) break;
+            const int item = work_item[slot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->work_empty[slot]));
+            if (item < 0) break;
+            const Item it = decode_item(p, item);
+            const int n_kv = it.n_kv[t];
+            if (n_kv == 0) continue;
+            const int64_t qi = int64_t(it.q0[t]) + row_in_tile;
+            float m_used = -CUDART_INF_F, l = 0.f;
+            for (int j = 0; j < n_kv && ok; ++j, ++sc) {
+                if (!(ok = mbar_wait(smem_u32(&bars->s_full[t]), sc & 1u, abort_flag))) break;
+                tc_fence_after();
+                const int64_t k0 = int64_t(j) * BKV;
+                const bool need_mask = (p.causal && k0 + BKV - 1 > it.q0[t]) || (k0 + BKV > p.Sk);
+                int64_t limit = p.Sk;  // keys >= limit are masked for this row
+                if (p.causal && qi + 1 < limit) limit = qi + 1;
+                // the whole score row (128 f32) in registers: one round trip to tensor memory
+                uint32_t r[BKV];
+                tmem_ld_slice(tS, r);
+                tmem_ld_slice(tS + 32, r + 32);
+                tmem_ld_slice(tS + 64, r + 64);
+                tmem_ld_slice(tS + 96, r + 96);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < BKV; ++i)
+                        if (k0 + i >= limit) r[i] = 0xff800000u;  // -inf: exp2 gives 0
+                }
+                // eight independent chains of three-input maxima, then one join
+                float mx8[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    mx8[c] = max3(__uint_as_float(r[16 * c]), __uint_as_float(r[16 * c + 1]), __uint_as_float(r[16 * c + 2]));
+#pragma unroll
+                    for (int i = 3; i + 1 < 16; i += 2)
+                        mx8[c] = max3(mx8[c], __uint_as_float(r[16 * c + i]), __uint_as_float(r[16 * c + i + 1]));
+                    mx8[c] = fmaxf(mx8[c], __uint_as_float(r[16 * c + 15]));
+                }
+                float mx = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) *
+                           p.scale_log2;  // scale > 0: max commutes with it
+                if (j == 0) {
+                    m_used = mx;
+                } else if (__any_sync(0xffffffffu, mx > m_used + RESCALE_THRESHOLD)) {
+                    // tcgen05.ld / tcgen05.st are warp-wide: when ANY row of the warp needs its O rescaled the whole warp
+                    // takes this path, rows that do not need it with alpha = 1. The previous O_t += P_t V has completed:
+                    // its commit precedes the one that released S_t.
+                    const float m_new = (mx > m_used + RESCALE_THRESHOLD) ? mx : m_used;
+                    const float alpha = fast_exp2(m_used - m_new);
+#pragma unroll 1
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld_slice(tO + c, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32_x32(tO + c, o);
+                    }
+                    l *= alpha;
+                    m_used = m_new;
+                }
+                // p = exp2(s * scale - m), row sum, P as bf16 over the first 64 columns of S_t
+                const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2), neg_m = pack2(-m_used, -m_used);
+                uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+#pragma unroll
+                for (int c = 0; c < BKV; c += 32) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float xa, xb;
+                        unpack2(fma2(pack2(__uint_as_float(r[c + i]), __uint_as_float(r[c + i + 1])), sl2, neg_m), xa, xb);
+                        const float a = fast_exp2(xa), b = fast_exp2(xb);
+                        sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(a, b));
+                        pk[i >> 1]         = pack_bf16x2(a, b);
+                    }
+                    if (c == 64) {
+                        // keys 0..63 of P_t were stored a whole chunk of exponentials ago, so this wait does not stall:
+                        // let the tensor core start on them
+                        tmem_st_wait();
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&bars->p_half[t]));
+                    }
+                    tmem_st_32x32_x16(tS + (c >> 1), pk);
+                }
+                {
+                    float s0, s1;
+                    unpack2(add2(sum2[0], sum2[1]), s0, s1);
+                    l += s0 + s1;
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(smem_u32(&bars->p_full[t]));
+            }
+            if (!ok) break;
+            if (!(ok = mbar_wait(smem_u32(&bars->o_full[t]), oc & 1u, abort_flag))) break;
+            ++oc;
+            tc_fence_after();
+            // the finished row of O_t into registers, then hand O_t back: the next item's first O_t = P V may overwrite it
+            uint32_t o[HD];
+            tmem_ld_slice(tO, o);
+            tmem_ld_slice(tO + 32, o + 32);
+            tmem_ld_slice(tO + 64, o + 64);
+            tmem_ld_slice(tO + 96, o + 96);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bars->o_empty[t]));
+            // Normalised rows go out as two [32 rows x 64 columns] pieces per warp: registers -> 128-byte-swizzled shared
+            // memory -> one bulk store each (rows past seq_q are clipped by the store). A row-per-thread store straight
+            // to global memory would touch 32 different lines per instruction.
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const uint32_t buf = sOut + uint32_t(warp) * 4096u, row_addr = buf + uint32_t(lane) * 128u;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                if (half == 1) {
+                    if (lane == 0) bulk_wait_read_0();  // the first piece has left shared memory
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int i = 0; i < 64; i += 8) {
+                    const uint32_t* v = o + half * 64 + i;
+                    const uint32_t a  = row_addr + ((uint32_t(i >> 3) ^ uint32_t(lane & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                                 "r"(pack_bf16x2(__uint_as_float(v[0]) * inv, __uint_as_float(v[1]) * inv)),
+                                 "r"(pack_bf16x2(__uint_as_float(v[2]) * inv, __uint_as_float(v[3]) * inv)),
+                                 "r"(pack_bf16x2(__uint_as_float(v[4]) * inv, __uint_as_float(v[5]) * inv)),
+                                 "r"(pack_bf16x2(__uint_as_float(v[6]) * inv, __uint_as_float(v[7]) * inv))
+                                 : "memory");
+                }
+                fence_proxy_async_smem();  // the bulk store reads shared memory through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_3d(&tmO, buf, half * 64, it.q0[t] + quarter * 32, it.head);
+                    bulk_commit();
+                }
+            }
+            if (p.lse && qi < p.Sq)
+                p.lse[int64_t(it.head) * p.Sq + qi] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
+            // the staging piece is rewritten by this warp's next item: its last store must have read it by then
+            if (lane == 0) bulk_wait_read_0();
+            __syncwarp();
+        }
+        if (lane == 0) bulk_wait_all();  // every store has landed before the CTA may exit
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_flag) *p.status = MIMK_E_DEVICE_WAIT;
+}
+
+}  // namespace
+
+int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s) {
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    // per device: the counters' address and the shared-memory opt-in
+    static int* counters[64]  = {};
+    static unsigned next_slot[64] = {};
+    static std::mutex mutex;
+    const int di = dev->device & 63;
+    int* counter = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mutex);
+        if (!counters[di]) {
+            void* sym = nullptr;
+            MIMK_CUDA_TRY(cudaGetSymbolAddress(&sym, g_work_counters));
+            MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            counters[di] = static_cast<int*>(sym);
+        }
+        counter = counters[di] + (next_slot[di]++ % COUNTER_SLOTS);
+    }
+    CUtensorMap tQ, tK, tV, tO;
+    const uint64_t row = HD * 2;
+    MIMK_TRY(make_tmap_bf16_3d(&tO, d.o, HD, uint64_t(d.seq_q), uint64_t(d.batch_heads), row, uint64_t(d.seq_q) * row, 64, 32));
+    MIMK_TRY(make_tmap_bf16_3d(&tQ, d.q, HD, uint64_t(d.seq_q), uint64_t(d.batch_heads), row, uint64_t(d.seq_q) * row, 64, BQ));
+    MIMK_TRY(make_tmap_bf16_3d(&tK, d.k, HD, uint64_t(d.seq_k), uint64_t(d.batch_heads), row, uint64_t(d.seq_k) * row, 64, BKV));
+    MIMK_TRY(make_tmap_bf16_3d(&tV, d.v, HD, uint64_t(d.seq_k), uint64_t(d.batch_heads), row, uint64_t(d.seq_k) * row, 64, BKV));
+    Params p;
+    p.Sq = d.seq_q, p.Sk = d.seq_k, p.BH = int(d.batch_heads);
+    p.O          = static_cast<__nv_bfloat16*>(d.o);
+    p.lse        = d.lse;
+    p.scale_log2 = d.scale * 1.4426950408889634f;
+    p.causal     = d.causal;
+    p.status     = dev->status_dev;
+    const int64_t pairs = (d.seq_q + 2 * BQ - 1) / (2 * BQ);
+    if (pairs * d.batch_heads >= (int64_t(1) << 30)) return MIMK_E_UNSUPPORTED;
+    p.num_pairs  = int(pairs);
+    p.head_group = d.causal ? 8 : 1;
+    p.num_items  = int(pairs * d.batch_heads);
+    p.counter = counter;
+    MIMK_CUDA_TRY(cudaMemsetAsync(p.counter, 0, sizeof(int), s));
+    const int grid = int(p.num_items < dev->sm_count ? p.num_items : dev->sm_count);
+    attn_tc_persistent_kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, tO, p);
+    return launch_status();
+}
+
+}  // namespace mimk
