@@ -208,15 +208,14 @@ extern "C" int mimk_attn_fwd(const mimk_attn_desc* d, void* stream) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (attn_tc_supported(*d)) {
         // The persistent kernel hides the per-item set-up and drain (about 6 us against 1.9 us per step of 128 keys):
-        // 24 % faster on items of 4 steps, 10 % on 8, level from 16 on; on long unmasked items, where the one-item kernel
-        // already runs at the clock the power cap allows, it measured 1 % slower. MIMK_ATTN_PERSIST=0 / 1 forces one.
+        // 27 % faster on items of 4 steps, 13 % on 8, 3 % on 32; config C4 (causal, mean 17 steps) 0.493 against 0.511 ms.
+        // MIMK_ATTN_PERSIST=0 selects the one-item-per-CTA kernel (for A/B measurements).
         static int persistent = -1;
         if (persistent < 0) {
             const char* e = getenv("MIMK_ATTN_PERSIST");
-            persistent    = !e ? 2 : (e[0] == '0' ? 0 : 1);
+            persistent    = (e && e[0] == '0') ? 0 : 1;
         }
-        const int64_t steps = (d->seq_k + 127) / 128;
-        const bool use_p    = persistent == 2 ? (d->causal || steps < 24) : persistent == 1;
+        const bool use_p = persistent != 0;
         return use_p ? attn_tc_persistent(*d, s) : attn_tc(*d, s);
     }
     return attn_simt(*d, s);

@@ -36,8 +36,12 @@ constexpr int KV_STAGES = 2;
 constexpr int NUM_THREADS = 384;  // softmax tile 0, softmax tile 1, {producer, MMA, two idle warps}
 constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
 // register budget moved between warpgroups with setmaxnreg; must fit what the CTA got at launch (see attn_tc.cu)
-constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 208, OTHER_REGS = 88;
-static_assert(2 * 128 * SOFTMAX_REGS + 128 * OTHER_REGS <= LAUNCH_REGS * NUM_THREADS, "setmaxnreg budget exceeds the CTA's registers");
+constexpr int LAUNCH_REGS = 168;
+template <int SOFTMAX_REGS, int OTHER_REGS>
+struct RegSplit {
+    static_assert(2 * 128 * SOFTMAX_REGS + 128 * OTHER_REGS <= LAUNCH_REGS * NUM_THREADS, "setmaxnreg budget exceeds the CTA's registers");
+    static_assert(SOFTMAX_REGS % 8 == 0 && OTHER_REGS % 8 == 0, "setmaxnreg takes multiples of 8");
+};
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 constexpr int WORK_SLOTS = 2;
 
@@ -105,9 +109,11 @@ __device__ __forceinline__ Item decode_item(const Params& p, int item) {
     return it;
 }
 
+template <int SOFTMAX_REGS, int OTHER_REGS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const Params p) {
+    (void)sizeof(RegSplit<SOFTMAX_REGS, OTHER_REGS>);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base     = (raw_addr + 1023u) & ~1023u;
@@ -224,9 +230,9 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                     mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, vb + uint64_t((k * 2048) >> 4), idesc_pv,
                                (!first || k > 0) ? 1u : 0u);
             };
-            uint32_t g = 0;            // K/V tiles consumed so far
-            uint32_t qc[2] = {0, 0};   // items in which tile slot t took part (parity of q_full / o_empty)
-            uint32_t pc[2] = {0, 0};   // P tiles consumed per tile slot (parity of p_half / p_full)
+            uint32_t g = 0;                // K/V tiles consumed so far
+            uint32_t qc0 = 0, qc1 = 0;     // items in which tile slot t took part (parity of q_full / o_empty)
+            uint32_t pc0 = 0, pc1 = 0;     // P tiles consumed per tile slot (parity of p_half / p_full)
             bool ok = true;
             for (uint32_t w = 0; ok; ++w) {
                 const uint32_t slot = w % WORK_SLOTS, wph = (w / WORK_SLOTS) & 1u;
@@ -235,59 +241,66 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 mbar_arrive(smem_u32(&bars->work_empty[slot]));
                 if (item < 0) break;
                 const Item it = decode_item(p, item);
-                if (it.n_max == 0) continue;
+                const int n0 = it.n_kv[0], n1 = it.n_kv[1], n_max = it.n_max;  // scalars: nothing below indexes an array by tile
+                if (n_max == 0) continue;
                 // first key tile: S_t = Q_t K_0^T for both tiles
-                for (int t = 0; t < 2 && ok; ++t)
-                    if (it.n_kv[t] > 0) ok = mbar_wait(smem_u32(&bars->q_full[t]), qc[t] & 1u, abort_flag);
+                if (n0 > 0) ok = mbar_wait(smem_u32(&bars->q_full[0]), qc0 & 1u, abort_flag);
+                if (ok && n1 > 0) ok = mbar_wait(smem_u32(&bars->q_full[1]), qc1 & 1u, abort_flag);
                 if (ok) ok = mbar_wait(smem_u32(&bars->k_full[g % KV_STAGES]), (g / KV_STAGES) & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                for (int t = 0; t < 2; ++t)
-                    if (it.n_kv[t] > 0) {
-                        issue_qk(t, g % KV_STAGES);
-                        if (it.n_kv[t] == 1) mma_commit(smem_u32(&bars->q_empty[t]));  // the item's only S for this tile
-                    }
+                if (n0 > 0) {
+                    issue_qk(0, g % KV_STAGES);
+                    if (n0 == 1) mma_commit(smem_u32(&bars->q_empty[0]));  // the item's only S for this tile
+                }
+                if (n1 > 0) {
+                    issue_qk(1, g % KV_STAGES);
+                    if (n1 == 1) mma_commit(smem_u32(&bars->q_empty[1]));
+                }
                 mma_commit(smem_u32(&bars->k_empty[g % KV_STAGES]));
-                for (int j = 0; j < it.n_max && ok; ++j) {
+                for (int j = 0; j < n_max && ok; ++j) {
                     const uint32_t gj = g + uint32_t(j);
                     const uint32_t s = gj % KV_STAGES, s1 = (gj + 1) % KV_STAGES;
                     const uint32_t ph = (gj / KV_STAGES) & 1u, ph1 = ((gj + 1) / KV_STAGES) & 1u;
                     bool v_ready = false, k_ready = false;
-                    for (int t = 0; t < 2 && ok; ++t) {
-                        if (j >= it.n_kv[t]) continue;
+                    // one key tile of one query tile: O_t += P_t V_j, then S_t = Q_t K_{j+1}^T
+                    auto tile_step = [&](const int t, const int n_kv, const uint32_t qc, uint32_t& pc) -> bool {
                         // the item's first O_t = P V overwrites O_t: the previous item's result must have been read
-                        if (j == 0 && !(ok = mbar_wait(smem_u32(&bars->o_empty[t]), (qc[t] & 1u) ^ 1u, abort_flag))) break;
+                        if (j == 0 && !mbar_wait(smem_u32(&bars->o_empty[t]), (qc & 1u) ^ 1u, abort_flag)) return false;
                         // the first 64 keys of P_t are ready before the rest: start O_t += P_t V on them
-                        if (!(ok = mbar_wait(smem_u32(&bars->p_half[t]), pc[t] & 1u, abort_flag))) break;
+                        if (!mbar_wait(smem_u32(&bars->p_half[t]), pc & 1u, abort_flag)) return false;
                         if (!v_ready) {
-                            if (!(ok = mbar_wait(smem_u32(&bars->v_full[s]), ph, abort_flag))) break;
+                            if (!mbar_wait(smem_u32(&bars->v_full[s]), ph, abort_flag)) return false;
                             v_ready = true;
                         }
                         tc_fence_after();
                         issue_pv(t, s, j == 0, 0, 4);
-                        if (!(ok = mbar_wait(smem_u32(&bars->p_full[t]), pc[t] & 1u, abort_flag))) break;
+                        if (!mbar_wait(smem_u32(&bars->p_full[t]), pc & 1u, abort_flag)) return false;
                         tc_fence_after();
                         issue_pv(t, s, j == 0, 4, 8);
-                        ++pc[t];
-                        if (j + 1 == it.n_kv[t]) mma_commit(smem_u32(&bars->o_full[t]));
-                        if (j + 1 < it.n_kv[t]) {
+                        ++pc;
+                        if (j + 1 == n_kv) mma_commit(smem_u32(&bars->o_full[t]));
+                        if (j + 1 < n_kv) {
                             if (!k_ready) {
-                                if (!(ok = mbar_wait(smem_u32(&bars->k_full[s1]), ph1, abort_flag))) break;
+                                if (!mbar_wait(smem_u32(&bars->k_full[s1]), ph1, abort_flag)) return false;
                                 k_ready = true;
                                 tc_fence_after();
                             }
                             issue_qk(t, s1);
                             // the item's last S for this tile: its Q buffer may be refilled once this has completed
-                            if (j + 2 == it.n_kv[t]) mma_commit(smem_u32(&bars->q_empty[t]));
+                            if (j + 2 == n_kv) mma_commit(smem_u32(&bars->q_empty[t]));
                         }
-                    }
+                        return true;
+                    };
+                    if (j < n0) ok = tile_step(0, n0, qc0, pc0);
+                    if (ok && j < n1) ok = tile_step(1, n1, qc1, pc1);
                     if (!ok) break;
                     mma_commit(smem_u32(&bars->v_empty[s]));
                     if (k_ready) mma_commit(smem_u32(&bars->k_empty[s1]));
                 }
-                g += uint32_t(it.n_max);
-                for (int t = 0; t < 2; ++t)
-                    if (it.n_kv[t] > 0) ++qc[t];
+                g += uint32_t(n_max);
+                qc0 += n0 > 0 ? 1u : 0u;
+                qc1 += n1 > 0 ? 1u : 0u;
             }
         }
       }
@@ -310,15 +323,16 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             if (lane == 0) mbar_arrive(smem_u32(&bars->work_empty[slot]));
             if (item < 0) break;
             const Item it = decode_item(p, item);
-            const int n_kv = it.n_kv[t];
+            const int n_kv = t ? it.n_kv[1] : it.n_kv[0];
+            const int q0   = t ? it.q0[1] : it.q0[0];
             if (n_kv == 0) continue;
-            const int64_t qi = int64_t(it.q0[t]) + row_in_tile;
+            const int64_t qi = int64_t(q0) + row_in_tile;
             float m_used = -CUDART_INF_F, l = 0.f;
             for (int j = 0; j < n_kv && ok; ++j, ++sc) {
                 if (!(ok = mbar_wait(smem_u32(&bars->s_full[t]), sc & 1u, abort_flag))) break;
                 tc_fence_after();
                 const int64_t k0 = int64_t(j) * BKV;
-                const bool need_mask = (p.causal && k0 + BKV - 1 > it.q0[t]) || (k0 + BKV > p.Sk);
+                const bool need_mask = (p.causal && k0 + BKV - 1 > q0) || (k0 + BKV > p.Sk);
                 int64_t limit = p.Sk;  // keys >= limit are masked for this row
                 if (p.causal && qi + 1 < limit) limit = qi + 1;
                 // the whole score row (128 f32) in registers: one round trip to tensor memory
@@ -435,7 +449,7 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 fence_proxy_async_smem();  // the bulk store reads shared memory through the async proxy
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_3d(&tmO, buf, half * 64, it.q0[t] + quarter * 32, it.head);
+                    tma_store_3d(&tmO, buf, half * 64, q0 + quarter * 32, it.head);
                     bulk_commit();
                 }
             }
@@ -476,7 +490,8 @@ int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s) {
         if (!counters[di]) {
             void* sym = nullptr;
             MIMK_CUDA_TRY(cudaGetSymbolAddress(&sym, g_work_counters));
-            MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_persistent_kernel<208, 88>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_persistent_kernel<200, 104>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
             counters[di] = static_cast<int*>(sym);
         }
         counter = counters[di] + (next_slot[di]++ % COUNTER_SLOTS);
@@ -502,7 +517,15 @@ int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s) {
     p.counter = counter;
     MIMK_CUDA_TRY(cudaMemsetAsync(p.counter, 0, sizeof(int), s));
     const int grid = int(p.num_items < dev->sm_count ? p.num_items : dev->sm_count);
-    attn_tc_persistent_kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, tO, p);
+    static int wide = -1;  // MIMK_ATTN_REGS=200 gives the producer / MMA warps 104 registers and the softmax warps 200
+    if (wide < 0) {
+        const char* e = getenv("MIMK_ATTN_REGS");
+        wide          = (e && atoi(e) == 200) ? 0 : 1;
+    }
+    if (wide)
+        attn_tc_persistent_kernel<208, 88><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, tO, p);
+    else
+        attn_tc_persistent_kernel<200, 104><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, tO, p);
     return launch_status();
 }
 
