@@ -453,7 +453,8 @@ def run_reference(args):
     import oracle as mo
     mo.build()
     W = WORKLOADS[args.workload]
-    for _ in range(min(args.warmup, 1)):
+    warm = min(args.warmup, 3)
+    for _ in range(warm):
         W.cpu_sample(mo, np)
     vals, sample = [], ""
     t0 = time.perf_counter()
@@ -462,10 +463,11 @@ def run_reference(args):
         vals.append(v)
         if time.perf_counter() - t0 > 150:
             break
+    ms_per_step = (time.perf_counter() - t0) * 1e3 / len(vals)   # one step = one pass over the bounded sample
     val = statistics.mean(vals)
     unit = W.unit
     line = {"impl": "reference", "metric": W.metric, "value": val, "unit": unit, "n_gpus": args.gpus,
-            "steps": len(vals), "warmup": min(args.warmup, 1), "ms_per_step": None, "higher_is_better": True,
+            "steps": len(vals), "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": W.dtype, "data": "synthetic",
             "config": {"workload": W.name},
             "cpu_baseline": {"value": val, "unit": unit, "cores": 1, "kind": "port", "sample": sample,
