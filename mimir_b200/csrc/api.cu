@@ -206,18 +206,16 @@ extern "C" int mimk_attn_fwd(const mimk_attn_desc* d, void* stream) {
     if (d->batch_heads == 0 || d->seq_q == 0 || d->head_dim == 0) return MIMK_OK;
     if (!d->q || !d->o || (d->seq_k > 0 && (!d->k || !d->v))) return MIMK_E_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (attn_tc_supported(*d)) {
-        // The persistent kernel hides the per-item set-up and drain (about 6 us against 1.9 us per step of 128 keys):
-        // 27 % faster on items of 4 steps, 13 % on 8, 3 % on 32; config C4 (causal, mean 17 steps) 0.493 against 0.511 ms.
-        // MIMK_ATTN_PERSIST=0 selects the one-item-per-CTA kernel (for A/B measurements).
-        static int persistent = -1;
-        if (persistent < 0) {
-            const char* e = getenv("MIMK_ATTN_PERSIST");
-            persistent    = (e && e[0] == '0') ? 0 : 1;
-        }
-        const bool use_p = persistent != 0;
-        return use_p ? attn_tc_persistent(*d, s) : attn_tc(*d, s);
+    // The persistent kernel hides the per-item set-up and drain (about 6 us against 1.9 us per step of 128 keys):
+    // 27 % faster on items of 4 steps, 13 % on 8, 3 % on 32; config C4 (causal, mean 17 steps) 0.493 against 0.511 ms.
+    // MIMK_ATTN_PERSIST=0 selects the one-item-per-CTA kernel (head_dim 128 only; for A/B measurements).
+    static int persistent = -1;
+    if (persistent < 0) {
+        const char* e = getenv("MIMK_ATTN_PERSIST");
+        persistent    = (e && e[0] == '0') ? 0 : 1;
     }
+    if (persistent && attn_tc_persistent_supported(*d)) return attn_tc_persistent(*d, s);
+    if (attn_tc_supported(*d)) return attn_tc(*d, s);
     return attn_simt(*d, s);
 }
 

@@ -29,9 +29,10 @@ using namespace attn;
 
 namespace {
 
-constexpr int BQ = 128, BKV = 128, HD = 128;
-constexpr int TILE_BYTES = 128 * 128 * 2;  // a [128 x 128] bf16 tile = two swizzle atoms of [128 x 64]
-constexpr int ATOM_BYTES = TILE_BYTES / 2;
+constexpr int BQ = 128, BKV = 128;
+constexpr int ATOM_BYTES = 128 * 64 * 2;  // one 128-byte-swizzle atom: 128 rows x 64 bf16
+// a [128 rows x head_dim] bf16 tile = head_dim / 64 atoms side by side
+__host__ __device__ constexpr int tile_bytes(int hd) { return (hd / 64) * ATOM_BYTES; }
 constexpr int KV_STAGES = 2;
 constexpr int NUM_THREADS = 384;  // softmax tile 0, softmax tile 1, {producer, MMA, two idle warps}
 constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
@@ -56,9 +57,9 @@ struct Bars {
     int abort_flag;
 };
 constexpr int OUT_STAGE_BYTES = 8 * 4096;  // per softmax warp: 32 rows x 128 bytes of O on their way to a bulk store
-constexpr int SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + OUT_STAGE_BYTES + 1024 + 256;
+__host__ __device__ constexpr int smem_bytes(int hd) { return (2 + 2 * KV_STAGES) * tile_bytes(hd) + OUT_STAGE_BYTES + 1024 + 256; }
 static_assert(sizeof(Bars) <= 256, "barrier block too large");
-static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
+static_assert(smem_bytes(128) <= 232448, "more shared memory than a CTA can have");
 
 struct Params {
     int64_t Sq, Sk;
@@ -109,11 +110,15 @@ __device__ __forceinline__ Item decode_item(const Params& p, int item) {
     return it;
 }
 
-template <int SOFTMAX_REGS, int OTHER_REGS>
+// HD: head_dim, 64 or 128 (one or two swizzle atoms per tile row; O_t takes HD tensor-memory columns).
+template <int HD, int SOFTMAX_REGS, int OTHER_REGS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const Params p) {
     (void)sizeof(RegSplit<SOFTMAX_REGS, OTHER_REGS>);
+    static_assert(HD == 64 || HD == 128, "head_dim 64 or 128");
+    constexpr int TILE_BYTES = tile_bytes(HD);
+    constexpr int ATOMS = HD / 64;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base     = (raw_addr + 1023u) & ~1023u;
@@ -184,8 +189,9 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                     if (!(ok = mbar_wait(smem_u32(&bars->q_empty[t]), (qc[t] & 1u) ^ 1u, abort_flag))) break;
                     const uint32_t qf = smem_u32(&bars->q_full[t]);
                     mbar_expect_tx(qf, TILE_BYTES);
-                    tma_load_3d(sQ + t * TILE_BYTES, &tmQ, 0, it.q0[t], it.head, qf);
-                    tma_load_3d(sQ + t * TILE_BYTES + ATOM_BYTES, &tmQ, 64, it.q0[t], it.head, qf);
+#pragma unroll
+                    for (int a = 0; a < ATOMS; ++a)
+                        tma_load_3d(sQ + t * TILE_BYTES + a * ATOM_BYTES, &tmQ, a * 64, it.q0[t], it.head, qf);
                     ++qc[t];
                 }
                 for (int j = 0; j < it.n_max && ok; ++j, ++g) {
@@ -193,13 +199,15 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                     if (!(ok = mbar_wait(smem_u32(&bars->k_empty[s]), ph ^ 1u, abort_flag))) break;
                     const uint32_t kf = smem_u32(&bars->k_full[s]);
                     mbar_expect_tx(kf, TILE_BYTES);
-                    tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, j * BKV, it.head, kf);
-                    tma_load_3d(sK + s * TILE_BYTES + ATOM_BYTES, &tmK, 64, j * BKV, it.head, kf);
+#pragma unroll
+                    for (int a = 0; a < ATOMS; ++a)
+                        tma_load_3d(sK + s * TILE_BYTES + a * ATOM_BYTES, &tmK, a * 64, j * BKV, it.head, kf);
                     if (!(ok = mbar_wait(smem_u32(&bars->v_empty[s]), ph ^ 1u, abort_flag))) break;
                     const uint32_t vf = smem_u32(&bars->v_full[s]);
                     mbar_expect_tx(vf, TILE_BYTES);
-                    tma_load_3d(sV + s * TILE_BYTES, &tmV, 0, j * BKV, it.head, vf);
-                    tma_load_3d(sV + s * TILE_BYTES + ATOM_BYTES, &tmV, 64, j * BKV, it.head, vf);
+#pragma unroll
+                    for (int a = 0; a < ATOMS; ++a)
+                        tma_load_3d(sV + s * TILE_BYTES + a * ATOM_BYTES, &tmV, a * 64, j * BKV, it.head, vf);
                 }
             }
         }
@@ -417,21 +425,19 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             tc_fence_after();
             // the finished row of O_t into registers, then hand O_t back: the next item's first O_t = P V may overwrite it
             uint32_t o[HD];
-            tmem_ld_slice(tO, o);
-            tmem_ld_slice(tO + 32, o + 32);
-            tmem_ld_slice(tO + 64, o + 64);
-            tmem_ld_slice(tO + 96, o + 96);
+#pragma unroll
+            for (int c = 0; c < HD; c += 32) tmem_ld_slice(tO + c, o + c);
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(smem_u32(&bars->o_empty[t]));
-            // Normalised rows go out as two [32 rows x 64 columns] pieces per warp: registers -> 128-byte-swizzled shared
+            // Normalised rows go out as [32 rows x 64 columns] pieces (one per 64 of head_dim) per warp: registers -> 128-byte-swizzled shared
             // memory -> one bulk store each (rows past seq_q are clipped by the store). A row-per-thread store straight
             // to global memory would touch 32 different lines per instruction.
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const uint32_t buf = sOut + uint32_t(warp) * 4096u, row_addr = buf + uint32_t(lane) * 128u;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                if (half == 1) {
+            for (int half = 0; half < ATOMS; ++half) {
+                if (half > 0) {
                     if (lane == 0) bulk_wait_read_0();  // the first piece has left shared memory
                     __syncwarp();
                 }
@@ -473,7 +479,31 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     if (threadIdx.x == 0 && *abort_flag) *p.status = MIMK_E_DEVICE_WAIT;
 }
 
+template <int HD>
+int launch_persistent(const CUtensorMap& tQ, const CUtensorMap& tK, const CUtensorMap& tV, const CUtensorMap& tO, const Params& p,
+                      int grid, cudaStream_t s) {
+    static bool configured[64] = {};  // per template instance and device: the shared-memory opt-in is a per-device setting
+    int dev = 0;
+    MIMK_CUDA_TRY(cudaGetDevice(&dev));
+    if (!configured[dev & 63]) {
+        MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_persistent_kernel<HD, 208, 88>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(HD)));
+        configured[dev & 63] = true;
+    }
+    attn_tc_persistent_kernel<HD, 208, 88><<<grid, NUM_THREADS, smem_bytes(HD), s>>>(tQ, tK, tV, tO, p);
+    return launch_status();
+}
+
 }  // namespace
+
+int attn_tc_persistent_supported(const mimk_attn_desc& d) {
+    if (d.dtype != MIMK_BF16 || (d.head_dim != 64 && d.head_dim != 128)) return 0;
+    if (d.seq_k <= 0 || d.seq_q <= 0) return 0;
+    if (d.causal && d.seq_q != d.seq_k) return 0;
+    if (d.batch_heads > 65535 || d.seq_q >= (int64_t(1) << 31) || d.seq_k >= (int64_t(1) << 31)) return 0;
+    if (!aligned16(d.q) || !aligned16(d.k) || !aligned16(d.v) || !aligned16(d.o)) return 0;
+    if (!(d.scale > 0.f)) return 0;
+    return 1;
+}
 
 int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s) {
     int st          = MIMK_OK;
@@ -490,13 +520,12 @@ int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s) {
         if (!counters[di]) {
             void* sym = nullptr;
             MIMK_CUDA_TRY(cudaGetSymbolAddress(&sym, g_work_counters));
-            MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_persistent_kernel<208, 88>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-            MIMK_CUDA_TRY(cudaFuncSetAttribute(attn_tc_persistent_kernel<200, 104>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
             counters[di] = static_cast<int*>(sym);
         }
         counter = counters[di] + (next_slot[di]++ % COUNTER_SLOTS);
     }
     CUtensorMap tQ, tK, tV, tO;
+    const uint64_t HD  = uint64_t(d.head_dim);
     const uint64_t row = HD * 2;
     MIMK_TRY(make_tmap_bf16_3d(&tO, d.o, HD, uint64_t(d.seq_q), uint64_t(d.batch_heads), row, uint64_t(d.seq_q) * row, 64, 32));
     MIMK_TRY(make_tmap_bf16_3d(&tQ, d.q, HD, uint64_t(d.seq_q), uint64_t(d.batch_heads), row, uint64_t(d.seq_q) * row, 64, BQ));
@@ -517,16 +546,7 @@ int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s) {
     p.counter = counter;
     MIMK_CUDA_TRY(cudaMemsetAsync(p.counter, 0, sizeof(int), s));
     const int grid = int(p.num_items < dev->sm_count ? p.num_items : dev->sm_count);
-    static int wide = -1;  // MIMK_ATTN_REGS=200 gives the producer / MMA warps 104 registers and the softmax warps 200
-    if (wide < 0) {
-        const char* e = getenv("MIMK_ATTN_REGS");
-        wide          = (e && atoi(e) == 200) ? 0 : 1;
-    }
-    if (wide)
-        attn_tc_persistent_kernel<208, 88><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, tO, p);
-    else
-        attn_tc_persistent_kernel<200, 104><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tQ, tK, tV, tO, p);
-    return launch_status();
+    return d.head_dim == 64 ? launch_persistent<64>(tQ, tK, tV, tO, p, grid, s) : launch_persistent<128>(tQ, tK, tV, tO, p, grid, s);
 }
 
 }  // namespace mimk

@@ -59,7 +59,8 @@ int permute_copy(const void* in, void* out, int esize, int rank, const int64_t* 
 int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_supported(const mimk_attn_desc& d);
 int attn_tc(const mimk_attn_desc& d, cudaStream_t s);
-// the persistent form (one CTA per SM pulls work items; hand-over between items pipelined); same support set
+// the persistent form (one CTA per SM pulls work items; hand-over between items pipelined)
+int attn_tc_persistent_supported(const mimk_attn_desc& d);  // bf16, head_dim 64 or 128
 int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s);
 
 // ---- device side ----------------------------------------------------------------------------------

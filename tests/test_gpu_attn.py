@@ -38,7 +38,7 @@ def test_attention_f32(T, bh, sq, sk, d, causal):
 
 
 @pytest.mark.parametrize("bh,s,d", [(2, 128, 128), (2, 256, 128), (3, 384, 128), (1, 1024, 128), (2, 200, 128),
-                                    (2, 512, 64)])
+                                    (2, 512, 64), (3, 300, 64), (2, 1024, 64), (5, 129, 64), (9, 4096 + 64, 64)])
 @pytest.mark.parametrize("causal", [True, False])
 def test_attention_bf16(T, bh, s, d, causal):
     q, k, v = (randn((bh, s, d), 10 + i, 1.0, torch.bfloat16) for i in range(3))
@@ -101,13 +101,14 @@ def test_attention_large_score_range(T):
         assert nerr(f64(o), want) <= TOL_BF16
 
 
+@pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("s", [1, 2, 127, 129, 255, 257, 383])
 @pytest.mark.parametrize("causal", [True, False])
-def test_attention_bf16_ragged_lengths(T, s, causal):
+def test_attention_bf16_ragged_lengths(T, s, causal, d):
     # query / key counts around the 128-row tile and 256-row pair boundaries: out-of-range rows are zero-filled by TMA
     # on the way in and never stored on the way out
-    q, k, v = (randn((3, s, 128), 50 + i + s, 1.0, torch.bfloat16) for i in range(3))
-    guard = torch.full((3, s + 8, 128), 7.0, dtype=torch.bfloat16, device="cuda")   # rows past s must stay untouched
+    q, k, v = (randn((3, s, d), 50 + i + s, 1.0, torch.bfloat16) for i in range(3))
+    guard = torch.full((3, s + 8, d), 7.0, dtype=torch.bfloat16, device="cuda")   # rows past s must stay untouched
     o = T.attention(q, k, v, scale=0.09, causal=causal)
     T.device_status()
     want = mo.attention(bits(q), bits(k), bits(v), scale=0.09, causal=causal, bf16=True)

@@ -82,7 +82,7 @@ def test_attention_shapes(T, seed):
     if seed % 3 == 0:
         dtype, d, tol = torch.float32, int(rng.choice([8, 32, 64, 80])), 1e-4
     else:
-        dtype, d, tol = torch.bfloat16, 128, TOL_BF16
+        dtype, d, tol = torch.bfloat16, int(rng.choice([64, 128])), TOL_BF16
     q, k, v = (randn((bh, s, d), seed * 3 + i, 1.0, dtype) for i in range(3))
     scale = float(d) ** -0.5
     o = T.attention(q, k, v, scale=scale, causal=causal)
