@@ -333,6 +333,11 @@ int mimk_host_gemm(const mimk_gemm_desc* desc);
 int mimk_host_attn_fwd(const mimk_attn_desc* desc);
 /* desc holds host pointers (x, w1, w3, w2, y); h is ignored. */
 int mimk_host_mlp_gated(const mimk_mlp_desc* desc);
+/* mimk_map_reduce_post with HOST operands: every input and epilogue input is uploaded, the result comes back in
+ * desc->out -- the per-operation wrapper of the reference for ANY map_reduce_post instance
+ * (src/mim/plug/gpu/phase/lower_map_reduce.cpp:111-126, 267-297, 317-395). Cells the write map never stores keep the
+ * bytes the caller's buffer held. */
+int mimk_host_map_reduce_post(const mimk_mrp_desc* desc);
 /* Page-lock / unlock a host range so that the copies above are asynchronous DMA. */
 int mimk_host_register(void* ptr, uint64_t bytes);
 int mimk_host_unregister(void* ptr);

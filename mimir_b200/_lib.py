@@ -25,7 +25,7 @@ SYMBOLS = (
     "mimk_status_str", "mimk_abi_version", "mimk_last_cuda_error", "mimk_device_check", "mimk_device_status", "mimk_selftest_wait_expiry",
     "mimk_gemm", "mimk_gemm_flat", "mimk_gemm_gather", "mimk_reduce", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map",
     "mimk_attn_fwd", "mimk_mlp_gated", "mimk_map_reduce_post", "mimk_mrp_classify", "mimk_chain_order", "mimk_chain_cost",
-    "mimk_host_rows", "mimk_host_rows_pair", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_register",
+    "mimk_host_rows", "mimk_host_rows_pair", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_map_reduce_post", "mimk_host_register",
     "mimk_host_unregister", "mimk_host_release",
 )
 
@@ -129,6 +129,7 @@ def lib() -> C.CDLL:
         L.mimk_host_rows.argtypes = [ci, vp, vp, vp, ci, ci, i64, i64, cf]
         L.mimk_host_rows_pair.argtypes = [vp, vp, vp, vp, ci, ci, i64, i64, cf]
         L.mimk_host_gemm.argtypes = [C.POINTER(GemmDesc)]
+        L.mimk_host_map_reduce_post.argtypes = [C.POINTER(MrpDesc)]
         L.mimk_host_attn_fwd.argtypes = [C.POINTER(AttnDesc)]
         L.mimk_host_mlp_gated.argtypes = [C.POINTER(MlpDesc)]
         L.mimk_host_register.argtypes = [vp, C.c_uint64]

@@ -232,6 +232,69 @@ extern "C" int mimk_host_attn_fwd(const mimk_attn_desc* h) {
     return mimk_device_status(c->up);
 }
 
+// The generic operation with host operands: what the reference's wrapper does around every map_reduce_post --
+// upload each input and epilogue input, run, download the result (lower_map_reduce.cpp:111-126, 267-297).
+extern "C" int mimk_host_map_reduce_post(const mimk_mrp_desc* h) {
+    if (!h) return MIMK_E_ARG;
+    if (h->ro < 0 || h->rn < h->ro || h->rn > MIMK_MRP_MAX_LOOPS || h->ro > MIMK_MRP_MAX_RANK) return MIMK_E_ARG;
+    if (h->nis < 0 || h->nis > MIMK_MRP_MAX_INPUTS || h->nps < 0 || h->nps > 1) return MIMK_E_ARG;
+    auto elems = [](const int64_t* shape, int rank, size_t* out) {
+        size_t n = 1;
+        for (int j = 0; j < rank; ++j) {
+            if (shape[j] < 0) return false;
+            n *= size_t(shape[j]);
+        }
+        *out = n;
+        return true;
+    };
+    auto known = [](int dt) { return dt == MIMK_F32 || dt == MIMK_BF16 || dt == MIMK_I32 || dt == MIMK_I64; };
+    size_t in_bytes[MIMK_MRP_MAX_INPUTS] = {}, post_bytes = 0, out_elems = 0, total = 0;
+    for (int i = 0; i < h->nis; ++i) {
+        size_t n = 0;
+        if (!known(h->in_dtype[i]) || h->in_map[i].rows < 0 || h->in_map[i].rows > MIMK_MRP_MAX_RANK) return MIMK_E_ARG;
+        if (!elems(h->in_shape[i], h->in_map[i].rows, &n)) return MIMK_E_ARG;
+        in_bytes[i] = n * dtype_size(h->in_dtype[i]);
+        if (in_bytes[i] && !h->in[i]) return MIMK_E_ARG;
+        total += round256(in_bytes[i]);
+    }
+    if (h->nps == 1) {
+        size_t n = 0;
+        if (!known(h->post_dtype[0]) || h->post_map[0].rows < 0 || h->post_map[0].rows > MIMK_MRP_MAX_RANK) return MIMK_E_ARG;
+        if (!elems(h->post_shape[0], h->post_map[0].rows, &n)) return MIMK_E_ARG;
+        post_bytes = n * dtype_size(h->post_dtype[0]);
+        if (post_bytes && !h->post_in[0]) return MIMK_E_ARG;
+        total += round256(post_bytes);
+    }
+    if (!known(h->out_dtype) || !elems(h->so, h->ro, &out_elems)) return MIMK_E_ARG;
+    const size_t out_bytes = out_elems * dtype_size(h->out_dtype);
+    if (out_bytes && !h->out) return MIMK_E_ARG;
+    total += round256(out_bytes);
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    HostCtx* c = nullptr;
+    MIMK_TRY(get_ctx(&c));
+    if (out_bytes == 0) return MIMK_OK;
+    uint8_t* base = nullptr;
+    MIMK_TRY(arena(*c, total, &base));
+    mimk_mrp_desc d = *h;
+    uint8_t* p      = base;
+    for (int i = 0; i < h->nis; ++i) {
+        d.in[i] = p;
+        if (in_bytes[i]) MIMK_CUDA_TRY(cudaMemcpyAsync(p, h->in[i], in_bytes[i], cudaMemcpyHostToDevice, c->up));
+        p += round256(in_bytes[i]);
+    }
+    if (h->nps == 1) {
+        d.post_in[0] = p;
+        if (post_bytes) MIMK_CUDA_TRY(cudaMemcpyAsync(p, h->post_in[0], post_bytes, cudaMemcpyHostToDevice, c->up));
+        p += round256(post_bytes);
+    }
+    d.out = p;
+    // a write map need not cover the result (packed or partial outputs): cells it never stores keep the caller's bytes
+    MIMK_CUDA_TRY(cudaMemcpyAsync(p, h->out, out_bytes, cudaMemcpyHostToDevice, c->up));
+    MIMK_TRY(mimk_map_reduce_post(&d, c->up));
+    MIMK_CUDA_TRY(cudaMemcpyAsync(h->out, d.out, out_bytes, cudaMemcpyDeviceToHost, c->up));
+    return mimk_device_status(c->up);
+}
+
 extern "C" int mimk_host_mlp_gated(const mimk_mlp_desc* h) {
     if (!h) return MIMK_E_ARG;
     if (h->m < 0 || h->k < 0 || h->f < 0 || h->n < 0) return MIMK_E_ARG;

@@ -120,3 +120,27 @@ def mlp_gated(x, w1, w3, w2, *, out=None):
     d.dtype, d.b_layout = _DT[x.dtype], lay
     L.check(L.lib().mimk_host_mlp_gated(C.byref(d)), "host mlp_gated")
     return out
+
+
+def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_maps=(), post_ins=(), *,
+                    acc_dtype=None, out_dtype=None, out=None) -> torch.Tensor:
+    """`map_reduce_post` on host tensors: the call the reference's GPU path wraps around EVERY operation (upload the
+    inputs and epilogue inputs, run, download the result). Arguments as mimir_b200.tensor.map_reduce_post; `out`
+    (optional) supplies the result buffer, whose cells a non-covering write map leaves as they are."""
+    from .tensor import _mrp_desc
+    _cpu(*ins, *post_ins, out)
+    So, Sr = [int(v) for v in So], [int(v) for v in Sr]
+    ins = [t.contiguous() for t in ins]
+    post_ins = [t.contiguous() for t in post_ins]
+    if acc_dtype is None:
+        acc_dtype = torch.float32 if ins and ins[0].dtype in (torch.float32, torch.bfloat16) else (ins[0].dtype if ins else torch.int32)
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else acc_dtype
+    if out is None:
+        out = torch.zeros(So, dtype=out_dtype)
+    elif tuple(out.shape) != tuple(So) or out.dtype != out_dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor of the result's shape and element type")
+    d = _mrp_desc(So, Sr, f, init, post, map_out, maps, [(t.data_ptr(), t.dtype, tuple(t.shape)) for t in ins], post_maps,
+                  [(t.data_ptr(), t.dtype, tuple(t.shape)) for t in post_ins], acc_dtype, out_dtype, out.data_ptr())
+    L.check(L.lib().mimk_host_map_reduce_post(C.byref(d)), "host map_reduce_post")
+    return out

@@ -59,6 +59,14 @@ def test_argument_validation_needs_no_device(lib):
     assert L.mimk_reduce(None, None, lib.F32, -1, 4, 1, lib.SUM, None) == 1
     assert L.mimk_reduce(None, None, lib.BF16, 1, 4, 1, lib.SUM, None) == 4
     assert L.mimk_map(99, None, None, None, lib.F32, 1, 1, 1, 0, None) == 1
+    assert L.mimk_map_reduce_post(None, None) == 1
+    assert L.mimk_host_map_reduce_post(None) == 1
+    m = lib.MrpDesc()
+    m.ro, m.rn = 3, 2                                   # more output loops than loops
+    assert L.mimk_map_reduce_post(C.byref(m), None) == 1
+    assert L.mimk_host_map_reduce_post(C.byref(m)) == 1
+    assert L.mimk_mrp_classify(None) == 0
+    assert L.mimk_chain_order(0, None, None, 0, 8, None, None) == 1
 
 
 def test_no_cpu_fallback_without_device(lib):
@@ -71,6 +79,19 @@ def test_no_cpu_fallback_without_device(lib):
     d.batch, d.m, d.n, d.k = 1, 4, 4, 4
     d.in_dtype, d.out_dtype = lib.F32, lib.F32
     assert L.mimk_gemm(C.byref(d), None) == 6
+    m = lib.MrpDesc()                                   # a valid empty-loop instance still needs the device
+    m.ro = m.rn = 1
+    m.sr[0] = m.so[0] = 4
+    m.nis, m.comb, m.acc_dtype, m.out_dtype = 1, lib.F_FIRST, lib.F32, lib.F32
+    m.in_dtype[0] = lib.F32
+    m.in_map[0].rows, m.map_out.rows = 1, 1
+    m.in_map[0].coef[0][0] = m.map_out.coef[0][0] = 1
+    m.in_shape[0][0] = 4
+    assert L.mimk_map_reduce_post(C.byref(m), None) == 6
+    buf = (C.c_float * 4)()
+    m.in_[0] = C.addressof(buf)
+    m.out = C.addressof(buf)
+    assert L.mimk_host_map_reduce_post(C.byref(m)) == 6
     with pytest.raises(ValueError):
         from mimir_b200 import tensor as T
         T.product_2d(torch.zeros(2, 2), torch.zeros(2, 2))

@@ -46,3 +46,30 @@ def test_host_gemm_and_attention(H):
     q, k, v = (_randn((2, 48, 16), 5 + i) for i in range(3))
     o = H.attention(q, k, v, scale=0.25, causal=True)
     assert nerr(o.double().numpy(), mo.attention(q.numpy(), k.numpy(), v.numpy(), scale=0.25, causal=True)) <= TOL_F32
+
+
+def test_host_map_reduce_post_known_answers_and_routed_contraction():
+    """The generic operation with host operands: the reference's integer known answers (bit exact) and a contraction
+    large enough to be handed to the tensor-core kernel, both through mimk_host_map_reduce_post."""
+    from mimir_b200 import _lib as L
+    from mimir_b200 import host as H
+    from mimir_b200 import tensor as T
+    # lit/buffer/exec_map_reduce.mim:25-32 (row sums, out[2] = 42) and exec_epilogue.mim:27-38 (transposed read, bias, +1: 46)
+    t = (torch.arange(12, dtype=torch.int32) + 1).reshape(3, 4)
+    out = H.map_reduce_post((3,), (3, 4), L.F_ADD, 0, L.P_ID, T.proj_map(2, (0,)), [T.id_map(2)], [t])
+    assert out.tolist() == [10, 26, 42]
+    tt = t.t().contiguous()
+    bias = torch.tensor([1, 2, 3], dtype=torch.int32)
+    out = H.map_reduce_post((3,), (3, 4), L.F_ADD, 0, L.P_ADD_PLUS1, T.proj_map(2, (0,)), [T.proj_map(2, (1, 0))], [tt],
+                            [T.id_map(1)], [bias])
+    assert out.tolist() == [12, 29, 46]
+    # a write map that covers every other cell leaves the rest of the caller's buffer alone
+    buf = torch.full((8,), -7, dtype=torch.int32)
+    H.map_reduce_post((8,), (4,), L.F_FIRST, 0, L.P_ID, [[2, 0]], [T.id_map(1)], [torch.arange(4, dtype=torch.int32)], out=buf)
+    assert buf.tolist() == [0, -7, 1, -7, 2, -7, 3, -7]
+    # f32 contraction given as a descriptor (routed to the contraction kernels), against the f64 truth
+    g = torch.Generator().manual_seed(3)
+    a, b = torch.randn(256, 192, generator=g), torch.randn(192, 320, generator=g)
+    c = H.map_reduce_post((256, 320), (256, 320, 192), L.F_MULADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)),
+                          [T.proj_map(3, (0, 2)), T.proj_map(3, (2, 1))], [a, b])
+    assert mo.normalised_error(c.numpy(), a.double().numpy() @ b.double().numpy()) <= 1e-5
