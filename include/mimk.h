@@ -53,7 +53,8 @@ int mimk_last_cuda_error(void);
 /* MIMK_OK iff the current device can run the kernels (compute capability 10.x). */
 int mimk_device_check(void);
 /* Synchronises `stream` and returns MIMK_E_DEVICE_WAIT if any kernel since the last call gave up on a bounded
- * wait (its results are then undefined), MIMK_OK otherwise. Clears the flag. */
+ * wait (its results are then undefined), MIMK_E_SHAPE if a gather / scatter met an index outside its axis (that
+ * access was skipped), MIMK_OK otherwise. Clears the flag. */
 int mimk_device_status(void* stream);
 
 /* Launches a one-CTA kernel that waits, with a limit of `limit_cycles` SM clocks, on a barrier nothing arrives on, and
@@ -177,6 +178,26 @@ enum {
  * (binary_ax); 2: y is [len*inner], broadcast over `outer` (a bias row); 3: unary, y unused. */
 int mimk_map(int op, const void* x, const void* y, void* out, int out_dtype, int64_t outer, int64_t len,
              int64_t inner, int y_mode, void* stream);
+
+/* ---- constructors and data-dependent indexing (tensor.mim:77-109, 519-563): not map_reduce_post instances ----
+ * Shapes are `rank` extents (rank <= MIMK_MRP_MAX_RANK), tensors dense row-major.
+ * mimk_splat: every element = the low bytes of value_bits (tensor.splat, tensor.mim:94-109); any element type.
+ * mimk_generate_affine: out[o] = sum_d coef[d] * o[d] + coef[rank] in wrap-around int64, converted to I32 / I64 / F32:
+ *   tensor.generate (tensor.mim:77-92) for bodies that are affine in the coordinates -- the coordinate tensors themselves
+ *   (coef = unit vector) from which any other body can be computed with the elementwise operators.
+ * mimk_gather: out[o] = input[o with o[dim] := index[o]], out has the index's shape (tensor.mim:519-541).
+ * mimk_scatter: out = input, then out[u with u[dim] := index[u]] = updates[u] for every u of the index's shape in
+ *   row-major order -- where two updates name one destination the later one wins (tensor.mim:543-563). out may alias
+ *   input.
+ * dtype: element type of input / updates / out (F32, BF16, I32, I64); index_dtype I32 or I64. The reference's index type
+ * `Idx (s_src#dim)` cannot hold an out-of-range value; here such a value skips its access and mimk_device_status reports
+ * MIMK_E_SHAPE. */
+int mimk_splat(void* out, int dtype, int64_t n, int64_t value_bits, void* stream);
+int mimk_generate_affine(void* out, int dtype, int rank, const int64_t* shape, const int64_t* coef, void* stream);
+int mimk_gather(const void* input, const void* index, void* out, int dtype, int index_dtype, int rank, const int64_t* s_src,
+                const int64_t* s_idx, int dim, void* stream);
+int mimk_scatter(const void* input, const void* index, const void* updates, void* out, int dtype, int index_dtype, int rank,
+                 const int64_t* s_src, const int64_t* s_idx, const int64_t* s_updates, int dim, void* stream);
 
 /* O[h,i,:] = softmax_j(scale * Q[h,i,:].K[h,j,:] (+ causal mask j <= i + seq_k - seq_q)) V[h,j,:].
  * Replaces: the composed program `softmax (q * transpose_2d k) * v` (lit/tensor/attn_exec.mim:20-22), seven

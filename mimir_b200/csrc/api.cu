@@ -132,7 +132,8 @@ extern "C" int mimk_device_status(void* stream) {
     MIMK_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     const int flag = *d->status_host;
     *d->status_host = 0;
-    return flag ? MIMK_E_DEVICE_WAIT : MIMK_OK;
+    // kernels store a status code there: a bounded wait that expired, or an index outside its axis in gather / scatter
+    return flag == MIMK_E_SHAPE ? MIMK_E_SHAPE : (flag ? MIMK_E_DEVICE_WAIT : MIMK_OK);
 }
 
 static int check_gemm(const mimk_gemm_desc* d) {

@@ -548,3 +548,132 @@ def dot_product(a: torch.Tensor, b: torch.Tensor, contract, batch=((), ())) -> t
     init = 0.0 if a.dtype in (torch.float32, torch.bfloat16) else 0
     return map_reduce_post(so, sr, L.F_MULADD, init, L.P_ID, proj_map(n, range(r_out)), [proj_map(n, s1), proj_map(n, s2)],
                            [a, b], acc_dtype=_acc(a), out_dtype=a.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ constructors, indexing
+def _i64s(vals):
+    vals = [int(v) for v in vals]
+    return (C.c_int64 * max(len(vals), 1))(*vals)
+
+
+def _bits(value, dtype) -> int:
+    """`value` as the raw bit pattern of one element of `dtype`."""
+    t = torch.tensor([value], dtype=dtype)
+    width = {1: torch.int8, 2: torch.int16, 4: torch.int32, 8: torch.int64}[t.element_size()]
+    return int(t.view(width).item())
+
+
+def splat(shape, value, dtype=torch.float32, device="cuda") -> torch.Tensor:
+    """`splat (s_out, value)`: every element is `value` (tensor.mim:94-109)."""
+    out = torch.empty([int(v) for v in shape], dtype=dtype, device=device)
+    L.check(L.lib().mimk_splat(out.data_ptr(), _DT[dtype], out.numel(), _bits(value, dtype), _stream()), "splat")
+    return out
+
+
+def generate_affine(shape, coef, dtype=torch.int64, device="cuda") -> torch.Tensor:
+    """out[o] = sum_d coef[d] * o[d] + coef[rank]: `generate` (tensor.mim:77-92) for a body affine in the coordinates."""
+    shape = [int(v) for v in shape]
+    if len(coef) != len(shape) + 1:
+        raise ValueError("one coefficient per axis plus a constant")
+    out = torch.empty(shape, dtype=dtype, device=device)
+    L.check(L.lib().mimk_generate_affine(out.data_ptr(), _DT[dtype], len(shape), _i64s(shape), _i64s(coef), _stream()), "generate")
+    return out
+
+
+def iota(shape, axis: int, dtype=torch.int64, device="cuda") -> torch.Tensor:
+    """The coordinate along `axis` at every position of `shape` (an I64 coordinate of `generate`'s body)."""
+    coef = [0] * (len(shape) + 1)
+    coef[axis] = 1
+    return generate_affine(shape, coef, dtype, device)
+
+
+def generate(shape, body) -> torch.Tensor:
+    """`generate s_out body` (tensor.mim:77-92): `body` is called ONCE with one I64 coordinate tensor per axis (each of
+    shape s_out, on the device) and returns the tensor of values -- the per-coordinate evaluation of the reference,
+    vectorised over the whole index space."""
+    shape = [int(v) for v in shape]
+    out = body(*[iota(shape, ax) for ax in range(len(shape))])
+    if tuple(out.shape) != tuple(shape):
+        raise ValueError("generate: body must return one value per coordinate")
+    return out
+
+
+def gather(dim: int, x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """`gather`: out[o] = x[o with o[dim] := index[o]], out has index's shape (tensor.mim:519-541)."""
+    _dev(x, index)
+    if x.dim() != index.dim() or index.dtype not in (torch.int32, torch.int64):
+        raise ValueError("gather: index must have the input's rank and an integer element type")
+    x, index = x.contiguous(), index.contiguous()
+    out = torch.empty(index.shape, dtype=x.dtype, device=x.device)
+    L.check(L.lib().mimk_gather(x.data_ptr(), index.data_ptr(), out.data_ptr(), _dt(x), _DT[index.dtype], x.dim(), _i64s(x.shape),
+                                _i64s(index.shape), int(dim), _stream()), "gather")
+    return out
+
+
+def scatter(dim: int, x: torch.Tensor, index: torch.Tensor, updates: torch.Tensor) -> torch.Tensor:
+    """`scatter`: a copy of x with x[u with u[dim] := index[u]] = updates[u] for every u of index's shape, visited in
+    row-major order -- a destination named twice keeps the later update (tensor.mim:543-563)."""
+    _dev(x, index, updates)
+    if x.dim() != index.dim() or x.dim() != updates.dim() or index.dtype not in (torch.int32, torch.int64):
+        raise ValueError("scatter: index and updates must have the input's rank; index an integer element type")
+    if updates.dtype != x.dtype:
+        raise TypeError("scatter: updates share the input's element type")
+    x, index, updates = x.contiguous(), index.contiguous(), updates.contiguous()
+    out = torch.empty_like(x)
+    L.check(L.lib().mimk_scatter(x.data_ptr(), index.data_ptr(), updates.data_ptr(), out.data_ptr(), _dt(x), _DT[index.dtype], x.dim(),
+                                 _i64s(x.shape), _i64s(index.shape), _i64s(updates.shape), int(dim), _stream()), "scatter")
+    return out
+
+
+def reshape(x: torch.Tensor, shape) -> torch.Tensor:
+    """Row-major `reshape` (tensor.mim:302-313): a dense row-major buffer read with another shape -- no copy."""
+    shape = [int(v) for v in shape]
+    n = 1
+    for v in shape:
+        n *= v
+    if n != x.numel():
+        raise ValueError("reshape: element counts differ")
+    return x.contiguous().view(shape)
+
+
+def repeat(x: torch.Tensor, shape) -> torch.Tensor:
+    """`repeat`: out[d] = x[d mod s_in] for s_out a multiple of s_in on every axis (tensor.mim:292-300, repeat_map 1209-1213).
+    The modulus becomes affine by splitting every output axis into (copy, position), o_d = copy_d * s_in_d + pos_d: the
+    result is written through its row-major view of shape (copies_0, s_in_0, copies_1, s_in_1, ...)."""
+    shape = [int(v) for v in shape]
+    r = x.dim()
+    if len(shape) != r or any(si == 0 or so % si for so, si in zip(shape, x.shape)):
+        raise ValueError("repeat: every output extent must be a multiple of the input's")
+    if 2 * r > L.MRP_MAX_RANK:
+        raise ValueError("repeat: rank too large for the generic kernel")
+    split = []
+    for d in range(r):
+        split += [shape[d] // x.shape[d], x.shape[d]]
+    out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    f, init = _copy_fn(x)
+    _mrp_into(out.view(split), split, f, init, L.P_ID, id_map(2 * r), [proj_map(2 * r, [2 * d + 1 for d in range(r)])], [x])
+    return out
+
+
+def concat(ax: int, xs) -> torch.Tensor:
+    """`concat ax`: the inputs joined along `ax` (tensor.mim:245-259): input k is copied to the output at offset
+    off_k = sum of the earlier inputs' extents along `ax` -- one copy-style map_reduce_post per input."""
+    xs = list(xs)
+    if not xs:
+        raise ValueError("concat of nothing")
+    r = xs[0].dim()
+    for t in xs:
+        if t.dim() != r or t.dtype != xs[0].dtype or any(t.shape[d] != xs[0].shape[d] for d in range(r) if d != ax):
+            raise ValueError("concat: inputs agree on rank, element type and every extent except along ax")
+    shape = list(xs[0].shape)
+    shape[ax] = sum(t.shape[ax] for t in xs)
+    out = torch.empty(shape, dtype=xs[0].dtype, device=xs[0].device)
+    off = 0
+    for t in xs:
+        if t.numel():
+            m_out = id_map(r)
+            m_out[ax][r] = off
+            f, init = _copy_fn(t)
+            _mrp_into(out, list(t.shape), f, init, L.P_ID, m_out, [id_map(r)], [t])
+        off += t.shape[ax]
+    return out

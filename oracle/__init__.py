@@ -296,3 +296,54 @@ def normalised_error(got, want) -> float:
     want = np.asarray(want, dtype=np.float64)
     denom = float(np.max(np.abs(want))) or 1.0
     return float(np.max(np.abs(got - want))) / denom
+
+
+# ---- constructors and data-dependent indexing (tensor.mim:77-109, 245-313, 519-563): the docstrings' loops, verbatim ----
+def generate(shape, body) -> np.ndarray:
+    """output[index] = body(index) for every index of `shape` (tensor.mim:81-87); body takes the coordinates as ints."""
+    first = body(*([0] * len(shape))) if all(shape) else 0
+    out = np.empty(shape, dtype=np.asarray(first).dtype)
+    for index in np.ndindex(*shape):
+        out[index] = body(*index)
+    return out
+
+
+def gather(dim: int, x: np.ndarray, index: np.ndarray) -> np.ndarray:
+    """tensor.mim:527-535."""
+    out = np.empty(index.shape, dtype=x.dtype)
+    for o in np.ndindex(*index.shape):
+        src = tuple(int(index[o]) if d == dim else o[d] for d in range(x.ndim))
+        out[o] = x[src]
+    return out
+
+
+def scatter(dim: int, x: np.ndarray, index: np.ndarray, updates: np.ndarray) -> np.ndarray:
+    """tensor.mim:549-557: row-major visiting order, so the last update of a destination wins."""
+    out = x.copy()
+    for u in np.ndindex(*index.shape):
+        dst = tuple(int(index[u]) if d == dim else u[d] for d in range(x.ndim))
+        out[dst] = updates[u]
+    return out
+
+
+def repeat(x: np.ndarray, shape) -> np.ndarray:
+    """out[d] = x[d mod s_in] (tensor.mim:292-300)."""
+    out = np.empty(shape, dtype=x.dtype)
+    for o in np.ndindex(*shape):
+        out[o] = x[tuple(o[d] % x.shape[d] for d in range(x.ndim))]
+    return out
+
+
+def concat(ax: int, xs) -> np.ndarray:
+    """out[o] = xs[k][o with o[ax] - off_k], k the input whose range o[ax] falls in (tensor.mim:245-259)."""
+    shape = list(xs[0].shape)
+    shape[ax] = sum(t.shape[ax] for t in xs)
+    out = np.empty(shape, dtype=xs[0].dtype)
+    for o in np.ndindex(*shape):
+        off = 0
+        for t in xs:
+            if o[ax] < off + t.shape[ax]:
+                out[o] = t[tuple(o[d] - off if d == ax else o[d] for d in range(len(shape)))]
+                break
+            off += t.shape[ax]
+    return out

@@ -1,0 +1,102 @@
+"""GPU parity of the constructors and the data-dependent indexing operators (splat, generate, gather, scatter, concat,
+repeat, reshape) against the oracle's restatement of the reference's loops: the reference's known answers and seeded
+cases; integer and copy work is bit exact."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T():
+    from mimir_b200 import tensor
+    return tensor
+
+
+def cu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_generate_exec_30(T):
+    # lit/tensor/generate_exec.mim:12-20
+    g = T.generate((2, 3), lambda i, _j: T.splat((2, 3), 20, torch.int32).masked_fill(i == 0, 10))
+    assert g.dtype == torch.int32 and int(g[0, 2]) + int(g[1, 1]) == 30
+    want = mo.generate((2, 3), lambda i, _j: np.int32(10 if i == 0 else 20))
+    assert np.array_equal(g.cpu().numpy(), want)
+
+
+def test_gather_scatter_exec_93(T):
+    # lit/tensor/gather_scatter_exec.mim:15-21
+    x = cu(np.array([[10, 11, 12], [20, 21, 22]], dtype=np.int32))
+    index = cu(np.array([[2, 0], [1, 1]], dtype=np.int32))
+    updates = cu(np.array([[10, 20], [30, 40]], dtype=np.int32))
+    g = T.gather(1, x, index)
+    s = T.scatter(1, x, index, updates)
+    T.device_status()
+    assert int(g[0, 0]) + int(g[1, 0]) + int(s[0, 0]) + int(s[1, 1]) == 93
+    assert s.cpu().tolist() == [[20, 11, 10], [20, 40, 22]]
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.int32, np.int64])
+@pytest.mark.parametrize("idx_dtype", [np.int32, np.int64])
+def test_gather_scatter_match_the_loops(T, dtype, idx_dtype):
+    rng = np.random.default_rng(17)
+    for dim in range(3):
+        s_src = (7, 9, 11)
+        s_idx = tuple(5 if d == dim else s_src[d] - (d % 2) for d in range(3))     # <= the source off the indexed axis
+        s_upd = tuple(v + 1 for v in s_idx)                                          # updates may be larger than the index
+        x = rng.integers(-100, 100, s_src).astype(dtype)
+        index = rng.integers(0, s_src[dim], s_idx).astype(idx_dtype)                # duplicates along the line are likely
+        upd = rng.integers(-100, 100, s_upd).astype(dtype)
+        g = T.gather(dim, cu(x), cu(index))
+        s = T.scatter(dim, cu(x), cu(index), cu(upd))
+        T.device_status()
+        assert np.array_equal(g.cpu().numpy(), mo.gather(dim, x, index)), dim
+        assert np.array_equal(s.cpu().numpy(), mo.scatter(dim, x, index, upd)), dim
+
+
+def test_gather_bf16_and_large(T):
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(64, 1000, 33, generator=g).to(torch.bfloat16).cuda()
+    index = torch.randint(0, 1000, (64, 300, 33), generator=g).cuda()
+    got = T.gather(1, x, index)
+    assert torch.equal(got, torch.gather(x, 1, index))          # the same element picks, bit for bit
+    upd = torch.randn(64, 300, 33, generator=g).to(torch.bfloat16).cuda()
+    sc = T.scatter(1, x, index, upd)
+    want = mo.scatter(1, x[:2].float().cpu().numpy(), index[:2].cpu().numpy(), upd[:2].float().cpu().numpy())
+    assert np.array_equal(sc[:2].float().cpu().numpy(), want)
+
+
+def test_out_of_range_index_is_reported_not_followed(T):
+    from mimir_b200 import _lib as L
+    x = cu(np.arange(12, dtype=np.int32).reshape(3, 4))
+    index = cu(np.array([[0, 9, 1]], dtype=np.int64))            # 9 is outside axis 1 (extent 4)
+    out = T.gather(1, x, index)
+    with pytest.raises(L.MimkError) as e:
+        T.device_status()
+    assert e.value.status == 2                                   # MIMK_E_SHAPE
+    assert out[0, 0].item() == 0 and out[0, 2].item() == 1       # the in-range picks were made
+    T.device_status()                                            # the flag is cleared, the context usable
+
+
+def test_splat_iota_reshape_repeat_concat(T):
+    assert torch.equal(T.splat((3, 5), 2.5), torch.full((3, 5), 2.5, device="cuda"))
+    assert torch.equal(T.splat((4,), -3, torch.int64), torch.full((4,), -3, dtype=torch.int64, device="cuda"))
+    assert torch.equal(T.splat((2, 2), 1.5, torch.bfloat16), torch.full((2, 2), 1.5, dtype=torch.bfloat16, device="cuda"))
+    co = T.iota((3, 4, 5), 1)
+    assert np.array_equal(co.cpu().numpy(), np.indices((3, 4, 5))[1])
+    lin = T.generate_affine((3, 4), (4, 1, 7), torch.int32)          # 4 i + j + 7
+    assert np.array_equal(lin.cpu().numpy(), (np.arange(12).reshape(3, 4) + 7).astype(np.int32))
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((3, 4, 5)).astype(np.float32)
+    assert np.array_equal(T.reshape(cu(x), (5, 12)).cpu().numpy(), x.reshape(5, 12))
+    assert np.array_equal(T.repeat(cu(x), (6, 4, 15)).cpu().numpy(), mo.repeat(x, (6, 4, 15)))
+    xi = rng.integers(0, 9, (2, 3)).astype(np.int64)
+    assert np.array_equal(T.repeat(cu(xi), (4, 9)).cpu().numpy(), np.tile(xi, (2, 3)))
+    parts = [rng.standard_normal((3, n, 5)).astype(np.float32) for n in (2, 0, 4, 1)]
+    assert np.array_equal(T.concat(1, [cu(p) for p in parts]).cpu().numpy(), mo.concat(1, parts))
+    assert np.array_equal(T.concat(0, [cu(x), cu(x)]).cpu().numpy(), np.concatenate([x, x], 0))
+    assert np.array_equal(T.concat(2, [cu(x), cu(x[:, :, :2])]).cpu().numpy(), np.concatenate([x, x[:, :, :2]], 2))

@@ -250,3 +250,23 @@ def test_causal_attention_matches_masked_dense():
     o32 = mo.attention(q, k, v, scale=0.25, causal=True, truth=False)
     assert mo.normalised_error(o32, o) < 1e-5
     assert np.array_equal(mo.attention(q, k, v, scale=0.25, causal=True, heads=[1])[0], o[1])
+
+
+# ------------------------------------------------------------------ constructors and data-dependent indexing
+def test_generate_exec_30():
+    # lit/tensor/generate_exec.mim:12-20 -- generate (2, 3) with body (i, _) -> i == 0 ? 10 : 20; g[0,2] + g[1,1] = 30
+    g = mo.generate((2, 3), lambda i, _j: np.int32(10 if i == 0 else 20))
+    assert int(g[0, 2]) + int(g[1, 1]) == 30
+
+
+def test_gather_scatter_exec_93():
+    # lit/tensor/gather_scatter_exec.mim:15-21 -- gather / scatter along axis 1; 12 + 21 + 20 + 40 = 93, the duplicate
+    # destination (1, 1) keeps the later update
+    x = np.array([[10, 11, 12], [20, 21, 22]], dtype=np.int32)
+    index = np.array([[2, 0], [1, 1]], dtype=np.int32)
+    updates = np.array([[10, 20], [30, 40]], dtype=np.int32)
+    g = mo.gather(1, x, index)
+    s = mo.scatter(1, x, index, updates)
+    assert g.tolist() == [[12, 10], [21, 21]]
+    assert s.tolist() == [[20, 11, 10], [20, 40, 22]]
+    assert int(g[0, 0]) + int(g[1, 0]) + int(s[0, 0]) + int(s[1, 1]) == 93
