@@ -193,6 +193,8 @@ int mimk_map(int op, const void* x, const void* y, void* out, int out_dtype, int
  * `Idx (s_src#dim)` cannot hold an out-of-range value; here such a value skips its access and mimk_device_status reports
  * MIMK_E_SHAPE. */
 int mimk_splat(void* out, int dtype, int64_t n, int64_t value_bits, void* stream);
+/* out[i] = cond[i] ? a[i] : b[i]: tensor.select (tensor.mim:378-384); cond holds one byte per element (non-zero = true). */
+int mimk_select(const void* cond, const void* a, const void* b, void* out, int dtype, int64_t n, void* stream);
 int mimk_generate_affine(void* out, int dtype, int rank, const int64_t* shape, const int64_t* coef, void* stream);
 int mimk_gather(const void* input, const void* index, void* out, int dtype, int index_dtype, int rank, const int64_t* s_src,
                 const int64_t* s_idx, int dim, void* stream);

@@ -89,6 +89,14 @@ __global__ void scatter_kernel(const I* __restrict__ index, const T* __restrict_
     }
 }
 
+// out[i] = cond[i] ? a[i] : b[i]   (tensor.select, tensor.mim:378-384; cond one byte per element, non-zero = true)
+template <class T>
+__global__ void select_kernel(const uint8_t* __restrict__ cond, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
+                              long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = cond[i] ? a[i] : b[i];
+}
+
 bool load_shape(Shape& s, int rank, const int64_t* ext, long long* total) {
     if (rank < 0 || rank > MAX_RANK || (rank > 0 && !ext)) return false;
     s.rank = rank;
@@ -233,4 +241,23 @@ extern "C" int mimk_scatter(const void* input, const void* index, const void* up
         case 4: return scatter_typed<uint32_t>(index, updates, out, index_dtype, lines, src, idx, ups, dim, dev, s);
         default: return scatter_typed<uint64_t>(index, updates, out, index_dtype, lines, src, idx, ups, dim, dev, s);
     }
+}
+
+extern "C" int mimk_select(const void* cond, const void* a, const void* b, void* out, int dtype, int64_t n, void* stream) {
+    if (n < 0) return MIMK_E_ARG;
+    if (!value_dtype_ok(dtype)) return MIMK_E_DTYPE;
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    if (n == 0) return MIMK_OK;
+    if (!cond || !a || !b || !out) return MIMK_E_ARG;
+    cudaStream_t s   = static_cast<cudaStream_t>(stream);
+    const unsigned g = grid_for(dev, n);
+    const uint8_t* c = static_cast<const uint8_t*>(cond);
+    switch (dtype_size(dtype)) {
+        case 2: select_kernel<uint16_t><<<g, 256, 0, s>>>(c, static_cast<const uint16_t*>(a), static_cast<const uint16_t*>(b), static_cast<uint16_t*>(out), n); break;
+        case 4: select_kernel<uint32_t><<<g, 256, 0, s>>>(c, static_cast<const uint32_t*>(a), static_cast<const uint32_t*>(b), static_cast<uint32_t*>(out), n); break;
+        default: select_kernel<uint64_t><<<g, 256, 0, s>>>(c, static_cast<const uint64_t*>(a), static_cast<const uint64_t*>(b), static_cast<uint64_t*>(out), n); break;
+    }
+    return launch_status();
 }

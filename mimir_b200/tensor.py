@@ -416,6 +416,14 @@ def broadcast_in_dim(x: torch.Tensor, shape, index) -> torch.Tensor:
     return map_reduce_post(shape, shape, f, init, L.P_ID, id_map(ro), [m], [x], acc_dtype=_acc(x), out_dtype=x.dtype)
 
 
+def broadcast(x: torch.Tensor, shape) -> torch.Tensor:
+    """`broadcast (s_in, s_out, input)`: same rank, every extent equal to the output's or 1; size-1 axes are expanded
+    (tensor.mim:209-218) -- broadcast_in_dim with the identity axis assignment."""
+    if x.dim() != len(shape):
+        raise ValueError("broadcast keeps the rank; use broadcast_in_dim to add axes")
+    return broadcast_in_dim(x, shape, range(x.dim()))
+
+
 def pad(x: torch.Tensor, lo, hi, value=0) -> torch.Tensor:
     """`pad`: x placed at offset `lo` inside a tensor filled with `value` (edge padding only)."""
     r = x.dim()
@@ -485,6 +493,37 @@ def conv(x: torch.Tensor, w: torch.Tensor, stride=(1, 1), dilation=(1, 1), paddi
     return map_reduce_post((n, cout, oh, ow), (n, cout, oh, ow, cin, kh, kw), L.F_MULADD, init, L.P_ID,
                            proj_map(7, (0, 1, 2, 3)), [mi, proj_map(7, (1, 4, 5, 6))], [xp, w], acc_dtype=_acc(x),
                            out_dtype=x.dtype)
+
+
+def conv_grouped(x: torch.Tensor, w: torch.Tensor, groups: int, stride=(1, 1), dilation=(1, 1), padding=(0, 0)) -> torch.Tensor:
+    """`conv_grouped R (groups, stride, dilation, padding) (input, weight)` (tensor.mim:440-451): NCHW input with
+    cin = groups * ci channels, weight [cout, ci, KH, KW] with group g owning output channels [g*co, (g+1)*co).
+    Loop vector (n, g, co, oh, ow, ci, kh, kw); input channel g*ci + ci and output channel g*co + co are affine because
+    input, weight and result are read through their row-major views with the group as an axis of its own
+    (conv_grouped_in_map / conv_grouped_w_map, tensor.mim:1284-1297)."""
+    _dev(x, w)
+    n, cin, h, wd = x.shape
+    cout, ci, kh, kw = w.shape
+    groups = int(groups)
+    if groups < 1 or ci * groups != cin:
+        raise ValueError("conv_grouped: weight must hold cin / groups input channels")
+    if cout % groups:
+        raise ValueError("conv_grouped: cout must be a multiple of groups")
+    co = cout // groups
+    xp = pad(x, (0, 0, padding[0], padding[1]), (0, 0, padding[0], padding[1])) if any(padding) else x.contiguous()
+    hp, wp = xp.shape[2], xp.shape[3]
+    oh = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+    ow = (wd + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    # loops: 0 n, 1 g, 2 co, 3 oh, 4 ow | 5 ci, 6 kh, 7 kw
+    mi = [[0] * 9 for _ in range(5)]                    # input viewed [n, g, ci, H, W]
+    mi[0][0], mi[1][1], mi[2][5] = 1, 1, 1
+    mi[3][3], mi[3][6] = stride[0], dilation[0]
+    mi[4][4], mi[4][7] = stride[1], dilation[1]
+    init = 0.0 if x.dtype in (torch.float32, torch.bfloat16) else 0
+    out = map_reduce_post((n, groups, co, oh, ow), (n, groups, co, oh, ow, ci, kh, kw), L.F_MULADD, init, L.P_ID,
+                          proj_map(8, (0, 1, 2, 3, 4)), [mi, proj_map(8, (1, 2, 5, 6, 7))],
+                          [xp.view(n, groups, ci, hp, wp), w.contiguous().view(groups, co, ci, kh, kw)], acc_dtype=_acc(x), out_dtype=x.dtype)
+    return out.view(n, cout, oh, ow)
 
 
 def pool(monoid: str, x: torch.Tensor, kernel, stride=None, dilation=(1, 1), padding=(0, 0)) -> torch.Tensor:
@@ -676,4 +715,33 @@ def concat(ax: int, xs) -> torch.Tensor:
             f, init = _copy_fn(t)
             _mrp_into(out, list(t.shape), f, init, L.P_ID, m_out, [id_map(r)], [t])
         off += t.shape[ax]
+    return out
+
+
+def select(cond: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """`select (cond, a, b)`: `core.select` mapped over tensors of one shape (tensor.mim:378-384) -- a where cond holds,
+    b elsewhere. cond is a Bool tensor."""
+    _dev(cond, a, b)
+    if cond.dtype != torch.bool or a.dtype != b.dtype or not (tuple(cond.shape) == tuple(a.shape) == tuple(b.shape)):
+        raise ValueError("select: a Bool tensor and two tensors of one element type, all of one shape")
+    cond, a, b = cond.contiguous(), a.contiguous(), b.contiguous()
+    out = torch.empty_like(a)
+    L.check(L.lib().mimk_select(cond.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(), _dt(a), a.numel(), _stream()), "select")
+    return out
+
+
+def from_array(values, dtype=torch.float32, device="cuda") -> torch.Tensor:
+    """`from_array`: a nested array literal as a tensor (tensor.mim:52-58)."""
+    return torch.tensor(values, dtype=dtype).to(device)
+
+
+def get(t: torch.Tensor, index):
+    """`get (t, index)`: one element as a host scalar (tensor.mim:60-63)."""
+    return t[tuple(int(i) for i in index)].item()
+
+
+def set_(t: torch.Tensor, index, value) -> torch.Tensor:
+    """`set (t, index, value)`: a copy of t with one element replaced (value semantics, tensor.mim:64-67)."""
+    out = t.clone()
+    out[tuple(int(i) for i in index)] = value
     return out

@@ -100,3 +100,32 @@ def test_splat_iota_reshape_repeat_concat(T):
     assert np.array_equal(T.concat(1, [cu(p) for p in parts]).cpu().numpy(), mo.concat(1, parts))
     assert np.array_equal(T.concat(0, [cu(x), cu(x)]).cpu().numpy(), np.concatenate([x, x], 0))
     assert np.array_equal(T.concat(2, [cu(x), cu(x[:, :, :2])]).cpu().numpy(), np.concatenate([x, x[:, :, :2]], 2))
+
+
+def test_select_and_grouped_convolution(T):
+    rng = np.random.default_rng(8)
+    a, b = rng.standard_normal((5, 7)).astype(np.float32), rng.standard_normal((5, 7)).astype(np.float32)
+    cond = rng.integers(0, 2, (5, 7)).astype(bool)
+    assert np.array_equal(T.select(cu(cond), cu(a), cu(b)).cpu().numpy(), np.where(cond, a, b))
+    # the generate_exec body with the library's own operators: i == 0 ? 10 : 20
+    i = T.iota((2, 3), 0)
+    g = T.select(i == 0, T.splat((2, 3), 10, torch.int32), T.splat((2, 3), 20, torch.int32))
+    assert int(g[0, 2]) + int(g[1, 1]) == 30
+    # conv_grouped (lit/tensor/conv_grouped.mim shapes, scaled down): groups 2 and 3, with stride / padding / dilation
+    for (n, cin, cout, groups, k, stride, dil, pad) in [(2, 8, 6, 2, 3, 1, 1, 1), (1, 6, 9, 3, 1, 1, 1, 0), (2, 4, 4, 2, 3, 2, 2, 2)]:
+        x = rng.standard_normal((n, cin, 9, 10)).astype(np.float32)
+        w = rng.standard_normal((cout, cin // groups, k, k)).astype(np.float32)
+        got = T.conv_grouped(cu(x), cu(w), groups, (stride, stride), (dil, dil), (pad, pad))
+        want = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), stride=stride, padding=pad,
+                                          dilation=dil, groups=groups).numpy()
+        assert got.shape == want.shape and mo.normalised_error(got.cpu().numpy(), want) < 1e-5
+    # groups = 1 is the dense convolution
+    x = rng.standard_normal((1, 3, 6, 6)).astype(np.float32)
+    w = rng.standard_normal((4, 3, 3, 3)).astype(np.float32)
+    assert torch.equal(T.conv_grouped(cu(x), cu(w), 1), T.conv(cu(x), cu(w)))
+    assert T.get(T.set_(T.from_array([[1, 2], [3, 4]], torch.int32), (1, 0), 9), (1, 0)) == 9
+
+
+def test_broadcast_expands_unit_axes(T):
+    x = np.arange(12, dtype=np.float32).reshape(3, 1, 4)
+    assert np.array_equal(T.broadcast(cu(x), (3, 5, 4)).cpu().numpy(), np.broadcast_to(x, (3, 5, 4)))
