@@ -55,6 +55,50 @@ __global__ void __launch_bounds__(TILE * ROWS) permute_kernel(const T* __restric
     }
 }
 
+// Two-byte elements, both transposed extents even: the same tiled copy moving PAIRS -- 32-bit global loads along the
+// input's contiguous axis, 32-bit global stores along the output's -- over a tile of 128 x 128 elements.
+constexpr int PT = 128, PROWS = 4, PPITCH = PT + 2;
+__global__ void __launch_bounds__(64 * PROWS) permute_pairs_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out,
+                                                                   const PermuteParams p) {
+    __shared__ __align__(4) uint16_t tile[PT][PPITCH];
+    const int xl = p.rank - 1, yl = p.qy;
+    for (int64_t blk = blockIdx.x; blk < p.n_blocks; blk += gridDim.x) {
+        int64_t rest    = blk;
+        const int64_t x0 = (rest % p.tiles_x) * PT;
+        rest /= p.tiles_x;
+        const int64_t y0 = (rest % p.tiles_y) * PT;
+        rest /= p.tiles_y;
+        int64_t ibase = 0, obase = 0;
+        for (int l = p.rank - 2; l >= 0; --l) {
+            if (l == yl) continue;
+            const int64_t c = rest % p.shape[l];
+            rest /= p.shape[l];
+            ibase += c * p.istr[l];
+            obase += c * p.ostr[l];
+        }
+        const int64_t y = y0 + 2 * threadIdx.x;  // this thread's pair along the input's contiguous axis
+#pragma unroll 8
+        for (int k = 0; k < PT; k += PROWS) {
+            const int64_t x = x0 + threadIdx.y + k;
+            if (x < p.shape[xl] && y < p.shape[yl])
+                *reinterpret_cast<uint32_t*>(&tile[threadIdx.y + k][2 * threadIdx.x]) =
+                    *reinterpret_cast<const uint32_t*>(in + ibase + y + x * p.istr[xl]);
+        }
+        __syncthreads();
+        const int64_t xo = x0 + 2 * threadIdx.x;  // this thread's pair along the output's contiguous axis
+#pragma unroll 8
+        for (int k = 0; k < PT; k += PROWS) {
+            const int yo_l    = threadIdx.y + k;
+            const int64_t yo  = y0 + yo_l;
+            if (xo < p.shape[xl] && yo < p.shape[yl]) {
+                const uint32_t v = uint32_t(tile[2 * threadIdx.x][yo_l]) | (uint32_t(tile[2 * threadIdx.x + 1][yo_l]) << 16);
+                *reinterpret_cast<uint32_t*>(out + obase + xo + yo * p.ostr[yl]) = v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace
 
 // out[o] = in[o permuted]: `perm[j]` is the output loop that indexes input axis j. `esize` = bytes per element (2, 4, 8).
@@ -75,13 +119,20 @@ int permute_copy(const void* in, void* out, int esize, int rank, const int64_t* 
     for (int l = rank - 1; l >= 0; --l) p.ostr[l] = stride, stride *= out_shape[l];
     stride = 1;
     for (int j = rank - 1; j >= 0; --j) p.istr[perm[j]] = stride, stride *= out_shape[perm[j]];
-    p.tiles_x  = (p.shape[rank - 1] + TILE - 1) / TILE;
-    p.tiles_y  = (p.shape[p.qy] + TILE - 1) / TILE;
+    const bool pairs = esize == 2 && p.shape[rank - 1] % 2 == 0 && p.shape[p.qy] % 2 == 0 &&
+                       (reinterpret_cast<uintptr_t>(in) & 3u) == 0 && (reinterpret_cast<uintptr_t>(out) & 3u) == 0;
+    const int tile = pairs ? PT : TILE;
+    p.tiles_x  = (p.shape[rank - 1] + tile - 1) / tile;
+    p.tiles_y  = (p.shape[p.qy] + tile - 1) / tile;
     p.n_blocks = p.tiles_x * p.tiles_y;
     for (int l = 0; l < rank - 1; ++l)
         if (l != p.qy) p.n_blocks *= p.shape[l];
     const int64_t cap = int64_t(dev->sm_count) * 32;
     const unsigned grid = unsigned(p.n_blocks < cap ? p.n_blocks : cap);
+    if (pairs) {
+        permute_pairs_kernel<<<grid, dim3(64, PROWS), 0, s>>>(static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out), p);
+        return launch_status();
+    }
     const dim3 block(TILE, ROWS);
     switch (esize) {
         case 2: permute_kernel<uint16_t><<<grid, block, 0, s>>>(static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out), p); break;

@@ -336,3 +336,35 @@ def test_long_batches_run_as_one_launch(T, nk):
     T.device_status()
     for i in (0, 50, 95):
         assert torch.equal(out[i], T.product_2d(a[i], bv[0], post="add", full=full[i]))
+
+
+def test_hlo_train_step_fixture(T):
+    """lit/tensor/hlo_train_aux.cpp:24-76 -- one training step of a one-layer tanh MLP (N=4, I=8, O=3): forward, the
+    backward products through transposed reads, the bias gradient as an axis fold, for the fixture's three input
+    patterns. The returned scalar is rebuilt from this library's operators and held to the fixture's 1e-4."""
+    N, I, O, lr, c = 4, 8, 3, 0.001, 0.5
+
+    def make(n, mode):
+        i = np.arange(n)
+        v = (i % 100) / np.float32(100.0) if mode == 0 else (np.full(n, 0.5) if mode == 1 else 0.01 * ((i % 7) + 1))
+        return v.astype(np.float32)
+    for mode in range(3):
+        w, b, x, t = make(I * O, mode).reshape(I, O), make(O, mode), make(N * I, mode).reshape(N, I), make(N * O, mode).reshape(N, O)
+        # the fixture's scalar reference
+        z = x @ w
+        a = np.tanh(z + b)
+        d = np.float32(c) * (a - t)
+        dW, db, dx = x.T @ d, d.sum(0), d @ w.T
+        ref = (w[0, 0] - lr * dW[0, 0]) + (b[0] - lr * db[0]) + dx[0, 0] + z[0].max()
+        # the same step from the operators
+        cw, cb, cx, ct = (torch.from_numpy(v).cuda() for v in (w, b, x, t))
+        gz = T.product_2d(cx, cw)
+        ga = T.product_2d(cx, cw, post="bias_tanh", bias=cb)
+        half = torch.full_like(ga, c)
+        gd = T.binary("mul", half, T.binary("sub", ga, ct))
+        gdW = T.transpose(T.product_2d(T.transpose_2d(gd).contiguous(), cx), (1, 0))      # dW = (d^T x)^T
+        gdx = T.product_2d(gd, T.transpose_2d(cw))                                       # dx = d w^T
+        gdb = T.reduce("sum", 0, gd)
+        rmax = T.reduce("max", 1, gz)
+        got = (w[0, 0] - lr * gdW[0, 0].item()) + (b[0] - lr * gdb[0].item()) + gdx[0, 0].item() + rmax[0].item()
+        assert abs(got - ref) <= 1e-4, (mode, got, ref)

@@ -254,3 +254,15 @@ def test_large_axis_permutations_are_tiled_copies(T, L, dtype):
         assert torch.equal(got, x.permute(perm).contiguous()), perm
     m = torch.randint(-1000, 1000, (3000, 1111), generator=g).to(dtype).cuda()
     assert torch.equal(T.transpose(m, (1, 0)), m.t().contiguous())
+
+
+def test_two_byte_permutations_with_even_extents_move_pairs(T, L):
+    """bf16 tensors whose transposed extents are even take the pair-moving kernel; extents that end inside its 128 x 128
+    tile, every permutation that moves the fastest axis. Bit exact."""
+    g = torch.Generator().manual_seed(10)
+    shape = (6, 258, 130)
+    x = torch.randn(shape, generator=g).to(torch.bfloat16).cuda()
+    for perm in ((2, 1, 0), (1, 2, 0), (2, 0, 1), (0, 2, 1)):
+        assert torch.equal(T.transpose(x, perm), x.permute(perm).contiguous()), perm
+    m = torch.randn(2050, 1026, generator=g).to(torch.bfloat16).cuda()
+    assert torch.equal(T.transpose(m, (1, 0)), m.t().contiguous())
