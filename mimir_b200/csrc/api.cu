@@ -80,6 +80,26 @@ int get_scratch(size_t bytes, void** out) {
     return MIMK_OK;
 }
 
+int get_aux_scratch(size_t bytes, void** out) {
+    int st        = MIMK_OK;
+    DeviceInfo* d = device_info(&st);
+    if (!d) return st;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (d->aux_bytes < bytes) {
+        if (d->aux) {
+            MIMK_CUDA_TRY(cudaDeviceSynchronize());  // work queued on any stream may still use the old buffer
+            MIMK_CUDA_TRY(cudaFree(d->aux));
+            d->aux       = nullptr;
+            d->aux_bytes = 0;
+        }
+        size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+        MIMK_CUDA_TRY(cudaMalloc(&d->aux, want));
+        d->aux_bytes = want;
+    }
+    *out = d->aux;
+    return MIMK_OK;
+}
+
 }  // namespace mimk
 
 using namespace mimk;
@@ -217,6 +237,12 @@ extern "C" int mimk_attn_fwd(const mimk_attn_desc* d, void* stream) {
     }
     if (persistent && attn_tc_persistent_supported(*d)) return attn_tc_persistent(*d, s);
     if (attn_tc_supported(*d)) return attn_tc(*d, s);
+    static int composed = -1;  // MIMK_ATTN_F32_COMPOSED=0 keeps every f32 problem on the one-launch CUDA-core kernel
+    if (composed < 0) {
+        const char* e = getenv("MIMK_ATTN_F32_COMPOSED");
+        composed      = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (composed && attn_f32_composed_supported(*d)) return attn_f32_composed(*d, s);
     return attn_simt(*d, s);
 }
 

@@ -33,11 +33,15 @@ struct DeviceInfo {
     volatile int* status_host = nullptr;
     void* scratch = nullptr;     // cached scratch buffer (grown on demand)
     size_t scratch_bytes = 0;
+    void* aux = nullptr;         // a second cached buffer, for callers that run scratch-using entry points themselves
+    size_t aux_bytes = 0;
 };
 // Per-device lazily created state; returns nullptr (and sets *status) when the device is unusable.
 DeviceInfo* device_info(int* status);
 // A scratch buffer of at least `bytes` on the current device, cached across calls (grows, never shrinks).
 int get_scratch(size_t bytes, void** out);
+// The second cached buffer (same growth rule); used by the composed f32 attention for its score matrix.
+int get_aux_scratch(size_t bytes, void** out);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t dtype_size(int dt) { return dt == MIMK_BF16 ? 2 : (dt == MIMK_I64 ? 8 : 4); }
@@ -60,6 +64,9 @@ int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_supported(const mimk_attn_desc& d);
 int attn_tc(const mimk_attn_desc& d, cudaStream_t s);
 // the persistent form (one CTA per SM pulls work items; hand-over between items pipelined)
+// f32 at scale: the composition S = Q K^T, softmax, O = P V on the contraction and row kernels (attn_f32.cu)
+int attn_f32_composed_supported(const mimk_attn_desc& d);
+int attn_f32_composed(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_persistent_supported(const mimk_attn_desc& d);  // bf16, head_dim 64 or 128
 int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s);
 

@@ -121,3 +121,16 @@ def test_attention_no_keys(T):
     k = torch.empty((2, 0, 16), device="cuda")
     o, lse = T.attention(q, k, k.clone(), scale=1.0, return_lse=True)
     assert torch.equal(o, torch.zeros_like(o)) and torch.isinf(lse).all() and (lse < 0).all()
+
+
+@pytest.mark.parametrize("bh,s,d,causal", [(3, 1024, 64, True), (2, 1024, 128, False), (20, 512, 64, True), (2, 640, 72, False)])
+def test_attention_f32_at_scale_runs_the_composition(T, bh, s, d, causal):
+    """f32 problems of 2^24 score-products or more run as S = Q K^T, softmax, O = P V on the contraction and row kernels
+    (three-TF32 products, f32-grade): held to the f32 tolerance against the f64 truth on sampled heads."""
+    q, k, v = (randn((bh, s, d), 70 + i, 1.0) for i in range(3))
+    scale = 1.0 / d ** 0.5
+    o = T.attention(q, k, v, scale=scale, causal=causal)
+    T.device_status()
+    heads = sorted({0, bh - 1, bh // 2})
+    want = mo.attention(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), scale=scale, causal=causal, heads=heads)
+    assert nerr(f64(o[heads]), want) <= TOL_F32
