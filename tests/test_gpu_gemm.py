@@ -368,3 +368,76 @@ def test_hlo_train_step_fixture(T):
         rmax = T.reduce("max", 1, gz)
         got = (w[0, 0] - lr * gdW[0, 0].item()) + (b[0] - lr * gdb[0].item()) + gdx[0, 0].item() + rmax[0].item()
         assert abs(got - ref) <= 1e-4, (mode, got, ref)
+
+
+def test_hlo_training_step_fixture(T):
+    """lit/tensor/hlo_step_aux.cpp:33-158 -- one SGD step of the tanh MLP 128/784/1024/10: forward, the softmax-loss
+    gradient, the backward contractions over transposed reads, column sums, and the digest of six update deltas, held to
+    the fixture's bound (1e-2 of the digest's scale + 1e-6)."""
+    B, I, H, O, lr, c = 128, 784, 1024, 10, np.float32(0.001), np.float32(-0.0078125)
+
+    def pat(n, mod, mul, sub):
+        return (mul * ((np.arange(n) % mod).astype(np.float32) / np.float32(mod) - np.float32(sub))).astype(np.float32)
+    W1, W2, W3 = pat(I * H, 89, 0.05, 0.5).reshape(I, H), pat(H * H, 83, 0.05, 0.5).reshape(H, H), pat(H * O, 79, 0.1, 0.5).reshape(H, O)
+    b1 = (0.01 * ((np.arange(H) % 7).astype(np.float32) - 3.0)).astype(np.float32)
+    b2 = (0.01 * ((np.arange(H) % 5).astype(np.float32) - 2.0)).astype(np.float32)
+    b3 = (0.01 * ((np.arange(O) % 3).astype(np.float32) - 1.0)).astype(np.float32)
+    X = pat(B * I, 97, 0.05, 0.0).reshape(B, I)
+    Y = np.zeros((B, O), np.float32)
+    Y[np.arange(B), np.arange(B) % O] = 1.0
+
+    def digest(mm, tanh, colsum, rowmax, rowsum, exp_shift, mul, add, scal, div):
+        """The fixture's computation over abstract operators, so that numpy (f64) and the library run the same program."""
+        h1 = tanh(mm(X_, W1_), b1_)
+        h2 = tanh(mm(h1, W2_), b2_)
+        logits = add(mm(h2, W3_), b3_, row=True)
+        e = exp_shift(logits, rowmax(logits))
+        ssum = rowsum(e)
+        gs = rowsum(scal(Y_, -c))
+        q = div(gs, ssum)                                         # the row sums are positive: the fixture's selects pick gs / |ssum|
+        dlog = add(scal(Y_, c), mul(e, q, col=True))
+        d2 = mm(dlog, W3_, bt=True)                              # dlog . W3^T
+        v59 = d2                                                  # s (1 - h2) + s h2 = s
+        s1 = mm(v59, W2_, bt=True)
+        v66 = mul(s1, add(scal(h1, -1.0), 1.0))
+        v68 = add(v66, mul(v66, h1))
+        dW1 = mm(X_, v68, at=True)
+        dW2 = mm(h1, v59, at=True)
+        dW3 = mm(h2, dlog, at=True)
+        return [dW1[3, 5], colsum(v68)[7], dW2[11, 13], colsum(v59)[17], dW3[19, 2], colsum(dlog)[3]]
+
+    # f64 reference
+    X_, Y_, W1_, W2_, W3_, b1_, b2_, b3_ = (a.astype(np.float64) for a in (X, Y, W1, W2, W3, b1, b2, b3))
+    ref = digest(lambda a, b, at=False, bt=False: (a.T if at else a) @ (b.T if bt else b), lambda z, b: np.tanh(z + b),
+                 lambda m: m.sum(0), lambda m: m.max(1), lambda m: m.sum(1), lambda m, r: np.exp(m - r[:, None]),
+                 lambda a, b, col=False: a * (b[:, None] if col else b), lambda a, b, row=False: a + b, lambda a, k: a * float(k),
+                 lambda a, b: a / b)
+    ref = [float(v) for v in ref]
+
+    # the same program on the library's operators
+    cu = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+    X_, Y_, W1_, W2_, W3_, b1_, b2_, b3_ = (cu(a) for a in (X, Y, W1, W2, W3, b1, b2, b3))
+
+    def mm(a, b, at=False, bt=False):
+        if at:
+            a = T.transpose(a, (1, 0))
+        return T.product_2d(a, T.transpose_2d(b) if bt else b)
+
+    def add(a, b, row=False):
+        if isinstance(b, float):
+            return T.binary("add", a, torch.full_like(a, b))
+        return T.binary_ax("add", 0, a, b) if row else T.binary("add", a, b)
+
+    def mul(a, b, col=False):
+        return T.binary_ax("mul", 1, a, b) if col else T.binary("mul", a, b)
+    got = digest(mm, lambda z, b: T.unary("tanh", T.binary_ax("add", 0, z, b)), lambda m: T.reduce("sum", 0, m),
+                 lambda m: T.reduce("max", 1, m), lambda m: T.reduce("sum", 1, m), lambda m, r: T.binary_ax("subexp", 1, m, r),
+                 mul, add, lambda a, k: T.binary("mul", a, torch.full_like(a, float(k))), lambda a, b: T.binary("div", a, b))
+    got = [float(v.item()) for v in got]
+    olds = [W1[3, 5], b1[7], W2[11, 13], b2[17], W3[19, 2], b3[3]]
+    delta = lambda old, g: float(np.float32(old) - (np.float32(old) - lr * np.float32(g)))
+    g_ref, g_got = [delta(o, g) for o, g in zip(olds, ref)], [delta(o, g) for o, g in zip(olds, got)]
+    scale = sum(abs(v) for v in g_ref)
+    assert abs(sum(g_got) - sum(g_ref)) <= 1e-2 * scale + 1e-6
+    for a, b in zip(got, ref):                                   # and every gradient element on its own
+        assert abs(a - b) <= 1e-4 * max(1.0, abs(b)) + 1e-6, (got, ref)
