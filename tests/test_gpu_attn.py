@@ -134,3 +134,27 @@ def test_attention_f32_at_scale_runs_the_composition(T, bh, s, d, causal):
     heads = sorted({0, bh - 1, bh // 2})
     want = mo.attention(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), scale=scale, causal=causal, heads=heads)
     assert nerr(f64(o[heads]), want) <= TOL_F32
+
+
+@pytest.mark.parametrize("n", [4, 64])
+def test_attn_aux_fixture(T, n):
+    """lit/tensor/attn_aux.cpp:25-67 with attn_exec.mim:20-28 -- out = softmax_rows((x wq)(x wk)^T) (x wv), D = 8, no
+    scale, no mask, inputs from the fixture's formulas; composed from the operators as the program composes it and through
+    the fused entry point; the fixture's bound |ref - out| <= 1e-4 + 1e-4 |ref| against its double-precision loops."""
+    D = 8
+    i = np.arange(n * D)
+    x = ((i % 13) / np.float32(13.0) - np.float32(0.4)).astype(np.float32).reshape(n, D)
+    j = np.arange(D * D)
+    wq = (((7 * j) % 11) / np.float32(11.0) - np.float32(0.5)).astype(np.float32).reshape(D, D)
+    wk = (((5 * j) % 9) / np.float32(9.0) - np.float32(0.5)).astype(np.float32).reshape(D, D)
+    wv = (((3 * j) % 7) / np.float32(7.0) - np.float32(0.5)).astype(np.float32).reshape(D, D)
+    q64, k64, v64 = (x.astype(np.float64) @ w.astype(np.float64) for w in (wq, wk, wv))
+    s = q64 @ k64.T
+    p = np.exp(s - s.max(1, keepdims=True))
+    ref = (p / p.sum(1, keepdims=True)) @ v64
+    cx, cq, ck, cv = (torch.from_numpy(a).cuda() for a in (x, wq, wk, wv))
+    q, k, v = T.product_2d(cx, cq), T.product_2d(cx, ck), T.product_2d(cx, cv)
+    composed = T.product_2d(T.softmax(1, T.product_2d(q, T.transpose_2d(k))), v)
+    fused = T.attention(q[None], k[None], v[None], scale=1.0, causal=False)[0]
+    for out in (composed, fused):
+        assert (np.abs(ref - f64(out)) <= 1e-4 + 1e-4 * np.abs(ref)).all()
