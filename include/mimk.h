@@ -205,9 +205,9 @@ int mimk_scatter(const void* input, const void* index, const void* updates, void
  * Replaces: the composed program `softmax (q * transpose_2d k) * v` (lit/tensor/attn_exec.mim:20-22), seven
  * map_reduce_post ops with a materialised score matrix; scale, mask and batching are extensions.
  * q,o: [batch_heads, seq_q, head_dim]; k,v: [batch_heads, seq_k, head_dim]; dtype F32 or BF16 (o same dtype);
- * bf16 with head_dim 64 or 128 runs fused on the tensor cores; f32 from 2^24 score-products on runs as the composition
- * S = Q K^T, softmax, O = P V on the contraction and row kernels (the score matrix lives in a cached library buffer; not
- * when lse is requested); every other combination on a warp-per-query CUDA-core kernel;
+ * bf16 with head_dim 64 or 128 runs fused on the tensor cores; f32, and bf16 with other head dims, from 2^24
+ * score-products on run as the composition S = Q K^T, softmax, O = P V on the contraction and row kernels (the score
+ * matrix lives in a cached library buffer; not when lse is requested); everything else on a warp-per-query CUDA-core kernel;
  * lse (optional, f32 [batch_heads, seq_q]) receives log-sum-exp of the scaled scores. */
 typedef struct mimk_attn_desc {
     int64_t batch_heads, seq_q, seq_k, head_dim;

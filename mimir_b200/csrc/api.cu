@@ -237,12 +237,12 @@ extern "C" int mimk_attn_fwd(const mimk_attn_desc* d, void* stream) {
     }
     if (persistent && attn_tc_persistent_supported(*d)) return attn_tc_persistent(*d, s);
     if (attn_tc_supported(*d)) return attn_tc(*d, s);
-    static int composed = -1;  // MIMK_ATTN_F32_COMPOSED=0 keeps every f32 problem on the one-launch CUDA-core kernel
+    static int composed = -1;  // MIMK_ATTN_COMPOSED=0 keeps every such problem on the one-launch CUDA-core kernel
     if (composed < 0) {
-        const char* e = getenv("MIMK_ATTN_F32_COMPOSED");
+        const char* e = getenv("MIMK_ATTN_COMPOSED");
         composed      = (e && e[0] == '0') ? 0 : 1;
     }
-    if (composed && attn_f32_composed_supported(*d)) return attn_f32_composed(*d, s);
+    if (composed && attn_composed_supported(*d)) return attn_composed(*d, s);
     return attn_simt(*d, s);
 }
 

@@ -64,9 +64,10 @@ int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_supported(const mimk_attn_desc& d);
 int attn_tc(const mimk_attn_desc& d, cudaStream_t s);
 // the persistent form (one CTA per SM pulls work items; hand-over between items pipelined)
-// f32 at scale: the composition S = Q K^T, softmax, O = P V on the contraction and row kernels (attn_f32.cu)
-int attn_f32_composed_supported(const mimk_attn_desc& d);
-int attn_f32_composed(const mimk_attn_desc& d, cudaStream_t s);
+// f32, and bf16 with other head dims, at scale: the composition S = Q K^T, softmax, O = P V on the contraction and row
+// kernels (attn_composed.cu)
+int attn_composed_supported(const mimk_attn_desc& d);
+int attn_composed(const mimk_attn_desc& d, cudaStream_t s);
 int attn_tc_persistent_supported(const mimk_attn_desc& d);  // bf16, head_dim 64 or 128
 int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s);
 

@@ -123,7 +123,8 @@ def test_attention_no_keys(T):
     assert torch.equal(o, torch.zeros_like(o)) and torch.isinf(lse).all() and (lse < 0).all()
 
 
-@pytest.mark.parametrize("bh,s,d,causal", [(3, 1024, 64, True), (2, 1024, 128, False), (20, 512, 64, True), (2, 640, 72, False)])
+@pytest.mark.parametrize("bh,s,d,causal", [(3, 1024, 64, True), (2, 1024, 128, False), (20, 512, 64, True), (2, 640, 72, False),
+                                                (1, 8320, 16, True)])   # the last: rows longer than the fused softmax takes
 def test_attention_f32_at_scale_runs_the_composition(T, bh, s, d, causal):
     """f32 problems of 2^24 score-products or more run as S = Q K^T, softmax, O = P V on the contraction and row kernels
     (three-TF32 products, f32-grade): held to the f32 tolerance against the f64 truth on sampled heads."""
@@ -158,3 +159,15 @@ def test_attn_aux_fixture(T, n):
     fused = T.attention(q[None], k[None], v[None], scale=1.0, causal=False)[0]
     for out in (composed, fused):
         assert (np.abs(ref - f64(out)) <= 1e-4 + 1e-4 * np.abs(ref)).all()
+
+
+@pytest.mark.parametrize("bh,s,d,causal", [(3, 1024, 96, True), (2, 512, 256, False), (5, 1024, 32, True), (2, 648, 40, False)])
+def test_attention_bf16_other_head_dims_run_the_composition(T, bh, s, d, causal):
+    """bf16 with a head_dim the fused kernels do not take: S = Q K^T (f32 scores), softmax to bf16 P, O = P V."""
+    q, k, v = (randn((bh, s, d), 80 + i, 1.0, torch.bfloat16) for i in range(3))
+    scale = 1.0 / d ** 0.5
+    o = T.attention(q, k, v, scale=scale, causal=causal)
+    T.device_status()
+    heads = sorted({0, bh - 1})
+    want = mo.attention(bits(q), bits(k), bits(v), scale=scale, causal=causal, bf16=True, heads=heads)
+    assert nerr(f64(o[heads]), want) <= TOL_BF16
