@@ -33,27 +33,38 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ 
     const int64_t m0 = int64_t(blockIdx.y) * TM, n0 = int64_t(blockIdx.x) * TN;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     float acc[4][4] = {};
-    for (int64_t k0 = 0; k0 < K; k0 += TK) {
-        // A tile: TM x TK, read with k fastest (unit stride in memory)
-        for (int i = threadIdx.x; i < TM * TK; i += 256) {
+    // Each thread moves four A and four B elements per k-tile. The next tile's elements are fetched into registers before
+    // the current tile is multiplied, so their global-memory latency overlaps the arithmetic (small problems have too few
+    // CTAs to hide it by occupancy). The per-cell order of the fold is untouched: ascending k, one fma per step.
+    float ra[4], rb[4];
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int i  = threadIdx.x + r * 256;
             const int kk = i % TK, mm = i / TK;
             const int64_t m = m0 + mm, k = k0 + kk;
-            As[kk][mm] = (m < M && k < K) ? ld(A, m * K + k) : 0.f;
+            ra[r] = (m < M && k < K) ? ld(A, m * K + k) : 0.f;
+            if (b_nk) {
+                const int64_t n = n0 + mm;
+                rb[r] = (n < N && k < K) ? ld(B, n * K + k) : 0.f;
+            } else {
+                const int nn = i % TN, kb = i / TN;
+                const int64_t n = n0 + nn, kr = k0 + kb;
+                rb[r] = (n < N && kr < K) ? ld(B, kr * N + n) : 0.f;
+            }
         }
-        if (b_nk) {
-            for (int i = threadIdx.x; i < TN * TK; i += 256) {
-                const int kk = i % TK, nn = i / TK;
-                const int64_t n = n0 + nn, k = k0 + kk;
-                Bs[kk][nn] = (n < N && k < K) ? ld(B, n * K + k) : 0.f;
-            }
-        } else {
-            for (int i = threadIdx.x; i < TN * TK; i += 256) {
-                const int nn = i % TN, kk = i / TN;
-                const int64_t n = n0 + nn, k = k0 + kk;
-                Bs[kk][nn] = (n < N && k < K) ? ld(B, k * N + n) : 0.f;
-            }
+    };
+    if (K > 0) fetch(0);
+    for (int64_t k0 = 0; k0 < K; k0 += TK) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int i = threadIdx.x + r * 256;
+            As[i % TK][i / TK] = ra[r];  // A tile: TM x TK, read with k fastest (unit stride in memory)
+            if (b_nk) Bs[i % TK][i / TK] = rb[r];
+            else Bs[i / TN][i % TN] = rb[r];
         }
         __syncthreads();
+        if (k0 + TK < K) fetch(k0 + TK);
 #pragma unroll
         for (int kk = 0; kk < TK; ++kk) {
             float a[4], b[4];
