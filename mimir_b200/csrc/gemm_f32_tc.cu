@@ -67,9 +67,22 @@ __global__ void split_kernel(const float* __restrict__ x, float* __restrict__ hi
         lo[i]         = to_tf32(v - h);
     }
 }
+// The same with the copies' rows padded to `kp` >= cols elements (zeros in the pad): a K that is not a multiple of 4 gets
+// the 16-byte row pitch the bulk loads need, and the zero columns add nothing to the products.
+__global__ void split_pad_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int64_t rows,
+                                 int64_t cols, int64_t kp) {
+    const int64_t n = rows * kp;
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t r = i / kp, c = i % kp;
+        const float v = c < cols ? x[r * cols + c] : 0.f;
+        const float h = to_tf32(v);
+        hi[i]         = h;
+        lo[i]         = to_tf32(v - h);
+    }
+}
 // The same for B stored [K, N]: written transposed as [N, K] (K contiguous) through a 32 x 32 shared-memory tile.
 __global__ void split_transpose_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int64_t K,
-                                       int64_t N) {
+                                       int64_t N, int64_t kp) {
     __shared__ float tile[32][33];
     const int64_t k0 = int64_t(blockIdx.y) * 32, n0 = int64_t(blockIdx.x) * 32;
     for (int r = threadIdx.y; r < 32; r += 8) {
@@ -79,11 +92,11 @@ __global__ void split_transpose_kernel(const float* __restrict__ x, float* __res
     __syncthreads();
     for (int r = threadIdx.y; r < 32; r += 8) {
         const int64_t n = n0 + r, k = k0 + threadIdx.x;
-        if (n < N && k < K) {
-            const float v = tile[threadIdx.x][r];
-            const float h = to_tf32(v);
-            hi[n * K + k] = h;
-            lo[n * K + k] = to_tf32(v - h);
+        if (n < N && k < kp) {  // columns K..kp of the copy are zeros (the tile holds 0 there)
+            const float v  = tile[threadIdx.x][r];
+            const float h  = to_tf32(v);
+            hi[n * kp + k] = h;
+            lo[n * kp + k] = to_tf32(v - h);
         }
     }
 }
@@ -352,11 +365,11 @@ int launch(const CUtensorMap& ah, const CUtensorMap& al, const CUtensorMap& bh, 
 // f32 operands, sizes from 128^3-ish upwards, TMA-friendly strides; everything else stays on the CUDA-core kernel.
 int gemm_f32_tc_supported(const mimk_gemm_desc& d) {
     if (d.in_dtype != MIMK_F32) return 0;
-    if (d.k <= 0 || d.k % 4 != 0) return 0;                        // 16-byte row pitch of the K-major split copies
+    if (d.k <= 0) return 0;
     if (d.out_dtype == MIMK_BF16 ? d.n % 8 != 0 : d.n % 4 != 0) return 0;  // 16-byte epilogue stores
     if (d.m < 128 || d.n < 128 || d.m * d.n * d.k < (int64_t(1) << 23)) return 0;
     if (d.m >= (int64_t(1) << 31) || d.n >= (int64_t(1) << 31) || d.k >= (int64_t(1) << 31)) return 0;
-    if (!aligned16(d.a) || !aligned16(d.b) || !aligned16(d.c)) return 0;
+    if (!aligned16(d.c)) return 0;  // the operands are re-written as padded hi / lo copies; only the result is stored as is
     if (d.post_full && !aligned16(d.post_full)) return 0;
     if (d.batch > 16) return 0;
     return 1;
@@ -366,7 +379,8 @@ int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s) {
     int st          = MIMK_OK;
     DeviceInfo* dev = device_info(&st);
     if (!dev) return st;
-    const size_t a_elems = size_t(d.m) * d.k, b_elems = size_t(d.n) * d.k;
+    const int64_t kp = (d.k + 3) & ~int64_t(3);  // row pitch of the hi / lo copies: 16-byte multiples
+    const size_t a_elems = size_t(d.m) * kp, b_elems = size_t(d.n) * kp;
     const size_t a_bytes = (a_elems * 4 + 255) & ~size_t(255), b_bytes = (b_elems * 4 + 255) & ~size_t(255);
     void* scratch = nullptr;
     MIMK_TRY(get_scratch(2 * a_bytes + 2 * b_bytes, &scratch));
@@ -379,25 +393,27 @@ int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s) {
         const float* B = static_cast<const float*>(d.b) + b * d.stride_b;
         if (b == 0 || d.stride_a != 0) {
             int grid = int((a_elems + 1023) / 1024 < size_t(dev->sm_count) * 8 ? (a_elems + 1023) / 1024 : size_t(dev->sm_count) * 8);
-            split_kernel<<<grid, 256, 0, s>>>(A, a_hi, a_lo, int64_t(a_elems));
+            if (kp == d.k) split_kernel<<<grid, 256, 0, s>>>(A, a_hi, a_lo, int64_t(a_elems));
+            else split_pad_kernel<<<grid, 256, 0, s>>>(A, a_hi, a_lo, d.m, d.k, kp);
             MIMK_TRY(launch_status());
         }
         if (b == 0 || d.stride_b != 0) {
             if (d.b_layout == MIMK_B_NK) {
                 int grid = int((b_elems + 1023) / 1024 < size_t(dev->sm_count) * 8 ? (b_elems + 1023) / 1024 : size_t(dev->sm_count) * 8);
-                split_kernel<<<grid, 256, 0, s>>>(B, b_hi, b_lo, int64_t(b_elems));
+                if (kp == d.k) split_kernel<<<grid, 256, 0, s>>>(B, b_hi, b_lo, int64_t(b_elems));
+                else split_pad_kernel<<<grid, 256, 0, s>>>(B, b_hi, b_lo, d.n, d.k, kp);
             } else {
                 dim3 grid((unsigned)((d.n + 31) / 32), (unsigned)((d.k + 31) / 32));
                 if (grid.y > 65535) return MIMK_E_UNSUPPORTED;
-                split_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(B, b_hi, b_lo, d.k, d.n);
+                split_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(B, b_hi, b_lo, d.k, d.n, kp);
             }
             MIMK_TRY(launch_status());
         }
         CUtensorMap tAh, tAl, tBh, tBl;
-        MIMK_TRY(make_tmap_f32_2d(&tAh, a_hi, uint64_t(d.k), uint64_t(d.m), BM));
-        MIMK_TRY(make_tmap_f32_2d(&tAl, a_lo, uint64_t(d.k), uint64_t(d.m), BM));
-        MIMK_TRY(make_tmap_f32_2d(&tBh, b_hi, uint64_t(d.k), uint64_t(d.n), BN));
-        MIMK_TRY(make_tmap_f32_2d(&tBl, b_lo, uint64_t(d.k), uint64_t(d.n), BN));
+        MIMK_TRY(make_tmap_f32_2d(&tAh, a_hi, uint64_t(kp), uint64_t(d.m), BM));
+        MIMK_TRY(make_tmap_f32_2d(&tAl, a_lo, uint64_t(kp), uint64_t(d.m), BM));
+        MIMK_TRY(make_tmap_f32_2d(&tBh, b_hi, uint64_t(kp), uint64_t(d.n), BN));
+        MIMK_TRY(make_tmap_f32_2d(&tBl, b_lo, uint64_t(kp), uint64_t(d.n), BN));
         Params p;
         p.M = d.m, p.N = d.n, p.K = d.k;
         p.C         = static_cast<uint8_t*>(d.c) + size_t(b * d.stride_c) * out_size;
