@@ -178,6 +178,9 @@ enum {
  * (binary_ax); 2: y is [len*inner], broadcast over `outer` (a bias row); 3: unary, y unused. */
 int mimk_map(int op, const void* x, const void* y, void* out, int out_dtype, int64_t outer, int64_t len,
              int64_t inner, int y_mode, void* stream);
+/* The same with the operands' element type given: x and y F32 or BF16 (both of in_dtype), arithmetic in f32. */
+int mimk_map_t(int op, const void* x, const void* y, void* out, int in_dtype, int out_dtype, int64_t outer, int64_t len,
+               int64_t inner, int y_mode, void* stream);
 
 /* ---- constructors and data-dependent indexing (tensor.mim:77-109, 519-563): not map_reduce_post instances ----
  * Shapes are `rank` extents (rank <= MIMK_MRP_MAX_RANK), tensors dense row-major.

@@ -62,6 +62,14 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
     float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
     return make_float4(a.x, a.y, b.x, b.y);
 }
+// the same through the read-only cache path, for operands that many threads re-read (a broadcast row)
+__device__ __forceinline__ float4 load4_cached(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load4_cached(const __nv_bfloat16* p) {
+    uint2 u = __ldg(reinterpret_cast<const uint2*>(p));
+    float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.x));
+    float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
 __device__ __forceinline__ void store4(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
 __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
     uint2 u;
@@ -269,29 +277,29 @@ __device__ __forceinline__ float apply_op(int op, float a, float b) {
         default: return a;
     }
 }
-template <class TOut>
-__global__ void map_kernel(int op, const float* __restrict__ x, const float* __restrict__ y, TOut* __restrict__ out,
+template <class TIn, class TOut>
+__global__ void map_kernel(int op, const TIn* __restrict__ x, const TIn* __restrict__ y, TOut* __restrict__ out,
                            int64_t outer, int64_t len, int64_t inner, int y_mode) {
     const int64_t total = outer * len * inner;
     for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total; t += int64_t(gridDim.x) * blockDim.x) {
         float b = 0.f;
         if (y_mode == 0) {
-            b = y[t];
+            b = ldf(y, t);
         } else if (y_mode == 1) {
             const int64_t o = t / (len * inner), i = t % inner;
-            b = y[o * inner + i];
+            b = ldf(y, o * inner + i);
         } else if (y_mode == 2) {
-            b = y[t % (len * inner)];
+            b = ldf(y, t % (len * inner));
         }
-        stf(out, t, apply_op(op, x[t], b));
+        stf(out, t, apply_op(op, ldf(x, t), b));
     }
 }
 
 // 128-bit form of map_kernel: four consecutive elements per thread. Requires 16-byte aligned x / y / out, a total
 // divisible by 4, and a broadcast operand whose index is constant over the four elements (y_mode 1 with inner == 1 and
 // len % 4 == 0) or runs with them (y_mode 0; y_mode 2 with (len * inner) % 4 == 0).
-template <class TOut>
-__global__ void __launch_bounds__(256) map_vec4_kernel(int op, const float* __restrict__ x, const float* __restrict__ y,
+template <class TIn, class TOut>
+__global__ void __launch_bounds__(256) map_vec4_kernel(int op, const TIn* __restrict__ x, const TIn* __restrict__ y,
                                                       TOut* __restrict__ out, int64_t total4, int64_t len, int64_t period4,
                                                       int y_mode) {
     for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total4; t += int64_t(gridDim.x) * blockDim.x) {
@@ -300,10 +308,10 @@ __global__ void __launch_bounds__(256) map_vec4_kernel(int op, const float* __re
         if (y_mode == 0) {
             b = load4(y + 4 * t);
         } else if (y_mode == 1) {
-            const float v = __ldg(y + (4 * t) / len);
+            const float v = ldf(y, (4 * t) / len);
             b             = make_float4(v, v, v, v);
         } else if (y_mode == 2) {
-            b = __ldg(reinterpret_cast<const float4*>(y) + (t % period4));
+            b = load4_cached(y + 4 * (t % period4));
         }
         float4 r;
         r.x = apply_op(op, a.x, b.x);
@@ -564,42 +572,54 @@ extern "C" int mimk_softmax_rmsnorm(const void* x, const void* gamma, void* y, i
                                                static_cast<cudaStream_t>(stream), *dev);
 }
 
-extern "C" int mimk_map(int op, const void* x, const void* y, void* out, int out_dtype, int64_t outer, int64_t len,
-                        int64_t inner, int y_mode, void* stream) {
+namespace {
+template <class TIn>
+int map_impl(int op, const TIn* x, const TIn* y, void* out, int out_dtype, int64_t outer, int64_t len, int64_t inner, int y_mode,
+             cudaStream_t s, const DeviceInfo& dev) {
+    const int64_t total = outer * len * inner;
+    const size_t in_al  = 4 * sizeof(TIn);  // four elements per access
+    auto al             = [&](const void* p) { return (reinterpret_cast<uintptr_t>(p) % in_al) == 0; };
+    const bool out_al   = (reinterpret_cast<uintptr_t>(out) % (out_dtype == MIMK_F32 ? 16 : 8)) == 0;
+    const bool y_ok     = y_mode == 3 || (y_mode == 0 && al(y)) || (y_mode == 1 && inner == 1 && len % 4 == 0) ||
+                      (y_mode == 2 && (len * inner) % 4 == 0 && al(y));
+    if (total % 4 == 0 && al(x) && out_al && y_ok) {
+        const int64_t total4 = total / 4, period4 = y_mode == 2 ? (len * inner) / 4 : 1;
+        const int vgrid      = grid_for(total4, 256, dev.sm_count, 8);
+        if (out_dtype == MIMK_F32)
+            map_vec4_kernel<<<vgrid, 256, 0, s>>>(op, x, y, static_cast<float*>(out), total4, len, period4, y_mode);
+        else
+            map_vec4_kernel<<<vgrid, 256, 0, s>>>(op, x, y, static_cast<__nv_bfloat16*>(out), total4, len, period4, y_mode);
+        return launch_status();
+    }
+    const int grid = grid_for(total, 256, dev.sm_count, 8);
+    if (out_dtype == MIMK_F32) map_kernel<<<grid, 256, 0, s>>>(op, x, y, static_cast<float*>(out), outer, len, inner, y_mode);
+    else map_kernel<<<grid, 256, 0, s>>>(op, x, y, static_cast<__nv_bfloat16*>(out), outer, len, inner, y_mode);
+    return launch_status();
+}
+}  // namespace
+
+extern "C" int mimk_map_t(int op, const void* x, const void* y, void* out, int in_dtype, int out_dtype, int64_t outer, int64_t len,
+                          int64_t inner, int y_mode, void* stream) {
     if (outer < 0 || len < 0 || inner < 0 || y_mode < 0 || y_mode > 3) return MIMK_E_ARG;
     const bool unary = op >= MIMK_OP_RELU && op <= MIMK_OP_COPY;
     const bool binary = op >= MIMK_OP_ADD && op <= MIMK_OP_SUBEXP;
     if (!unary && !binary) return MIMK_E_ARG;
     if (binary && y_mode == 3) return MIMK_E_ARG;
-    if (out_dtype != MIMK_F32 && out_dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    if ((in_dtype != MIMK_F32 && in_dtype != MIMK_BF16) || (out_dtype != MIMK_F32 && out_dtype != MIMK_BF16)) return MIMK_E_DTYPE;
     int st          = MIMK_OK;
     DeviceInfo* dev = device_info(&st);
     if (!dev) return st;
-    const int64_t total = outer * len * inner;
-    if (total == 0) return MIMK_OK;
+    if (outer * len * inner == 0) return MIMK_OK;
     if (!x || !out || (binary && !y)) return MIMK_E_ARG;
     if (unary) y_mode = 3;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool out_al = (reinterpret_cast<uintptr_t>(out) % (out_dtype == MIMK_F32 ? 16 : 8)) == 0;
-    const bool y_ok   = y_mode == 3 || (y_mode == 0 && aligned16(y)) || (y_mode == 1 && inner == 1 && len % 4 == 0) ||
-                      (y_mode == 2 && (len * inner) % 4 == 0 && aligned16(y));
-    if (total % 4 == 0 && aligned16(x) && out_al && y_ok) {
-        const int64_t total4 = total / 4, period4 = y_mode == 2 ? (len * inner) / 4 : 1;
-        const int vgrid      = grid_for(total4, 256, dev->sm_count, 8);
-        if (out_dtype == MIMK_F32)
-            map_vec4_kernel<<<vgrid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),
-                                                  static_cast<float*>(out), total4, len, period4, y_mode);
-        else
-            map_vec4_kernel<<<vgrid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),
-                                                  static_cast<__nv_bfloat16*>(out), total4, len, period4, y_mode);
-        return launch_status();
-    }
-    int grid       = grid_for(total, 256, dev->sm_count, 8);
-    if (out_dtype == MIMK_F32)
-        map_kernel<<<grid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),
-                                        static_cast<float*>(out), outer, len, inner, y_mode);
-    else
-        map_kernel<<<grid, 256, 0, s>>>(op, static_cast<const float*>(x), static_cast<const float*>(y),
-                                        static_cast<__nv_bfloat16*>(out), outer, len, inner, y_mode);
-    return launch_status();
+    if (in_dtype == MIMK_F32)
+        return map_impl(op, static_cast<const float*>(x), static_cast<const float*>(y), out, out_dtype, outer, len, inner, y_mode, s, *dev);
+    return map_impl(op, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(y), out, out_dtype, outer, len, inner,
+                    y_mode, s, *dev);
+}
+
+extern "C" int mimk_map(int op, const void* x, const void* y, void* out, int out_dtype, int64_t outer, int64_t len,
+                        int64_t inner, int y_mode, void* stream) {
+    return mimk_map_t(op, x, y, out, MIMK_F32, out_dtype, outer, len, inner, y_mode, stream);
 }

@@ -173,36 +173,46 @@ def softmax_rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, *, out_dty
     return out
 
 
+def _same_float(*ts):
+    dt = ts[0].dtype
+    if dt not in (torch.float32, torch.bfloat16) or any(t.dtype != dt for t in ts):
+        raise TypeError("elementwise operators take F32 or BF16 tensors of one element type")
+    return dt
+
+
 def unary(op: str, x: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
     _dev(x)
+    _same_float(x)
     x = x.contiguous()
     out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
-    L.check(L.lib().mimk_map(_UNOP[op], x.data_ptr(), None, out.data_ptr(), _dt(out), 1, x.numel(), 1, 3, _stream()),
+    L.check(L.lib().mimk_map_t(_UNOP[op], x.data_ptr(), None, out.data_ptr(), _dt(x), _dt(out), 1, x.numel(), 1, 3, _stream()),
             "unary")
     return out
 
 
 def binary(op: str, x: torch.Tensor, y: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
     _dev(x, y)
+    _same_float(x, y)
     if x.shape != y.shape:
         raise ValueError("binary expects operands of one shape")
     x, y = x.contiguous(), y.contiguous()
     out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
-    L.check(L.lib().mimk_map(_BINOP[op], x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(out), 1, x.numel(), 1, 0,
-                             _stream()), "binary")
+    L.check(L.lib().mimk_map_t(_BINOP[op], x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(x), _dt(out), 1, x.numel(), 1, 0,
+                               _stream()), "binary")
     return out
 
 
 def binary_ax(op: str, ax: int, x: torch.Tensor, y: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
     """`binary_ax app ax (x, y)`: y lacks axis `ax` of x and is broadcast along it."""
     _dev(x, y)
+    _same_float(x, y)
     x, y = x.contiguous(), y.contiguous()
     ax, outer, ln, inner = _view3(x, ax)
     if tuple(y.shape) != tuple(x.shape[:ax] + x.shape[ax + 1:]):
         raise ValueError("binary_ax: y must have x's shape without axis ax")
     out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
-    L.check(L.lib().mimk_map(_BINOP[op], x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(out), outer, ln, inner, 1,
-                             _stream()), "binary_ax")
+    L.check(L.lib().mimk_map_t(_BINOP[op], x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(x), _dt(out), outer, ln, inner, 1,
+                               _stream()), "binary_ax")
     return out
 
 

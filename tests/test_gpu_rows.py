@@ -143,3 +143,24 @@ def test_full_size_softmax_properties(T):
     rows = [0, 1, 8191, 16383]
     want = mo.softmax_rows(x[rows].cpu().numpy(), truth=True)
     assert nerr(f64(y[rows]), want) < TOL_BF16
+
+
+def test_elementwise_operators_on_bf16_operands():
+    """unary / binary / binary_ax with BF16 operands: arithmetic in f32 on the exact operand values, one rounding at the
+    store -- bit-identical to f32 arithmetic on the widened operands followed by round-to-nearest-even."""
+    from mimir_b200 import tensor as T
+    g = torch.Generator().manual_seed(6)
+    for shape in ((64, 1024), (7, 33, 5)):                       # the 128-bit path and the scalar path
+        x = torch.randn(shape, generator=g).to(torch.bfloat16).cuda()
+        y = torch.randn(shape, generator=g).to(torch.bfloat16).cuda()
+        assert torch.equal(T.binary("add", x, y), (x.float() + y.float()).to(torch.bfloat16))
+        assert torch.equal(T.binary("mul", x, y, out_dtype=torch.float32), x.float() * y.float())
+        assert torch.equal(T.unary("relu", x), torch.relu(x))
+        got = T.unary("silu", x, out_dtype=torch.float32)
+        want = x.double() / (1 + torch.exp(-x.double()))
+        assert ((got.double() - want).abs().max() / want.abs().max()).item() <= 1e-5
+        for ax in range(len(shape)):
+            yb = torch.randn([s for i, s in enumerate(shape) if i != ax], generator=g).to(torch.bfloat16).cuda()
+            assert torch.equal(T.binary_ax("sub", ax, x, yb), (x.float() - yb.float().unsqueeze(ax)).to(torch.bfloat16))
+    with pytest.raises(TypeError):
+        T.binary("add", torch.zeros(4, device="cuda"), torch.zeros(4, device="cuda", dtype=torch.bfloat16))
