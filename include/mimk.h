@@ -130,7 +130,8 @@ int mimk_gemm_flat(int64_t m, int64_t n, int64_t k, const void* a, const void* b
                    int32_t out_dtype, int32_t b_layout, int32_t post, const void* post_row, void* stream);
 
 /* out[o,i] = fold_a g(x[o,a,i]) over the middle axis of a [outer, len, inner] view; inner == 1 is a row reduce.
- * Replaces: tensor.reduce (tensor.mim:1151-1157) lowered by gpu.lower_btensor_map_reduce. dtype F32 (x and out). */
+ * Replaces: tensor.reduce (tensor.mim:1151-1157) lowered by gpu.lower_btensor_map_reduce. dtype F32 or BF16 (x and out;
+ * accumulation in f32 either way). */
 int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner, int monoid,
                 void* stream);
 

@@ -209,14 +209,14 @@ __global__ void softmax_strided_kernel(const TIn* __restrict__ x, TOut* __restri
 }
 
 // ---- reduce ------------------------------------------------------------------------------------
-template <class Op>
-__global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t rows,
+template <class Op, class TIn, class TOut>
+__global__ void __launch_bounds__(256) reduce_rows_kernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t rows,
                                                          int64_t cols, int vec_ok) {
     __shared__ float red[32];
     Op op;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const float* xr = x + row * cols;
-        float acc       = Op::ident();
+        const TIn* xr = x + row * cols;
+        float acc     = Op::ident();
         if (vec_ok) {
             const int64_t nvec = cols >> 2;
             for (int64_t i = threadIdx.x; i < nvec; i += 256) {
@@ -224,17 +224,17 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restric
                 acc      = op(acc, op(op(v.x, v.y), op(v.z, v.w)));
             }
         } else {
-            for (int64_t c = threadIdx.x; c < cols; c += 256) acc = op(acc, xr[c]);
+            for (int64_t c = threadIdx.x; c < cols; c += 256) acc = op(acc, ldf(xr, c));
         }
         acc = block_reduce<256>(acc, red, op);
-        if (threadIdx.x == 0) out[row] = acc;
+        if (threadIdx.x == 0) stf(out, row, acc);
     }
 }
 
 // inner > 1: thread per (o, i) column; blockIdx.y splits the reduced axis into `gridDim.y` slices whose partial
 // results go to `partial` [slice, outer*inner] (or straight to `out` when there is a single slice).
-template <class Op>
-__global__ void reduce_mid_kernel(const float* __restrict__ x, float* __restrict__ dst, int64_t outer, int64_t len,
+template <class Op, class TIn, class TDst>
+__global__ void reduce_mid_kernel(const TIn* __restrict__ x, TDst* __restrict__ dst, int64_t outer, int64_t len,
                                   int64_t inner, int64_t slice_len) {
     Op op;
     const int64_t total = outer * inner;
@@ -242,20 +242,20 @@ __global__ void reduce_mid_kernel(const float* __restrict__ x, float* __restrict
     const int64_t a1    = a0 + slice_len < len ? a0 + slice_len : len;
     for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total; t += int64_t(gridDim.x) * blockDim.x) {
         const int64_t o = t / inner, i = t % inner;
-        const float* p = x + o * len * inner + i;
-        float acc      = Op::ident();
-        for (int64_t a = a0; a < a1; ++a) acc = op(acc, p[a * inner]);
-        dst[int64_t(blockIdx.y) * total + t] = acc;
+        const TIn* p = x + o * len * inner + i;
+        float acc    = Op::ident();
+        for (int64_t a = a0; a < a1; ++a) acc = op(acc, ldf(p, a * inner));
+        stf(dst, int64_t(blockIdx.y) * total + t, acc);
     }
 }
-template <class Op>
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t total,
+template <class Op, class TOut>
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, TOut* __restrict__ out, int64_t total,
                                        int slices) {
     Op op;
     for (int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; t < total; t += int64_t(gridDim.x) * blockDim.x) {
         float acc = Op::ident();
         for (int s = 0; s < slices; ++s) acc = op(acc, partial[int64_t(s) * total + t]);
-        out[t] = acc;
+        stf(out, t, acc);
     }
 }
 
@@ -373,11 +373,11 @@ int dispatch_rows(const void* x, const float* gamma, void* y, int in_dtype, int 
     return MIMK_E_DTYPE;
 }
 
-template <class Op>
-int reduce_impl(const float* x, float* out, int64_t outer, int64_t len, int64_t inner, cudaStream_t s,
+template <class Op, class TIn, class TOut>
+int reduce_impl(const TIn* x, TOut* out, int64_t outer, int64_t len, int64_t inner, cudaStream_t s,
                 const DeviceInfo& dev) {
     if (inner == 1) {
-        const int vec_ok = (len % 4 == 0) && aligned16(x);
+        const int vec_ok = (len % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(TIn))) == 0;
         int grid         = int(outer < int64_t(dev.sm_count) * 8 ? outer : int64_t(dev.sm_count) * 8);
         reduce_rows_kernel<Op><<<grid, 256, 0, s>>>(x, out, outer, len, vec_ok);
         return launch_status();
@@ -490,7 +490,7 @@ using namespace mimk;
 extern "C" int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner, int monoid,
                            void* stream) {
     if (outer < 0 || len < 0 || inner < 0) return MIMK_E_ARG;
-    if (dtype != MIMK_F32) return MIMK_E_DTYPE;
+    if (dtype != MIMK_F32 && dtype != MIMK_BF16) return MIMK_E_DTYPE;
     if (monoid < MIMK_SUM || monoid > MIMK_MIN) return MIMK_E_ARG;
     int st          = MIMK_OK;
     DeviceInfo* dev = device_info(&st);
@@ -498,6 +498,15 @@ extern "C" int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, i
     if (outer * inner == 0) return MIMK_OK;
     if (!out || (len > 0 && !x)) return MIMK_E_ARG;  // len == 0: every cell is the monoid's identity, x is not read
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == MIMK_BF16) {  // bf16 in, f32 accumulation, bf16 out
+        const __nv_bfloat16* xh = static_cast<const __nv_bfloat16*>(x);
+        __nv_bfloat16* oh       = static_cast<__nv_bfloat16*>(out);
+        switch (monoid) {
+            case MIMK_SUM: return reduce_impl<SumOp>(xh, oh, outer, len, inner, s, *dev);
+            case MIMK_MAX: return reduce_impl<MaxOp>(xh, oh, outer, len, inner, s, *dev);
+            default: return reduce_impl<MinOp>(xh, oh, outer, len, inner, s, *dev);
+        }
+    }
     const float* xf = static_cast<const float*>(x);
     float* of       = static_cast<float*>(out);
     switch (monoid) {

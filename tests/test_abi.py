@@ -57,7 +57,7 @@ def test_argument_validation_needs_no_device(lib):
     assert L.mimk_attn_fwd(None, None) == 1
     assert L.mimk_mlp_gated(None, None) == 1
     assert L.mimk_reduce(None, None, lib.F32, -1, 4, 1, lib.SUM, None) == 1
-    assert L.mimk_reduce(None, None, lib.BF16, 1, 4, 1, lib.SUM, None) == 4
+    assert L.mimk_reduce(None, None, lib.I32, 1, 4, 1, lib.SUM, None) == 4
     assert L.mimk_map(99, None, None, None, lib.F32, 1, 1, 1, 0, None) == 1
     assert L.mimk_map_reduce_post(None, None) == 1
     assert L.mimk_host_map_reduce_post(None) == 1

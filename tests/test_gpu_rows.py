@@ -164,3 +164,18 @@ def test_elementwise_operators_on_bf16_operands():
             assert torch.equal(T.binary_ax("sub", ax, x, yb), (x.float() - yb.float().unsqueeze(ax)).to(torch.bfloat16))
     with pytest.raises(TypeError):
         T.binary("add", torch.zeros(4, device="cuda"), torch.zeros(4, device="cuda", dtype=torch.bfloat16))
+
+
+def test_reduce_on_bf16_operands():
+    """reduce with BF16 operands: f32 accumulation of the exact operand values, one rounding at the store; every axis of a
+    rank-3 tensor (row kernel, middle-axis kernel with and without a split of the folded axis)."""
+    from mimir_b200 import tensor as T
+    g = torch.Generator().manual_seed(12)
+    for shape in ((48, 1024, 8), (6, 4096, 3), (33, 70, 129)):
+        x = torch.randn(shape, generator=g).to(torch.bfloat16).cuda()
+        for ax in range(3):
+            assert torch.equal(T.reduce("max", ax, x), x.amax(ax))
+            s = T.reduce("sum", ax, x)
+            want = x.double().sum(ax)
+            assert s.dtype == torch.bfloat16
+            assert ((s.double() - want).abs().max() / want.abs().max()).item() <= TOL_BF16
