@@ -122,7 +122,8 @@ bool plan_gemm(const mimk_mrp_desc& d, Plan& p) {
 
 bool plan_reduce(const mimk_mrp_desc& d, Plan& p) {
     if (d.nis != 1 || d.nps != 0 || d.post != MIMK_P_ID || d.rn != d.ro + 1 || d.ro < 1) return false;
-    if (d.acc_dtype != MIMK_F32 || d.in_dtype[0] != MIMK_F32 || d.out_dtype != MIMK_F32 || !out_is_identity(d)) return false;
+    if (d.acc_dtype != MIMK_F32 || !out_is_identity(d)) return false;
+    if ((d.in_dtype[0] != MIMK_F32 && d.in_dtype[0] != MIMK_BF16) || d.out_dtype != d.in_dtype[0]) return false;
     const uint32_t init = init32(d);
     if (d.comb == MIMK_F_ADD && init == 0u) p.monoid = MIMK_SUM;
     else if (d.comb == MIMK_F_MAX && init == 0xff800000u) p.monoid = MIMK_MAX;
@@ -173,8 +174,8 @@ int broadcast_kind(const mimk_mrp_desc& d, int i, int* ax) {
 
 bool plan_map(const mimk_mrp_desc& d, Plan& p) {
     if (d.rn != d.ro || d.ro < 1 || d.nps != 0 || d.acc_dtype != MIMK_F32 || !out_is_identity(d)) return false;
-    for (int i = 0; i < d.nis; ++i)
-        if (d.in_dtype[i] != MIMK_F32) return false;
+    for (int i = 0; i < d.nis; ++i)  // operands of one floating-point element type
+        if ((d.in_dtype[i] != MIMK_F32 && d.in_dtype[i] != MIMK_BF16) || d.in_dtype[i] != d.in_dtype[0]) return false;
     int ax = 0;
     if (d.nis == 1 && d.comb == MIMK_F_FIRST) {
         if (broadcast_kind(d, 0, &ax) != 0) return false;
@@ -255,10 +256,11 @@ bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status) {
     switch (p.route) {
         case MIMK_ROUTE_GEMM: *status = mimk_gemm(&p.gemm, stream); return true;
         case MIMK_ROUTE_REDUCE:
-            *status = mimk_reduce(d.in[0], d.out, MIMK_F32, p.outer, p.len, p.inner, p.monoid, stream);
+            *status = mimk_reduce(d.in[0], d.out, d.in_dtype[0], p.outer, p.len, p.inner, p.monoid, stream);
             return true;
         case MIMK_ROUTE_MAP:
-            *status = mimk_map(p.op, d.in[0], d.nis == 2 ? d.in[1] : nullptr, d.out, d.out_dtype, p.outer, p.len, p.inner, p.y_mode, stream);
+            *status = mimk_map_t(p.op, d.in[0], d.nis == 2 ? d.in[1] : nullptr, d.out, d.in_dtype[0], d.out_dtype, p.outer, p.len, p.inner,
+                                 p.y_mode, stream);
             return true;
         case MIMK_ROUTE_PERMUTE: {
             const int esize = d.out_dtype == MIMK_BF16 ? 2 : d.out_dtype == MIMK_I64 ? 8 : 4;

@@ -266,3 +266,15 @@ def test_two_byte_permutations_with_even_extents_move_pairs(T, L):
         assert torch.equal(T.transpose(x, perm), x.permute(perm).contiguous()), perm
     m = torch.randn(2050, 1026, generator=g).to(torch.bfloat16).cuda()
     assert torch.equal(T.transpose(m, (1, 0)), m.t().contiguous())
+
+
+def test_bf16_descriptors_reach_the_fold_and_map_kernels(T, L):
+    g = torch.Generator().manual_seed(14)
+    x = torch.randn(1024, 2048, generator=g).to(torch.bfloat16).cuda()
+    y = torch.randn(1024, 2048, generator=g).to(torch.bfloat16).cuda()
+    s = T.map_reduce_post((1024,), (1024, 2048), L.F_MAX, float("-inf"), L.P_ID, T.proj_map(2, (0,)), [T.id_map(2)], [x],
+                          out_dtype=torch.bfloat16)
+    assert torch.equal(s, x.amax(1))
+    m = T.map_reduce_post((1024, 2048), (1024, 2048), L.F_MUL2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [x, y],
+                          out_dtype=torch.bfloat16)
+    assert torch.equal(m, (x.float() * y.float()).to(torch.bfloat16))

@@ -102,3 +102,13 @@ def test_axis_folds_and_maps(TL):
     assert T.mrp_route([2048, 1024], [2048, 1024], L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0])], [[1024, 4096]],
                        [F32]) == "generic"
     assert T.mrp_route([64, 32], [64, 32], L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0])], [[32, 64]], [F32]) == "generic"
+
+
+def test_bf16_folds_and_maps_are_recognised_too(TL):
+    T, L = TL
+    big = [1024, 2048]
+    assert T.mrp_route([1024], big, L.F_ADD, 0.0, L.P_ID, T.proj_map(2, [0]), [T.id_map(2)], [big], [BF16], out_dtype=BF16) == "reduce"
+    assert T.mrp_route([1024], big, L.F_ADD, 0.0, L.P_ID, T.proj_map(2, [0]), [T.id_map(2)], [big], [BF16], out_dtype=F32) == "generic"
+    assert T.mrp_route(big, big, L.F_ADD2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [big, big], [BF16, BF16],
+                       out_dtype=BF16) == "map"
+    assert T.mrp_route(big, big, L.F_ADD2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [big, big], [BF16, F32]) == "generic"
