@@ -192,7 +192,7 @@ int mimk_map_t(int op, const void* x, const void* y, void* out, int in_dtype, in
  * mimk_gather: out[o] = input[o with o[dim] := index[o]], out has the index's shape (tensor.mim:519-541).
  * mimk_scatter: out = input, then out[u with u[dim] := index[u]] = updates[u] for every u of the index's shape in
  *   row-major order -- where two updates name one destination the later one wins (tensor.mim:543-563). out may alias
- *   input.
+ *   input. Large index tensors use the library's cached scratch buffer (one int per element of input).
  * dtype: element type of input / updates / out (F32, BF16, I32, I64); index_dtype I32 or I64. The reference's index type
  * `Idx (s_src#dim)` cannot hold an out-of-range value; here such a value skips its access and mimk_device_status reports
  * MIMK_E_SHAPE. */

@@ -89,6 +89,48 @@ __global__ void scatter_kernel(const I* __restrict__ index, const T* __restrict_
     }
 }
 
+// The same rule with one thread per update, for index tensors whose lines are long or few: first every update proposes
+// its position along `dim` for its destination (atomicMax -- two updates can only meet on one line, where a later
+// position means a later visit in row-major order), then the update that holds the destination's maximum stores.
+template <class I>
+__device__ __forceinline__ bool scatter_target(const I* __restrict__ index, long long i, const Shape& src, const Shape& idx,
+                                               const Shape& ups, int dim, int* status, long long* dst, long long* u_off, int* k) {
+    const long long sel = (long long)index[i];
+    if (sel < 0 || sel >= src.ext[dim]) {
+        *status = MIMK_E_SHAPE;
+        return false;
+    }
+    long long rest = i, o = 0, u = 0, o_str = 1, u_str = 1;
+    for (int d = idx.rank - 1; d >= 0; --d) {
+        const long long c = rest % idx.ext[d];
+        rest /= idx.ext[d];
+        if (d == dim) *k = int(c);
+        o += (d == dim ? sel : c) * o_str;
+        u += c * u_str;
+        o_str *= src.ext[d], u_str *= ups.ext[d];
+    }
+    *dst = o, *u_off = u;
+    return true;
+}
+template <class I>
+__global__ void scatter_propose_kernel(const I* __restrict__ index, int* __restrict__ winner, long long n, Shape src, Shape idx,
+                                       Shape ups, int dim, int* status) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        long long dst, u;
+        int k;
+        if (scatter_target(index, i, src, idx, ups, dim, status, &dst, &u, &k)) atomicMax(winner + dst, k);
+    }
+}
+template <class T, class I>
+__global__ void scatter_commit_kernel(const I* __restrict__ index, const T* __restrict__ upd, const int* __restrict__ winner,
+                                      T* __restrict__ out, long long n, Shape src, Shape idx, Shape ups, int dim, int* status) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        long long dst, u;
+        int k;
+        if (scatter_target(index, i, src, idx, ups, dim, status, &dst, &u, &k) && winner[dst] == k) out[dst] = upd[u];
+    }
+}
+
 // out[i] = cond[i] ? a[i] : b[i]   (tensor.select, tensor.mim:378-384; cond one byte per element, non-zero = true)
 template <class T>
 __global__ void select_kernel(const uint8_t* __restrict__ cond, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
@@ -174,17 +216,35 @@ int gather_typed(const void* in, const void* index, void* out, int index_dtype, 
     return launch_status();
 }
 
-template <class T>
-int scatter_typed(const void* index, const void* upd, void* out, int index_dtype, long long lines, const Shape& src, const Shape& idx,
-                  const Shape& ups, int dim, DeviceInfo* dev, cudaStream_t s) {
+template <class T, class I>
+int scatter_any(const I* index, const T* upd, T* out, long long n_idx, long long n_src, const Shape& src, const Shape& idx,
+                const Shape& ups, int dim, DeviceInfo* dev, cudaStream_t s) {
+    const long long lines = n_idx / idx.ext[dim];
+    // few or long lines leave one-thread-per-line without parallelism: one thread per update and a winner per destination
+    if (n_idx >= 4096 && idx.ext[dim] > 4 && idx.ext[dim] < (int64_t(1) << 31)) {
+        void* scratch = nullptr;
+        MIMK_TRY(get_scratch(size_t(n_src) * sizeof(int), &scratch));
+        int* winner = static_cast<int*>(scratch);
+        MIMK_CUDA_TRY(cudaMemsetAsync(winner, 0xff, size_t(n_src) * sizeof(int), s));  // -1: no update names this cell
+        const unsigned g = grid_for(dev, n_idx);
+        scatter_propose_kernel<I><<<g, 256, 0, s>>>(index, winner, n_idx, src, idx, ups, dim, dev->status_dev);
+        MIMK_TRY(launch_status());
+        scatter_commit_kernel<T, I><<<g, 256, 0, s>>>(index, upd, winner, out, n_idx, src, idx, ups, dim, dev->status_dev);
+        return launch_status();
+    }
     const unsigned g = grid_for(dev, lines, 128);
-    if (index_dtype == MIMK_I32)
-        scatter_kernel<T, int><<<g, 128, 0, s>>>(static_cast<const int*>(index), static_cast<const T*>(upd), static_cast<T*>(out), lines,
-                                                  src, idx, ups, dim, dev->status_dev);
-    else
-        scatter_kernel<T, long long><<<g, 128, 0, s>>>(static_cast<const long long*>(index), static_cast<const T*>(upd),
-                                                        static_cast<T*>(out), lines, src, idx, ups, dim, dev->status_dev);
+    scatter_kernel<T, I><<<g, 128, 0, s>>>(index, upd, out, lines, src, idx, ups, dim, dev->status_dev);
     return launch_status();
+}
+
+template <class T>
+int scatter_typed(const void* index, const void* upd, void* out, int index_dtype, long long n_idx, long long n_src, const Shape& src,
+                  const Shape& idx, const Shape& ups, int dim, DeviceInfo* dev, cudaStream_t s) {
+    if (index_dtype == MIMK_I32)
+        return scatter_any(static_cast<const int*>(index), static_cast<const T*>(upd), static_cast<T*>(out), n_idx, n_src, src, idx, ups,
+                           dim, dev, s);
+    return scatter_any(static_cast<const long long*>(index), static_cast<const T*>(upd), static_cast<T*>(out), n_idx, n_src, src, idx,
+                       ups, dim, dev, s);
 }
 
 bool value_dtype_ok(int dt) { return dt == MIMK_F32 || dt == MIMK_BF16 || dt == MIMK_I32 || dt == MIMK_I64; }
@@ -235,11 +295,10 @@ extern "C" int mimk_scatter(const void* input, const void* index, const void* up
         MIMK_CUDA_TRY(cudaMemcpyAsync(out, input, size_t(n_src) * dtype_size(dtype), cudaMemcpyDeviceToDevice, s));
     if (n_idx == 0) return MIMK_OK;
     if (!index || !updates) return MIMK_E_ARG;
-    const long long lines = n_idx / idx.ext[dim];
     switch (dtype_size(dtype)) {
-        case 2: return scatter_typed<uint16_t>(index, updates, out, index_dtype, lines, src, idx, ups, dim, dev, s);
-        case 4: return scatter_typed<uint32_t>(index, updates, out, index_dtype, lines, src, idx, ups, dim, dev, s);
-        default: return scatter_typed<uint64_t>(index, updates, out, index_dtype, lines, src, idx, ups, dim, dev, s);
+        case 2: return scatter_typed<uint16_t>(index, updates, out, index_dtype, n_idx, n_src, src, idx, ups, dim, dev, s);
+        case 4: return scatter_typed<uint32_t>(index, updates, out, index_dtype, n_idx, n_src, src, idx, ups, dim, dev, s);
+        default: return scatter_typed<uint64_t>(index, updates, out, index_dtype, n_idx, n_src, src, idx, ups, dim, dev, s);
     }
 }
 

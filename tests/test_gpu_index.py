@@ -129,3 +129,20 @@ def test_select_and_grouped_convolution(T):
 def test_broadcast_expands_unit_axes(T):
     x = np.arange(12, dtype=np.float32).reshape(3, 1, 4)
     assert np.array_equal(T.broadcast(cu(x), (3, 5, 4)).cpu().numpy(), np.broadcast_to(x, (3, 5, 4)))
+
+
+@pytest.mark.parametrize("dim", [0, 1, 2])
+def test_scatter_with_one_thread_per_update_keeps_the_last_visit(T, dim):
+    """Index tensors large enough for the one-thread-per-update form (a winner per destination): a narrow source axis
+    makes almost every destination a duplicate; the loops' row-major rule decides, bit for bit."""
+    rng = np.random.default_rng(23 + dim)
+    s_src = [30, 40, 50]
+    s_src[dim] = 6                                               # few destinations per line: heavy duplication
+    s_idx = [30, 40, 50]
+    s_idx[dim] = 45
+    x = rng.integers(-1000, 1000, s_src).astype(np.int32)
+    index = rng.integers(0, 6, s_idx).astype(np.int64)
+    upd = rng.integers(-1000, 1000, s_idx).astype(np.int32)
+    got = T.scatter(dim, cu(x), cu(index), cu(upd))
+    T.device_status()
+    assert np.array_equal(got.cpu().numpy(), mo.scatter(dim, x, index, upd))
