@@ -135,15 +135,23 @@ int mimk_gemm_flat(int64_t m, int64_t n, int64_t k, const void* a, const void* b
 int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner, int monoid,
                 void* stream);
 
-/* mimk_reduce for callers that must not have the library allocate: same arguments, same results, but no
+/* How many f32 partial results mimk_reduce / mimk_reduce_static keep for this problem on a device with `sm_count` SMs:
+ * 0 when the reduced axis is not split (row reductions, or enough columns to fill the machine), else slices * outer *
+ * inner. Pure host logic (needs no device): lets a caller of mimk_reduce_static see beforehand whether a plan fits
+ * MIMK_REDUCE_STATIC_BYTES. No counterpart in the reference. */
+int mimk_reduce_plan(int64_t outer, int64_t len, int64_t inner, int sm_count, int64_t* partial_floats);
+
+/* mimk_reduce for callers that must not have the library allocate: the same arguments and, for F32 operands, the same
+ * results bit for bit (one plan, the same kernels) -- F32 ONLY, a BF16 request returns MIMK_E_DTYPE -- but no
  * cudaMalloc / cudaFree / cudaHostAlloc is ever issued, on any call. (No counterpart in the reference, whose
  * generated wrappers allocate per operation.) Two kinds of caller need this: an embedder that plans all device
  * memory itself -- a fixed memory budget, or an allocator of its own that a hidden cudaMalloc would bypass -- and
  * a latency-critical loop that cannot take the device-wide synchronisation an allocation may imply.
  * Where mimk_reduce keeps the partial results of a split reduction in a cached allocation, this entry point keeps
  * them in a fixed 1 MiB array inside the library image (MIMK_REDUCE_STATIC_BYTES; every GPU that loads the library
- * holds it until the process exits). A call whose plan needs more partials than fit returns MIMK_E_WORKSPACE and
- * launches nothing; on a 148-SM B200 no plan exceeds about 0.9 MiB.
+ * holds it until the process exits). A call whose plan needs more partials than fit (mimk_reduce_plan tells) returns
+ * MIMK_E_WORKSPACE and launches nothing; the plan grows with the SM count, and with the 148 SMs of a B200 no plan
+ * exceeds 227 072 floats (0.87 MiB), so there the refusal cannot occur.
  * The first call on each device resolves the array's device address (with that device current) and reads two
  * device attributes; make that first call before any stream capture begins. All calls on a device share the one
  * array, so two calls whose kernels may overlap on the GPU (different streams, no dependency between them) race

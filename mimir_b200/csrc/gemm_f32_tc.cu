@@ -50,6 +50,9 @@ struct Params {
     const void* post_full;
     int post;
     int* status;
+    const float* A0;  // the operands as the caller gave them, for the scalar fold of non-finite cells
+    const float* B0;
+    int b_nk;
 };
 
 __device__ __forceinline__ float to_tf32(float x) {
@@ -58,13 +61,19 @@ __device__ __forceinline__ float to_tf32(float x) {
     return __uint_as_float(y);
 }
 
+// The tail of the split. A head that is not finite (v is inf or NaN, or a finite v that rounds up past the largest TF32
+// value) has no tail: inf - inf would put a NaN where the scalar fold has an inf. Cells whose products involve such an
+// operand come out of the tensor cores non-finite either way (inf * 0 from a zero tail is NaN); the epilogue recomputes
+// exactly those cells with the scalar fold.
+__device__ __forceinline__ float tail_of(float v, float h) { return isfinite(h) ? to_tf32(v - h) : 0.f; }
+
 // hi / lo split of a row-major [rows, cols] matrix, same layout out.
 __global__ void split_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int64_t n) {
     for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
         const float v = x[i];
         const float h = to_tf32(v);
         hi[i]         = h;
-        lo[i]         = to_tf32(v - h);
+        lo[i]         = tail_of(v, h);
     }
 }
 // The same with the copies' rows padded to `kp` >= cols elements (zeros in the pad): a K that is not a multiple of 4 gets
@@ -77,7 +86,7 @@ __global__ void split_pad_kernel(const float* __restrict__ x, float* __restrict_
         const float v = c < cols ? x[r * cols + c] : 0.f;
         const float h = to_tf32(v);
         hi[i]         = h;
-        lo[i]         = to_tf32(v - h);
+        lo[i]         = tail_of(v, h);
     }
 }
 // The same for B stored [K, N]: written transposed as [N, K] (K contiguous) through a 32 x 32 shared-memory tile.
@@ -96,7 +105,7 @@ __global__ void split_transpose_kernel(const float* __restrict__ x, float* __res
             const float v  = tile[threadIdx.x][r];
             const float h  = to_tf32(v);
             hi[n * kp + k] = h;
-            lo[n * kp + k] = to_tf32(v - h);
+            lo[n * kp + k] = tail_of(v, h);
         }
     }
 }
@@ -266,6 +275,41 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_consta
             }
             if (!ok) break;
             if (row < p.M) {
+                // columns of this row whose tensor-core result is not finite: recomputed below
+                uint32_t bad[BN / 32];
+#pragma unroll
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t m = 0;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) m |= isfinite(sum[c + i]) ? 0u : (1u << i);
+                    bad[c / 32] = m;
+                }
+                // A non-finite cell means an operand of its fold was inf / NaN (or a head overflowed, or the sum did): the
+                // split products are then not the f32 products (inf * 0 from a zero tail is NaN). Such cells take the
+                // scalar fold of the CUDA-core kernel -- ascending k, one fma per step -- from the caller's operands.
+#pragma unroll 1
+                for (int w = 0; w < BN / 32; ++w) {
+                    uint32_t m = w == 0 ? bad[0] : w == 1 ? bad[1] : w == 2 ? bad[2] : bad[3];
+                    while (m) {
+                        const int i = __ffs(m) - 1;
+                        m &= m - 1;
+                        const int64_t col = n0 + w * 32 + i;
+                        if (col >= p.N) continue;
+                        const float* a = p.A0 + row * p.K;
+                        float acc      = 0.f;
+                        if (p.b_nk) {
+                            const float* b = p.B0 + col * p.K;
+                            for (int64_t k = 0; k < p.K; ++k) acc = fmaf(a[k], b[k], acc);
+                        } else {
+                            const float* b = p.B0 + col;
+                            for (int64_t k = 0; k < p.K; ++k) acc = fmaf(a[k], b[k * p.N], acc);
+                        }
+                        const int idx = w * 32 + i;
+#pragma unroll
+                        for (int j = 0; j < BN; ++j)
+                            if (j == idx) sum[j] = acc;
+                    }
+                }
 #pragma unroll
                 for (int c = 0; c < BN; c += 32) {
                     float* v           = sum + c;
@@ -421,6 +465,7 @@ int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s) {
         p.post_full = d.post_full ? static_cast<const uint8_t*>(d.post_full) + size_t(b * d.stride_c) * out_size : nullptr;
         p.post      = d.post;
         p.status    = dev->status_dev;
+        p.A0 = A, p.B0 = B, p.b_nk = d.b_layout == MIMK_B_NK;
         MIMK_TRY(d.out_dtype == MIMK_BF16 ? launch<__nv_bfloat16>(tAh, tAl, tBh, tBl, p, dev->sm_count, s)
                                           : launch<float>(tAh, tAl, tBh, tBl, p, dev->sm_count, s));
     }

@@ -3,9 +3,12 @@
 // They stand in for the wrapper the reference emits around every GPU-lowered operation (MimIR
 // src/mim/plug/gpu/phase/lower_map_reduce.cpp:317-395: gpu.buf_alloc_copy per input, gpu.alloc.block for the
 // output, gpu.launch, gpu.buf_copy_to_host, gpu.free -- all blocking on the null stream). Here the device buffers
-// come from a cached arena, copies are asynchronous, and row-wise operators are streamed through the device in
-// row blocks on two streams so that the upload of block i+1, the kernel on block i and the download of block i-1
-// overlap.
+// come from a cached arena, copies are asynchronous, and every operator is cut into pieces that travel through three
+// streams -- `up` (host to device copies), `work` (kernels) and `down` (device to host copies), ordered by events -- so
+// that the upload of piece i+1, the kernel on piece i and the download of piece i-1 overlap: row blocks for the
+// row-wise operators, row panels of A and C for a contraction (B resident), groups of heads for attention, row panels
+// of the result for the gated MLP. A call that fails part-way drains all three streams before it returns, so no copy
+// to or from the caller's buffers is left in flight.
 #include <mutex>
 
 #include "common.cuh"
@@ -17,7 +20,7 @@ struct HostCtx {
     bool ready = false;
     void* arena = nullptr;
     size_t arena_bytes = 0;
-    cudaStream_t up = nullptr, down = nullptr;
+    cudaStream_t up = nullptr, work = nullptr, down = nullptr;
     static constexpr int MAX_EVENTS = 64;
     cudaEvent_t uploaded[MAX_EVENTS], computed[MAX_EVENTS], drained[MAX_EVENTS];
 };
@@ -31,6 +34,7 @@ int get_ctx(HostCtx** out) {
     HostCtx& c = g_ctx[dev->device];
     if (!c.ready) {
         MIMK_CUDA_TRY(cudaStreamCreateWithFlags(&c.up, cudaStreamNonBlocking));
+        MIMK_CUDA_TRY(cudaStreamCreateWithFlags(&c.work, cudaStreamNonBlocking));
         MIMK_CUDA_TRY(cudaStreamCreateWithFlags(&c.down, cudaStreamNonBlocking));
         for (int i = 0; i < HostCtx::MAX_EVENTS; ++i) {
             MIMK_CUDA_TRY(cudaEventCreateWithFlags(&c.uploaded[i], cudaEventDisableTiming));
@@ -60,6 +64,27 @@ int arena(HostCtx& c, size_t bytes, uint8_t** out) {
 
 inline size_t round256(size_t b) { return (b + 255) & ~size_t(255); }
 
+// Ends a host call: waits for everything queued on the three streams (also after a failure in the middle, so that no
+// asynchronous copy still touches the caller's buffers) and folds in the device status word.
+int finish(HostCtx& c, int st) {
+    const cudaError_t e0 = cudaStreamSynchronize(c.up), e1 = cudaStreamSynchronize(c.work), e2 = cudaStreamSynchronize(c.down);
+    if (st != MIMK_OK) {
+        mimk_device_status(c.work);  // clear the word; the first failure is what the caller hears
+        return st;
+    }
+    if (e0 != cudaSuccess) return note_cuda_error(e0);
+    if (e1 != cudaSuccess) return note_cuda_error(e1);
+    if (e2 != cudaSuccess) return note_cuda_error(e2);
+    return mimk_device_status(c.work);
+}
+
+// The event ring: piece b uses slot b % MAX_EVENTS of each event array. Before a slot is recorded again, the host waits
+// for the download that last used it, so an event is never re-recorded while a stream still waits on it.
+int ring_guard(HostCtx& c, int64_t b) {
+    if (b >= HostCtx::MAX_EVENTS) MIMK_CUDA_TRY(cudaEventSynchronize(c.drained[int(b % HostCtx::MAX_EVENTS)]));
+    return MIMK_OK;
+}
+
 }  // namespace
 }  // namespace mimk
 
@@ -88,18 +113,9 @@ extern "C" int mimk_host_release(void) {
 }
 
 namespace {
-// kind 0..2: one result `y`; kind 3: softmax into `y` and RMSNorm into `y2` from ONE upload of x.
-int host_rows_impl(int kind, const void* x, const void* gamma, void* y, void* y2, int in_dtype, int out_dtype,
+int host_rows_body(HostCtx* c, int kind, const void* x, const void* gamma, void* y, void* y2, int in_dtype, int out_dtype,
                    int64_t rows, int64_t cols, float eps) {
     const bool both = kind == 3;
-    if ((!both && (kind < MIMK_ROWS_SOFTMAX || kind > MIMK_ROWS_SOFTMAX_RMSNORM)) || rows < 0 || cols < 0) return MIMK_E_ARG;
-    if ((in_dtype != MIMK_F32 && in_dtype != MIMK_BF16) || (out_dtype != MIMK_F32 && out_dtype != MIMK_BF16))
-        return MIMK_E_DTYPE;
-    std::lock_guard<std::mutex> lock(g_host_mutex);
-    HostCtx* c = nullptr;
-    MIMK_TRY(get_ctx(&c));
-    if (rows * cols == 0) return MIMK_OK;
-    if (!x || !y || (both && !y2) || (kind != MIMK_ROWS_SOFTMAX && !gamma)) return MIMK_E_ARG;
     const size_t in_row = size_t(cols) * dtype_size(in_dtype), out_row = size_t(cols) * dtype_size(out_dtype);
     // Row blocks of about 32 MiB of input: small enough to overlap, large enough to fill the machine.
     int64_t block_rows = int64_t((size_t(32) << 20) / in_row);
@@ -123,16 +139,23 @@ int host_rows_impl(int kind, const void* x, const void* gamma, void* y, void* y2
         const int64_t nr = rows - r0 < block_rows ? rows - r0 : block_rows;
         uint8_t* d_in    = base + g_bytes + size_t(slot) * in_slot;
         uint8_t* d_out   = base + g_bytes + size_t(slots) * in_slot + size_t(slot) * out_slot;
-        // the slot is free again once the download that last used it has drained
-        if (b >= slots) MIMK_CUDA_TRY(cudaStreamWaitEvent(c->up, c->drained[int((b - slots) % HostCtx::MAX_EVENTS)], 0));
+        MIMK_TRY(ring_guard(*c, b));
+        // the input slot is free once the kernels that last read it are done, the output slot once its download drained
+        if (b >= slots) {
+            const int prev = int((b - slots) % HostCtx::MAX_EVENTS);
+            MIMK_CUDA_TRY(cudaStreamWaitEvent(c->up, c->computed[prev], 0));
+            MIMK_CUDA_TRY(cudaStreamWaitEvent(c->work, c->drained[prev], 0));
+        }
         MIMK_CUDA_TRY(cudaMemcpyAsync(d_in, static_cast<const uint8_t*>(x) + size_t(r0) * in_row, size_t(nr) * in_row,
                                       cudaMemcpyHostToDevice, c->up));
-        if (kind == MIMK_ROWS_SOFTMAX || both) MIMK_TRY(mimk_softmax(d_in, d_out, in_dtype, out_dtype, nr, cols, 1, c->up));
-        if (kind == MIMK_ROWS_RMSNORM) MIMK_TRY(mimk_rmsnorm(d_in, d_gamma, d_out, in_dtype, out_dtype, nr, cols, eps, c->up));
-        if (both) MIMK_TRY(mimk_rmsnorm(d_in, d_gamma, d_out + out_one, in_dtype, out_dtype, nr, cols, eps, c->up));
+        MIMK_CUDA_TRY(cudaEventRecord(c->uploaded[ev], c->up));
+        MIMK_CUDA_TRY(cudaStreamWaitEvent(c->work, c->uploaded[ev], 0));
+        if (kind == MIMK_ROWS_SOFTMAX || both) MIMK_TRY(mimk_softmax(d_in, d_out, in_dtype, out_dtype, nr, cols, 1, c->work));
+        if (kind == MIMK_ROWS_RMSNORM) MIMK_TRY(mimk_rmsnorm(d_in, d_gamma, d_out, in_dtype, out_dtype, nr, cols, eps, c->work));
+        if (both) MIMK_TRY(mimk_rmsnorm(d_in, d_gamma, d_out + out_one, in_dtype, out_dtype, nr, cols, eps, c->work));
         if (kind == MIMK_ROWS_SOFTMAX_RMSNORM)
-            MIMK_TRY(mimk_softmax_rmsnorm(d_in, d_gamma, d_out, in_dtype, out_dtype, nr, cols, eps, c->up));
-        MIMK_CUDA_TRY(cudaEventRecord(c->computed[ev], c->up));
+            MIMK_TRY(mimk_softmax_rmsnorm(d_in, d_gamma, d_out, in_dtype, out_dtype, nr, cols, eps, c->work));
+        MIMK_CUDA_TRY(cudaEventRecord(c->computed[ev], c->work));
         MIMK_CUDA_TRY(cudaStreamWaitEvent(c->down, c->computed[ev], 0));
         MIMK_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(y) + size_t(r0) * out_row, d_out, size_t(nr) * out_row,
                                       cudaMemcpyDeviceToHost, c->down));
@@ -140,12 +163,23 @@ int host_rows_impl(int kind, const void* x, const void* gamma, void* y, void* y2
             MIMK_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(y2) + size_t(r0) * out_row, d_out + out_one, size_t(nr) * out_row,
                                           cudaMemcpyDeviceToHost, c->down));
         MIMK_CUDA_TRY(cudaEventRecord(c->drained[ev], c->down));
-        // keep at most MAX_EVENTS blocks in flight so that an event is never re-recorded while still awaited
-        if (b + 1 >= HostCtx::MAX_EVENTS) MIMK_CUDA_TRY(cudaEventSynchronize(c->drained[int((b + 1) % HostCtx::MAX_EVENTS)]));
     }
-    MIMK_CUDA_TRY(cudaStreamSynchronize(c->down));
-    MIMK_CUDA_TRY(cudaStreamSynchronize(c->up));
     return MIMK_OK;
+}
+
+// kind 0..2: one result `y`; kind 3: softmax into `y` and RMSNorm into `y2` from ONE upload of x.
+int host_rows_impl(int kind, const void* x, const void* gamma, void* y, void* y2, int in_dtype, int out_dtype,
+                   int64_t rows, int64_t cols, float eps) {
+    const bool both = kind == 3;
+    if ((!both && (kind < MIMK_ROWS_SOFTMAX || kind > MIMK_ROWS_SOFTMAX_RMSNORM)) || rows < 0 || cols < 0) return MIMK_E_ARG;
+    if ((in_dtype != MIMK_F32 && in_dtype != MIMK_BF16) || (out_dtype != MIMK_F32 && out_dtype != MIMK_BF16))
+        return MIMK_E_DTYPE;
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    HostCtx* c = nullptr;
+    MIMK_TRY(get_ctx(&c));
+    if (rows * cols == 0) return MIMK_OK;
+    if (!x || !y || (both && !y2) || (kind != MIMK_ROWS_SOFTMAX && !gamma)) return MIMK_E_ARG;
+    return finish(*c, host_rows_body(c, kind, x, gamma, y, y2, in_dtype, out_dtype, rows, cols, eps));
 }
 }  // namespace
 
@@ -160,16 +194,11 @@ extern "C" int mimk_host_rows_pair(const void* x, const void* gamma, void* y_sof
     return host_rows_impl(3, x, gamma, y_softmax, y_rmsnorm, in_dtype, out_dtype, rows, cols, eps);
 }
 
-extern "C" int mimk_host_gemm(const mimk_gemm_desc* h) {
-    if (!h) return MIMK_E_ARG;
-    if (h->batch < 0 || h->m < 0 || h->n < 0 || h->k < 0) return MIMK_E_ARG;
-    if ((h->in_dtype != MIMK_F32 && h->in_dtype != MIMK_BF16) || (h->out_dtype != MIMK_F32 && h->out_dtype != MIMK_BF16))
-        return MIMK_E_DTYPE;
-    std::lock_guard<std::mutex> lock(g_host_mutex);
-    HostCtx* c = nullptr;
-    MIMK_TRY(get_ctx(&c));
-    if (h->batch == 0 || h->m == 0 || h->n == 0) return MIMK_OK;
-    if (!h->c || (h->k > 0 && (!h->a || !h->b))) return MIMK_E_ARG;
+namespace {
+// C = post(A B) with host operands. One batch entry whose A has at least two panels of rows is pipelined: B (and the
+// bias row) first, then per panel of rows the upload of the A panel (and of the full-shape epilogue operand's panel),
+// the contraction of that panel on `work`, and the download of its rows of C. Everything else goes up, runs, comes down.
+int host_gemm_body(HostCtx* c, const mimk_gemm_desc* h) {
     const size_t es = dtype_size(h->in_dtype), os = dtype_size(h->out_dtype);
     // batch strides: a dense batch is uploaded as one block; stride 0 (shared operand) as a single matrix
     const size_t a_elems = size_t(h->m) * h->k * (h->stride_a ? h->batch : 1);
@@ -184,19 +213,115 @@ extern "C" int mimk_host_gemm(const mimk_gemm_desc* h) {
     MIMK_TRY(arena(*c, a_b + b_b + c_b + row_b + full_b, &base));
     mimk_gemm_desc d = *h;
     d.a = base, d.b = base + a_b, d.c = base + a_b + b_b;
-    if (a_elems) MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.a), h->a, a_elems * es, cudaMemcpyHostToDevice, c->up));
+    if (h->post_row) d.post_row = base + a_b + b_b + c_b;
+    if (h->post_full) d.post_full = base + a_b + b_b + c_b + row_b;
+    uint8_t *d_a = base, *d_c = base + a_b + b_b, *d_full = base + a_b + b_b + c_b + row_b;
+
+    // panels of about 16 MiB of A (or of C, whichever row is longer), whole 256-row tiles
+    int64_t panel = h->m;
+    if (h->batch == 1 && h->k > 0 && h->in_dtype == MIMK_BF16) {  // f32 operands are re-split per call: one call
+        const size_t row_bytes = size_t(h->k) * es > size_t(h->n) * os ? size_t(h->k) * es : size_t(h->n) * os;
+        int64_t rows           = int64_t((size_t(16) << 20) / row_bytes) & ~int64_t(255);
+        if (rows >= 256 && rows * 2 <= h->m) panel = rows;
+    }
     if (b_elems) MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.b), h->b, b_elems * es, cudaMemcpyHostToDevice, c->up));
-    if (h->post_row) {
-        d.post_row = base + a_b + b_b + c_b;
+    if (h->post_row)
         MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.post_row), h->post_row, size_t(h->n) * 4, cudaMemcpyHostToDevice, c->up));
+    if (panel == h->m) {
+        if (a_elems) MIMK_CUDA_TRY(cudaMemcpyAsync(d_a, h->a, a_elems * es, cudaMemcpyHostToDevice, c->up));
+        if (h->post_full) MIMK_CUDA_TRY(cudaMemcpyAsync(d_full, h->post_full, c_elems * os, cudaMemcpyHostToDevice, c->up));
+        MIMK_CUDA_TRY(cudaEventRecord(c->uploaded[0], c->up));
+        MIMK_CUDA_TRY(cudaStreamWaitEvent(c->work, c->uploaded[0], 0));
+        MIMK_TRY(mimk_gemm(&d, c->work));
+        MIMK_CUDA_TRY(cudaEventRecord(c->computed[0], c->work));
+        MIMK_CUDA_TRY(cudaStreamWaitEvent(c->down, c->computed[0], 0));
+        MIMK_CUDA_TRY(cudaMemcpyAsync(h->c, d.c, c_elems * os, cudaMemcpyDeviceToHost, c->down));
+        return MIMK_OK;
     }
-    if (h->post_full) {
-        d.post_full = base + a_b + b_b + c_b + row_b;
-        MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.post_full), h->post_full, c_elems * os, cudaMemcpyHostToDevice, c->up));
+    const int64_t npanels = (h->m + panel - 1) / panel;
+    for (int64_t b = 0; b < npanels; ++b) {
+        const int ev     = int(b % HostCtx::MAX_EVENTS);
+        const int64_t r0 = b * panel, nr = h->m - r0 < panel ? h->m - r0 : panel;
+        MIMK_TRY(ring_guard(*c, b));
+        MIMK_CUDA_TRY(cudaMemcpyAsync(d_a + size_t(r0) * h->k * es, static_cast<const uint8_t*>(h->a) + size_t(r0) * h->k * es,
+                                      size_t(nr) * h->k * es, cudaMemcpyHostToDevice, c->up));
+        if (h->post_full)
+            MIMK_CUDA_TRY(cudaMemcpyAsync(d_full + size_t(r0) * h->n * os, static_cast<const uint8_t*>(h->post_full) + size_t(r0) * h->n * os,
+                                          size_t(nr) * h->n * os, cudaMemcpyHostToDevice, c->up));
+        MIMK_CUDA_TRY(cudaEventRecord(c->uploaded[ev], c->up));
+        MIMK_CUDA_TRY(cudaStreamWaitEvent(c->work, c->uploaded[ev], 0));
+        mimk_gemm_desc dp = d;
+        dp.m = nr;
+        dp.a = d_a + size_t(r0) * h->k * es;
+        dp.c = d_c + size_t(r0) * h->n * os;
+        if (h->post_full) dp.post_full = d_full + size_t(r0) * h->n * os;
+        MIMK_TRY(mimk_gemm(&dp, c->work));
+        MIMK_CUDA_TRY(cudaEventRecord(c->computed[ev], c->work));
+        MIMK_CUDA_TRY(cudaStreamWaitEvent(c->down, c->computed[ev], 0));
+        MIMK_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(h->c) + size_t(r0) * h->n * os, dp.c, size_t(nr) * h->n * os,
+                                      cudaMemcpyDeviceToHost, c->down));
+        MIMK_CUDA_TRY(cudaEventRecord(c->drained[ev], c->down));
     }
-    MIMK_TRY(mimk_gemm(&d, c->up));
-    MIMK_CUDA_TRY(cudaMemcpyAsync(h->c, d.c, c_elems * os, cudaMemcpyDeviceToHost, c->up));
-    return mimk_device_status(c->up);
+    return MIMK_OK;
+}
+
+// Attention with host operands, in groups of heads: the upload of group g+1's q, k, v overlaps the kernel on group g and
+// the download of group g-1's rows of o. A group holds about 32 MiB of q + k + v (at least 8 heads when there are that
+// many), so that a launch still fills the machine.
+int host_attn_body(HostCtx* c, const mimk_attn_desc* h) {
+    const size_t es   = dtype_size(h->dtype);
+    const size_t q_h  = size_t(h->seq_q) * h->head_dim * es, k_h = size_t(h->seq_k) * h->head_dim * es;
+    const size_t q_b  = size_t(h->batch_heads) * q_h, k_b = size_t(h->batch_heads) * k_h;
+    const size_t l_b  = h->lse ? size_t(h->batch_heads) * h->seq_q * 4 : 0;
+    uint8_t* base     = nullptr;
+    MIMK_TRY(arena(*c, 2 * round256(q_b) + 2 * round256(k_b) + round256(l_b), &base));
+    uint8_t* p   = base;
+    uint8_t* d_q = p; p += round256(q_b);
+    uint8_t* d_k = p; p += round256(k_b);
+    uint8_t* d_v = p; p += round256(k_b);
+    uint8_t* d_o = p; p += round256(q_b);
+    float* d_l   = h->lse ? reinterpret_cast<float*>(p) : nullptr;
+    int64_t group = int64_t((size_t(32) << 20) / (q_h + 2 * k_h + 1));
+    if (group < 8) group = 8;
+    if (group * 2 > h->batch_heads) group = h->batch_heads;
+    const int64_t ngroups = (h->batch_heads + group - 1) / group;
+    for (int64_t b = 0; b < ngroups; ++b) {
+        const int ev     = int(b % HostCtx::MAX_EVENTS);
+        const int64_t h0 = b * group, nh = h->batch_heads - h0 < group ? h->batch_heads - h0 : group;
+        MIMK_TRY(ring_guard(*c, b));
+        MIMK_CUDA_TRY(cudaMemcpyAsync(d_q + h0 * q_h, static_cast<const uint8_t*>(h->q) + h0 * q_h, nh * q_h, cudaMemcpyHostToDevice, c->up));
+        if (k_h) {
+            MIMK_CUDA_TRY(cudaMemcpyAsync(d_k + h0 * k_h, static_cast<const uint8_t*>(h->k) + h0 * k_h, nh * k_h, cudaMemcpyHostToDevice, c->up));
+            MIMK_CUDA_TRY(cudaMemcpyAsync(d_v + h0 * k_h, static_cast<const uint8_t*>(h->v) + h0 * k_h, nh * k_h, cudaMemcpyHostToDevice, c->up));
+        }
+        MIMK_CUDA_TRY(cudaEventRecord(c->uploaded[ev], c->up));
+        MIMK_CUDA_TRY(cudaStreamWaitEvent(c->work, c->uploaded[ev], 0));
+        mimk_attn_desc d = *h;
+        d.batch_heads    = nh;
+        d.q = d_q + h0 * q_h, d.k = d_k + h0 * k_h, d.v = d_v + h0 * k_h, d.o = d_o + h0 * q_h;
+        d.lse = h->lse ? d_l + h0 * h->seq_q : nullptr;
+        MIMK_TRY(mimk_attn_fwd(&d, c->work));
+        MIMK_CUDA_TRY(cudaEventRecord(c->computed[ev], c->work));
+        MIMK_CUDA_TRY(cudaStreamWaitEvent(c->down, c->computed[ev], 0));
+        MIMK_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(h->o) + h0 * q_h, d.o, nh * q_h, cudaMemcpyDeviceToHost, c->down));
+        if (h->lse) MIMK_CUDA_TRY(cudaMemcpyAsync(h->lse + h0 * h->seq_q, d.lse, size_t(nh) * h->seq_q * 4, cudaMemcpyDeviceToHost, c->down));
+        MIMK_CUDA_TRY(cudaEventRecord(c->drained[ev], c->down));
+    }
+    return MIMK_OK;
+}
+}  // namespace
+
+extern "C" int mimk_host_gemm(const mimk_gemm_desc* h) {
+    if (!h) return MIMK_E_ARG;
+    if (h->batch < 0 || h->m < 0 || h->n < 0 || h->k < 0) return MIMK_E_ARG;
+    if ((h->in_dtype != MIMK_F32 && h->in_dtype != MIMK_BF16) || (h->out_dtype != MIMK_F32 && h->out_dtype != MIMK_BF16))
+        return MIMK_E_DTYPE;
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    HostCtx* c = nullptr;
+    MIMK_TRY(get_ctx(&c));
+    if (h->batch == 0 || h->m == 0 || h->n == 0) return MIMK_OK;
+    if (!h->c || (h->k > 0 && (!h->a || !h->b))) return MIMK_E_ARG;
+    return finish(*c, host_gemm_body(c, h));
 }
 
 extern "C" int mimk_host_attn_fwd(const mimk_attn_desc* h) {
@@ -208,28 +333,7 @@ extern "C" int mimk_host_attn_fwd(const mimk_attn_desc* h) {
     MIMK_TRY(get_ctx(&c));
     if (h->batch_heads == 0 || h->seq_q == 0 || h->head_dim == 0) return MIMK_OK;
     if (!h->q || !h->o || (h->seq_k > 0 && (!h->k || !h->v))) return MIMK_E_ARG;
-    const size_t es  = dtype_size(h->dtype);
-    const size_t q_b = size_t(h->batch_heads) * h->seq_q * h->head_dim * es;
-    const size_t k_b = size_t(h->batch_heads) * h->seq_k * h->head_dim * es;
-    const size_t l_b = h->lse ? size_t(h->batch_heads) * h->seq_q * 4 : 0;
-    uint8_t* base    = nullptr;
-    MIMK_TRY(arena(*c, 2 * round256(q_b) + 2 * round256(k_b) + round256(l_b), &base));
-    mimk_attn_desc d = *h;
-    uint8_t* p       = base;
-    d.q = p, p += round256(q_b);
-    d.k = p, p += round256(k_b);
-    d.v = p, p += round256(k_b);
-    d.o = p, p += round256(q_b);
-    d.lse = h->lse ? reinterpret_cast<float*>(p) : nullptr;
-    MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.q), h->q, q_b, cudaMemcpyHostToDevice, c->up));
-    if (k_b) {
-        MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.k), h->k, k_b, cudaMemcpyHostToDevice, c->up));
-        MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.v), h->v, k_b, cudaMemcpyHostToDevice, c->up));
-    }
-    MIMK_TRY(mimk_attn_fwd(&d, c->up));
-    MIMK_CUDA_TRY(cudaMemcpyAsync(h->o, d.o, q_b, cudaMemcpyDeviceToHost, c->up));
-    if (h->lse) MIMK_CUDA_TRY(cudaMemcpyAsync(h->lse, d.lse, l_b, cudaMemcpyDeviceToHost, c->up));
-    return mimk_device_status(c->up);
+    return finish(*c, host_attn_body(c, h));
 }
 
 // The generic operation with host operands: what the reference's wrapper does around every map_reduce_post --
@@ -273,6 +377,7 @@ extern "C" int mimk_host_map_reduce_post(const mimk_mrp_desc* h) {
     HostCtx* c = nullptr;
     MIMK_TRY(get_ctx(&c));
     if (out_bytes == 0) return MIMK_OK;
+    auto body = [&]() -> int {
     uint8_t* base = nullptr;
     MIMK_TRY(arena(*c, total, &base));
     mimk_mrp_desc d = *h;
@@ -290,38 +395,76 @@ extern "C" int mimk_host_map_reduce_post(const mimk_mrp_desc* h) {
     d.out = p;
     // a write map need not cover the result (packed or partial outputs): cells it never stores keep the caller's bytes
     MIMK_CUDA_TRY(cudaMemcpyAsync(p, h->out, out_bytes, cudaMemcpyHostToDevice, c->up));
-    MIMK_TRY(mimk_map_reduce_post(&d, c->up));
-    MIMK_CUDA_TRY(cudaMemcpyAsync(h->out, d.out, out_bytes, cudaMemcpyDeviceToHost, c->up));
-    return mimk_device_status(c->up);
+    MIMK_CUDA_TRY(cudaEventRecord(c->uploaded[0], c->up));
+    MIMK_CUDA_TRY(cudaStreamWaitEvent(c->work, c->uploaded[0], 0));
+    MIMK_TRY(mimk_map_reduce_post(&d, c->work));
+    MIMK_CUDA_TRY(cudaMemcpyAsync(h->out, d.out, out_bytes, cudaMemcpyDeviceToHost, c->work));
+    return MIMK_OK;
+    };
+    return finish(*c, body());
 }
 
-extern "C" int mimk_host_mlp_gated(const mimk_mlp_desc* h) {
-    if (!h) return MIMK_E_ARG;
-    if (h->m < 0 || h->k < 0 || h->f < 0 || h->n < 0) return MIMK_E_ARG;
-    if (h->dtype != MIMK_BF16) return MIMK_E_DTYPE;
-    std::lock_guard<std::mutex> lock(g_host_mutex);
-    HostCtx* c = nullptr;
-    MIMK_TRY(get_ctx(&c));
-    if (h->m == 0 || h->n == 0) return MIMK_OK;
-    if (!h->x || !h->w1 || !h->w3 || !h->w2 || !h->y) return MIMK_E_ARG;
+namespace {
+// The gated MLP block with host operands. Uploads in the order the stages need them: X, W1, W3, then W2 while stage 1
+// (H = silu(X W1) * (X W3)) runs; stage 2 (Y = H W2) runs in panels of rows whose downloads overlap the next panel.
+int host_mlp_body(HostCtx* c, const mimk_mlp_desc* h) {
     const size_t x_b = round256(size_t(h->m) * h->k * 2), w1_b = round256(size_t(h->k) * h->f * 2);
     const size_t w2_b = round256(size_t(h->f) * h->n * 2), y_b = round256(size_t(h->m) * h->n * 2);
     const size_t h_b  = round256(size_t(h->m) * h->f * 2);
     uint8_t* base     = nullptr;
     MIMK_TRY(arena(*c, x_b + 2 * w1_b + w2_b + y_b + h_b, &base));
-    mimk_mlp_desc d = *h;
-    uint8_t* p      = base;
-    d.x = p, p += x_b;
-    d.w1 = p, p += w1_b;
-    d.w3 = p, p += w1_b;
-    d.w2 = p, p += w2_b;
-    d.y = p, p += y_b;
-    d.h = p;
-    MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.x), h->x, size_t(h->m) * h->k * 2, cudaMemcpyHostToDevice, c->up));
-    MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.w1), h->w1, size_t(h->k) * h->f * 2, cudaMemcpyHostToDevice, c->up));
-    MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.w3), h->w3, size_t(h->k) * h->f * 2, cudaMemcpyHostToDevice, c->up));
-    MIMK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(d.w2), h->w2, size_t(h->f) * h->n * 2, cudaMemcpyHostToDevice, c->up));
-    MIMK_TRY(mimk_mlp_gated(&d, c->up));
-    MIMK_CUDA_TRY(cudaMemcpyAsync(h->y, d.y, size_t(h->m) * h->n * 2, cudaMemcpyDeviceToHost, c->up));
-    return mimk_device_status(c->up);
+    uint8_t* p   = base;
+    uint8_t* d_x = p; p += x_b;
+    uint8_t* d_w1 = p; p += w1_b;
+    uint8_t* d_w3 = p; p += w1_b;
+    uint8_t* d_w2 = p; p += w2_b;
+    uint8_t* d_y = p; p += y_b;
+    uint8_t* d_h = p;
+    MIMK_CUDA_TRY(cudaMemcpyAsync(d_x, h->x, size_t(h->m) * h->k * 2, cudaMemcpyHostToDevice, c->up));
+    MIMK_CUDA_TRY(cudaMemcpyAsync(d_w1, h->w1, size_t(h->k) * h->f * 2, cudaMemcpyHostToDevice, c->up));
+    MIMK_CUDA_TRY(cudaMemcpyAsync(d_w3, h->w3, size_t(h->k) * h->f * 2, cudaMemcpyHostToDevice, c->up));
+    MIMK_CUDA_TRY(cudaEventRecord(c->uploaded[0], c->up));
+    MIMK_CUDA_TRY(cudaMemcpyAsync(d_w2, h->w2, size_t(h->f) * h->n * 2, cudaMemcpyHostToDevice, c->up));
+    MIMK_CUDA_TRY(cudaEventRecord(c->uploaded[1], c->up));
+    MIMK_CUDA_TRY(cudaStreamWaitEvent(c->work, c->uploaded[0], 0));
+    mimk_gemm_desc g1 = {};
+    g1.batch = 1, g1.m = h->m, g1.n = h->f, g1.k = h->k;
+    g1.a = d_x, g1.b = d_w1, g1.c = d_h;
+    g1.in_dtype = MIMK_BF16, g1.out_dtype = MIMK_BF16, g1.b_layout = h->b_layout, g1.post = MIMK_POST_ID;
+    if (!gemm_tc_supported(g1)) return MIMK_E_UNSUPPORTED;
+    MIMK_TRY(gemm_tc_any(g1, c->work, 1, d_w3));
+    MIMK_CUDA_TRY(cudaStreamWaitEvent(c->work, c->uploaded[1], 0));
+    int64_t panel = int64_t((size_t(16) << 20) / (size_t(h->n) * 2 + 1)) & ~int64_t(255);
+    if (panel < 256 || panel * 2 > h->m) panel = h->m;
+    const int64_t npanels = (h->m + panel - 1) / panel;
+    for (int64_t b = 0; b < npanels; ++b) {
+        const int ev     = int(b % HostCtx::MAX_EVENTS);
+        const int64_t r0 = b * panel, nr = h->m - r0 < panel ? h->m - r0 : panel;
+        MIMK_TRY(ring_guard(*c, b));
+        mimk_gemm_desc g2 = {};
+        g2.batch = 1, g2.m = nr, g2.n = h->n, g2.k = h->f;
+        g2.a = d_h + size_t(r0) * h->f * 2, g2.b = d_w2, g2.c = d_y + size_t(r0) * h->n * 2;
+        g2.in_dtype = MIMK_BF16, g2.out_dtype = MIMK_BF16, g2.b_layout = h->b_layout, g2.post = MIMK_POST_ID;
+        MIMK_TRY(mimk_gemm(&g2, c->work));
+        MIMK_CUDA_TRY(cudaEventRecord(c->computed[ev], c->work));
+        MIMK_CUDA_TRY(cudaStreamWaitEvent(c->down, c->computed[ev], 0));
+        MIMK_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(h->y) + size_t(r0) * h->n * 2, g2.c, size_t(nr) * h->n * 2,
+                                      cudaMemcpyDeviceToHost, c->down));
+        MIMK_CUDA_TRY(cudaEventRecord(c->drained[ev], c->down));
+    }
+    return MIMK_OK;
+}
+}  // namespace
+
+extern "C" int mimk_host_mlp_gated(const mimk_mlp_desc* h) {
+    if (!h) return MIMK_E_ARG;
+    if (h->m < 0 || h->k < 0 || h->f < 0 || h->n < 0) return MIMK_E_ARG;
+    if (h->dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    if (h->b_layout != MIMK_B_KN && h->b_layout != MIMK_B_NK) return MIMK_E_ARG;
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    HostCtx* c = nullptr;
+    MIMK_TRY(get_ctx(&c));
+    if (h->m == 0 || h->n == 0) return MIMK_OK;
+    if (!h->x || !h->w1 || !h->w3 || !h->w2 || !h->y) return MIMK_E_ARG;
+    return finish(*c, host_mlp_body(c, h));
 }

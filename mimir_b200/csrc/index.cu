@@ -220,8 +220,11 @@ template <class T, class I>
 int scatter_any(const I* index, const T* upd, T* out, long long n_idx, long long n_src, const Shape& src, const Shape& idx,
                 const Shape& ups, int dim, DeviceInfo* dev, cudaStream_t s) {
     const long long lines = n_idx / idx.ext[dim];
-    // few or long lines leave one-thread-per-line without parallelism: one thread per update and a winner per destination
-    if (n_idx >= 4096 && idx.ext[dim] > 4 && idx.ext[dim] < (int64_t(1) << 31)) {
+    // few or long lines leave one-thread-per-line without parallelism: one thread per update and a winner per destination.
+    // The winner table has one int per element of the input and is cleared on every call, so this pays only while the
+    // input is not much larger than the index tensor: a handful of updates into a huge table keeps the per-line kernel,
+    // which touches the updated cells alone.
+    if (n_idx >= 4096 && idx.ext[dim] > 4 && idx.ext[dim] < (int64_t(1) << 31) && n_src <= 8 * n_idx) {
         void* scratch = nullptr;
         MIMK_TRY(get_scratch(size_t(n_src) * sizeof(int), &scratch));
         int* winner = static_cast<int*>(scratch);

@@ -373,42 +373,68 @@ int dispatch_rows(const void* x, const float* gamma, void* y, int in_dtype, int 
     return MIMK_E_DTYPE;
 }
 
-template <class Op, class TIn, class TOut>
-int reduce_impl(const TIn* x, TOut* out, int64_t outer, int64_t len, int64_t inner, cudaStream_t s,
-                const DeviceInfo& dev) {
+// How a fold of the middle axis of [outer, len, inner] is laid over the machine: `gx` CTAs over the outer * inner
+// columns and, when those alone cannot fill it, `slices` pieces of `slice_len` along the reduced axis whose partial
+// results a second kernel combines. The one plan behind mimk_reduce and mimk_reduce_static.
+struct ReducePlan {
+    int gx, slices;
+    int64_t slice_len;
+};
+ReducePlan reduce_plan(int64_t outer, int64_t len, int64_t inner, int sm_count) {
+    ReducePlan p;
+    const int64_t total = outer * inner;
+    p.gx                = grid_for(total, 256, sm_count, 8);
+    p.slices            = 1;
+    p.slice_len         = len;
+    if (inner > 1 && int64_t(p.gx) < 2 * sm_count && len >= 256) {
+        int64_t want = (4LL * sm_count + p.gx - 1) / p.gx;
+        int64_t maxs = len / 64;
+        int slices   = int(want < maxs ? want : maxs);
+        if (slices < 1) slices = 1;
+        if (slices > 1024) slices = 1024;
+        if (slices > 1) {
+            p.slice_len = (len + slices - 1) / slices;
+            p.slices    = int((len + p.slice_len - 1) / p.slice_len);
+        }
+    }
+    return p;
+}
+
+// `partials(n, &ptr)` supplies room for n floats when the plan splits the axis: the cached allocation for mimk_reduce,
+// the array in the library image for mimk_reduce_static. Nothing there needs clearing: every partial the second kernel
+// reads is written by the first kernel of the same call.
+template <class Op, class TIn, class TOut, class Partials>
+int reduce_impl(const TIn* x, TOut* out, int64_t outer, int64_t len, int64_t inner, cudaStream_t s, int sm_count,
+                Partials partials) {
     if (inner == 1) {
         const int vec_ok = (len % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(TIn))) == 0;
-        int grid         = int(outer < int64_t(dev.sm_count) * 8 ? outer : int64_t(dev.sm_count) * 8);
+        int grid         = int(outer < int64_t(sm_count) * 8 ? outer : int64_t(sm_count) * 8);
         reduce_rows_kernel<Op><<<grid, 256, 0, s>>>(x, out, outer, len, vec_ok);
         return launch_status();
     }
     const int64_t total = outer * inner;
     const int threads   = 256;
-    int gx              = grid_for(total, threads, dev.sm_count, 8);
-    // Split the reduced axis when the columns alone cannot fill the machine.
-    int slices = 1;
-    if (int64_t(gx) < 2 * dev.sm_count && len >= 256) {
-        int64_t want = (4LL * dev.sm_count + gx - 1) / gx;
-        int64_t maxs = len / 64;
-        slices       = int(want < maxs ? want : maxs);
-        if (slices < 1) slices = 1;
-        if (slices > 1024) slices = 1024;
-    }
-    if (slices == 1) {
-        reduce_mid_kernel<Op><<<dim3(gx, 1), threads, 0, s>>>(x, out, outer, len, inner, len);
+    const ReducePlan p  = reduce_plan(outer, len, inner, sm_count);
+    if (p.slices == 1) {
+        reduce_mid_kernel<Op><<<dim3(p.gx, 1), threads, 0, s>>>(x, out, outer, len, inner, len);
         return launch_status();
     }
-    const int64_t slice_len = (len + slices - 1) / slices;
-    slices                  = int((len + slice_len - 1) / slice_len);
-    void* scratch           = nullptr;
-    MIMK_TRY(get_scratch(size_t(slices) * size_t(total) * sizeof(float), &scratch));
-    reduce_mid_kernel<Op><<<dim3(gx, slices), threads, 0, s>>>(x, static_cast<float*>(scratch), outer, len, inner,
-                                                              slice_len);
+    float* scratch = nullptr;
+    MIMK_TRY(partials(size_t(p.slices) * size_t(total), &scratch));
+    reduce_mid_kernel<Op><<<dim3(p.gx, p.slices), threads, 0, s>>>(x, scratch, outer, len, inner, p.slice_len);
     MIMK_TRY(launch_status());
-    reduce_partials_kernel<Op><<<gx, threads, 0, s>>>(static_cast<const float*>(scratch), out, total, slices);
+    reduce_partials_kernel<Op><<<p.gx, threads, 0, s>>>(static_cast<const float*>(scratch), out, total, p.slices);
     return launch_status();
 }
 
+struct CachedPartials {
+    int operator()(size_t n, float** out) const {
+        void* p = nullptr;
+        MIMK_TRY(get_scratch(n * sizeof(float), &p));
+        *out = static_cast<float*>(p);
+        return MIMK_OK;
+    }
+};
 
 // ---- reduce without any allocation ------------------------------------------------------------------
 
@@ -446,41 +472,16 @@ int static_setup(StaticSetup** out) {
     return MIMK_OK;
 }
 
-// Same plan and kernels as reduce_impl (kept in step with it by hand so that both give identical bits); only the
-// home of the partial results differs. Nothing needs clearing: every partial that the second kernel reads is
-// written by the first kernel of the same call.
-template <class Op>
-int reduce_static_impl(const float* x, float* out, int64_t outer, int64_t len, int64_t inner, cudaStream_t s,
-                       const StaticSetup& st) {
-    if (inner == 1) {
-        const int vec_ok = (len % 4 == 0) && aligned16(x);
-        int grid         = int(outer < int64_t(st.sm_count) * 8 ? outer : int64_t(st.sm_count) * 8);
-        reduce_rows_kernel<Op><<<grid, 256, 0, s>>>(x, out, outer, len, vec_ok);
-        return launch_status();
+// The partials of a split plan live in the array of the library image; a plan that needs more is refused before any
+// launch.
+struct StaticPartials {
+    float* base;
+    int operator()(size_t n, float** out) const {
+        if (n > STATIC_PARTIALS) return MIMK_E_WORKSPACE;
+        *out = base;
+        return MIMK_OK;
     }
-    const int64_t total = outer * inner;
-    const int threads   = 256;
-    int gx              = grid_for(total, threads, st.sm_count, 8);
-    int slices          = 1;
-    if (int64_t(gx) < 2 * st.sm_count && len >= 256) {
-        int64_t want = (4LL * st.sm_count + gx - 1) / gx;
-        int64_t maxs = len / 64;
-        slices       = int(want < maxs ? want : maxs);
-        if (slices < 1) slices = 1;
-        if (slices > 1024) slices = 1024;
-    }
-    if (slices == 1) {
-        reduce_mid_kernel<Op><<<dim3(gx, 1), threads, 0, s>>>(x, out, outer, len, inner, len);
-        return launch_status();
-    }
-    const int64_t slice_len = (len + slices - 1) / slices;
-    slices                  = int((len + slice_len - 1) / slice_len);
-    if (size_t(slices) * size_t(total) > STATIC_PARTIALS) return MIMK_E_WORKSPACE;
-    reduce_mid_kernel<Op><<<dim3(gx, slices), threads, 0, s>>>(x, st.partials, outer, len, inner, slice_len);
-    MIMK_TRY(launch_status());
-    reduce_partials_kernel<Op><<<gx, threads, 0, s>>>(st.partials, out, total, slices);
-    return launch_status();
-}
+};
 
 }  // namespace
 }  // namespace mimk
@@ -502,18 +503,27 @@ extern "C" int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, i
         const __nv_bfloat16* xh = static_cast<const __nv_bfloat16*>(x);
         __nv_bfloat16* oh       = static_cast<__nv_bfloat16*>(out);
         switch (monoid) {
-            case MIMK_SUM: return reduce_impl<SumOp>(xh, oh, outer, len, inner, s, *dev);
-            case MIMK_MAX: return reduce_impl<MaxOp>(xh, oh, outer, len, inner, s, *dev);
-            default: return reduce_impl<MinOp>(xh, oh, outer, len, inner, s, *dev);
+            case MIMK_SUM: return reduce_impl<SumOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials());
+            case MIMK_MAX: return reduce_impl<MaxOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials());
+            default: return reduce_impl<MinOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials());
         }
     }
     const float* xf = static_cast<const float*>(x);
     float* of       = static_cast<float*>(out);
     switch (monoid) {
-        case MIMK_SUM: return reduce_impl<SumOp>(xf, of, outer, len, inner, s, *dev);
-        case MIMK_MAX: return reduce_impl<MaxOp>(xf, of, outer, len, inner, s, *dev);
-        default: return reduce_impl<MinOp>(xf, of, outer, len, inner, s, *dev);
+        case MIMK_SUM: return reduce_impl<SumOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials());
+        case MIMK_MAX: return reduce_impl<MaxOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials());
+        default: return reduce_impl<MinOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials());
     }
+}
+
+extern "C" int mimk_reduce_plan(int64_t outer, int64_t len, int64_t inner, int sm_count, int64_t* partial_floats) {
+    if (outer < 0 || len < 0 || inner < 0 || sm_count < 1 || !partial_floats) return MIMK_E_ARG;
+    *partial_floats = 0;
+    if (outer * inner == 0 || inner == 1) return MIMK_OK;
+    const ReducePlan p = reduce_plan(outer, len, inner, sm_count);
+    if (p.slices > 1) *partial_floats = int64_t(p.slices) * outer * inner;
+    return MIMK_OK;
 }
 
 extern "C" int mimk_reduce_static(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner,
@@ -529,9 +539,9 @@ extern "C" int mimk_reduce_static(const void* x, void* out, int dtype, int64_t o
     const float* xf = static_cast<const float*>(x);
     float* of       = static_cast<float*>(out);
     switch (monoid) {
-        case MIMK_SUM: return reduce_static_impl<SumOp>(xf, of, outer, len, inner, s, *st);
-        case MIMK_MAX: return reduce_static_impl<MaxOp>(xf, of, outer, len, inner, s, *st);
-        default: return reduce_static_impl<MinOp>(xf, of, outer, len, inner, s, *st);
+        case MIMK_SUM: return reduce_impl<SumOp>(xf, of, outer, len, inner, s, st->sm_count, StaticPartials{st->partials});
+        case MIMK_MAX: return reduce_impl<MaxOp>(xf, of, outer, len, inner, s, st->sm_count, StaticPartials{st->partials});
+        default: return reduce_impl<MinOp>(xf, of, outer, len, inner, s, st->sm_count, StaticPartials{st->partials});
     }
 }
 
@@ -547,13 +557,14 @@ extern "C" int mimk_softmax(const void* x, void* y, int in_dtype, int out_dtype,
     if (!x || !y) return MIMK_E_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (inner == 1) return dispatch_rows<ROWS_SOFTMAX>(x, nullptr, y, in_dtype, out_dtype, outer, len, 0.f, s, *dev);
-    if (in_dtype != MIMK_F32) return MIMK_E_DTYPE;
     int grid = grid_for(outer * inner, 128, dev->sm_count, 16);
-    if (out_dtype == MIMK_F32)
-        softmax_strided_kernel<<<grid, 128, 0, s>>>(static_cast<const float*>(x), static_cast<float*>(y), outer, len, inner);
-    else
-        softmax_strided_kernel<<<grid, 128, 0, s>>>(static_cast<const float*>(x), static_cast<__nv_bfloat16*>(y), outer,
-                                                    len, inner);
+    const bool in16 = in_dtype == MIMK_BF16, out16 = out_dtype == MIMK_BF16;
+    const float* xf          = static_cast<const float*>(x);
+    const __nv_bfloat16* xh  = static_cast<const __nv_bfloat16*>(x);
+    if (!in16 && !out16) softmax_strided_kernel<<<grid, 128, 0, s>>>(xf, static_cast<float*>(y), outer, len, inner);
+    else if (!in16) softmax_strided_kernel<<<grid, 128, 0, s>>>(xf, static_cast<__nv_bfloat16*>(y), outer, len, inner);
+    else if (!out16) softmax_strided_kernel<<<grid, 128, 0, s>>>(xh, static_cast<float*>(y), outer, len, inner);
+    else softmax_strided_kernel<<<grid, 128, 0, s>>>(xh, static_cast<__nv_bfloat16*>(y), outer, len, inner);
     return launch_status();
 }
 

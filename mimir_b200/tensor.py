@@ -108,6 +108,8 @@ def bmm(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
         raise ValueError("bmm expects rank-3 tensors")
     if a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
         raise ValueError("contracting dims don't match")
+    if a.dtype != b.dtype:
+        raise TypeError("bmm: both operands share the ring's element type")
     a = a.contiguous()
     b_store, layout = _b_layout(b)
     bt, m, k = a.shape

@@ -105,3 +105,28 @@ def test_host_shape_errors_mirror_the_reference(lib):
         pytest.skip("shape checks run after the device check")
     with pytest.raises(ValueError, match="contracting dims don't match"):
         T.product_2d(torch.zeros(2, 3, device="cuda"), torch.zeros(4, 2, device="cuda"))
+
+
+def test_reduce_plan_fits_the_static_array_on_148_sms(lib):
+    """mimk_reduce_static keeps its partial results in MIMK_REDUCE_STATIC_BYTES of the library image. The plan (shared
+    with mimk_reduce) must fit there for every shape on a 148-SM device; with more SMs it can grow past it, which is
+    when the entry point answers MIMK_E_WORKSPACE."""
+    L = lib.lib()
+    cap = (1 << 20) // 4
+    n = C.c_int64(0)
+    worst = 0
+    for total in [1, 2, 7, 255, 256, 257, 1000, 4096, 20000, 50000, 75000, 75775, 75776, 75777, 100000, 10 ** 6]:
+        for ln in [1, 63, 255, 256, 300, 4096, 9000, 65536, 10 ** 6]:
+            for outer in (1, 3):
+                if total % outer:
+                    continue
+                assert L.mimk_reduce_plan(outer, ln, total // outer, 148, C.byref(n)) == 0
+                assert 0 <= n.value <= cap, (total, ln, n.value)
+                worst = max(worst, n.value)
+                if n.value:
+                    assert n.value % total == 0 and ln >= 256       # whole slices, only long axes are split
+    assert worst > cap // 2                                          # the sweep reaches the large plans
+    assert L.mimk_reduce_plan(1, 4096, 1, 148, C.byref(n)) == 0 and n.value == 0          # row reduce: no partials
+    assert L.mimk_reduce_plan(1, 10 ** 6, 100000, 264, C.byref(n)) == 0 and n.value > cap   # a larger machine can exceed
+    assert L.mimk_reduce_plan(-1, 4, 4, 148, C.byref(n)) == 1
+    assert L.mimk_reduce_plan(1, 4, 4, 148, None) == 1

@@ -280,6 +280,34 @@ def test_f32_on_tensor_cores_keeps_f32_accuracy(T, M, N, K, nk):
     assert nerr(f64(c[rows]), want) <= TOL_F32
 
 
+@pytest.mark.parametrize("nk", [False, True])
+def test_f32_on_tensor_cores_non_finite_operands(T, nk):
+    # inf / NaN operands (and a finite value whose TF32 head rounds up to inf) must give what the scalar ascending fold
+    # gives -- +-inf where every product has one sign, NaN where inf meets 0 or -inf -- not the NaN a head/tail split of
+    # inf would spread over the row
+    M, N, K = 256, 384, 512
+    a, b = uniform((M, K), 90), uniform((N, K) if nk else (K, N), 91)
+    a[3, 5], a[10, 0], a[200, 17] = float("inf"), float("nan"), 3.4028e38
+    a[77, 8] = float("-inf")
+    if nk:
+        b[9, 7], b[300, 8] = float("-inf"), 0.0
+    else:
+        b[7, 9], b[8, 300] = float("-inf"), 0.0
+    c = T.product_2d(a, T.transpose_2d(b) if nk else b).cpu().numpy()
+    T.device_status()
+    want = mo.gemm(a.cpu().numpy(), b.cpu().numpy(), b_nk=nk)
+    assert (np.isnan(c) == np.isnan(want)).all()
+    inf = np.isinf(want)
+    assert (np.isinf(c) == inf).all() and (c[inf] == want[inf]).all()
+    assert np.isnan(want[77, 300]) and np.isinf(want[3, 0]) and np.isnan(want[10]).all()   # the case is what it claims
+    fin = np.isfinite(want)
+    truth = mo.gemm_truth(np.where(np.isfinite(a.cpu().numpy()), a.cpu().numpy(), 0), np.where(np.isfinite(b.cpu().numpy()), b.cpu().numpy(), 0), b_nk=nk)
+    rows = [r for r in range(M) if r not in (3, 10, 77, 200)]
+    cols = [j for j in range(N) if j != 9]
+    sub = np.ix_(rows, cols)
+    assert fin[sub].all() and nerr(c[sub].astype(np.float64), truth[sub]) <= TOL_F32
+
+
 def test_chain_product_matches_the_chain_as_written():
     """Whatever association the price list picks (lit/tensor/reassoc.mim's chains, scaled up), the product is the one
     the chain as written gives, within the float tolerance of the f64 truth."""

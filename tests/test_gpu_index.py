@@ -146,3 +146,17 @@ def test_scatter_with_one_thread_per_update_keeps_the_last_visit(T, dim):
     got = T.scatter(dim, cu(x), cu(index), cu(upd))
     T.device_status()
     assert np.array_equal(got.cpu().numpy(), mo.scatter(dim, x, index, upd))
+
+
+def test_scatter_few_updates_into_a_large_table(T):
+    """An index tensor past the one-thread-per-update threshold scattered into an input far larger than itself: the
+    library must not clear a winner table of the input's size for it (the per-line kernel runs), and the loops' rule
+    still decides the duplicates."""
+    rng = np.random.default_rng(31)
+    x = rng.integers(-1000, 1000, (64, 40000)).astype(np.int32)        # 2.56 M cells
+    index = rng.integers(0, 40000, (64, 80)).astype(np.int64)          # 5120 updates, some duplicates per line
+    index[:, 40:] = index[:, :40]
+    upd = rng.integers(-1000, 1000, (64, 80)).astype(np.int32)
+    got = T.scatter(1, cu(x), cu(index), cu(upd))
+    T.device_status()
+    assert np.array_equal(got.cpu().numpy(), mo.scatter(1, x, index, upd))

@@ -103,6 +103,20 @@ def test_softmax_middle_axis(T):
     assert nerr(f64(got), mo.softmax(x.cpu().numpy(), 1)) < TOL_F32
 
 
+def test_softmax_middle_axis_bf16(T):
+    # bf16 operands along an axis that is not the last one (statistics in f32, result rounded to bf16)
+    x = randn((4, 37, 6), 52, dtype=torch.bfloat16)
+    want = mo.softmax(x.float().cpu().numpy().astype(np.float64), 1)
+    assert nerr(f64(T.softmax(1, x)), want) < TOL_BF16
+    assert nerr(f64(T.softmax(1, x, out_dtype=torch.float32)), want) < TOL_F32
+
+
+def test_bmm_rejects_mixed_element_types(T):
+    a = randn((2, 8, 8), 53)
+    with pytest.raises(TypeError):
+        T.bmm(a, a.to(torch.bfloat16))
+
+
 def test_elementwise_and_binary_ax(T):
     x = randn((6, 10, 4), 61)
     y = randn((6, 10, 4), 62)
