@@ -123,6 +123,12 @@ typedef struct mimk_gather_dst {
     int64_t ldc, col_off; /* in elements */
 } mimk_gather_dst;
 int mimk_gemm_gather(const mimk_gemm_desc* desc, const void* b2, const mimk_gather_dst* dsts, void* stream);
+/* mimk_gemm whose left operand arrives as `panels` row-major [m, k / panels] matrices stored one after another -- panel g
+ * holds columns [g k/panels, (g+1) k/panels) of A. That is the layout an all-gather of column slabs delivers (every
+ * rank's [m, k/panels] slab, in rank order), so the contraction that consumes a gathered matrix reads it where the
+ * collective put it, with no transposing copy in between. bf16 operands, batch = 1, k / panels a multiple of 64.
+ * No counterpart in the reference, which has no multi-device support (src/mim/plug/nvptx/phase/nvptx.cpp:186-204). */
+int mimk_gemm_kpanels(const mimk_gemm_desc* desc, int64_t panels, void* stream);
 /* The same call with scalar arguments only (batch = 1, no full-shape epilogue operand): emitted code can call it
  * without building a struct in memory -- an `extern con` with scalar parameters is all the binding needs
  * (lit/cps/ds_external_cimp.mim:13-20). */

@@ -107,7 +107,8 @@ using namespace mimk;
 namespace mimk {
 // The paired-SM kernel when the problem has enough 256-row tiles, else the one-CTA kernel.
 // MIMK_GEMM_2CTA=0 forces the one-CTA kernel, =2 the paired one whenever it can run (for A/B measurements).
-int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather) {
+int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather,
+                int64_t a_panels) {
     static int allow_pair = -1;
     if (allow_pair < 0) {
         const char* e = getenv("MIMK_GEMM_2CTA");
@@ -115,9 +116,9 @@ int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* 
     }
     // the paired kernel takes one launch per batch entry; long batches go to the one-CTA kernel, which walks
     // (batch, tile) pairs in a single launch
-    if (allow_pair == 2 && d.batch <= 64 && gemm_tc_supported(d)) return gemm_tc2(d, s, gated, b2, gather);
-    if (allow_pair && d.batch <= 64 && gemm_tc2_supported(d, gated)) return gemm_tc2(d, s, gated, b2, gather);
-    return gemm_tc(d, s, gated, b2, gather);
+    if (allow_pair == 2 && d.batch <= 64 && gemm_tc_supported(d)) return gemm_tc2(d, s, gated, b2, gather, a_panels);
+    if (allow_pair && d.batch <= 64 && gemm_tc2_supported(d, gated)) return gemm_tc2(d, s, gated, b2, gather, a_panels);
+    return gemm_tc(d, s, gated, b2, gather, a_panels);
 }
 }  // namespace mimk
 
@@ -206,6 +207,19 @@ extern "C" int mimk_gemm_gather(const mimk_gemm_desc* d, const void* b2, const m
     dd.c              = g->dst[0];  // only its alignment is looked at; the tiles go to g->dst[*]
     if (!gemm_tc_supported(dd)) return MIMK_E_UNSUPPORTED;
     return gemm_tc_any(dd, static_cast<cudaStream_t>(stream), b2 ? 1 : 0, b2, g);
+}
+
+extern "C" int mimk_gemm_kpanels(const mimk_gemm_desc* d, int64_t panels, void* stream) {
+    MIMK_TRY(check_gemm(d));
+    if (panels < 1) return MIMK_E_ARG;
+    if (panels == 1) return mimk_gemm(d, stream);
+    int st = MIMK_OK;
+    if (!device_info(&st)) return st;
+    if (d->batch != 1 || d->k % panels != 0 || (d->k / panels) % 64 != 0) return MIMK_E_UNSUPPORTED;
+    if (d->m == 0 || d->n == 0) return MIMK_OK;
+    if (!d->a || !d->b || !d->c) return MIMK_E_ARG;
+    if (!gemm_tc_supported(*d)) return MIMK_E_UNSUPPORTED;
+    return gemm_tc_any(*d, static_cast<cudaStream_t>(stream), 0, nullptr, nullptr, panels);
 }
 
 extern "C" int mimk_gemm_flat(int64_t m, int64_t n, int64_t k, const void* a, const void* b, void* c, int32_t in_dtype,

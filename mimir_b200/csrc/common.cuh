@@ -49,11 +49,15 @@ inline size_t dtype_size(int dt) { return dt == MIMK_BF16 ? 2 : (dt == MIMK_I64 
 // kernels implemented in the other translation units
 int gemm_simt(const mimk_gemm_desc& d, cudaStream_t s);
 int gemm_tc_supported(const mimk_gemm_desc& d);
-int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr);
+// a_panels > 1: A is given as that many row-major [m, k / a_panels] matrices one after another (the layout an all-gather
+// of column slabs delivers); k / a_panels must then be a multiple of 64
+int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr,
+            int64_t a_panels = 1);
 int gemm_tc2_supported(const mimk_gemm_desc& d, int gated);  // the paired-SM (cta_group::2) form
-int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr);
+int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr,
+             int64_t a_panels = 1);
 int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
-                const mimk_gather_dst* gather = nullptr);  // picks between the two
+                const mimk_gather_dst* gather = nullptr, int64_t a_panels = 1);  // picks between the two
 int gemm_f32_tc_supported(const mimk_gemm_desc& d);  // f32 operands on the tensor cores (3xTF32)
 int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s);
 // map_reduce_post instances that are a contraction, an axis fold or an elementwise map go to those kernels (mrp_route.cu)

@@ -54,6 +54,7 @@ struct Params {
     int64_t M, N, K;
     int64_t batch, stride_c;  // batch entries; elements between consecutive results (and full-shape epilogue operands)
     int a_batched, b_batched; // 0: every batch entry reads the same operand (batch coordinate 0)
+    int a_panel_k, a_panel_rows;  // A as K-panels: columns per panel (K when A is one matrix) and rows between panels
     // The result tile goes to `n_dst` matrices of leading dimension `ldc`, at column offset `col_off`: one destination
     // (C itself, ldc = N) for an ordinary call; this GPU's and its peers' copies of a gathered matrix when the all-gather
     // of a column-sharded contraction is fused into the epilogue (plain stores to peer-mapped addresses over NVLink).
@@ -134,7 +135,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t sa   = tile_base + stage * STAGE_BYTES;
                     const uint32_t sb   = sa + A_BYTES;
                     mbar_expect_tx(full, A_BYTES + (GATED ? 2 : 1) * BN * BK * 2);
-                    tma_load_3d(sa, &tmA, kb * BK, m0, za, full);
+                    const int ka = kb * BK, pa = ka / p.a_panel_k;  // the K-panel of A this k-block lies in
+                    tma_load_3d(sa, &tmA, ka - pa * p.a_panel_k, m0 + pa * p.a_panel_rows, za, full);
                     if (!B_MN) {
                         tma_load_3d(sb, &tmB, kb * BK, n0, zb, full);
                         if (GATED) tma_load_3d(sb + BN * BK * 2, &tmB2, kb * BK, n0, zb, full);
@@ -414,7 +416,8 @@ int gemm_tc_supported(const mimk_gemm_desc& d) {
     return 1;
 }
 
-int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather) {
+int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather,
+            int64_t a_panels) {
     int st          = MIMK_OK;
     DeviceInfo* dev = device_info(&st);
     if (!dev) return st;
@@ -430,7 +433,9 @@ int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, 
     const uint64_t sb = b_b ? uint64_t(d.stride_b) * 2 : (whole_b < (uint64_t(1) << 40) ? whole_b : row_b);
     const void* B2 = b2 ? b2 : d.b;
     CUtensorMap tA, tB, tB2;
-    MIMK_TRY(make_tmap_bf16_3d(&tA, d.a, uint64_t(d.k), uint64_t(d.m), na, uint64_t(d.k) * 2, sa, BK, BM));
+    if (a_panels < 1 || (a_panels > 1 && (d.batch != 1 || d.k % a_panels != 0 || (d.k / a_panels) % BK != 0))) return MIMK_E_UNSUPPORTED;
+    const uint64_t kp = uint64_t(d.k / a_panels);  // A as a [panels * m, k / panels] matrix: panel g starts at row g * m
+    MIMK_TRY(make_tmap_bf16_3d(&tA, d.a, kp, uint64_t(d.m) * uint64_t(a_panels), na, kp * 2, sa, BK, BM));
     if (b_mn) {
         MIMK_TRY(make_tmap_bf16_3d(&tB, d.b, uint64_t(d.n), uint64_t(d.k), nb, uint64_t(d.n) * 2, sb, 64, BK));
         MIMK_TRY(make_tmap_bf16_3d(&tB2, B2, uint64_t(d.n), uint64_t(d.k), nb, uint64_t(d.n) * 2, sb, 64, BK));
@@ -442,6 +447,7 @@ int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, 
     p.M = d.m, p.N = d.n, p.K = d.k;
     p.batch = d.batch, p.stride_c = d.batch > 1 ? d.stride_c : 0;
     p.a_batched = a_b, p.b_batched = b_b;
+    p.a_panel_k = a_panels > 1 ? int(kp) : int((d.k + BK - 1) / BK * BK), p.a_panel_rows = a_panels > 1 ? int(d.m) : 0;
     if (gather) {
         if (d.batch != 1) return MIMK_E_UNSUPPORTED;
         p.n_dst = gather->n_dst;

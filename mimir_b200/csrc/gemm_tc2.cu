@@ -51,6 +51,7 @@ static_assert(sizeof(Bars) <= 256, "barrier block too large");
 
 struct Params {
     int64_t M, N, K;
+    int a_panel_k, a_panel_rows;  // A as K-panels: columns per panel (K when A is one matrix) and rows between panels
     // The result tile goes to `n_dst` matrices of leading dimension `ldc`, at column offset `col_off`: one destination
     // (C itself, ldc = N) for an ordinary call; this GPU's and its peers' copies of a gathered matrix when the all-gather
     // of a column-sharded contraction is fused into the epilogue (plain stores to peer-mapped addresses over NVLink).
@@ -188,7 +189,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const uint32_t sa = tile_base + stage * STAGE_BYTES;
                     const uint32_t sb = sa + A_BYTES;
                     if (rank == 0) mbar_expect_tx(smem_u32(&bars->full[stage]), 2 * STAGE_BYTES);  // both CTAs' bytes
-                    tma_load_2d_pair(sa, &tmA, kb * BK, m0, full_even);
+                    const int ka = kb * BK, pa = ka / p.a_panel_k;  // the K-panel of A this k-block lies in
+                    tma_load_2d_pair(sa, &tmA, ka - pa * p.a_panel_k, m0 + pa * p.a_panel_rows, full_even);
                     if (!B_MN) {
                         tma_load_2d_pair(sb, &tmB, kb * BK, n0, full_even);
                         if (GATED) tma_load_2d_pair(sb + BH_BYTES, &tmB2, kb * BK, n0, full_even);
@@ -389,7 +391,8 @@ int gemm_tc2_supported(const mimk_gemm_desc& d, int gated) {
     return d.m >= 512 && tiles >= 74;
 }
 
-int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather) {
+int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather,
+             int64_t a_panels) {
     int st          = MIMK_OK;
     DeviceInfo* dev = device_info(&st);
     if (!dev) return st;
@@ -401,7 +404,9 @@ int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
         const uint8_t* B  = static_cast<const uint8_t*>(d.b) + size_t(b * d.stride_b) * 2;
         const uint8_t* B2 = b2 ? static_cast<const uint8_t*>(b2) + size_t(b * d.stride_b) * 2 : B;
         CUtensorMap tA, tB, tB2;
-        MIMK_TRY(make_tmap_bf16_2d(&tA, A, uint64_t(d.k), uint64_t(d.m), uint64_t(d.k) * 2, BK, BM));
+        if (a_panels < 1 || (a_panels > 1 && (d.batch != 1 || d.k % a_panels != 0 || (d.k / a_panels) % BK != 0))) return MIMK_E_UNSUPPORTED;
+        const uint64_t kp = uint64_t(d.k / a_panels);  // A as a [panels * m, k / panels] matrix: panel g starts at row g * m
+        MIMK_TRY(make_tmap_bf16_2d(&tA, A, kp, uint64_t(d.m) * uint64_t(a_panels), kp * 2, BK, BM));
         if (b_mn) {
             MIMK_TRY(make_tmap_bf16_2d(&tB, B, uint64_t(d.n), uint64_t(d.k), uint64_t(d.n) * 2, 64, BK));
             MIMK_TRY(make_tmap_bf16_2d(&tB2, B2, uint64_t(d.n), uint64_t(d.k), uint64_t(d.n) * 2, 64, BK));
@@ -411,6 +416,7 @@ int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
         }
         Params p;
         p.M = d.m, p.N = d.n, p.K = d.k;
+        p.a_panel_k = a_panels > 1 ? int(kp) : int((d.k + BK - 1) / BK * BK), p.a_panel_rows = a_panels > 1 ? int(d.m) : 0;
         if (gather) {
             if (d.batch != 1) return MIMK_E_UNSUPPORTED;
             p.n_dst = gather->n_dst;

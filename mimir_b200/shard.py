@@ -58,6 +58,10 @@ def gather_columns(local: torch.Tensor, total_cols: int) -> torch.Tensor:
     rank, world = _world()
     if world == 1:
         return local
+    if local.dim() == 2 and local.shape[1] * world == total_cols:
+        # equal slabs: gather them as [world, m, n] panels (the collective's own layout), then ONE copy interleaves them
+        m, n = local.shape
+        return gather_panels(local).permute(1, 0, 2).reshape(m, world * n)
     return gather_rows(local.t().contiguous(), total_cols).t().contiguous()
 
 
@@ -179,12 +183,41 @@ def tp_mlp_gated(x, w1_shard, w3_shard, w2_shard, h: "GatheredMatrix | None" = N
         (h if y is None else y).barrier()
         return out
     h_local = torch.empty((x.shape[0], f_local), dtype=x.dtype, device=x.device)
-    gemm_gather_local(x, w1_shard, w3_shard, h_local)
-    slab = T.product_2d(gather_columns(h_local, f_local * world), w2_shard)
+    slab = tp_mlp_gated_nccl(x, w1_shard, w3_shard, w2_shard, h_local, gather_y=y is not None)
     if y is None:
         return slab
-    y.local.copy_(gather_columns(slab, slab.shape[1] * world))
+    y.local.copy_(slab)
     return y.local
+
+
+_panel_buffers = {}
+
+
+def gather_panels(local: torch.Tensor) -> torch.Tensor:
+    """NCCL all-gather of every rank's [m, n] column slab into one [world, m, n] tensor (panel g = rank g's slab): the
+    collective's natural layout, no transposing copy on either side. The receive buffer is cached per shape."""
+    rank, world = _world()
+    key = (tuple(local.shape), local.dtype, local.device)
+    buf = _panel_buffers.get(key)
+    if buf is None:
+        buf = _panel_buffers[key] = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(buf, local.contiguous())
+    return buf
+
+
+def tp_mlp_gated_nccl(x, w1_shard, w3_shard, w2_shard, h_local, gather_y: bool = False):
+    """The tensor-parallel gated MLP with a separate NCCL all-gather of H: stage 1 into the local slab, all-gather into
+    [world, m, F/world] panels, stage 2 reads the panels in place as the K-panels of its left operand
+    (mimir_b200.tensor.product_2d_panels). gather_y: all-gather the Y column slabs too and return the whole Y."""
+    from . import tensor as T
+    rank, world = _world()
+    gemm_gather_local(x, w1_shard, w3_shard, h_local)
+    if world == 1:
+        return T.product_2d(h_local, w2_shard)
+    slab = T.product_2d_panels(gather_panels(h_local), w2_shard)
+    if not gather_y:
+        return slab
+    return gather_columns(slab, slab.shape[1] * world)
 
 
 def gemm_gather_local(x, w1_shard, w3_shard, h_local):

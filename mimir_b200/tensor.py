@@ -101,6 +101,30 @@ def product_2d(a: torch.Tensor, b: torch.Tensor, *, post=None, bias=None, full=N
     return out
 
 
+def product_2d_panels(a_panels: torch.Tensor, b: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
+    """C = A . b where A [m, G * kp] is given as its G column panels `a_panels` [G, m, kp] -- what an all-gather of
+    column slabs delivers -- so that the consumer of a gathered matrix reads it in place (mimk_gemm_kpanels)."""
+    _dev(a_panels, b)
+    if a_panels.dim() != 3 or b.dim() != 2:
+        raise ValueError("product_2d_panels expects [G, m, kp] panels and a rank-2 right operand")
+    G, m, kp = a_panels.shape
+    if G * kp != b.shape[0]:
+        raise ValueError("contracting dims don't match")
+    if a_panels.dtype != b.dtype:
+        raise TypeError("product_2d_panels: both operands share the ring's element type")
+    a_panels = a_panels.contiguous()
+    b_store, layout = _b_layout(b)
+    n = b.shape[1]
+    out = torch.empty((m, n), dtype=out_dtype or a_panels.dtype, device=a_panels.device)
+    d = L.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, m, n, G * kp
+    d.a, d.b, d.c = a_panels.data_ptr(), b_store.data_ptr(), out.data_ptr()
+    d.stride_c = m * n
+    d.in_dtype, d.out_dtype, d.b_layout, d.post = _dt(a_panels), _dt(out), layout, L.POST_ID
+    L.check(L.lib().mimk_gemm_kpanels(C.byref(d), G, _stream()), "product_2d_panels")
+    return out
+
+
 def bmm(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
     """C[B,m,n] = sum_k a[B,m,k] * b[B,k,n] (tensor.mim:404-407, batching axis 0)."""
     _dev(a, b)

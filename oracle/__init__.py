@@ -47,6 +47,63 @@ def lib() -> C.CDLL:
     return _lib
 
 
+# ---------------------------------------------------------------------------------------------
+# timed builds (the benchmark's CPU-baseline legs only; parity always runs on the strict build above)
+# ---------------------------------------------------------------------------------------------
+TIMED_FLAGS = {
+    "fast": "g++ -O3 -march=native -ffp-contract=fast",
+    "fastmath": "g++ -O3 -march=native -ffp-contract=fast -ffast-math",
+}
+
+
+def _host_tag() -> str:
+    """Names the host CPU (model + ISA flags): -march=native code is built per machine and never carried to another."""
+    import hashlib
+    text = ""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith(("model name", "flags")):
+                    text += line
+                if line.strip() == "" and text:
+                    break
+    except OSError:
+        pass
+    import platform
+    return hashlib.sha1((text or platform.processor() or "unknown").encode()).hexdigest()[:10]
+
+
+def build_timed() -> dict:
+    """Compile the two timed variants for THIS host (a few seconds) and return {variant: path}."""
+    tag = _host_tag()
+    paths = {v: os.path.join(_HERE, "_ref", f"libmimir_oracle_{v}_{tag}.so") for v in TIMED_FLAGS}
+    src = os.path.join(_HERE, "mimir_oracle.cpp")
+    if any(not os.path.exists(p) or os.path.getmtime(p) < os.path.getmtime(src) for p in paths.values()):
+        subprocess.run(["make", "-C", _HERE, "timed", f"TAG={tag}"], check=True, capture_output=True)
+    return paths
+
+
+class timed_build:
+    """`with oracle.timed_build("fast"): ...` runs the direct loops of this module on a timed variant of the library
+    (same source, the flags in TIMED_FLAGS) instead of the strict parity build. For timing only."""
+
+    def __init__(self, variant: str):
+        self.path = build_timed()[variant]
+
+    def __enter__(self):
+        global _lib
+        lib()
+        self.saved = _lib
+        _lib = C.CDLL(self.path)
+        _lib.mo_map_reduce_post.restype = C.c_int
+        return self
+
+    def __exit__(self, *exc):
+        global _lib
+        _lib = self.saved
+        return False
+
+
 def _p(a: np.ndarray):
     return a.ctypes.data_as(C.c_void_p)
 

@@ -308,6 +308,23 @@ def test_f32_on_tensor_cores_non_finite_operands(T, nk):
     assert fin[sub].all() and nerr(c[sub].astype(np.float64), truth[sub]) <= TOL_F32
 
 
+@pytest.mark.parametrize("M,G,kp,N", [(300, 4, 128, 264), (2560, 8, 256, 2048), (512, 2, 64, 8)])
+@pytest.mark.parametrize("nk", [False, True])
+def test_left_operand_as_k_panels(T, M, G, kp, N, nk):
+    """A handed over as G column panels [G, M, kp] (an all-gather's receive buffer) gives the bits of the product with
+    the panels laid side by side, on the one-CTA and on the paired-SM kernel."""
+    a = randn((M, G * kp), 300 + M, dtype=torch.bfloat16)
+    b = randn((N, G * kp) if nk else (G * kp, N), 301 + M, 0.05, dtype=torch.bfloat16)
+    bv = T.transpose_2d(b) if nk else b
+    panels = a.reshape(M, G, kp).permute(1, 0, 2).contiguous()
+    got = T.product_2d_panels(panels, bv)
+    T.device_status()
+    assert torch.equal(got, T.product_2d(a, bv))
+    rows = [0, M - 1]
+    want = mo.gemm_truth(bits(a), bits(b), b_nk=nk, bf16=True, rows=rows)
+    assert nerr(f64(got[rows]), want) <= TOL_BF16
+
+
 def test_chain_product_matches_the_chain_as_written():
     """Whatever association the price list picks (lit/tensor/reassoc.mim's chains, scaled up), the product is the one
     the chain as written gives, within the float tolerance of the f64 truth."""
