@@ -241,16 +241,16 @@ extern "C" int mimk_attn_fwd(const mimk_attn_desc* d, void* stream) {
     if (d->batch_heads == 0 || d->seq_q == 0 || d->head_dim == 0) return MIMK_OK;
     if (!d->q || !d->o || (d->seq_k > 0 && (!d->k || !d->v))) return MIMK_E_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // The persistent kernel hides the per-item set-up and drain (about 6 us against 1.9 us per step of 128 keys):
-    // 27 % faster on items of 4 steps, 13 % on 8, 3 % on 32; config C4 (causal, mean 17 steps) 0.493 against 0.511 ms.
-    // MIMK_ATTN_PERSIST=0 selects the one-item-per-CTA kernel (head_dim 128 only; for A/B measurements).
-    static int persistent = -1;
-    if (persistent < 0) {
-        const char* e = getenv("MIMK_ATTN_PERSIST");
-        persistent    = (e && e[0] == '0') ? 0 : 1;
+    // bf16 with head_dim 64 or 128 runs on the persistent tensor-core kernel (attn_tc_p.cu). MIMK_ATTN_PAIRED=1 sends head_dim
+    // 128 to the paired-SM kernel instead (attn_tc2.cu: cta_group::2, double-buffered scores) -- held to the same tolerance; measured at
+    // 128 heads x 4096: 0.56 / 0.92 ms (causal / full) against 0.49 / 0.87 ms here, so it is not the default.
+    static int paired = -1;
+    if (paired < 0) {
+        const char* e = getenv("MIMK_ATTN_PAIRED");
+        paired        = (e && e[0] == '1') ? 1 : 0;
     }
-    if (persistent && attn_tc_persistent_supported(*d)) return attn_tc_persistent(*d, s);
-    if (attn_tc_supported(*d)) return attn_tc(*d, s);
+    if (paired && attn_tc_pair_supported(*d)) return attn_tc_pair(*d, s);
+    if (attn_tc_persistent_supported(*d)) return attn_tc_persistent(*d, s);
     static int composed = -1;  // MIMK_ATTN_COMPOSED=0 keeps every such problem on the one-launch CUDA-core kernel
     if (composed < 0) {
         const char* e = getenv("MIMK_ATTN_COMPOSED");

@@ -1,18 +1,34 @@
-// Attention forward, persistent form of attn_tc.cu: one CTA per SM takes (head, query-tile pair) work items from a
-// global counter until none is left, and the hand-over between items is pipelined.
+// Attention forward on the 5th-generation tensor cores: O = softmax(scale * Q K^T [+ causal mask]) V, bf16 in/out,
+// f32 scores, statistics and accumulation, head_dim 64 or 128. Persistent: one CTA per SM takes (head, query-tile pair)
+// work items from a global counter until none is left, and the hand-over between items is pipelined.
 //
-// Same program as attn_tc.cu -- `softmax (q * transpose_2d k) * v` (MimIR lit/tensor/attn_exec.mim:20-22) with scale, an
-// optional causal mask and batch x heads -- and the same roles and tensor-memory layout (S0 S1 O0 O1, P over S). What a
-// one-item CTA pays per item and this kernel hides: the CTA launch, barrier and tensor-memory set-up, the load latency
-// of Q and of the first K/V tiles, the pipeline fill and drain. Measured with the one-item kernel at head_dim 128:
-// 5.8 us per item beside 1.84 us per step of 128 keys, i.e. 3.2 steps' worth on items that are 4 to 64 steps long.
+// The reference computes this as the composed program `softmax (q * transpose_2d k) * v` (MimIR
+// lit/tensor/attn_exec.mim:20-22): two contractions around the four-op softmax (tensor.mim:1172-1176) with the whole
+// score matrix in memory. Here the score tile never leaves the SM:
+//
+//   a work item is two query tiles of 128 rows of one (batch, head); the CTA walks their key/value tiles of 128 keys
+//   warps 0..3    softmax of query tile 0, one thread per row: tcgen05.ld the 128 f32 scores of the row into
+//   warps 4..7    softmax of query tile 1   registers, running max / sum, exp2 with the scale folded in, P written
+//                 back over S in tensor memory as bf16 (tcgen05.st); O is rescaled in tensor memory only when the
+//                 running max has grown by more than 2^8 since the last rescale
+//   (registers are moved from the third warpgroup to the two softmax warpgroups with setmaxnreg: 208 vs 88 per thread)
+//   warp 8        work fetch + TMA producer: Q, then K and V tiles into two-stage rings (128-byte-swizzled shared memory)
+//   warp 9        MMA issuer (one thread): S_t = Q_t K^T  (tcgen05.mma, M128 N128 K16 x 8, both operands in shared
+//                 memory) and O_t += P_t V (A operand = P_t in tensor memory, B operand = V as an MN-major tile)
+//   TMEM (512 columns): S_0 | S_1 | O_0 | O_1; P_t aliases the first 64 columns of S_t.
+// While one tile's warps do their exponentials the tensor core works on the other tile.
+//
+// What a one-item CTA would pay per item and this kernel hides: the CTA launch, barrier and tensor-memory set-up, the load
+// latency of Q and of the first K/V tiles, the pipeline fill and drain (measured at head_dim 128: 5.8 us per item beside
+// 1.84 us per step of 128 keys, i.e. 3.2 steps' worth on items that are 4 to 64 steps long).
 //   producer   fetches the next item as soon as the K/V ring has room: its Q tiles are loaded when the last S = Q K^T
 //              of the previous item has been issued, its first K/V tiles while the previous item's last steps compute
 //   MMA        issues S = Q K^T of the next item's first key tile right behind the previous item's last O += P V; the
 //              first O += P V of an item (which overwrites O_t) waits until the previous item's O_t has been read
 //   softmax    reads the finished O_t into registers, releases it, then normalises and stores from registers
 // Barriers live across items, so every role keeps running counts (K/V tiles, S tiles, P tiles, items per tile) and
-// derives stage and parity from them. Every wait is bounded as in attn_tc.cu.
+// derives stage and parity from them. Every mbarrier wait is bounded; on expiry the CTA records MIMK_E_DEVICE_WAIT and
+// unwinds.
 #include <math_constants.h>
 
 #include <cstdlib>
@@ -36,7 +52,8 @@ __host__ __device__ constexpr int tile_bytes(int hd) { return (hd / 64) * ATOM_B
 constexpr int KV_STAGES = 2;
 constexpr int NUM_THREADS = 384;  // softmax tile 0, softmax tile 1, {producer, MMA, two idle warps}
 constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
-// register budget moved between warpgroups with setmaxnreg; must fit what the CTA got at launch (see attn_tc.cu)
+// setmaxnreg moves registers between warpgroups inside what the CTA got at launch (168 per thread under
+// __launch_bounds__(384, 1)). An increase that the pool cannot satisfy would block for ever, so the budget is checked.
 constexpr int LAUNCH_REGS = 168;
 template <int SOFTMAX_REGS, int OTHER_REGS>
 struct RegSplit {
@@ -83,7 +100,8 @@ struct Item {
     int n_kv[2], n_max;
 };
 
-// Items are numbered so that taking them in order is longest-first inside groups of heads (see attn_tc.cu): inside a
+// Items are numbered so that taking them in order is longest-first inside groups of heads (the heads of a group share
+// the L2 with their K / V streams; all heads at once thrash it): inside a
 // group all heads' longest query-tile pair comes first, then all second-longest, and so on.
 __device__ __forceinline__ Item decode_item(const Params& p, int item) {
     Item it;

@@ -65,15 +65,16 @@ bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status);
 // axis permutation as a tiled copy (permute.cu); perm[j] = the output loop that indexes input axis j
 int permute_copy(const void* in, void* out, int esize, int rank, const int64_t* out_shape, const int* perm, cudaStream_t s);
 int attn_simt(const mimk_attn_desc& d, cudaStream_t s);
-int attn_tc_supported(const mimk_attn_desc& d);
-int attn_tc(const mimk_attn_desc& d, cudaStream_t s);
-// the persistent form (one CTA per SM pulls work items; hand-over between items pipelined)
 // f32, and bf16 with other head dims, at scale: the composition S = Q K^T, softmax, O = P V on the contraction and row
 // kernels (attn_composed.cu)
 int attn_composed_supported(const mimk_attn_desc& d);
 int attn_composed(const mimk_attn_desc& d, cudaStream_t s);
-int attn_tc_persistent_supported(const mimk_attn_desc& d);  // bf16, head_dim 64 or 128
+// bf16, head_dim 64 or 128: one CTA per SM pulls (head, query-tile pair) items, hand-over between items pipelined
+int attn_tc_persistent_supported(const mimk_attn_desc& d);
 int attn_tc_persistent(const mimk_attn_desc& d, cudaStream_t s);
+// bf16, head_dim 128, on paired SMs (cta_group::2): one query tile per CTA, double-buffered scores (attn_tc2.cu)
+int attn_tc_pair_supported(const mimk_attn_desc& d);
+int attn_tc_pair(const mimk_attn_desc& d, cudaStream_t s);
 
 // ---- device side ----------------------------------------------------------------------------------
 #ifdef __CUDACC__

@@ -1,0 +1,90 @@
+"""Every environment switch that selects another kernel for the same operator, exercised in a fresh process (the library
+reads each switch once) against the oracle: the alternative kernels are product code and are held to the same
+tolerances as the defaults."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+SCRIPT = r"""
+import sys
+import numpy as np, torch
+import oracle as mo
+from mimir_b200 import tensor as T
+from tests.util import TOL_BF16, TOL_F32, bits, f64, nerr, randn, uniform
+what = sys.argv[1]
+if what == "attn":
+    for s, causal in ((384, True), (1024, False), (200, True)):
+        q, k, v = (randn((3, s, 128), 10 + i, 1.0, torch.bfloat16) for i in range(3))
+        o, lse = T.attention(q, k, v, scale=0.09, causal=causal, return_lse=True)
+        T.device_status()
+        want = mo.attention(bits(q), bits(k), bits(v), scale=0.09, causal=causal, bf16=True)
+        assert nerr(f64(o), want) <= TOL_BF16, (s, causal)
+        sc = np.einsum("hid,hjd->hij", f64(q), f64(k)) * 0.09
+        if causal:
+            sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
+        want_lse = np.log(np.exp(sc - sc.max(-1, keepdims=True)).sum(-1)) + sc.max(-1)
+        assert np.abs(lse.cpu().numpy() - want_lse).max() < 2e-3
+    # many items per CTA pair and a score range that forces rescales of O
+    g = torch.Generator().manual_seed(5)
+    q = (torch.randn(40, 1024, 128, generator=g) * 2).to(torch.bfloat16).cuda()
+    k = (torch.randn(40, 1024, 128, generator=g) * 2).to(torch.bfloat16).cuda()
+    k[:, 600:, :] *= 3
+    v = torch.randn(40, 1024, 128, generator=g).to(torch.bfloat16).cuda()
+    o = T.attention(q, k, v, scale=0.25, causal=True)
+    T.device_status()
+    heads = [0, 17, 39]
+    want = mo.attention(bits(q), bits(k), bits(v), scale=0.25, causal=True, bf16=True, heads=heads)
+    assert torch.isfinite(o.float()).all() and nerr(f64(o[heads]), want) <= TOL_BF16
+elif what == "attn_f32":
+    q, k, v = (randn((3, 1024, 64), 70 + i, 1.0) for i in range(3))
+    o = T.attention(q, k, v, scale=0.125, causal=True)
+    T.device_status()
+    assert nerr(f64(o), mo.attention(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), scale=0.125, causal=True)) <= TOL_F32
+elif what == "gemm_bf16":
+    for (m, n, k) in ((2560, 2048, 512), (300, 264, 128)):
+        a, b = randn((m, k), 1, 1.0, torch.bfloat16), randn((n, k), 2, 0.05, torch.bfloat16)
+        c = T.product_2d(a, T.transpose_2d(b))
+        T.device_status()
+        rows = [0, m // 2, m - 1]
+        assert nerr(f64(c[rows]), mo.gemm_truth(bits(a), bits(b), b_nk=True, bf16=True, rows=rows)) <= TOL_BF16
+elif what == "gemm_f32":
+    a, b = uniform((512, 1024), 3), uniform((1024, 384), 4)
+    c = T.product_2d(a, b)
+    T.device_status()
+    assert nerr(f64(c), mo.gemm_truth(a.cpu().numpy(), b.cpu().numpy())) <= TOL_F32
+elif what == "mrp":
+    # instances the recognisers would hand to the contraction / fold kernels: here they stay on the per-cell kernel
+    from mimir_b200 import _lib as L
+    a, b = uniform((128, 96), 6), uniform((96, 160), 7)
+    c = T.map_reduce_post((128, 160), (128, 160, 96), L.F_MULADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)),
+                          [T.proj_map(3, (0, 2)), T.proj_map(3, (2, 1))], [a, b])
+    T.device_status()
+    assert np.array_equal(c.cpu().numpy(), mo.gemm(a.cpu().numpy(), b.cpu().numpy()))      # ascending fold: the oracle's bits
+    x = randn((2048, 1024), 5)
+    assert nerr(f64(T.reduce("sum", 1, x)), mo.reduce_axis(x.cpu().numpy(), 1, "sum", truth=True)) <= TOL_F32
+print("switch ok", what)
+"""
+
+CASES = [
+    ("MIMK_ATTN_PAIRED", "1", "attn"),          # head_dim 128 on the paired-SM kernel (attn_tc2.cu)
+    ("MIMK_ATTN_COMPOSED", "0", "attn_f32"),    # f32 attention stays on the warp-per-query kernel
+    ("MIMK_GEMM_2CTA", "0", "gemm_bf16"),       # bf16 contraction on the one-CTA kernel only
+    ("MIMK_GEMM_2CTA", "2", "gemm_bf16"),       # ... and on the paired kernel whenever it can run
+    ("MIMK_F32_TC", "0", "gemm_f32"),           # f32 contraction on the CUDA cores
+    ("MIMK_MRP_ROUTE", "0", "mrp"),             # every map_reduce_post instance on the per-cell kernel
+]
+
+
+@pytest.mark.parametrize("var,value,what", CASES)
+def test_alternative_kernel_behind_a_switch(var, value, what):
+    env = dict(os.environ)
+    env[var] = value
+    env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+    r = subprocess.run([sys.executable, "-c", SCRIPT, what], cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and f"switch ok {what}" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
