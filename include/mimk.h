@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define MIMK_ABI_VERSION 1
+#define MIMK_ABI_VERSION 2 /* 2: mimk_affine_map carries per-result floordiv / rem (div, mod) */
 
 /* ---- element types (math.F32 / math.BF16, src/mim/plug/math/math.mim:26,34; I32/I64 of the core plugin) ---- */
 enum { MIMK_F32 = 0, MIMK_BF16 = 1, MIMK_I32 = 2, MIMK_I64 = 3 };
@@ -265,8 +265,14 @@ int mimk_mlp_gated(const mimk_mlp_desc* desc, void* stream);
  * types. One thread per output cell walks its reduction, like the kernel gpu::phase::LowerMapReduce::build_kernel
  * generates (src/mim/plug/gpu/phase/lower_map_reduce.cpp:148-265), but with the access maps as data.
  * An access map is a matrix: result j = sum_l coef[j][l] * loop[l] + coef[j][n_loops], in wrap-around int64
- * (include/mim/plug/affine/phase/lower_index.h:14-20); buffers are row-major. Every access is bounds-checked on the
- * host against the loop bounds before launch (MIMK_E_SHAPE), so a wrong map never reads outside a buffer. */
+ * (include/mim/plug/affine/phase/lower_index.h:14-20), optionally followed per result by a floor division and a
+ * remainder -- result j = (linear_j floordiv div[j]) rem mod[j], each applied when > 0, unsigned like the reference's
+ * lowering of affine.semiop.floordiv / rem to core.div (lower_index.h:22-27). That is the form affine.delinearize takes
+ * (src/mim/plug/affine/affine.mim:103-108), hence `reshape_map` (src/mim/plug/tensor/tensor.mim:1224-1233), the unpack
+ * copy behind a packed dot_product (tensor.mim:1405-1411), and what fuse_read_through composes behind a consumer's map
+ * when it absorbs a reshape (src/mim/plug/tensor/phase/fuse.cpp:542-589). Buffers are row-major. Every access is
+ * bounds-checked on the host against the loop bounds before launch (MIMK_E_SHAPE), so a wrong map never reads outside a
+ * buffer; a map with div / mod must have a linear part that cannot go negative. */
 #define MIMK_MRP_MAX_LOOPS 8
 #define MIMK_MRP_MAX_RANK 6
 #define MIMK_MRP_MAX_INPUTS 4
@@ -291,6 +297,8 @@ typedef struct mimk_affine_map {
     int32_t rows; /* number of results (the rank of the tensor it indexes) */
     int32_t pad_;
     int64_t coef[MIMK_MRP_MAX_RANK][MIMK_MRP_MAX_LOOPS + 1];
+    int64_t div[MIMK_MRP_MAX_RANK]; /* > 0: the linear form of result j is floor-divided by it; 0: not */
+    int64_t mod[MIMK_MRP_MAX_RANK]; /* > 0: then reduced modulo it; 0: not */
 } mimk_affine_map;
 typedef struct mimk_mrp_desc {
     int32_t ro, rn;                   /* output loops, all loops (rn >= ro) */
@@ -320,9 +328,11 @@ int mimk_map_reduce_post(const mimk_mrp_desc* desc, void* stream);
  * (tensor.mim:361-394, 1162-1167) are handed to mimk_gemm, mimk_reduce and mimk_map. These fold in another order than
  * the ascending per-cell fold, which is why integer instances and instances with fewer than 2^20 combiner
  * applications always stay on the per-cell kernel. A copy that permutes axes (tensor.transpose, tensor.mim:1443-1468;
- * any element type, 2^20 elements or more) runs as a tiled copy through shared memory. MIMK_MRP_ROUTE=0 in the environment keeps every instance there.
+ * any element type, 2^20 elements or more) runs as a tiled copy through shared memory; a copy through `reshape_map`
+ * of a whole tensor (tensor.reshape, tensor.mim:1224-1241) moves no element and is one device-to-device copy, at any size.
+ * MIMK_MRP_ROUTE=0 in the environment keeps every instance on the per-cell kernel.
  * Pure host logic: needs no device. No counterpart in the reference, whose GPU lowering has the one kernel shape. */
-enum { MIMK_ROUTE_GENERIC = 0, MIMK_ROUTE_GEMM = 1, MIMK_ROUTE_REDUCE = 2, MIMK_ROUTE_MAP = 3, MIMK_ROUTE_PERMUTE = 4 };
+enum { MIMK_ROUTE_GENERIC = 0, MIMK_ROUTE_GEMM = 1, MIMK_ROUTE_REDUCE = 2, MIMK_ROUTE_MAP = 3, MIMK_ROUTE_PERMUTE = 4, MIMK_ROUTE_COPY = 5 };
 int mimk_mrp_classify(const mimk_mrp_desc* desc);
 
 /* ---- matrix-chain association ------------------------------------------------------------------------------

@@ -79,7 +79,8 @@ P_ID, P_ADD, P_ADD_PLUS1, P_ADD_RELU, P_ADD_TANH, P_RELU, P_SILU = range(7)
 
 
 class AffineMap(C.Structure):
-    _fields_ = [("rows", C.c_int32), ("pad_", C.c_int32), ("coef", (C.c_int64 * (MRP_MAX_LOOPS + 1)) * MRP_MAX_RANK)]
+    _fields_ = [("rows", C.c_int32), ("pad_", C.c_int32), ("coef", (C.c_int64 * (MRP_MAX_LOOPS + 1)) * MRP_MAX_RANK),
+                ("div", C.c_int64 * MRP_MAX_RANK), ("mod", C.c_int64 * MRP_MAX_RANK)]
 
 
 class MrpDesc(C.Structure):

@@ -102,6 +102,8 @@ __device__ __forceinline__ long long map_offset(const mimk_affine_map& m, int n,
     for (int j = 0; j < m.rows; ++j) {
         unsigned long long v = (unsigned long long)m.coef[j][n];
         for (int l = 0; l < n; ++l) v += (unsigned long long)m.coef[j][l] * (unsigned long long)loop[l];
+        if (m.div[j] > 0) v /= (unsigned long long)m.div[j];  // affine.semiop.floordiv, then rem: the shape of delinearize
+        if (m.mod[j] > 0) v %= (unsigned long long)m.mod[j];
         off = off * (unsigned long long)shape[j] + v;
     }
     return (long long)off;
@@ -136,6 +138,8 @@ __global__ void __launch_bounds__(256) mrp_generic_kernel(const __grid_constant_
         for (int j = 0; j < d.ro; ++j) {
             unsigned long long v = (unsigned long long)d.map_out.coef[j][d.rn];
             for (int l = 0; l < d.rn; ++l) v += (unsigned long long)d.map_out.coef[j][l] * (unsigned long long)loop[l];
+            if (d.map_out.div[j] > 0) v /= (unsigned long long)d.map_out.div[j];
+            if (d.map_out.mod[j] > 0) v %= (unsigned long long)d.map_out.mod[j];
             wc[j] = (long long)v;
         }
         Val p0;
@@ -147,7 +151,8 @@ __global__ void __launch_bounds__(256) mrp_generic_kernel(const __grid_constant_
     }
 }
 
-// Range of an affine form over the box 0 <= loop[l] < bound[l]: every result coordinate must stay in [0, extent).
+// Range of an access map over the box 0 <= loop[l] < bound[l]: every result coordinate must stay in [0, extent). The
+// linear form is bounded first, then the floordiv / rem are applied to the bounds.
 bool map_in_range(const mimk_affine_map& m, int n, const int64_t* bounds, const int64_t* shape) {
     for (int j = 0; j < m.rows; ++j) {
         __int128 lo = m.coef[j][n], hi = m.coef[j][n];
@@ -155,6 +160,17 @@ bool map_in_range(const mimk_affine_map& m, int n, const int64_t* bounds, const 
             const __int128 c = m.coef[j][l];
             const __int128 span = c * (__int128)(bounds[l] - 1);
             if (span < 0) lo += span; else hi += span;
+        }
+        if (m.div[j] < 0 || m.mod[j] < 0) return false;
+        if (m.div[j] > 0 || m.mod[j] > 0) {
+            // the division is unsigned: a linear part that can go negative would wrap to a huge index
+            if (lo < 0) return false;
+            if (m.div[j] > 0) lo /= m.div[j], hi /= m.div[j];
+            if (m.mod[j] > 0) {
+                // inside one period the remainder keeps the interval; across a period boundary it covers [0, mod)
+                if (lo / m.mod[j] == hi / m.mod[j]) lo %= m.mod[j], hi %= m.mod[j];
+                else lo = 0, hi = m.mod[j] - 1;
+            }
         }
         if (lo < 0 || hi >= (__int128)shape[j]) return false;
     }

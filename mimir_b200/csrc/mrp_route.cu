@@ -24,7 +24,7 @@ namespace {
 bool row_is_loop(const mimk_affine_map& m, int j, int n, int l) {
     for (int c = 0; c < n; ++c)
         if (m.coef[j][c] != (c == l ? 1 : 0)) return false;
-    return m.coef[j][n] == 0;
+    return m.coef[j][n] == 0 && m.div[j] <= 0 && m.mod[j] <= 0;
 }
 
 // The write map stores output loop vector o at o, and the result has exactly the loop bounds as its shape.
@@ -219,6 +219,26 @@ bool plan_permute(const mimk_mrp_desc& d, Plan& p) {
     return p.perm[d.ro - 1] != d.ro - 1;  // the same fastest axis on both sides: the per-cell kernel is coalesced already
 }
 
+// A copy whose input map is `reshape_map` of the whole operand -- delinearize(linearize(o, s_out), s_in), tensor.mim:1224-1233
+// -- reads element i of the flat input into element i of the flat output: no element moves.
+bool plan_reshape(const mimk_mrp_desc& d) {
+    if (d.comb != MIMK_F_FIRST || d.post != MIMK_P_ID || d.nis != 1 || d.nps != 0 || d.rn != d.ro || d.ro < 1) return false;
+    if (d.in_dtype[0] != d.out_dtype || !out_is_identity(d)) return false;
+    const mimk_affine_map& m = d.in_map[0];
+    if (m.rows < 1 || prod(d.in_shape[0], 0, m.rows) != prod(d.so, 0, d.ro)) return false;
+    for (int j = 0; j < m.rows; ++j) {
+        // linearize(o, s_out): the row-major strides of the result's shape, no constant
+        for (int l = 0; l < d.ro; ++l)
+            if (m.coef[j][l] != prod(d.so, l + 1, d.ro)) return false;
+        if (m.coef[j][d.rn] != 0) return false;
+        // delinearize(., s_in)#j = (lin floordiv stride_j) rem s_in#j; a division by 1 and the outermost rem may be left out
+        const int64_t stride = prod(d.in_shape[0], j + 1, m.rows);
+        if (!(m.div[j] == stride || (stride == 1 && m.div[j] <= 0))) return false;
+        if (!(m.mod[j] == d.in_shape[0][j] || (j == 0 && m.mod[j] <= 0))) return false;
+    }
+    return true;
+}
+
 // Below this many combiner applications the per-cell kernel is kept: it is launch-bound there anyway, and it keeps
 // the ascending fold of the classic nest bit for bit.
 constexpr long long ROUTE_MIN_WORK = 1ll << 20;
@@ -233,6 +253,10 @@ Plan make_plan(const mimk_mrp_desc& d) {
     for (int l = 0; l < d.rn; ++l) {
         if (d.sr[l] <= 0) return p;
         work *= (long double)d.sr[l];
+    }
+    if (plan_reshape(d)) {  // bits only, the same at any size
+        p.route = MIMK_ROUTE_COPY;
+        return p;
     }
     if (work < (long double)ROUTE_MIN_WORK) return p;
     if (plan_gemm(d, p)) p.route = MIMK_ROUTE_GEMM;
@@ -265,6 +289,12 @@ bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status) {
         case MIMK_ROUTE_PERMUTE: {
             const int esize = d.out_dtype == MIMK_BF16 ? 2 : d.out_dtype == MIMK_I64 ? 8 : 4;
             *status = permute_copy(d.in[0], d.out, esize, d.ro, d.sr, p.perm, static_cast<cudaStream_t>(stream));
+            return true;
+        }
+        case MIMK_ROUTE_COPY: {
+            const size_t esize = d.out_dtype == MIMK_BF16 ? 2 : d.out_dtype == MIMK_I64 ? 8 : 4;
+            *status = note_cuda_error(cudaMemcpyAsync(d.out, d.in[0], size_t(prod(d.so, 0, d.ro)) * esize, cudaMemcpyDeviceToDevice,
+                                                      static_cast<cudaStream_t>(stream)));
             return true;
         }
         default: return false;

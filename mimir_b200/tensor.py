@@ -299,6 +299,44 @@ def id_map(n: int):
     return proj_map(n, range(n))
 
 
+class AccessMap(list):
+    """An access map with, per result, an optional floordiv and rem behind the linear form: result j =
+    (row_j . (loops, 1)) floordiv div[j] rem mod[j] (each applied when > 0) -- the shape affine.delinearize has
+    (affine.mim:103-108). A plain list of coefficient rows is a map without either."""
+
+    def __init__(self, rows, div=None, mod=None):
+        super().__init__([list(r) for r in rows])
+        self.div = [int(v) for v in (div if div is not None else [0] * len(self))]
+        self.mod = [int(v) for v in (mod if mod is not None else [0] * len(self))]
+        if len(self.div) != len(self) or len(self.mod) != len(self):
+            raise ValueError("div / mod need one entry per result")
+
+
+def reshape_map(s_in, s_out) -> AccessMap:
+    """`reshape_map (s_in, s_out)`: o -> delinearize(linearize(o, s_out), s_in), the row-major output-to-input index
+    map (tensor.mim:1224-1233)."""
+    s_in, s_out = [int(v) for v in s_in], [int(v) for v in s_out]
+    if math.prod(s_in) != math.prod(s_out):
+        raise ValueError("reshape_map: element counts differ")
+    lin = [math.prod(s_out[l + 1:]) for l in range(len(s_out))] + [0]
+    return AccessMap([lin for _ in s_in], div=[math.prod(s_in[j + 1:]) for j in range(len(s_in))], mod=s_in)
+
+
+def compose_reshape(consumer_map, n_loops: int, s_view, s_in) -> AccessMap:
+    """What fuse_read_through leaves when a consumer reads a reshape of `s_in` to `s_view` through `consumer_map` (over
+    n_loops loop variables, one result per axis of the view): the consumer's coordinates are linearised over the view's
+    shape and delinearised over the stored shape (fuse.cpp:542-589 with reshape_map, tensor.mim:1224-1233)."""
+    s_view, s_in = [int(v) for v in s_view], [int(v) for v in s_in]
+    if getattr(consumer_map, "div", None) and (any(consumer_map.div) or any(consumer_map.mod)):
+        raise ValueError("compose_reshape: the consumer's map must be affine")
+    lin = [0] * (n_loops + 1)
+    for j, row in enumerate(consumer_map):
+        stride = math.prod(s_view[j + 1:])
+        for l in range(n_loops + 1):
+            lin[l] += stride * int(row[l])
+    return AccessMap([lin for _ in s_in], div=[math.prod(s_in[j + 1:]) for j in range(len(s_in))], mod=s_in)
+
+
 def _fill_map(dst, m, n_loops):
     rows = len(m)
     if rows > L.MRP_MAX_RANK:
@@ -311,6 +349,8 @@ def _fill_map(dst, m, n_loops):
         for l in range(n_loops):
             dst.coef[j][l] = row[l]
         dst.coef[j][n_loops] = row[n_loops]
+        dst.div[j] = getattr(m, "div", None)[j] if getattr(m, "div", None) else 0
+        dst.mod[j] = getattr(m, "mod", None)[j] if getattr(m, "mod", None) else 0
 
 
 def _mrp_desc(So, Sr, f, init, post, map_out, maps, in_meta, post_maps, post_meta, acc_dtype, out_dtype, out_ptr):
@@ -356,7 +396,7 @@ def _mrp_desc(So, Sr, f, init, post, map_out, maps, in_meta, post_maps, post_met
     return d
 
 
-ROUTES = {0: "generic", 1: "gemm", 2: "reduce", 3: "map", 4: "permute"}
+ROUTES = {0: "generic", 1: "gemm", 2: "reduce", 3: "map", 4: "permute", 5: "copy"}
 
 
 def mrp_route(So, Sr, f: int, init, post: int, map_out, maps, in_shapes, in_dtypes, post_maps=(), post_shapes=(),

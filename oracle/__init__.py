@@ -143,9 +143,43 @@ def id_map(n: int) -> np.ndarray:
     return proj_map(n, range(n))
 
 
+class DivModMap:
+    """An access map with a floordiv and a rem per result behind the linear form: result j =
+    (matrix[j] . (loops, 1)) floordiv div[j] rem mod[j], each applied when > 0 (affine.semiop.floordiv / rem; the form
+    affine.delinearize has, affine.mim:103-108). Accepted wherever a plain coefficient matrix is."""
+
+    def __init__(self, matrix, div, mod):
+        self.matrix = np.asarray(matrix, dtype=np.int64)
+        self.div, self.mod = [int(v) for v in div], [int(v) for v in mod]
+        assert len(self.div) == len(self.mod) == self.matrix.shape[0]
+
+
+def reshape_map(s_in, s_out) -> DivModMap:
+    """`reshape_map (s_in, s_out)`: o -> delinearize(linearize(o, s_out), s_in) (tensor.mim:1224-1233)."""
+    s_in, s_out = [int(v) for v in s_in], [int(v) for v in s_out]
+    lin = [int(np.prod(s_out[l + 1:], dtype=np.int64)) for l in range(len(s_out))] + [0]
+    return DivModMap([lin for _ in s_in], [int(np.prod(s_in[j + 1:], dtype=np.int64)) for j in range(len(s_in))], s_in)
+
+
+def _split_maps(maps):
+    """(plain matrices, flattened (div, mod) pairs or None)"""
+    mats = [m.matrix if isinstance(m, DivModMap) else np.asarray(m, dtype=np.int64) for m in maps]
+    if not any(isinstance(m, DivModMap) for m in maps):
+        return mats, None
+    dm = []
+    for m, mat in zip(maps, mats):
+        for j in range(mat.shape[0]):
+            dm += [m.div[j], m.mod[j]] if isinstance(m, DivModMap) else [0, 0]
+    return mats, _i64(dm)
+
+
 def map_reduce_post(So, Sr, f, init, post, map_out, maps, ins, post_maps=(), post_ins=(), out_dtype=None,
-                    in_dtypes=None, post_dtypes=None) -> np.ndarray:
-    """The one real op (tensor.mim:159-169).  `init` is a numpy scalar of the accumulator type."""
+                    in_dtypes=None, post_dtypes=None, dst=None) -> np.ndarray:
+    """The one real op (tensor.mim:159-169).  `init` is a numpy scalar of the accumulator type. Maps are coefficient
+    matrices or DivModMap objects."""
+    maps, in_dm = _split_maps(list(maps))
+    post_maps, p_dm = _split_maps(list(post_maps))
+    (map_out,), out_dm = _split_maps([map_out])
     So, Sr = [int(s) for s in So], [int(s) for s in Sr]
     Ro, Rn = len(So), len(Sr)
     ins = [np.ascontiguousarray(a) for a in ins]
@@ -157,7 +191,9 @@ def map_reduce_post(So, Sr, f, init, post, map_out, maps, ins, post_maps=(), pos
     if out_dtype is None:
         out_dtype = acc_dt
     init_bits = int(np.frombuffer(init.tobytes().ljust(8, b"\0"), dtype=np.int64)[0])
-    out = np.zeros(So if So else (), dtype=_DT2NP[out_dtype])
+    # destination passing, as btensor.map_reduce does (btensor.mim:102-115): cells the write map never stores keep
+    # what `dst` held (zeros without one)
+    out = np.zeros(So if So else (), dtype=_DT2NP[out_dtype]) if dst is None else np.array(dst, dtype=_DT2NP[out_dtype], copy=True).reshape(So)
 
     def pack(arrs, mps, n):
         ranks = np.asarray([a.ndim for a in arrs], dtype=np.int32)
@@ -178,7 +214,9 @@ def map_reduce_post(So, Sr, f, init, post, map_out, maps, ins, post_maps=(), pos
         C.c_int(Ro), C.c_int(Rn), _p(_i64(Sr + [0])), _p(_i64(So + [0])),
         C.c_int(len(ins)), iptr, _p(idt), _p(ir), _p(ish), _p(imp),
         C.c_int(len(post_ins)), pptr, _p(pdt), _p(pr), _p(psh), _p(pmp),
-        _p(mo), C.c_int(f), C.c_int64(init_bits), C.c_int(post), C.c_int(out_dtype), _p(out))
+        _p(mo), C.c_int(f), C.c_int64(init_bits), C.c_int(post), C.c_int(out_dtype), _p(out),
+        _p(in_dm) if in_dm is not None else None, _p(p_dm) if p_dm is not None else None,
+        _p(out_dm) if out_dm is not None else None)
     if rc != 0:
         raise ValueError(f"map_reduce_post: access outside a buffer or bad ranks (code {rc})")
     return out

@@ -197,31 +197,52 @@ MO_API int mo_map_reduce_post(int Ro, int Rn, const int64_t* Sr, const int64_t* 
                        const int64_t* in_shapes, const int64_t* in_maps,                            //
                        int nps, const void* const* pins, const int* p_dt, const int* p_rank,        //
                        const int64_t* p_shapes, const int64_t* p_maps,                              //
-                       const int64_t* map_out, int comb_id, int64_t init_bits, int post_id, int out_dt, void* out) {
+                       const int64_t* map_out, int comb_id, int64_t init_bits, int post_id, int out_dt, void* out,
+                       // optional floordiv / rem per map result, (div, mod) pairs in the order of the maps' results; NULL = none
+                       const int64_t* in_divmod, const int64_t* p_divmod, const int64_t* out_divmod) {
     if (Ro < 0 || Rn < Ro || Rn > 16 || nis > 8 || nps > 8) return -1;
     std::vector<Map> maps(nis), pmaps(nps);
+    std::vector<int64_t> divs, mods, pdivs, pmods;
     std::vector<const int64_t*> ishape(nis), pshape(nps);
     std::vector<int64_t> isize(nis), psize(nps);
     {
-        const int64_t *s = in_shapes, *m = in_maps;
+        // (div, mod) pairs are unzipped into one array of divs and one of mods per map
+        const int64_t *s = in_shapes, *m = in_maps, *dm = in_divmod;
         for (int i = 0; i < nis; ++i) {
             ishape[i] = s;
             maps[i]   = Map{in_rank[i], m, nullptr, nullptr};
+            if (dm) {
+                for (int j = 0; j < in_rank[i]; ++j) divs.push_back(dm[2 * j]), mods.push_back(dm[2 * j + 1]);
+                dm += 2 * in_rank[i];
+            }
             isize[i]  = 1;
             for (int j = 0; j < in_rank[i]; ++j) isize[i] *= s[j];
             s += in_rank[i];
             m += int64_t(in_rank[i]) * (Rn + 1);
         }
-        s = p_shapes, m = p_maps;
+        s = p_shapes, m = p_maps, dm = p_divmod;
         for (int j = 0; j < nps; ++j) {
             pshape[j] = s;
             pmaps[j]  = Map{p_rank[j], m, nullptr, nullptr};
+            if (dm) {
+                for (int k = 0; k < p_rank[j]; ++k) pdivs.push_back(dm[2 * k]), pmods.push_back(dm[2 * k + 1]);
+                dm += 2 * p_rank[j];
+            }
             psize[j]  = 1;
             for (int k = 0; k < p_rank[j]; ++k) psize[j] *= s[k];
             s += p_rank[j];
             m += int64_t(p_rank[j]) * (Ro + 1);
         }
     }
+    // the vectors are complete now: hand each map its slice
+    {
+        size_t at = 0;
+        for (int i = 0; i < nis && in_divmod; ++i) maps[i].divs = divs.data() + at, maps[i].mods = mods.data() + at, at += size_t(in_rank[i]);
+        at = 0;
+        for (int j = 0; j < nps && p_divmod; ++j) pmaps[j].divs = pdivs.data() + at, pmaps[j].mods = pmods.data() + at, at += size_t(p_rank[j]);
+    }
+    std::vector<int64_t> odivs, omods;
+    for (int j = 0; j < Ro && out_divmod; ++j) odivs.push_back(out_divmod[2 * j]), omods.push_back(out_divmod[2 * j + 1]);
     Map mout{Ro, map_out, nullptr, nullptr};
     int64_t osize = 1;
     for (int j = 0; j < Ro; ++j) osize *= So[j];
@@ -266,6 +287,8 @@ MO_API int mo_map_reduce_post(int Ro, int Rn, const int64_t* Sr, const int64_t* 
                 const int64_t* c = map_out + int64_t(j) * (Rn + 1);
                 uint64_t v       = uint64_t(c[Rn]);
                 for (int l = 0; l < Rn; ++l) v += uint64_t(c[l]) * uint64_t(loop[l]);
+                if (!odivs.empty() && odivs[j] > 0) v /= uint64_t(odivs[j]);
+                if (!omods.empty() && omods[j] > 0) v %= uint64_t(omods[j]);
                 wc[j] = int64_t(v);
             }
         }
@@ -275,7 +298,9 @@ MO_API int mo_map_reduce_post(int Ro, int Rn, const int64_t* Sr, const int64_t* 
             pin[j] = load_val(pins[j], p_dt[j], off);
         }
         Val res      = post(post_id, acc, pin);
-        int64_t woff = linear_offset(mout, Rn, loop, So);
+        (void)mout;
+        int64_t woff = 0;  // row-major offset of the write coordinates (mem.h:36-42)
+        for (int j = 0; j < Ro; ++j) woff = int64_t(uint64_t(woff) * uint64_t(So[j]) + uint64_t(wc[j]));
         if (woff < 0 || woff >= osize) return -4;
         store_val(out, out_dt, woff, res);
     }

@@ -35,7 +35,7 @@ def test_header_symbols_are_exported(lib):
 
 def test_abi_version_and_status_strings(lib):
     L = lib.lib()
-    assert L.mimk_abi_version() == 1
+    assert L.mimk_abi_version() == 2
     assert L.mimk_status_str(0) == b"ok"
     for code in range(1, 10):
         s = L.mimk_status_str(code)

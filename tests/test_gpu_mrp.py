@@ -278,3 +278,86 @@ def test_bf16_descriptors_reach_the_fold_and_map_kernels(T, L):
     m = T.map_reduce_post((1024, 2048), (1024, 2048), L.F_MUL2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [x, y],
                           out_dtype=torch.bfloat16)
     assert torch.equal(m, (x.float() * y.float()).to(torch.bfloat16))
+
+
+def test_remaining_buffer_known_answers(T, L):
+    """lit/buffer/exec_strip (24), exec_unroll (111), exec_size1 (42), exec_pad_concat (42), exec_get_set (50),
+    exec_local_tensors (42), two_same_shape_binary / _set (42) and lit/btensor/read_transpose (5), through the C ABI."""
+    ones = cu(np.ones((2, 8, 3), np.int32))
+    mi = [[1, 0, 0, 0, 0], [0, 4, 1, 0, 0], [0, 0, 0, 1, 0]]       # the 8-loop strip-mined by 4: (i, 4 jo + ji, k)
+    out = T.map_reduce_post((2,), (2, 2, 4, 3), L.F_ADD, 0, L.P_ID, T.proj_map(4, (0,)), [mi], [ones])
+    assert out.tolist() == [24, 24]
+    out = T.map_reduce_post((2,), (2, 37, 3), L.F_ADD, 0, L.P_ID, T.proj_map(3, (0,)), [T.id_map(3)], [cu(np.ones((2, 37, 3), np.int32))])
+    assert int(out[1]) == 111
+    a, b = cu(np.array([[7, 8, 9]], np.int32)), cu(np.array([[10, 20, 30], [4, 5, 6]], np.int32))
+    p, c = T.pad(a, (0, 1), (0, 1), 5), T.concat(0, [a, b])
+    assert p.tolist() == [[5, 7, 8, 9, 5]] and int(c[1, 2]) + int(p[0, 1]) + int(p[0, 0]) == 42
+    t, u = cu(np.array([10, 20, 30], np.int32)), cu(np.array([1, 2], np.int32))
+    p, c = T.pad(t, (1,), (2,), 5), T.concat(0, [t, u])
+    assert p.tolist() == [5, 10, 20, 30, 5, 5] and int(p[3]) + int(c[4]) + int(c[0]) == 42
+    t = cu((np.arange(12, dtype=np.int32) + 1).reshape(3, 4))
+    s = T.set_(t, (0, 0), 42)
+    assert T.get(s, (0, 0)) + T.get(s, (1, 2)) + T.get(t, (0, 0)) == 50
+    m = cu(np.array([[10, 20], [30, 40]], np.int32))
+    s, bc = T.set_(m, (1, 1), 2), T.broadcast(cu(np.array([[5, 7]], np.int32)), (2, 2))
+    assert T.get(s, (1, 1)) + T.get(s, (1, 0)) + T.get(bc, (1, 0)) + T.get(bc, (0, 0)) == 42
+    x = np.array([[10, 1, 2, 3], [4, 5, 30, 7], [8, 9, 10, 11]], np.int32)
+    y = np.array([[5, 1, 1, 1], [1, 1, 3, 1], [1, 1, 1, 1]], np.int32)
+    add = T.map_reduce_post((3, 4), (3, 4), L.F_ADD2, 0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [cu(x), cu(y)])
+    sub = T.map_reduce_post((3, 4), (3, 4), L.F_ADD2, 0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [cu(x), cu(-y)])
+    c = T.concat(0, [add, sub])
+    assert int(c[0, 0]) + int(c[4, 2]) == 42
+    t = cu(np.array([[12, 2, 3, 4], [5, 6, 30, 8], [9, 10, 11, 12]], np.int32))
+    assert T.get(T.set_(t, (0, 0), 2), (1, 2)) + T.get(T.set_(t, (1, 2), 40), (0, 0)) == 42
+    d = T.map_reduce_post((4, 2), (4, 2), L.F_FIRST, 0, L.P_ID, T.id_map(2), [T.proj_map(2, (1, 0))], [cu(np.full((2, 4), 5, np.int32))])
+    assert int(d[3, 1]) == 5
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64, np.float32])
+def test_maps_with_floordiv_and_rem(T, L, dtype):
+    """reshape_map (tensor.mim:1224-1233) as an input map, bit for bit against the oracle's interpreter: the plain
+    reshape (which the library recognises and runs as one copy), the unpack of a packed shape (tensor.mim:1405-1411),
+    and a fold that reads a reshape through a composed map (what fuse_read_through leaves, fuse.cpp:542-589)."""
+    rng = np.random.default_rng(3)
+    x = rng.integers(-1000, 1000, (3, 4, 5)).astype(dtype)
+    f_first, f_add = (L.F_FIRST, L.F_ADD)
+    o_first = mo.F_FIRST_F32 if dtype == np.float32 else mo.F_FIRST_I32
+    init = 0.0 if dtype == np.float32 else 0
+    for s_out in [(10, 6), (60,), (2, 2, 15), (5, 4, 3)]:
+        r = len(s_out)
+        got = T.map_reduce_post(s_out, s_out, f_first, init, L.P_ID, T.id_map(r), [T.reshape_map((3, 4, 5), s_out)], [cu(x)])
+        assert np.array_equal(got.cpu().numpy(), x.reshape(s_out))
+        assert T.mrp_route(s_out, s_out, f_first, init, L.P_ID, T.id_map(r), [T.reshape_map((3, 4, 5), s_out)], [(3, 4, 5)],
+                           [torch.from_numpy(x).dtype], acc_dtype=torch.from_numpy(x).dtype if dtype != np.float32 else torch.float32,
+                           out_dtype=torch.from_numpy(x).dtype) == "copy"
+    # a strided slice of the reshaped view is not a whole-tensor reshape: the per-cell kernel evaluates the map
+    view = T.compose_reshape([[2, 0, 1], [0, 1, 0]], 2, (10, 6), (3, 4, 5))           # view[2 o0 + 1, o1]
+    got = T.map_reduce_post((4, 6), (4, 6), f_first, init, L.P_ID, T.id_map(2), [view], [cu(x)])
+    assert np.array_equal(got.cpu().numpy(), x.reshape(10, 6)[1:9:2])
+    if dtype != np.float32:
+        # row sums of a (6, 10) view of the stored (3, 4, 5): the consumer's (o, r) composed behind the reshape
+        comp = T.compose_reshape(T.id_map(2), 2, (6, 10), (3, 4, 5))
+        got = T.map_reduce_post((6,), (6, 10), f_add, 0, L.P_ID, T.proj_map(2, (0,)), [comp], [cu(x)])
+        lin = [10, 1, 0]
+        want = mo.map_reduce_post((6,), (6, 10), mo.F_ADD_I32 if dtype == np.int32 else mo.F_ADD_I32, dtype(0), mo.P_ID, mo.proj_map(2, (0,)),
+                                  [mo.DivModMap([lin, lin, lin], [20, 5, 1], [3, 4, 5])], [x.astype(np.int32)])
+        assert np.array_equal(got.cpu().numpy().astype(np.int64), want.astype(np.int64))
+    # a map whose floordiv / rem could leave the operand is refused before any launch
+    bad = T.AccessMap([[1, 0]], div=[1], mod=[0])
+    with pytest.raises(Exception):
+        T.map_reduce_post((70,), (70,), f_first, init, L.P_ID, T.id_map(1), [bad], [cu(x.reshape(60))])
+    neg = T.AccessMap([[1, -3]], div=[2], mod=[0])                                     # linear part can go negative
+    with pytest.raises(Exception):
+        T.map_reduce_post((10,), (10,), f_first, init, L.P_ID, T.id_map(1), [neg], [cu(x.reshape(60))])
+
+
+def test_large_reshape_read_through_at_scale(T, L):
+    """A fold reading a reshape through a composed floordiv / rem map at a size where every thread's index arithmetic
+    matters: column sums of a (4096, 600) view of a tensor stored (600, 64, 64), against numpy (f32 sums of small
+    integers are exact)."""
+    rng = np.random.default_rng(4)
+    x = rng.integers(-3, 4, (600, 64, 64)).astype(np.float32)
+    comp = T.compose_reshape(T.proj_map(2, (1, 0)), 2, (4096, 600), (600, 64, 64))       # view[r, o]: fold over the rows
+    got = T.map_reduce_post((600,), (600, 4096), L.F_ADD, 0.0, L.P_ID, T.proj_map(2, (0,)), [comp], [cu(x)])
+    T.device_status()
+    assert np.array_equal(got.cpu().numpy(), x.reshape(4096, 600).sum(0))

@@ -112,3 +112,27 @@ def test_bf16_folds_and_maps_are_recognised_too(TL):
     assert T.mrp_route(big, big, L.F_ADD2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [big, big], [BF16, BF16],
                        out_dtype=BF16) == "map"
     assert T.mrp_route(big, big, L.F_ADD2, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [big, big], [BF16, F32]) == "generic"
+
+
+def test_reshape_maps_are_recognised_and_floordiv_maps_disqualify_the_rest(TL):
+    T, L = TL
+    # reshape_map of the whole operand (tensor.mim:1224-1233): one copy, at any size and for any element type
+    for s_in, s_out in [((3, 4, 5), (10, 6)), ((3, 4, 5), (60,)), ((60,), (3, 4, 5)), ((2048, 512), (1024, 1024))]:
+        r = len(s_out)
+        for dt in (F32, I32):
+            assert T.mrp_route(s_out, s_out, L.F_FIRST, 0.0 if dt == F32 else 0, L.P_ID, T.id_map(r), [T.reshape_map(s_in, s_out)],
+                               [s_in], [dt], acc_dtype=dt, out_dtype=dt) == "copy"
+    # the division by the innermost stride (1) and the outermost rem may be left out: still a reshape
+    m = T.reshape_map((3, 4, 5), (10, 6))
+    m.div[2], m.mod[0] = 0, 0
+    assert T.mrp_route((10, 6), (10, 6), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [m], [(3, 4, 5)], [F32]) == "copy"
+    # anything else with a floordiv / rem stays on the per-cell kernel: another rem, a fold through a reshape, a contraction
+    m = T.reshape_map((3, 4, 5), (10, 6))
+    m.mod[1] = 2
+    assert T.mrp_route((10, 6), (10, 6), L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [m], [(3, 4, 5)], [F32]) == "generic"
+    big = (2048, 4096)
+    comp = T.compose_reshape(T.id_map(2), 2, big, (4096, 2048))
+    assert T.mrp_route((2048,), big, L.F_ADD, 0.0, L.P_ID, T.proj_map(2, [0]), [comp], [(4096, 2048)], [F32]) == "generic"
+    a_map = T.AccessMap(T.proj_map(3, (0, 2)), div=[0, 0], mod=[0, 1024])
+    assert T.mrp_route((1024, 1024), (1024, 1024, 1024), L.F_MULADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)),
+                       [a_map, T.proj_map(3, (2, 1))], [(1024, 1024), (1024, 1024)], [F32, F32]) == "generic"

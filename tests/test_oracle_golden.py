@@ -270,3 +270,173 @@ def test_gather_scatter_exec_93():
     assert g.tolist() == [[12, 10], [21, 21]]
     assert s.tolist() == [[20, 11, 10], [20, 40, 22]]
     assert int(g[0, 0]) + int(g[1, 0]) + int(s[0, 0]) + int(s[1, 1]) == 93
+
+
+# ------------------------------------------------------------------ the remaining integer known answers of lit/buffer and lit/btensor
+def _pad(x, lo, hi, value):
+    """tensor.pad, constant mode (tensor.mim:275-290): the result filled with `value`, the input copied in at offset lo."""
+    r = x.ndim
+    shape = [lo[d] + x.shape[d] + hi[d] for d in range(r)]
+    mo_ = np.zeros((r, r + 1), np.int64)
+    for d in range(r):
+        mo_[d, d], mo_[d, r] = 1, lo[d]
+    return mo.map_reduce_post(shape, x.shape, mo.F_FIRST_I32, np.int32(0), mo.P_ID, mo_, [mo.id_map(r)], [x],
+                              dst=np.full(shape, value, x.dtype))
+
+
+def _set(t, index, value):
+    s = t.copy()
+    s[index] = value                # tensor.set: a copy with one cell replaced (tensor.mim, `set`)
+    return s
+
+
+def test_exec_strip_24():
+    # lit/buffer/exec_strip.mim:16-29 -- ones (2, 8, 3) summed over the last two axes with the 8-loop strip-mined by 4:
+    # loops (i, jo, ji, k), input read at (i, 4 jo + ji, k); out[1] = 24
+    t = np.ones((2, 8, 3), np.int32)
+    mi = np.zeros((3, 5), np.int64); mi[0, 0] = 1; mi[1, 1] = 4; mi[1, 2] = 1; mi[2, 3] = 1
+    out = mo.map_reduce_post((2,), (2, 2, 4, 3), mo.F_ADD_I32, np.int32(0), mo.P_ID, mo.proj_map(4, (0,)), [mi], [t])
+    assert out.tolist() == [24, 24]
+
+
+def test_exec_unroll_111():
+    # lit/buffer/exec_unroll.mim:18-28 -- ones (2, 37, 3), an unroll schedule that changes no value; out[1] = 111
+    t = np.ones((2, 37, 3), np.int32)
+    out = mo.map_reduce_post((2,), (2, 37, 3), mo.F_ADD_I32, np.int32(0), mo.P_ID, mo.proj_map(3, (0,)), [mo.id_map(3)], [t])
+    assert int(out[1]) == 111
+
+
+def test_exec_size1_42_and_pad_concat_42():
+    # lit/buffer/exec_size1.mim:14-28 -- size-1 axes: pad (1,3) by one cell of 5 on either side of axis 1, concat along 0
+    a = np.array([[7, 8, 9]], np.int32)
+    b = np.array([[10, 20, 30], [4, 5, 6]], np.int32)
+    p = _pad(a, (0, 1), (0, 1), 5)
+    c = mo.concat(0, [a, b])
+    assert p.tolist() == [[5, 7, 8, 9, 5]]
+    assert int(c[1, 2]) + int(p[0, 1]) + int(p[0, 0]) == 42
+    # lit/buffer/exec_pad_concat.mim:13-27 -- rank 1: pad by (1, 2), concat of lengths 3 and 2
+    t, u = np.array([10, 20, 30], np.int32), np.array([1, 2], np.int32)
+    p = _pad(t, (1,), (2,), 5)
+    c = mo.concat(0, [t, u])
+    assert p.tolist() == [5, 10, 20, 30, 5, 5]
+    assert int(p[3]) + int(c[4]) + int(c[0]) == 42
+
+
+def test_exec_get_set_50_local_tensors_42_and_same_shape_42():
+    # lit/buffer/exec_get_set.mim:9-16
+    t = (np.arange(12, dtype=np.int32) + 1).reshape(3, 4)
+    s = _set(t, (0, 0), 42)
+    assert int(s[0, 0]) + int(s[1, 2]) + int(t[0, 0]) == 50
+    # lit/buffer/exec_local_tensors.mim:12-16 -- broadcast (1, 2) -> (2, 2) as a copy whose read map drops the unit axis
+    m = np.array([[10, 20], [30, 40]], np.int32)
+    s = _set(m, (1, 1), 2)
+    row = np.array([[5, 7]], np.int32)
+    bmap = np.zeros((2, 3), np.int64); bmap[1, 1] = 1
+    b = mo.map_reduce_post((2, 2), (2, 2), mo.F_FIRST_I32, np.int32(0), mo.P_ID, mo.id_map(2), [bmap], [row])
+    assert b.tolist() == [[5, 7], [5, 7]]
+    assert int(s[1, 1]) + int(s[1, 0]) + int(b[1, 0]) + int(b[0, 0]) == 42
+    # lit/buffer/two_same_shape_binary.mim:11-24 -- two maps of one shape, concatenated
+    x = np.array([[10, 1, 2, 3], [4, 5, 30, 7], [8, 9, 10, 11]], np.int32)
+    y = np.array([[5, 1, 1, 1], [1, 1, 3, 1], [1, 1, 1, 1]], np.int32)
+    c = mo.concat(0, [x + y, x - y])
+    assert int(c[0, 0]) + int(c[4, 2]) == 42
+    # lit/buffer/two_same_shape_set.mim:8-18 -- two sets of one tensor do not see each other
+    t = np.array([[12, 2, 3, 4], [5, 6, 30, 8], [9, 10, 11, 12]], np.int32)
+    a, b = _set(t, (0, 0), 2), _set(t, (1, 2), 40)
+    assert int(a[1, 2]) + int(b[0, 0]) == 42
+
+
+def test_btensor_read_transpose_5():
+    # lit/btensor/read_transpose.mim:12-24 -- a (2, 4) buffer of fives copied through proj_map (1, 0) into (4, 2); cell [3, 1]
+    m = np.full((2, 4), 5, np.int32)
+    d = mo.map_reduce_post((4, 2), (4, 2), mo.F_FIRST_I32, np.int32(0), mo.P_ID, mo.id_map(2), [mo.proj_map(2, (1, 0))], [m])
+    assert int(d[3, 1]) == 5 and d.shape == (4, 2)
+
+
+def test_reshape_map_and_packed_unpack():
+    """Access maps with floordiv / rem: `reshape_map` (tensor.mim:1224-1233) alone, the unpack copy behind a packed
+    dot_product (tensor.mim:1405-1411: the packed result of exec_tile reshaped... here through reshape_map of its packed
+    shape), and a consumer that reads a reshape through a composed map (fuse_read_through, fuse.cpp:542-589)."""
+    x = (np.arange(60, dtype=np.int32) * 7 - 100).reshape(3, 4, 5)
+    y = mo.map_reduce_post((10, 6), (10, 6), mo.F_FIRST_I32, np.int32(0), mo.P_ID, mo.id_map(2), [mo.reshape_map((3, 4, 5), (10, 6))], [x])
+    assert np.array_equal(y, x.reshape(10, 6))
+    # exec_tile's packed product C_packed[io, ii, jo, ji] (lit/buffer/exec_tile.mim:23-45): a reshape of the packed shape
+    # (2,2,2,2) to (4,4) is NOT the matrix (the packing interleaves jo and ii); reading it through the packing's own map is
+    a = np.repeat(np.arange(1, 5, dtype=np.int32)[:, None], 8, axis=1)
+    b = np.repeat(np.array([[1, 3, 5, 7]], dtype=np.int32), 8, axis=0)
+    ma = np.zeros((2, 7), np.int64); ma[0, 0] = 2; ma[0, 2] = 1; ma[1, 4] = 4; ma[1, 5] = 1
+    mb = np.zeros((2, 7), np.int64); mb[0, 4] = 4; mb[0, 5] = 1; mb[1, 1] = 2; mb[1, 3] = 1
+    packed = mo.map_reduce_post((2, 2, 2, 2), (2, 2, 2, 2, 2, 4), mo.F_MULADD_I32, np.int32(0), mo.P_ID,
+                                mo.proj_map(6, (0, 2, 1, 3)), [ma, mb], [a, b])
+    flat = mo.map_reduce_post((16,), (16,), mo.F_FIRST_I32, np.int32(0), mo.P_ID, mo.id_map(1), [mo.reshape_map((2, 2, 2, 2), (16,))], [packed])
+    assert np.array_equal(flat, packed.reshape(16))
+    # row sums of a (6, 10) VIEW of a tensor stored (3, 4, 5): the consumer's map (o, r) composed behind the reshape
+    lin = [10, 1, 0]
+    comp = mo.DivModMap([lin, lin, lin], [20, 5, 1], [3, 4, 5])
+    sums = mo.map_reduce_post((6,), (6, 10), mo.F_ADD_I32, np.int32(0), mo.P_ID, mo.proj_map(2, (0,)), [comp], [x])
+    assert np.array_equal(sums, x.reshape(6, 10).sum(1))
+
+
+# ------------------------------------------------------------------ the reference's training-step fixtures, through the oracle
+def test_hlo_train_fixture_through_the_interpreter():
+    """lit/tensor/hlo_train_aux.cpp:24-76 -- one training step of a one-layer tanh MLP (N=4, I=8, O=3) for the fixture's three
+    input patterns, every contraction and fold through the map_reduce_post interpreter (as lowered, f32), held to the
+    fixture's 1e-4 against its own scalar recipe in f64."""
+    N, I, O, lr, c = 4, 8, 3, 0.001, 0.5
+    for mode in range(3):
+        def make(n):
+            i = np.arange(n)
+            v = (i % 100) / np.float32(100.0) if mode == 0 else (np.full(n, 0.5) if mode == 1 else 0.01 * ((i % 7) + 1))
+            return v.astype(np.float32)
+        w, b, x, t = make(I * O).reshape(I, O), make(O), make(N * I).reshape(N, I), make(N * O).reshape(N, O)
+        z64 = x.astype(np.float64) @ w.astype(np.float64)
+        d64 = c * (np.tanh(z64 + b) - t)
+        ref = (w[0, 0] - lr * (x.T.astype(np.float64) @ d64)[0, 0]) + (b[0] - lr * d64.sum(0)[0]) + (d64 @ w.T.astype(np.float64))[0, 0] + z64[0].max()
+        z = mo.product_2d(x, w)
+        a = mo.product_2d(x, w, post=mo.P_BIAS_TANH_F32, post_in=b)
+        d = (np.float32(c) * (a - t)).astype(np.float32)
+        dW = mo.product_2d(mo.transpose_2d(x), d)                       # x^T d
+        dx = mo.product_2d(d, w, b_transposed=True)                     # d w^T: w read through transpose_2d
+        db = mo.reduce(d, 0)
+        got = (w[0, 0] - lr * dW[0, 0]) + (b[0] - lr * db[0]) + dx[0, 0] + mo.reduce(z, 1, "max")[0]
+        assert abs(float(got) - float(ref)) <= 1e-4, (mode, got, ref)
+
+
+def test_hlo_step_fixture_through_the_direct_loops():
+    """lit/tensor/hlo_step_aux.cpp:33-158 -- one SGD step of the tanh MLP 128/784/1024/10 (softmax-loss gradient, backward
+    contractions over transposed reads, column sums, the digest of six update deltas): the contractions and folds on the
+    oracle's as-lowered f32 loops, against the same program in f64; the fixture's bound (1e-2 of the digest's scale + 1e-6)."""
+    B, I, H, O, lr, c = 128, 784, 1024, 10, np.float32(0.001), np.float32(-0.0078125)
+
+    def pat(n, mod, mul, sub):
+        return (mul * ((np.arange(n) % mod).astype(np.float32) / np.float32(mod) - np.float32(sub))).astype(np.float32)
+    W1, W2, W3 = pat(I * H, 89, 0.05, 0.5).reshape(I, H), pat(H * H, 83, 0.05, 0.5).reshape(H, H), pat(H * O, 79, 0.1, 0.5).reshape(H, O)
+    b1 = (0.01 * ((np.arange(H) % 7).astype(np.float32) - 3.0)).astype(np.float32)
+    b2 = (0.01 * ((np.arange(H) % 5).astype(np.float32) - 2.0)).astype(np.float32)
+    b3 = (0.01 * ((np.arange(O) % 3).astype(np.float32) - 1.0)).astype(np.float32)
+    X = pat(B * I, 97, 0.05, 0.0).reshape(B, I)
+    Y = np.zeros((B, O), np.float32)
+    Y[np.arange(B), np.arange(B) % O] = 1.0
+
+    def step(mm, colsum, rowsum, rowmax, dt):
+        X_, Y_, W1_, W2_, W3_ = (a.astype(dt) for a in (X, Y, W1, W2, W3))
+        h1 = np.tanh(mm(X_, W1_) + b1.astype(dt))
+        h2 = np.tanh(mm(h1, W2_) + b2.astype(dt))
+        logits = mm(h2, W3_) + b3.astype(dt)
+        e = np.exp(logits - rowmax(logits)[:, None])
+        q = rowsum(Y_ * dt(-c)) / rowsum(e)
+        dlog = Y_ * dt(c) + e * q[:, None]
+        v59 = mm(dlog, W3_.T.copy())
+        v66 = mm(v59, W2_.T.copy()) * (1 - h1)
+        v68 = v66 + v66 * h1
+        return [mm(X_.T.copy(), v68)[3, 5], colsum(v68)[7], mm(h1.T.copy(), v59)[11, 13], colsum(v59)[17],
+                mm(h2.T.copy(), dlog)[19, 2], colsum(dlog)[3]]
+
+    ref = step(lambda a, b: a @ b, lambda m: m.sum(0), lambda m: m.sum(1), lambda m: m.max(1), np.float64)
+    got = step(lambda a, b: mo.gemm(a, b), lambda m: mo.reduce_axis(m, 0), lambda m: mo.reduce_axis(m, 1),
+               lambda m: mo.reduce_axis(m, 1, "max"), np.float32)
+    olds = [W1[3, 5], b1[7], W2[11, 13], b2[17], W3[19, 2], b3[3]]
+    delta = lambda old, g: float(np.float32(old) - (np.float32(old) - lr * np.float32(g)))
+    g_ref, g_got = [delta(o, g) for o, g in zip(olds, ref)], [delta(o, g) for o, g in zip(olds, got)]
+    scale = sum(abs(v) for v in g_ref)
+    assert abs(sum(g_got) - sum(g_ref)) <= 1e-2 * scale + 1e-6
