@@ -284,6 +284,10 @@ enum { /* combiners f(acc, ins) */
     MIMK_F_SUBEXP = 5,  /* exp(a - b)  */
     MIMK_F_DIV = 6, MIMK_F_ADD2 = 7, MIMK_F_MUL2 = 8, /* a / b, a + b, a * b (acc ignored): binary / binary_ax */
     MIMK_F_MIX = 9,     /* acc + a + (acc type)b         lit/btensor/map_reduce_post.mim:17-18 */
+    /* combiners with an injective producer inlined, as fuse_map_reduce leaves them (src/mim/plug/tensor/phase/fuse.cpp:183-358;
+       softmax after fusion, fuse.cpp:225-245): */
+    MIMK_F_ADD_SUBEXP = 10, /* acc + exp(a - b)              the sum fold of softmax with exp(x - max) inlined */
+    MIMK_F_SUBEXP_DIV = 11, /* exp(a - b) / c (acc ignored)  the divide with the exponential recomputed; three inputs */
 };
 enum { /* epilogues post(acc, post_ins) */
     MIMK_P_ID = 0,
@@ -334,6 +338,28 @@ int mimk_map_reduce_post(const mimk_mrp_desc* desc, void* stream);
  * Pure host logic: needs no device. No counterpart in the reference, whose GPU lowering has the one kernel shape. */
 enum { MIMK_ROUTE_GENERIC = 0, MIMK_ROUTE_GEMM = 1, MIMK_ROUTE_REDUCE = 2, MIMK_ROUTE_MAP = 3, MIMK_ROUTE_PERMUTE = 4, MIMK_ROUTE_COPY = 5 };
 int mimk_mrp_classify(const mimk_mrp_desc* desc);
+
+/* ---- programs: a list of map_reduce_post operations -----------------------------------------------------------
+ * `ops` are executed in order; an input (or epilogue input) whose pointer equals the `out` of an earlier operation reads
+ * that operation's result. Chains that spell a known composition run as ONE fused kernel instead of op by op:
+ *   softmax     max-fold, exp(x - max), sum-fold, divide along one axis (the `softmax` lam, tensor.mim:1172-1176), also in
+ *               the three-operation form fuse_tensor leaves (the exponential inlined into the sum fold and recomputed in
+ *               the divide, fuse.cpp:225-245)                                            -> mimk_softmax, one pass over x
+ *   attention   S = q k^T (k read through transpose_2d), softmax of S along its last axis, O = P v
+ *               (lit/tensor/attn_exec.mim:20-22), with or without a leading batch loop   -> mimk_attn_fwd, scale 1, no mask
+ * A chain is fused only when its temporaries (every result inside it but the last) feed nothing outside it in `ops`; they are
+ * then never written. Everything else runs through mimk_map_reduce_post. These are the recognisers the compiler-side lowering
+ * needs once it emits launcher calls per operation; no counterpart in the reference, whose GPU lowering handles one operation
+ * at a time (src/mim/plug/gpu/phase/lower_map_reduce.cpp:317-395).
+ * mimk_program_classify is pure host logic (needs no device): steps[i] says how operation i runs. */
+enum {
+    MIMK_STEP_OP = 0,        /* by itself, through mimk_map_reduce_post */
+    MIMK_STEP_SOFTMAX = 1,   /* first operation of a softmax chain: the chain runs as mimk_softmax */
+    MIMK_STEP_ATTENTION = 2, /* first operation of an attention chain: the chain runs as mimk_attn_fwd */
+    MIMK_STEP_ABSORBED = 3,  /* a later operation of a fused chain */
+};
+int mimk_program_classify(const mimk_mrp_desc* ops, int32_t n_ops, int32_t* steps);
+int mimk_program_run(const mimk_mrp_desc* ops, int32_t n_ops, void* stream);
 
 /* ---- matrix-chain association ------------------------------------------------------------------------------
  * In which order to multiply the chain A0 . A1 . ... . A(n-1), matrix i being dims[i] x dims[i+1]; transposed[i] != 0

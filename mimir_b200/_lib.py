@@ -24,7 +24,7 @@ ROWS_SOFTMAX, ROWS_RMSNORM, ROWS_SOFTMAX_RMSNORM = 0, 1, 2
 SYMBOLS = (
     "mimk_status_str", "mimk_abi_version", "mimk_last_cuda_error", "mimk_device_check", "mimk_device_status", "mimk_selftest_wait_expiry",
     "mimk_gemm", "mimk_gemm_flat", "mimk_gemm_gather", "mimk_gemm_kpanels", "mimk_reduce", "mimk_reduce_plan", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map", "mimk_map_t",
-    "mimk_splat", "mimk_select", "mimk_generate_affine", "mimk_gather", "mimk_scatter", "mimk_attn_fwd", "mimk_mlp_gated", "mimk_map_reduce_post", "mimk_mrp_classify", "mimk_chain_order", "mimk_chain_cost",
+    "mimk_splat", "mimk_select", "mimk_generate_affine", "mimk_gather", "mimk_scatter", "mimk_attn_fwd", "mimk_mlp_gated", "mimk_map_reduce_post", "mimk_mrp_classify", "mimk_program_classify", "mimk_program_run", "mimk_chain_order", "mimk_chain_cost",
     "mimk_host_rows", "mimk_host_rows_pair", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_map_reduce_post", "mimk_host_register",
     "mimk_host_unregister", "mimk_host_release",
 )
@@ -74,7 +74,8 @@ class MlpDesc(C.Structure):
 
 
 MRP_MAX_LOOPS, MRP_MAX_RANK, MRP_MAX_INPUTS = 8, 6, 4
-F_ADD, F_MULADD, F_MAX, F_MIN, F_FIRST, F_SUBEXP, F_DIV, F_ADD2, F_MUL2, F_MIX = range(10)
+F_ADD, F_MULADD, F_MAX, F_MIN, F_FIRST, F_SUBEXP, F_DIV, F_ADD2, F_MUL2, F_MIX, F_ADD_SUBEXP, F_SUBEXP_DIV = range(12)
+STEP_OP, STEP_SOFTMAX, STEP_ATTENTION, STEP_ABSORBED = range(4)
 P_ID, P_ADD, P_ADD_PLUS1, P_ADD_RELU, P_ADD_TANH, P_RELU, P_SILU = range(7)
 
 
@@ -128,6 +129,8 @@ def lib() -> C.CDLL:
         L.mimk_splat.argtypes = [vp, ci, i64, i64, vp]
         L.mimk_select.argtypes = [vp, vp, vp, vp, ci, i64, vp]
         L.mimk_generate_affine.argtypes = [vp, ci, ci, C.POINTER(i64), C.POINTER(i64), vp]
+        L.mimk_program_classify.argtypes = [C.POINTER(MrpDesc), C.c_int32, C.POINTER(C.c_int32)]
+        L.mimk_program_run.argtypes = [C.POINTER(MrpDesc), C.c_int32, vp]
         L.mimk_gather.argtypes = [vp, vp, vp, ci, ci, ci, C.POINTER(i64), C.POINTER(i64), ci, vp]
         L.mimk_scatter.argtypes = [vp, vp, vp, vp, ci, ci, ci, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64), ci, vp]
         L.mimk_mlp_gated.argtypes = [C.POINTER(MlpDesc), vp]

@@ -62,6 +62,16 @@ int gemm_f32_tc_supported(const mimk_gemm_desc& d);  // f32 operands on the tens
 int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s);
 // map_reduce_post instances that are a contraction, an axis fold or an elementwise map go to those kernels (mrp_route.cu)
 bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status);
+// What a descriptor's access maps spell, whatever its size (the router itself leaves small instances on the per-cell
+// kernel): route MIMK_ROUTE_*, and the arguments of the specialised entry point that would take it.
+struct MrpPlan {
+    int route = MIMK_ROUTE_GENERIC;
+    mimk_gemm_desc gemm{};
+    int64_t outer = 0, len = 0, inner = 0;  // reduce / map: the [outer, len, inner] view
+    int monoid = 0, op = 0, y_mode = 3;
+    int perm[MIMK_MRP_MAX_RANK] = {};
+};
+MrpPlan mrp_plan(const mimk_mrp_desc& d);
 // axis permutation as a tiled copy (permute.cu); perm[j] = the output loop that indexes input axis j
 int permute_copy(const void* in, void* out, int esize, int rank, const int64_t* out_shape, const int* perm, cudaStream_t s);
 int attn_simt(const mimk_attn_desc& d, cudaStream_t s);

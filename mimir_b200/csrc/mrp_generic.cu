@@ -44,6 +44,8 @@ __device__ __forceinline__ Val combine(int id, int acc_dt, Val acc, const Val* i
             case MIMK_F_DIV: r.f = in[0].f / in[1].f; break;
             case MIMK_F_ADD2: r.f = in[0].f + in[1].f; break;
             case MIMK_F_MUL2: r.f = in[0].f * in[1].f; break;
+            case MIMK_F_ADD_SUBEXP: r.f = acc.f + expf(in[0].f - in[1].f); break;
+            case MIMK_F_SUBEXP_DIV: r.f = expf(in[0].f - in[1].f) / in[2].f; break;
             default: break;
         }
     } else {
@@ -130,7 +132,7 @@ __global__ void __launch_bounds__(256) mrp_generic_kernel(const __grid_constant_
             Val in[MIMK_MRP_MAX_INPUTS];
             for (int i = 0; i < d.nis; ++i)
                 in[i] = load_val(d.in[i], d.in_dtype[i], map_offset(d.in_map[i], d.rn, loop, d.in_shape[i]));
-            for (int i = d.nis; i < 2; ++i) in[i].i = 0, in[i].f = 0.f;
+            for (int i = d.nis; i < 3; ++i) in[i].i = 0, in[i].f = 0.f;
             acc = combine(d.comb, d.acc_dtype, acc, in);
         }
         for (int l = d.ro; l < d.rn; ++l) loop[l] = 0;
@@ -188,15 +190,16 @@ extern "C" int mimk_map_reduce_post(const mimk_mrp_desc* d, void* stream) {
     if (!d) return MIMK_E_ARG;
     if (d->ro < 0 || d->rn < d->ro || d->rn > MIMK_MRP_MAX_LOOPS || d->ro > MIMK_MRP_MAX_RANK) return MIMK_E_ARG;
     if (d->nis < 0 || d->nis > MIMK_MRP_MAX_INPUTS || d->nps < 0 || d->nps > 1) return MIMK_E_ARG;
-    if (d->comb < MIMK_F_ADD || d->comb > MIMK_F_MIX || d->post < MIMK_P_ID || d->post > MIMK_P_SILU) return MIMK_E_ARG;
+    if (d->comb < MIMK_F_ADD || d->comb > MIMK_F_SUBEXP_DIV || d->post < MIMK_P_ID || d->post > MIMK_P_SILU) return MIMK_E_ARG;
     if (d->acc_dtype != MIMK_F32 && d->acc_dtype != MIMK_I32 && d->acc_dtype != MIMK_I64) return MIMK_E_DTYPE;
     const bool facc = d->acc_dtype == MIMK_F32;
     if (facc ? (d->out_dtype != MIMK_F32 && d->out_dtype != MIMK_BF16) : (d->out_dtype != MIMK_I32 && d->out_dtype != MIMK_I64))
         return MIMK_E_DTYPE;
-    const int need = (d->comb == MIMK_F_MULADD || d->comb == MIMK_F_SUBEXP || d->comb == MIMK_F_DIV || d->comb == MIMK_F_ADD2 ||
-                      d->comb == MIMK_F_MUL2 || d->comb == MIMK_F_MIX) ? 2 : 1;
+    const int need = d->comb == MIMK_F_SUBEXP_DIV ? 3
+                     : (d->comb == MIMK_F_MULADD || d->comb == MIMK_F_SUBEXP || d->comb == MIMK_F_DIV || d->comb == MIMK_F_ADD2 ||
+                        d->comb == MIMK_F_MUL2 || d->comb == MIMK_F_MIX || d->comb == MIMK_F_ADD_SUBEXP) ? 2 : 1;
     if (d->nis != need) return MIMK_E_ARG;
-    if (!facc && (d->comb == MIMK_F_SUBEXP || d->comb == MIMK_F_DIV)) return MIMK_E_DTYPE;
+    if (!facc && (d->comb == MIMK_F_SUBEXP || d->comb == MIMK_F_DIV || d->comb == MIMK_F_ADD_SUBEXP || d->comb == MIMK_F_SUBEXP_DIV)) return MIMK_E_DTYPE;
     if (facc && d->comb == MIMK_F_MIX) return MIMK_E_DTYPE;
     const bool post_needs = d->post >= MIMK_P_ADD && d->post <= MIMK_P_ADD_TANH;
     if (post_needs != (d->nps == 1)) return MIMK_E_ARG;

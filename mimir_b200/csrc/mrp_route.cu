@@ -43,14 +43,7 @@ int64_t prod(const int64_t* v, int lo, int hi) {
     return p;
 }
 
-struct Plan {
-    int route = MIMK_ROUTE_GENERIC;
-    mimk_gemm_desc gemm{};
-    // reduce / map
-    int64_t outer = 0, len = 0, inner = 0;
-    int monoid = 0, op = 0, y_mode = 3;
-    int perm[MIMK_MRP_MAX_RANK] = {};
-};
+using Plan = MrpPlan;
 
 // Operand `i` as a matrix [..batch, r, c]: its last two results are loops (lr, lc); with a leading batch result (loop 0)
 // when the operand has one. Returns 0 = no match, 1 = matrix without batch axis, 2 = matrix with batch axis.
@@ -243,7 +236,7 @@ bool plan_reshape(const mimk_mrp_desc& d) {
 // the ascending fold of the classic nest bit for bit.
 constexpr long long ROUTE_MIN_WORK = 1ll << 20;
 
-Plan make_plan(const mimk_mrp_desc& d) {
+Plan make_plan(const mimk_mrp_desc& d, bool any_size = false) {
     Plan p;
     if (d.ro < 0 || d.rn < d.ro || d.rn > MIMK_MRP_MAX_LOOPS || d.ro > MIMK_MRP_MAX_RANK) return p;
     if (d.nis < 1 || d.nis > 2) return p;
@@ -258,7 +251,7 @@ Plan make_plan(const mimk_mrp_desc& d) {
         p.route = MIMK_ROUTE_COPY;
         return p;
     }
-    if (work < (long double)ROUTE_MIN_WORK) return p;
+    if (!any_size && work < (long double)ROUTE_MIN_WORK) return p;
     if (plan_gemm(d, p)) p.route = MIMK_ROUTE_GEMM;
     else if (plan_reduce(d, p)) p.route = MIMK_ROUTE_REDUCE;
     else if (plan_map(d, p)) p.route = MIMK_ROUTE_MAP;
@@ -267,6 +260,8 @@ Plan make_plan(const mimk_mrp_desc& d) {
 }
 
 }  // namespace
+
+MrpPlan mrp_plan(const mimk_mrp_desc& d) { return make_plan(d, true); }
 
 // Runs `d` on a specialised kernel when one applies. Returns false when the generic kernel should take it; otherwise
 // *status holds the specialised entry point's status. MIMK_MRP_ROUTE=0 in the environment keeps everything generic.

@@ -433,6 +433,58 @@ def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_ma
     return out
 
 
+# ------------------------------------------------------------------------------------------------ programs
+STEPS = {0: "op", 1: "softmax", 2: "attention", 3: "absorbed"}
+
+
+class Operand:
+    """An operand known by address, element type and shape only (for classifying a program without a device)."""
+
+    def __init__(self, ptr: int, dtype, shape):
+        self.ptr, self.dtype, self.shape = int(ptr), dtype, tuple(int(v) for v in shape)
+
+
+def _meta(t):
+    return (t.ptr, t.dtype, t.shape) if isinstance(t, Operand) else (t.data_ptr(), t.dtype, tuple(t.shape))
+
+
+class Program:
+    """An ordered list of `map_reduce_post` operations whose results feed later operations (by address), as a lowering
+    that emits one launcher call per operation produces it. `run` executes it through mimk_program_run: chains that spell
+    softmax (tensor.mim:1172-1176, also in fuse_tensor's three-operation form) or attention (lit/tensor/attn_exec.mim:20-22)
+    run as one fused kernel, everything else op by op."""
+
+    def __init__(self):
+        self.descs, self.keep = [], []
+
+    def op(self, out, Sr, f: int, init, post: int, map_out, maps, ins, post_maps=(), post_ins=(), *, acc_dtype=None):
+        """Append one operation writing into `out` (a tensor or an Operand); returns `out` for use as a later input."""
+        So = list(_meta(out)[2])
+        if acc_dtype is None:
+            dt = _meta(ins[0])[1] if ins else _meta(out)[1]
+            acc_dtype = torch.float32 if dt in (torch.float32, torch.bfloat16) else dt
+        d = _mrp_desc(So, [int(v) for v in Sr], f, init, post, map_out, maps, [_meta(t) for t in ins], post_maps,
+                      [_meta(t) for t in post_ins], acc_dtype, _meta(out)[1], _meta(out)[0])
+        self.descs.append(d)
+        self.keep.append((out, ins, post_ins))
+        return out
+
+    def _array(self):
+        arr = (L.MrpDesc * max(len(self.descs), 1))()
+        for i, d in enumerate(self.descs):
+            C.memmove(C.byref(arr[i]), C.byref(d), C.sizeof(L.MrpDesc))
+        return arr
+
+    def classify(self):
+        """How each operation would run: "op", "softmax" / "attention" (first operation of a fused chain), "absorbed"."""
+        steps = (C.c_int32 * max(len(self.descs), 1))()
+        L.check(L.lib().mimk_program_classify(self._array(), len(self.descs), steps), "program_classify")
+        return [STEPS[steps[i]] for i in range(len(self.descs))]
+
+    def run(self):
+        L.check(L.lib().mimk_program_run(self._array(), len(self.descs), _stream()), "program_run")
+
+
 # ------------------------------------------------------------------------------------------------ the rest of the op surface
 # Every operator below is ONE `map_reduce_post` with the access maps the reference's `_impl` lams build
 # (tensor.mim:1086-1134, 1182-1327, 1367-1411, 1443-1468), run by the generic kernel.

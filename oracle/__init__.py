@@ -25,6 +25,7 @@ _DT2NP = {I32: np.int32, I64: np.int64, F32: np.float32, F64: np.float64, BF16: 
 # combiner / epilogue ids (keep in step with mimir_oracle.cpp)
 F_ADD_I32, F_MULADD_I32, F_MIX_I32_I64, F_ADD_F32, F_MULADD_F32, F_FMAX_F32, F_SUBEXP_F32, F_DIV_F32 = range(8)
 F_ADD2_F32, F_FIRST_F32, F_MULADD_F64, F_ADD_F64, F_FMIN_F32, F_MUL2_F32, F_FIRST_I32 = range(8, 15)
+F_ADD_SUBEXP_F32, F_SUBEXP_DIV_F32 = 15, 16
 P_ID, P_CONV_ADD_I64, P_ADD_PLUS1_I32, P_BIAS_RELU_F32, P_BIAS_TANH_F32, P_BIAS_F32, P_F64_TO_F32 = range(7)
 
 

@@ -111,6 +111,8 @@ enum {
     MO_F_FMIN_F32 = 12,
     MO_F_MUL2_F32 = 13,    // binary app = u * v
     MO_F_FIRST_I32 = 14,
+    MO_F_ADD_SUBEXP_F32 = 15,  // acc + exp(u - v): the sum fold of softmax with its producer inlined (fuse.cpp:225-245)
+    MO_F_SUBEXP_DIV_F32 = 16,  // exp(u - v) / w: the divide with the exponential recomputed
 };
 enum {
     MO_P_ID = 0,
@@ -146,6 +148,8 @@ static inline Val comb(int id, Val acc, const Val* in) {
         case MO_F_FIRST_I32: r.i32 = in[0].i32; break;
         case MO_F_MULADD_F64: r.f64 = acc.f64 + in[0].f64 * in[1].f64; break;
         case MO_F_ADD_F64: r.f64 = acc.f64 + in[0].f64; break;
+        case MO_F_ADD_SUBEXP_F32: r.f32 = acc.f32 + std::exp(in[0].f32 - in[1].f32); break;
+        case MO_F_SUBEXP_DIV_F32: r.f32 = std::exp(in[0].f32 - in[1].f32) / in[2].f32; break;
     }
     return r;
 }
