@@ -1,4 +1,4 @@
-// Device helpers shared by the tensor-core attention kernels: exp2 on the special-function unit and on the FMA pipe,
+// Device helpers shared by the tensor-core attention kernels: exp2 on the special-function unit,
 // packed f32x2 arithmetic, three-input maxima, 32-column tensor-memory loads and stores.
 #pragma once
 #include <cstdint>
@@ -31,31 +31,6 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-__device__ __forceinline__ uint64_t add2_rd(uint64_t a, uint64_t b) {  // round towards -inf
-    uint64_t d;
-    asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-
-// 2^x for two values x <= 8 on the FMA pipe instead of the special-function unit: split x into floor and fraction
-// with a round-down add of 1.5 * 2^23, evaluate a cubic minimax polynomial of 2^frac on [0,1) (relative error 8.8e-5,
-// far below the bf16 rounding P receives), and add floor(x) into the exponent field.
-__device__ __forceinline__ void poly_exp2_x2(float xa, float xb, float& ea, float& eb) {
-    const uint64_t x    = pack2(fmaxf(xa, -127.f), fmaxf(xb, -127.f));
-    const uint64_t xf   = add2_rd(x, pack2(12582912.f, 12582912.f));
-    const uint64_t fl   = add2(xf, pack2(-12582912.f, -12582912.f));
-    const uint64_t frac = fma2(fl, pack2(-1.f, -1.f), x);
-    uint64_t pf = fma2(pack2(0.077119089663028717041015625f, 0.077119089663028717041015625f), frac,
-                       pack2(0.227564394474029541015625f, 0.227564394474029541015625f));
-    pf          = fma2(pf, frac, pack2(0.695146143436431884765625f, 0.695146143436431884765625f));
-    pf          = fma2(pf, frac, pack2(1.0f, 1.0f));
-    float pa, pb, fa, fb;
-    unpack2(pf, pa, pb);
-    unpack2(xf, fa, fb);
-    ea = __int_as_float(__float_as_int(pa) + (__float_as_int(fa) << 23));
-    eb = __int_as_float(__float_as_int(pb) + (__float_as_int(fb) << 23));
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));

@@ -13,8 +13,14 @@
 //                 running max has grown by more than 2^8 since the last rescale
 //   (registers are moved from the third warpgroup to the two softmax warpgroups with setmaxnreg: 208 vs 88 per thread)
 //   warp 8        work fetch + TMA producer: Q, then K and V tiles into two-stage rings (128-byte-swizzled shared memory)
-//   warp 9        MMA issuer (one thread): S_t = Q_t K^T  (tcgen05.mma, M128 N128 K16 x 8, both operands in shared
-//                 memory) and O_t += P_t V (A operand = P_t in tensor memory, B operand = V as an MN-major tile)
+//   warp 9        MMA issuer: S_t = Q_t K^T  (tcgen05.mma, M128 N128 K16 x 8, both operands in shared memory) and
+//                 O_t += P_t V (A operand = P_t in tensor memory, B operand = V as an MN-major tile). The whole warp
+//                 runs the role's control flow and one elected lane issues: descriptor arithmetic then stays in uniform
+//                 registers, which matters because the tensor core queues only about two MMAs, so the issuing thread
+//                 must deliver one every 64 clocks while sharing its scheduler with two softmax warps (measured: 8
+//                 MMAs per 612 clk issued from a one-lane branch, 552 clk this way, 520 clk on an otherwise idle SM).
+//                 K / V stages are released by the softmax warps (they observe the completion of every contraction
+//                 anyway): each tcgen05.commit less shortens this warp's path from one tile to the next
 //   TMEM (512 columns): S_0 | S_1 | O_0 | O_1; P_t aliases the first 64 columns of S_t.
 // While one tile's warps do their exponentials the tensor core works on the other tile.
 //
@@ -62,6 +68,10 @@ struct RegSplit {
 };
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 constexpr int WORK_SLOTS = 2;
+// O_t += P_t V starts when this many keys of P_t are stored; the rest follows behind it. With 96 of 128 the tensor core is
+// still busy with the first part when the last 32 keys arrive, and little of the contraction is left behind them.
+constexpr int P_FIRST_KEYS = 96;
+static_assert(P_FIRST_KEYS % 32 == 0 && P_FIRST_KEYS > 0 && P_FIRST_KEYS < 128, "P is handed over at a 32-key chunk boundary");
 
 struct Bars {
     uint64_t q_full[2], q_empty[2];
@@ -160,9 +170,9 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         }
         for (int s = 0; s < KV_STAGES; ++s) {
             mbar_init(smem_u32(&bars->k_full[s]), 1);
-            mbar_init(smem_u32(&bars->k_empty[s]), 1);
+            mbar_init(smem_u32(&bars->k_empty[s]), 2);  // one release per query tile
             mbar_init(smem_u32(&bars->v_full[s]), 1);
-            mbar_init(smem_u32(&bars->v_empty[s]), 1);
+            mbar_init(smem_u32(&bars->v_empty[s]), 2);
         }
         for (int w = 0; w < WORK_SLOTS; ++w) {
             mbar_init(smem_u32(&bars->work_full[w]), 1);
@@ -231,7 +241,13 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         }
       } else if (warp == MMA_WARP) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // One thread issues both tiles' contractions in the fixed order tile 0, tile 1, tile 0, ...: that order is what
+        // keeps the two softmax warpgroups half a period apart (two independent issuing threads fall into step, and
+        // then the exponentials of both tiles and the contractions of both tiles take turns instead of overlapping).
+        // The K / V stages are released by the softmax warps, which see the completion of these contractions anyway:
+        // every tcgen05.commit less shortens this thread's path from one tile to the next.
+        {
+            const bool leader = elect_one();  // the lane that issues; everything else below is warp-uniform
             const uint32_t idesc_qk = idesc_bf16_f32(BQ, BKV, 0, 0);
             const uint32_t idesc_pv = idesc_bf16_f32(BQ, HD, 0, 1);
             static_assert(KV_STAGES == 2, "stage selection below assumes two stages");
@@ -241,21 +257,29 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             // S_t = Q_t K^T with K in ring stage `stage`: 8 k-steps of 16 over head_dim
             auto issue_qk = [&](int t, uint32_t stage) {
                 const uint64_t qa = dQ0 + (t ? TILE_STEP : 0), kb = dK0 + (stage ? TILE_STEP : 0);
+                if (leader) {
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint64_t off = uint64_t(((k >> 2) * ATOM_BYTES + (k & 3) * 32) >> 4);
-                    mma_f16_ss(tmem_base + t * 128, qa + off, kb + off, idesc_qk, k > 0 ? 1u : 0u);
+                    for (int k = 0; k < HD / 16; ++k) {
+                        const uint64_t off = uint64_t(((k >> 2) * ATOM_BYTES + (k & 3) * 32) >> 4);
+                        mma_f16_ss(tmem_base + t * 128, qa + off, kb + off, idesc_qk, k > 0 ? 1u : 0u);
+                    }
+                    mma_commit(smem_u32(&bars->s_full[t]));
                 }
-                mma_commit(smem_u32(&bars->s_full[t]));
+                __syncwarp();
             };
             // O_t (+)= P_t V with V in ring stage `stage`, k-steps [k0, k1) of 16 keys; `first` = first key tile of the item
             auto issue_pv = [&](int t, uint32_t stage, bool first, int k0, int k1) {
                 const uint64_t vb = dV0 + (stage ? TILE_STEP : 0);
+                if (leader) {
 #pragma unroll
-                for (int k = k0; k < k1; ++k)
-                    mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, vb + uint64_t((k * 2048) >> 4), idesc_pv,
-                               (!first || k > 0) ? 1u : 0u);
+                    for (int k = k0; k < k1; ++k)
+                        mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, vb + uint64_t((k * 2048) >> 4), idesc_pv,
+                                   (!first || k > 0) ? 1u : 0u);
+                }
+                __syncwarp();
             };
+            auto commit  = [&](uint64_t* bar) { if (leader) mma_commit(smem_u32(bar)); };
+            auto release = [&](uint64_t* bar) { if (leader) mbar_arrive(smem_u32(bar)); };
             uint32_t g = 0;                // K/V tiles consumed so far
             uint32_t qc0 = 0, qc1 = 0;     // items in which tile slot t took part (parity of q_full / o_empty)
             uint32_t pc0 = 0, pc1 = 0;     // P tiles consumed per tile slot (parity of p_half / p_full)
@@ -264,7 +288,8 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 const uint32_t slot = w % WORK_SLOTS, wph = (w / WORK_SLOTS) & 1u;
                 if (!(ok = mbar_wait(smem_u32(&bars->work_full[slot]), wph, abort_flag))) break;
                 const int item = work_item[slot];
-                mbar_arrive(smem_u32(&bars->work_empty[slot]));
+                __syncwarp();  // every lane has read the slot
+                release(&bars->work_empty[slot]);
                 if (item < 0) break;
                 const Item it = decode_item(p, item);
                 const int n0 = it.n_kv[0], n1 = it.n_kv[1], n_max = it.n_max;  // scalars: nothing below indexes an array by tile
@@ -277,13 +302,16 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 tc_fence_after();
                 if (n0 > 0) {
                     issue_qk(0, g % KV_STAGES);
-                    if (n0 == 1) mma_commit(smem_u32(&bars->q_empty[0]));  // the item's only S for this tile
+                    if (n0 == 1) commit(&bars->q_empty[0]);  // the item's only S for this tile
+                } else {
+                    release(&bars->k_empty[g % KV_STAGES]);  // in place of the warpgroup that has no tile
                 }
                 if (n1 > 0) {
                     issue_qk(1, g % KV_STAGES);
-                    if (n1 == 1) mma_commit(smem_u32(&bars->q_empty[1]));
+                    if (n1 == 1) commit(&bars->q_empty[1]);
+                } else {
+                    release(&bars->k_empty[g % KV_STAGES]);
                 }
-                mma_commit(smem_u32(&bars->k_empty[g % KV_STAGES]));
                 for (int j = 0; j < n_max && ok; ++j) {
                     const uint32_t gj = g + uint32_t(j);
                     const uint32_t s = gj % KV_STAGES, s1 = (gj + 1) % KV_STAGES;
@@ -291,22 +319,51 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                     bool v_ready = false, k_ready = false;
                     // one key tile of one query tile: O_t += P_t V_j, then S_t = Q_t K_{j+1}^T
                     auto tile_step = [&](const int t, const int n_kv, const uint32_t qc, uint32_t& pc) -> bool {
+                        if (j >= n_kv) {
+                            // this tile has no key tile j (and none after it): pass the V stage of tile j and the K stage
+                            // of tile j + 1 on in its warpgroup's place, once they are filled (a release before that
+                            // could complete the PREVIOUS phase of the barrier)
+                            if (!v_ready) {
+                                if (!mbar_wait(smem_u32(&bars->v_full[s]), ph, abort_flag)) return false;
+                                v_ready = true;
+                            }
+                            release(&bars->v_empty[s]);
+                            if (j + 1 < n_max) {
+                                if (!k_ready) {
+                                    if (!mbar_wait(smem_u32(&bars->k_full[s1]), ph1, abort_flag)) return false;
+                                    k_ready = true;
+                                    tc_fence_after();
+                                }
+                                release(&bars->k_empty[s1]);
+                            }
+                            return true;
+                        }
                         // the item's first O_t = P V overwrites O_t: the previous item's result must have been read
                         if (j == 0 && !mbar_wait(smem_u32(&bars->o_empty[t]), (qc & 1u) ^ 1u, abort_flag)) return false;
-                        // the first 64 keys of P_t are ready before the rest: start O_t += P_t V on them
+                        // the first keys of P_t are ready before the rest: start O_t += P_t V on them
                         if (!mbar_wait(smem_u32(&bars->p_half[t]), pc & 1u, abort_flag)) return false;
                         if (!v_ready) {
                             if (!mbar_wait(smem_u32(&bars->v_full[s]), ph, abort_flag)) return false;
                             v_ready = true;
                         }
                         tc_fence_after();
-                        issue_pv(t, s, j == 0, 0, 4);
+                        issue_pv(t, s, j == 0, 0, P_FIRST_KEYS / 16);
                         if (!mbar_wait(smem_u32(&bars->p_full[t]), pc & 1u, abort_flag)) return false;
                         tc_fence_after();
-                        issue_pv(t, s, j == 0, 4, 8);
+                        issue_pv(t, s, j == 0, P_FIRST_KEYS / 16, BKV / 16);
                         ++pc;
-                        if (j + 1 == n_kv) mma_commit(smem_u32(&bars->o_full[t]));
-                        if (j + 1 < n_kv) {
+                        if (j + 1 == n_kv) {
+                            commit(&bars->o_full[t]);
+                            // the other tile goes on: K of tile j + 1 is passed on in this warpgroup's place
+                            if (j + 1 < n_max) {
+                                if (!k_ready) {
+                                    if (!mbar_wait(smem_u32(&bars->k_full[s1]), ph1, abort_flag)) return false;
+                                    k_ready = true;
+                                    tc_fence_after();
+                                }
+                                release(&bars->k_empty[s1]);
+                            }
+                        } else {
                             if (!k_ready) {
                                 if (!mbar_wait(smem_u32(&bars->k_full[s1]), ph1, abort_flag)) return false;
                                 k_ready = true;
@@ -314,15 +371,12 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                             }
                             issue_qk(t, s1);
                             // the item's last S for this tile: its Q buffer may be refilled once this has completed
-                            if (j + 2 == n_kv) mma_commit(smem_u32(&bars->q_empty[t]));
+                            if (j + 2 == n_kv) commit(&bars->q_empty[t]);
                         }
                         return true;
                     };
-                    if (j < n0) ok = tile_step(0, n0, qc0, pc0);
-                    if (ok && j < n1) ok = tile_step(1, n1, qc1, pc1);
-                    if (!ok) break;
-                    mma_commit(smem_u32(&bars->v_empty[s]));
-                    if (k_ready) mma_commit(smem_u32(&bars->k_empty[s1]));
+                    ok = tile_step(0, n0, qc0, pc0);
+                    if (ok) ok = tile_step(1, n1, qc1, pc1);
                 }
                 g += uint32_t(n_max);
                 qc0 += n0 > 0 ? 1u : 0u;
@@ -340,6 +394,8 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         const uint32_t tS = tmem_base + t * 128 + lane_sel, tO = tmem_base + 256 + t * 128 + lane_sel;
         uint32_t sc = 0;  // S tiles consumed so far by this tile slot (parity of s_full)
         uint32_t oc = 0;  // items in which this tile slot took part (parity of o_full)
+        uint32_t g  = 0;  // K/V tiles of all items so far (stage of the K / V barriers this warpgroup releases)
+        const bool releaser = quarter == 0 && lane == 0;
         bool ok = true;
         for (uint32_t w = 0; ok; ++w) {
             const uint32_t slot = w % WORK_SLOTS, wph = (w / WORK_SLOTS) & 1u;
@@ -351,38 +407,74 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             const Item it = decode_item(p, item);
             const int n_kv = t ? it.n_kv[1] : it.n_kv[0];
             const int q0   = t ? it.q0[1] : it.q0[0];
-            if (n_kv == 0) continue;
+            if (n_kv == 0) {
+                g += uint32_t(it.n_max);
+                continue;
+            }
             const int64_t qi = int64_t(q0) + row_in_tile;
             float m_used = -CUDART_INF_F, l = 0.f;
             for (int j = 0; j < n_kv && ok; ++j, ++sc) {
                 if (!(ok = mbar_wait(smem_u32(&bars->s_full[t]), sc & 1u, abort_flag))) break;
                 tc_fence_after();
+                // S_t of key tile j is complete, and with it everything this tile's MMA thread issued before it: the K
+                // stage of tile j and the V stage of tile j - 1 have been read for this query tile
+                if (releaser) {
+                    mbar_arrive(smem_u32(&bars->k_empty[(g + uint32_t(j)) % KV_STAGES]));
+                    if (j > 0) mbar_arrive(smem_u32(&bars->v_empty[(g + uint32_t(j) - 1u) % KV_STAGES]));
+                }
                 const int64_t k0 = int64_t(j) * BKV;
                 const bool need_mask = (p.causal && k0 + BKV - 1 > q0) || (k0 + BKV > p.Sk);
                 int64_t limit = p.Sk;  // keys >= limit are masked for this row
                 if (p.causal && qi + 1 < limit) limit = qi + 1;
                 // the whole score row (128 f32) in registers: one round trip to tensor memory
                 uint32_t r[BKV];
+                uint32_t pk[16];
+                const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2);
+                uint64_t sum2[2]   = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+                auto mask_chunk = [&](const int c) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (k0 + c + i >= limit) r[c + i] = 0xff800000u;  // -inf: exp2 gives 0
+                };
+                // p = exp2(s * scale - m) for keys [c, c + 32) of the row, added to the row sum, packed as bf16 into pk
+                auto exp_chunk = [&](const int c, const float m_ref) {
+                    const uint64_t neg_m = pack2(-m_ref, -m_ref);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float xa, xb;
+                        unpack2(fma2(pack2(__uint_as_float(r[c + i]), __uint_as_float(r[c + i + 1])), sl2, neg_m), xa, xb);
+                        const float a = fast_exp2(xa), b = fast_exp2(xb);
+                        sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(a, b));
+                        pk[i >> 1]         = pack_bf16x2(a, b);
+                    }
+                };
+                // two independent chains of three-input maxima per 32 keys, eight in all, then one join
+                float mx8[8];
+                auto max_chunk = [&](const int c) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int b = c + 16 * h;
+                        float m = max3(__uint_as_float(r[b]), __uint_as_float(r[b + 1]), __uint_as_float(r[b + 2]));
+#pragma unroll
+                        for (int i = 3; i + 1 < 16; i += 2) m = max3(m, __uint_as_float(r[b + i]), __uint_as_float(r[b + i + 1]));
+                        mx8[(c >> 4) + h] = fmaxf(m, __uint_as_float(r[b + 15]));
+                    }
+                };
                 tmem_ld_slice(tS, r);
                 tmem_ld_slice(tS + 32, r + 32);
                 tmem_ld_slice(tS + 64, r + 64);
                 tmem_ld_slice(tS + 96, r + 96);
                 tmem_ld_wait();
                 if (need_mask) {
-#pragma unroll
-                    for (int i = 0; i < BKV; ++i)
-                        if (k0 + i >= limit) r[i] = 0xff800000u;  // -inf: exp2 gives 0
+                    mask_chunk(0);
+                    mask_chunk(32);
+                    mask_chunk(64);
+                    mask_chunk(96);
                 }
-                // eight independent chains of three-input maxima, then one join
-                float mx8[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    mx8[c] = max3(__uint_as_float(r[16 * c]), __uint_as_float(r[16 * c + 1]), __uint_as_float(r[16 * c + 2]));
-#pragma unroll
-                    for (int i = 3; i + 1 < 16; i += 2)
-                        mx8[c] = max3(mx8[c], __uint_as_float(r[16 * c + i]), __uint_as_float(r[16 * c + i + 1]));
-                    mx8[c] = fmaxf(mx8[c], __uint_as_float(r[16 * c + 15]));
-                }
+                max_chunk(0);
+                max_chunk(32);
+                max_chunk(64);
+                max_chunk(96);
                 float mx = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) *
                            p.scale_log2;  // scale > 0: max commutes with it
                 if (j == 0) {
@@ -405,22 +497,12 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                     l *= alpha;
                     m_used = m_new;
                 }
-                // p = exp2(s * scale - m), row sum, P as bf16 over the first 64 columns of S_t
-                const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2), neg_m = pack2(-m_used, -m_used);
-                uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+                // P as bf16 over the first 64 columns of S_t
 #pragma unroll
                 for (int c = 0; c < BKV; c += 32) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float xa, xb;
-                        unpack2(fma2(pack2(__uint_as_float(r[c + i]), __uint_as_float(r[c + i + 1])), sl2, neg_m), xa, xb);
-                        const float a = fast_exp2(xa), b = fast_exp2(xb);
-                        sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(a, b));
-                        pk[i >> 1]         = pack_bf16x2(a, b);
-                    }
-                    if (c == 64) {
-                        // keys 0..63 of P_t were stored a whole chunk of exponentials ago, so this wait does not stall:
+                    exp_chunk(c, m_used);
+                    if (c == P_FIRST_KEYS) {
+                        // the first keys of P_t were stored a whole chunk of exponentials ago, so this wait does not stall:
                         // let the tensor core start on them
                         tmem_st_wait();
                         tc_fence_before();
@@ -441,6 +523,8 @@ attn_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             if (!(ok = mbar_wait(smem_u32(&bars->o_full[t]), oc & 1u, abort_flag))) break;
             ++oc;
             tc_fence_after();
+            if (releaser) mbar_arrive(smem_u32(&bars->v_empty[(g + uint32_t(n_kv) - 1u) % KV_STAGES]));  // the last O_t += P_t V has read its V stage
+            g += uint32_t(it.n_max);
             // the finished row of O_t into registers, then hand O_t back: the next item's first O_t = P V may overwrite it
             uint32_t o[HD];
 #pragma unroll
