@@ -132,6 +132,10 @@ constexpr int TRACE_ROLES = 6, TRACE_CAP = 1024;  // roles: producer, issuer of 
 // A time stamp of one step of one role of the first cluster's CTAs: (code, key tile) and the global timer (ns), stored at the role's own
 // running index (plain stores, no atomics: the traced warp is barely disturbed). For reading the pipeline.
 __device__ __forceinline__ void trace(const Params& p, int role, uint32_t& idx, int code, uint32_t g) {
+#ifndef MIMK_ATTN_PAIR_TRACE
+    // compiled out unless asked for: even the untaken branch per step cost the hot loops 8 % (0.562 -> 0.518 ms at 128 heads x 4096)
+    (void)p, (void)role, (void)idx, (void)code, (void)g;
+#else
     if (p.trace && blockIdx.x < 2 && idx < TRACE_CAP) {
         long long* at = p.trace + ((size_t(blockIdx.x) * TRACE_ROLES + role) * TRACE_CAP + idx) * 2;
         unsigned long long ns;
@@ -140,6 +144,7 @@ __device__ __forceinline__ void trace(const Params& p, int role, uint32_t& idx, 
         at[1] = static_cast<long long>(ns);
         ++idx;
     }
+#endif
 }
 
 // ---- cluster-scope helpers -------------------------------------------------------------------------------------------
@@ -418,7 +423,10 @@ attn_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // and its commit costs a thread about as long as the group runs, so one thread for both was the bottleneck. The
         // streams need no order between them beyond what the barriers give.
 #define DBG_G (qk_g)
-        if (lane == 0 && rank == 0) {
+        if (rank == 0) {
+            // the whole warp runs the control flow and one elected lane issues: descriptor arithmetic stays in uniform
+            // registers, and the issuing thread must deliver an instruction every 64 clocks on a scheduler it shares
+            const bool leader = elect_one();
             const uint32_t idesc_qk = idesc_bf16_f32(2 * BQ, BKV, 0, 0);
             const uint64_t dQ0 = smem_desc_sw128(sQ, 16, 1024), dK0 = smem_desc_sw128(sK, 16, 1024);
             uint32_t tri = 0;
@@ -428,7 +436,8 @@ attn_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 const uint32_t slot = item % WORK_SLOTS, wph = (item / WORK_SLOTS) & 1u;
                 if (!(ok = mbar_wait(smem_u32(&bars->work_full[slot]), wph, abort_flag))) { note_wait(6, int(DBG_G)); break; }
                 const int val = work_item[slot];
-                mbar_arrive(smem_u32(&bars->work_empty[slot]));  // the item's length is all this thread needs of it
+                __syncwarp();
+                if (leader) mbar_arrive(smem_u32(&bars->work_empty[slot]));  // the item's length is all this warp needs of it
                 if (val < 0) break;
                 const int n = decode_item(p, val).n;
                 if (!(ok = mbar_wait(smem_u32(&bars->q_full[item % Q_STAGES]), (item / Q_STAGES) & 1u, abort_flag))) { note_wait(7, int(DBG_G)); break; }
@@ -440,15 +449,18 @@ attn_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     if (qk_g >= 2 && !(ok = mbar_wait(smem_u32(&bars->s_free[b]), ((qk_g >> 1) - 1u) & 1u, abort_flag))) { note_wait(17, int(DBG_G)); break; }
                     tc_fence_after();
                     const uint64_t kb = dK0 + uint64_t((s * KH_BYTES) >> 4);
+                    if (leader) {
 #pragma unroll
-                    for (int k = 0; k < HD / 16; ++k) {
-                        const uint64_t qoff = uint64_t(((k >> 2) * ATOM_BYTES + (k & 3) * 32) >> 4);
-                        const uint64_t koff = uint64_t(((k >> 2) * KH_ATOM + (k & 3) * 32) >> 4);
-                        mma_ss_pair(tmem_base + COL_S + b * 128, qa + qoff, kb + koff, idesc_qk, k > 0 ? 1u : 0u);
+                        for (int k = 0; k < HD / 16; ++k) {
+                            const uint64_t qoff = uint64_t(((k >> 2) * ATOM_BYTES + (k & 3) * 32) >> 4);
+                            const uint64_t koff = uint64_t(((k >> 2) * KH_ATOM + (k & 3) * 32) >> 4);
+                            mma_ss_pair(tmem_base + COL_S + b * 128, qa + qoff, kb + koff, idesc_qk, k > 0 ? 1u : 0u);
+                        }
+                        // ONE completion signal per group: the K and Q stages are handed back to the producers by the
+                        // softmax threads that see it (a commit costs the issuing thread a few hundred cycles)
+                        commit_pair(smem_u32(&bars->s_full[b]));
                     }
-                    // ONE completion signal per group: the K and Q stages are handed back to the producers by the softmax
-                    // threads that see it (a commit costs the issuing thread a few hundred cycles)
-                    commit_pair(smem_u32(&bars->s_full[b]));
+                    __syncwarp();
                     trace(p, 1, tri, 1, qk_g);
                 }
             }
@@ -457,7 +469,8 @@ attn_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #undef DBG_G
         // ---------------- issuer of O (+)= P V (even CTA) ----------------
 #define DBG_G (pv_g)
-        if (lane == 0 && rank == 0) {
+        if (rank == 0) {
+            const bool leader = elect_one();
             const uint32_t idesc_pv = idesc_bf16_f32(2 * BQ, HD, 0, 1);
             const uint64_t dV0 = smem_desc_sw128(sV, ATOM_BYTES, 1024);
             uint32_t tri = 0;
@@ -467,7 +480,8 @@ attn_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 const uint32_t slot = item % WORK_SLOTS, wph = (item / WORK_SLOTS) & 1u;
                 if (!(ok = mbar_wait(smem_u32(&bars->work_full[slot]), wph, abort_flag))) { note_wait(9, int(DBG_G)); break; }
                 const int val = work_item[slot];
-                mbar_arrive(smem_u32(&bars->work_empty[slot]));
+                __syncwarp();
+                if (leader) mbar_arrive(smem_u32(&bars->work_empty[slot]));
                 if (val < 0) break;
                 const int n = decode_item(p, val).n;
                 // the item's first O = P V overwrites O: both CTAs have read the previous item's result
@@ -478,11 +492,14 @@ attn_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     if (!(ok = mbar_wait(smem_u32(&bars->p_full[b]), (pv_g >> 1) & 1u, abort_flag))) { note_wait(16, int(DBG_G)); break; }
                     tc_fence_after();
                     const uint64_t vb = dV0 + uint64_t((s * VH_BYTES) >> 4);
+                    if (leader) {
 #pragma unroll
-                    for (int k = 0; k < BKV / 16; ++k)
-                        mma_ts_pair(tmem_base + COL_O, tmem_base + COL_P + b * 64 + k * 8, vb + uint64_t((k * 2048) >> 4), idesc_pv,
-                                    (j > 0 || k > 0) ? 1u : 0u);
-                    commit_pair(smem_u32(&bars->pv_done[b]));  // the V stage goes back through the softmax thread that sees this
+                        for (int k = 0; k < BKV / 16; ++k)
+                            mma_ts_pair(tmem_base + COL_O, tmem_base + COL_P + b * 64 + k * 8, vb + uint64_t((k * 2048) >> 4), idesc_pv,
+                                        (j > 0 || k > 0) ? 1u : 0u);
+                        commit_pair(smem_u32(&bars->pv_done[b]));  // the V stage goes back through the softmax thread that sees this
+                    }
+                    __syncwarp();
                     trace(p, 4, tri, 2, pv_g);
                 }
             }
@@ -791,12 +808,17 @@ int attn_tc_pair(const mimk_attn_desc& d, cudaStream_t s) {
         debug         = (e && e[0] == '1') ? 1 : 0;
     }
     if (debug) MIMK_CUDA_TRY(cudaMemsetAsync(wait_records(), 0, 128 * sizeof(int), s));
+    // Time stamps of the roles: only in a build with -DMIMK_ATTN_PAIR_TRACE, and then only with MIMK_ATTN_TRACE=1
     static int tracing = -1;
     static long long* trace_buf[64] = {};
+#ifdef MIMK_ATTN_PAIR_TRACE
     if (tracing < 0) {
         const char* e = getenv("MIMK_ATTN_TRACE");
         tracing       = (e && e[0] == '1') ? 1 : 0;
     }
+#else
+    tracing = 0;
+#endif
     p.trace = nullptr;
     if (tracing) {  // measurement aid only: allocates, and waits for the kernel
         if (!trace_buf[di]) MIMK_CUDA_TRY(cudaMalloc(&trace_buf[di], 2 * TRACE_ROLES * TRACE_CAP * 2 * sizeof(long long)));
