@@ -166,6 +166,23 @@ int mimk_reduce_plan(int64_t outer, int64_t len, int64_t inner, int sm_count, in
 int mimk_reduce_static(const void* x, void* out, int dtype, int64_t outer, int64_t len, int64_t inner, int monoid,
                        void* stream);
 
+/* An injective elementwise producer inlined into a consumer's operand read -- what tensor::phase::Fuse::fuse_map_reduce
+ * does (src/mim/plug/tensor/phase/fuse.cpp:183-358, legality at :225-233): every element v the consumer reads becomes
+ *   outer_op(inner_op(v, y[...]))
+ * inner_op: a binary MIMK_OP_* with the second operand y placed by y_mode exactly as in mimk_map (0 same shape, 1
+ * [outer, inner] broadcast along the consumer's folded axis, 2 [len*inner] broadcast over `outer`), or a unary one /
+ * MIMK_OP_COPY (y unused, y_mode 3); outer_op: a unary MIMK_OP_* or MIMK_OP_COPY. y has the element type of x. */
+typedef struct mimk_producer {
+    int32_t inner_op, outer_op, y_mode, pad_;
+    const void* y;
+} mimk_producer;
+/* mimk_reduce over produced values: out[o,i] = fold_a pre(x[o,a,i]) in one pass over x -- sum of squares, sum of
+ * exp(x - max) (the softmax denominator), max |x|, sum of (x - mean)^2, a weighted row sum ... -- without the produced
+ * tensor ever being written. The folds run on the same kernels as mimk_reduce (128-bit loads, split axis). dtype F32 or
+ * BF16 (x, y, out); arithmetic in f32. */
+int mimk_reduce_fused(const void* x, const mimk_producer* pre, void* out, int dtype, int64_t outer, int64_t len,
+                      int64_t inner, int monoid, void* stream);
+
 /* y = softmax(x) along the middle axis of a [outer, len, inner] view, in one pass over HBM.
  * Replaces: the four map_reduce_post ops the `softmax` lam expands to (tensor.mim:1172-1176).
  * x F32 (or BF16), y F32 or BF16; statistics in f32. */
@@ -187,6 +204,7 @@ enum {
     MIMK_OP_SUBEXP = 6, /* exp(x - y): the softmax producer, tensor.mim:1175 */
     /* unary (y operand ignored) */
     MIMK_OP_RELU = 16, MIMK_OP_TANH = 17, MIMK_OP_EXP = 18, MIMK_OP_SILU = 19, MIMK_OP_NEG = 20, MIMK_OP_COPY = 21,
+    MIMK_OP_SQUARE = 22, MIMK_OP_ABS = 23,
 };
 /* out[o,a,i] = op(x[o,a,i], y[...]) over a [outer, len, inner] view of x (F32).
  * y_mode 0: y has x's shape (tensor.binary); 1: y is [outer, inner], broadcast along the middle axis
@@ -289,6 +307,13 @@ enum { /* combiners f(acc, ins) */
     MIMK_F_ADD_SUBEXP = 10, /* acc + exp(a - b)              the sum fold of softmax with exp(x - max) inlined */
     MIMK_F_SUBEXP_DIV = 11, /* exp(a - b) / c (acc ignored)  the divide with the exponential recomputed; three inputs */
 };
+/* The general form of a combiner with an inlined producer: f(acc, a [, b]) = fold(acc, outer(inner(a, b))) with
+ * fold one of MIMK_F_ADD / MAX / MIN / FIRST, inner a binary MIMK_OP_* over the two inputs (a, b) or a unary one /
+ * MIMK_OP_COPY over the single input, outer a unary MIMK_OP_* or MIMK_OP_COPY. Floating-point accumulators only.
+ * MIMK_F_ADD_SUBEXP is MIMK_F_COMPOSED(MIMK_F_ADD, MIMK_OP_SUBEXP, MIMK_OP_COPY). When the maps spell a fold along one
+ * axis with the second input broadcast as mimk_producer allows, the instance runs on mimk_reduce_fused. */
+#define MIMK_F_COMPOSED_BASE 0x01000000
+#define MIMK_F_COMPOSED(fold, inner, outer) (MIMK_F_COMPOSED_BASE | (fold) | ((inner) << 8) | ((outer) << 16))
 enum { /* epilogues post(acc, post_ins) */
     MIMK_P_ID = 0,
     MIMK_P_ADD = 1,       /* widen(acc) + p0 (unsigned widening when the output type is wider)  map_reduce_post.mim:19-20 */
@@ -357,6 +382,8 @@ enum {
     MIMK_STEP_SOFTMAX = 1,   /* first operation of a softmax chain: the chain runs as mimk_softmax */
     MIMK_STEP_ATTENTION = 2, /* first operation of an attention chain: the chain runs as mimk_attn_fwd */
     MIMK_STEP_ABSORBED = 3,  /* a later operation of a fused chain */
+    MIMK_STEP_FOLD_OF_MAP = 4, /* an elementwise map whose only reader is the fold after it: the pair runs as
+                                  mimk_reduce_fused and the produced tensor is never written (fuse.cpp:183-358) */
 };
 int mimk_program_classify(const mimk_mrp_desc* ops, int32_t n_ops, int32_t* steps);
 int mimk_program_run(const mimk_mrp_desc* ops, int32_t n_ops, void* stream);

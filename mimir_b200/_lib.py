@@ -16,14 +16,14 @@ SUM, MAX, MIN = 0, 1, 2
 POST_ID, POST_BIAS, POST_BIAS_RELU, POST_BIAS_TANH, POST_RELU, POST_SILU, POST_ADD_FULL = range(7)
 B_KN, B_NK = 0, 1
 OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MAX, OP_MIN, OP_SUBEXP = range(7)
-OP_RELU, OP_TANH, OP_EXP, OP_SILU, OP_NEG, OP_COPY = range(16, 22)
+OP_RELU, OP_TANH, OP_EXP, OP_SILU, OP_NEG, OP_COPY, OP_SQUARE, OP_ABS = range(16, 24)
 E_DEVICE_WAIT = 7
 ROWS_SOFTMAX, ROWS_RMSNORM, ROWS_SOFTMAX_RMSNORM = 0, 1, 2
 
 # every symbol include/mimk.h declares
 SYMBOLS = (
     "mimk_status_str", "mimk_abi_version", "mimk_last_cuda_error", "mimk_device_check", "mimk_device_status", "mimk_selftest_wait_expiry",
-    "mimk_gemm", "mimk_gemm_flat", "mimk_gemm_gather", "mimk_gemm_kpanels", "mimk_reduce", "mimk_reduce_plan", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map", "mimk_map_t",
+    "mimk_gemm", "mimk_gemm_flat", "mimk_gemm_gather", "mimk_gemm_kpanels", "mimk_reduce", "mimk_reduce_fused", "mimk_reduce_plan", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map", "mimk_map_t",
     "mimk_splat", "mimk_select", "mimk_generate_affine", "mimk_gather", "mimk_scatter", "mimk_attn_fwd", "mimk_mlp_gated", "mimk_map_reduce_post", "mimk_mrp_classify", "mimk_program_classify", "mimk_program_run", "mimk_chain_order", "mimk_chain_cost",
     "mimk_host_rows", "mimk_host_rows_pair", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_map_reduce_post", "mimk_host_register",
     "mimk_host_unregister", "mimk_host_release",
@@ -73,9 +73,22 @@ class MlpDesc(C.Structure):
     ]
 
 
+class Producer(C.Structure):
+    """mimk_producer: outer_op(inner_op(v, y[...])) applied to every element a fold reads."""
+    _fields_ = [("inner_op", C.c_int32), ("outer_op", C.c_int32), ("y_mode", C.c_int32), ("pad_", C.c_int32), ("y", C.c_void_p)]
+
+
+F_COMPOSED_BASE = 0x01000000
+
+
+def f_composed(fold: int, inner: int, outer: int = OP_COPY) -> int:
+    """MIMK_F_COMPOSED: the combiner fold(acc, outer(inner(a, b)))."""
+    return F_COMPOSED_BASE | fold | (inner << 8) | (outer << 16)
+
+
 MRP_MAX_LOOPS, MRP_MAX_RANK, MRP_MAX_INPUTS = 8, 6, 4
 F_ADD, F_MULADD, F_MAX, F_MIN, F_FIRST, F_SUBEXP, F_DIV, F_ADD2, F_MUL2, F_MIX, F_ADD_SUBEXP, F_SUBEXP_DIV = range(12)
-STEP_OP, STEP_SOFTMAX, STEP_ATTENTION, STEP_ABSORBED = range(4)
+STEP_OP, STEP_SOFTMAX, STEP_ATTENTION, STEP_ABSORBED, STEP_FOLD_OF_MAP = range(5)
 P_ID, P_ADD, P_ADD_PLUS1, P_ADD_RELU, P_ADD_TANH, P_RELU, P_SILU = range(7)
 
 
@@ -119,6 +132,7 @@ def lib() -> C.CDLL:
         L.mimk_gemm_flat.argtypes = [i64, i64, i64, vp, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp, vp]
         L.mimk_reduce.argtypes = [vp, vp, ci, i64, i64, i64, ci, vp]
         L.mimk_reduce_static.argtypes = [vp, vp, ci, i64, i64, i64, ci, vp]
+        L.mimk_reduce_fused.argtypes = [vp, C.POINTER(Producer), vp, ci, i64, i64, i64, ci, vp]
         L.mimk_reduce_plan.argtypes = [i64, i64, i64, ci, C.POINTER(i64)]
         L.mimk_softmax.argtypes = [vp, vp, ci, ci, i64, i64, i64, vp]
         L.mimk_rmsnorm.argtypes = [vp, vp, vp, ci, ci, i64, i64, cf, vp]

@@ -64,11 +64,21 @@ int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s);
 bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status);
 // What a descriptor's access maps spell, whatever its size (the router itself leaves small instances on the per-cell
 // kernel): route MIMK_ROUTE_*, and the arguments of the specialised entry point that would take it.
+inline bool op_is_binary(int op) { return op >= MIMK_OP_ADD && op <= MIMK_OP_SUBEXP; }
+inline bool op_is_unary(int op) { return op >= MIMK_OP_RELU && op <= MIMK_OP_ABS; }  // COPY included
+// A composed combiner taken apart; false when `comb` is not one or names an unknown part.
+inline bool decode_composed(int comb, int* fold, int* inner, int* outer) {
+    if ((comb & ~0x00ffffff) != MIMK_F_COMPOSED_BASE) return false;
+    *fold = comb & 0xff, *inner = (comb >> 8) & 0xff, *outer = (comb >> 16) & 0xff;
+    if (*fold != MIMK_F_ADD && *fold != MIMK_F_MAX && *fold != MIMK_F_MIN && *fold != MIMK_F_FIRST) return false;
+    return (op_is_binary(*inner) || op_is_unary(*inner)) && op_is_unary(*outer);
+}
 struct MrpPlan {
     int route = MIMK_ROUTE_GENERIC;
     mimk_gemm_desc gemm{};
     int64_t outer = 0, len = 0, inner = 0;  // reduce / map: the [outer, len, inner] view
     int monoid = 0, op = 0, y_mode = 3;
+    int pre_inner = -1, pre_outer = -1, pre_y_mode = 3;  // reduce with an inlined producer (pre_inner >= 0); its y is input 1
     int perm[MIMK_MRP_MAX_RANK] = {};
 };
 MrpPlan mrp_plan(const mimk_mrp_desc& d);
@@ -88,6 +98,26 @@ int attn_tc_pair(const mimk_attn_desc& d, cudaStream_t s);
 
 // ---- device side ----------------------------------------------------------------------------------
 #ifdef __CUDACC__
+// the scalar meaning of MIMK_OP_* (unary ones ignore b)
+__device__ __forceinline__ float apply_op(int op, float a, float b) {
+    switch (op) {
+        case MIMK_OP_ADD: return a + b;
+        case MIMK_OP_SUB: return a - b;
+        case MIMK_OP_MUL: return a * b;
+        case MIMK_OP_DIV: return a / b;
+        case MIMK_OP_MAX: return fmaxf(a, b);
+        case MIMK_OP_MIN: return fminf(a, b);
+        case MIMK_OP_SUBEXP: return expf(a - b);
+        case MIMK_OP_RELU: return fmaxf(0.f, a);
+        case MIMK_OP_TANH: return tanhf(a);
+        case MIMK_OP_EXP: return expf(a);
+        case MIMK_OP_SILU: return a / (1.f + expf(-a));
+        case MIMK_OP_NEG: return -a;
+        case MIMK_OP_SQUARE: return a * a;
+        case MIMK_OP_ABS: return fabsf(a);
+        default: return a;
+    }
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -46,7 +46,17 @@ __device__ __forceinline__ Val combine(int id, int acc_dt, Val acc, const Val* i
             case MIMK_F_MUL2: r.f = in[0].f * in[1].f; break;
             case MIMK_F_ADD_SUBEXP: r.f = acc.f + expf(in[0].f - in[1].f); break;
             case MIMK_F_SUBEXP_DIV: r.f = expf(in[0].f - in[1].f) / in[2].f; break;
-            default: break;
+            default:
+                if (id & MIMK_F_COMPOSED_BASE) {  // fold(acc, outer(inner(a, b))): a producer inlined into the operand read
+                    const float v = apply_op((id >> 16) & 0xff, apply_op((id >> 8) & 0xff, in[0].f, in[1].f), 0.f);
+                    switch (id & 0xff) {
+                        case MIMK_F_ADD: r.f = acc.f + v; break;
+                        case MIMK_F_MAX: r.f = fmaxf(acc.f, v); break;
+                        case MIMK_F_MIN: r.f = fminf(acc.f, v); break;
+                        default: r.f = v; break;
+                    }
+                }
+                break;
         }
     } else {
         unsigned long long a = (unsigned long long)acc.i, x = (unsigned long long)in[0].i, y = (unsigned long long)in[1].i;
@@ -190,17 +200,21 @@ extern "C" int mimk_map_reduce_post(const mimk_mrp_desc* d, void* stream) {
     if (!d) return MIMK_E_ARG;
     if (d->ro < 0 || d->rn < d->ro || d->rn > MIMK_MRP_MAX_LOOPS || d->ro > MIMK_MRP_MAX_RANK) return MIMK_E_ARG;
     if (d->nis < 0 || d->nis > MIMK_MRP_MAX_INPUTS || d->nps < 0 || d->nps > 1) return MIMK_E_ARG;
-    if (d->comb < MIMK_F_ADD || d->comb > MIMK_F_SUBEXP_DIV || d->post < MIMK_P_ID || d->post > MIMK_P_SILU) return MIMK_E_ARG;
+    int c_fold = 0, c_inner = 0, c_outer = 0;
+    const bool composed = decode_composed(d->comb, &c_fold, &c_inner, &c_outer);
+    if (!composed && (d->comb < MIMK_F_ADD || d->comb > MIMK_F_SUBEXP_DIV)) return MIMK_E_ARG;
+    if (d->post < MIMK_P_ID || d->post > MIMK_P_SILU) return MIMK_E_ARG;
     if (d->acc_dtype != MIMK_F32 && d->acc_dtype != MIMK_I32 && d->acc_dtype != MIMK_I64) return MIMK_E_DTYPE;
     const bool facc = d->acc_dtype == MIMK_F32;
     if (facc ? (d->out_dtype != MIMK_F32 && d->out_dtype != MIMK_BF16) : (d->out_dtype != MIMK_I32 && d->out_dtype != MIMK_I64))
         return MIMK_E_DTYPE;
-    const int need = d->comb == MIMK_F_SUBEXP_DIV ? 3
+    const int need = composed ? (op_is_binary(c_inner) ? 2 : 1) : d->comb == MIMK_F_SUBEXP_DIV ? 3
                      : (d->comb == MIMK_F_MULADD || d->comb == MIMK_F_SUBEXP || d->comb == MIMK_F_DIV || d->comb == MIMK_F_ADD2 ||
                         d->comb == MIMK_F_MUL2 || d->comb == MIMK_F_MIX || d->comb == MIMK_F_ADD_SUBEXP) ? 2 : 1;
     if (d->nis != need) return MIMK_E_ARG;
     if (!facc && (d->comb == MIMK_F_SUBEXP || d->comb == MIMK_F_DIV || d->comb == MIMK_F_ADD_SUBEXP || d->comb == MIMK_F_SUBEXP_DIV)) return MIMK_E_DTYPE;
     if (facc && d->comb == MIMK_F_MIX) return MIMK_E_DTYPE;
+    if (composed && !facc) return MIMK_E_DTYPE;
     const bool post_needs = d->post >= MIMK_P_ADD && d->post <= MIMK_P_ADD_TANH;
     if (post_needs != (d->nps == 1)) return MIMK_E_ARG;
     if (!facc && (d->post == MIMK_P_ADD_RELU || d->post == MIMK_P_ADD_TANH || d->post == MIMK_P_SILU)) return MIMK_E_DTYPE;

@@ -114,13 +114,20 @@ bool plan_gemm(const mimk_mrp_desc& d, Plan& p) {
 }
 
 bool plan_reduce(const mimk_mrp_desc& d, Plan& p) {
-    if (d.nis != 1 || d.nps != 0 || d.post != MIMK_P_ID || d.rn != d.ro + 1 || d.ro < 1) return false;
+    // a plain fold, or one whose combiner has an elementwise producer inlined: fold(acc, outer(inner(a [, b])))
+    int fold = d.comb, inner_op = -1, outer_op = MIMK_OP_COPY;
+    const bool composed = decode_composed(d.comb, &fold, &inner_op, &outer_op);
+    if (d.comb == MIMK_F_ADD_SUBEXP) fold = MIMK_F_ADD, inner_op = MIMK_OP_SUBEXP;
+    const int nis = inner_op >= 0 && op_is_binary(inner_op) ? 2 : 1;
+    if (d.nis != nis || d.nps != 0 || d.post != MIMK_P_ID || d.rn != d.ro + 1 || d.ro < 1) return false;
     if (d.acc_dtype != MIMK_F32 || !out_is_identity(d)) return false;
     if ((d.in_dtype[0] != MIMK_F32 && d.in_dtype[0] != MIMK_BF16) || d.out_dtype != d.in_dtype[0]) return false;
+    if (nis == 2 && d.in_dtype[1] != d.in_dtype[0]) return false;
+    (void)composed;
     const uint32_t init = init32(d);
-    if (d.comb == MIMK_F_ADD && init == 0u) p.monoid = MIMK_SUM;
-    else if (d.comb == MIMK_F_MAX && init == 0xff800000u) p.monoid = MIMK_MAX;
-    else if (d.comb == MIMK_F_MIN && init == 0x7f800000u) p.monoid = MIMK_MIN;
+    if (fold == MIMK_F_ADD && init == 0u) p.monoid = MIMK_SUM;
+    else if (fold == MIMK_F_MAX && init == 0xff800000u) p.monoid = MIMK_MAX;
+    else if (fold == MIMK_F_MIN && init == 0x7f800000u) p.monoid = MIMK_MIN;
     else return false;
     const mimk_affine_map& m = d.in_map[0];
     if (m.rows != d.rn) return false;
@@ -134,6 +141,26 @@ bool plan_reduce(const mimk_mrp_desc& d, Plan& p) {
         if (!row_is_loop(m, j, d.rn, l) || d.in_shape[0][j] != d.sr[l]) return false;
     }
     p.outer = prod(d.sr, 0, ax), p.len = d.sr[d.ro], p.inner = prod(d.sr, ax, d.ro);
+    if (inner_op < 0) return true;
+    p.pre_inner = inner_op, p.pre_outer = outer_op, p.pre_y_mode = 3;
+    if (nis == 1) return true;
+    // where the producer's second operand sits relative to the folded operand's axes (axis j of x is loop
+    // j below `ax`, the folded loop at `ax`, loop j - 1 above): all of them (0), all but the folded one (1), or the
+    // folded one and everything after it (2)
+    const mimk_affine_map& y = d.in_map[1];
+    auto loop_of = [&](int j) { return j < ax ? j : j == ax ? d.ro : j - 1; };
+    auto rows_from = [&](int first_axis, int skip) {
+        int j = first_axis;
+        for (int r = 0; r < y.rows; ++r, ++j) {
+            if (j == skip) ++j;
+            if (j >= m.rows || !row_is_loop(y, r, d.rn, loop_of(j)) || d.in_shape[1][r] != d.sr[loop_of(j)]) return false;
+        }
+        return true;
+    };
+    if (y.rows == m.rows && rows_from(0, -1)) p.pre_y_mode = 0;
+    else if (y.rows == m.rows - 1 && rows_from(0, ax)) p.pre_y_mode = 1;
+    else if (y.rows == m.rows - ax && rows_from(ax, -1)) p.pre_y_mode = 2;
+    else return false;
     return true;
 }
 
@@ -275,7 +302,12 @@ bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status) {
     switch (p.route) {
         case MIMK_ROUTE_GEMM: *status = mimk_gemm(&p.gemm, stream); return true;
         case MIMK_ROUTE_REDUCE:
-            *status = mimk_reduce(d.in[0], d.out, d.in_dtype[0], p.outer, p.len, p.inner, p.monoid, stream);
+            if (p.pre_inner >= 0) {
+                const mimk_producer pre{p.pre_inner, p.pre_outer, p.pre_y_mode, 0, d.nis == 2 ? d.in[1] : nullptr};
+                *status = mimk_reduce_fused(d.in[0], &pre, d.out, d.in_dtype[0], p.outer, p.len, p.inner, p.monoid, stream);
+            } else {
+                *status = mimk_reduce(d.in[0], d.out, d.in_dtype[0], p.outer, p.len, p.inner, p.monoid, stream);
+            }
             return true;
         case MIMK_ROUTE_MAP:
             *status = mimk_map_t(p.op, d.in[0], d.nis == 2 ? d.in[1] : nullptr, d.out, d.in_dtype[0], d.out_dtype, p.outer, p.len, p.inner,

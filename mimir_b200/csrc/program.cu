@@ -159,12 +159,45 @@ bool match_attention(const mimk_mrp_desc* ops, int n, int at, Attention& a) {
     return true;
 }
 
+// An elementwise map (unary, binary, binary_ax, bias-style broadcast) followed by a fold of its result along one axis,
+// the result read by nothing else: the fold runs over the produced values without the tensor being written.
+struct FoldOfMap {
+    const void* x = nullptr;
+    void* out = nullptr;
+    mimk_producer pre{};
+    int dtype = 0, monoid = 0;
+    int64_t outer = 0, len = 0, inner = 0;
+};
+bool match_fold_of_map(const mimk_mrp_desc* ops, int n, int at, FoldOfMap& f) {
+    if (at + 2 > n) return false;
+    const mimk_mrp_desc &m = ops[at], &r = ops[at + 1];
+    const MrpPlan pm = mrp_plan(m), pf = mrp_plan(r);
+    if (pm.route != MIMK_ROUTE_MAP || pf.route != MIMK_ROUTE_REDUCE || pf.pre_inner >= 0) return false;
+    if (r.in[0] != m.out || !is_float(m.in_dtype[0]) || m.out_dtype != m.in_dtype[0] || r.in_dtype[0] != m.out_dtype) return false;
+    if (pm.outer * pm.len * pm.inner != pf.outer * pf.len * pf.inner) return false;
+    if (read_outside(ops, n, at, at + 2, m.out)) return false;
+    // where the map's second operand sits in the fold's [outer, len, inner] view
+    int mode = -1;
+    if (pm.y_mode == 3 || pm.y_mode == 0) mode = pm.y_mode;
+    else if (pm.y_mode == 1 && pm.outer == pf.outer && pm.len == pf.len && pm.inner == pf.inner) mode = 1;
+    else if (pm.y_mode == 2 && pm.outer == pf.outer && pm.len == pf.len * pf.inner) mode = 2;
+    else if (pm.y_mode == 2 && pf.outer == 1 && pm.outer == pf.len && pm.len == pf.inner) mode = 1;  // y lacks the leading, folded axis
+    if (mode < 0) return false;
+    const bool unary = pm.y_mode == 3;
+    f.x = m.in[0], f.out = r.out, f.dtype = m.in_dtype[0], f.monoid = pf.monoid;
+    f.outer = pf.outer, f.len = pf.len, f.inner = pf.inner;
+    f.pre.inner_op = pm.op, f.pre.outer_op = MIMK_OP_COPY, f.pre.y_mode = mode, f.pre.pad_ = 0;
+    f.pre.y = unary ? nullptr : m.in[1];
+    return true;
+}
+
 // steps[i] for every operation; returns the number of fused chains.
-int classify(const mimk_mrp_desc* ops, int n, int32_t* steps, Softmax* sm, Attention* at_out) {
+int classify(const mimk_mrp_desc* ops, int n, int32_t* steps, Softmax* sm, Attention* at_out, FoldOfMap* fm_out) {
     int chains = 0;
     for (int i = 0; i < n;) {
         Attention a;
         Softmax s;
+        FoldOfMap fm;
         if (match_attention(ops, n, i, a)) {
             steps[i] = MIMK_STEP_ATTENTION;
             for (int k = 1; k < a.len_ops; ++k) steps[i + k] = MIMK_STEP_ABSORBED;
@@ -175,6 +208,10 @@ int classify(const mimk_mrp_desc* ops, int n, int32_t* steps, Softmax* sm, Atten
             for (int k = 1; k < s.len_ops; ++k) steps[i + k] = MIMK_STEP_ABSORBED;
             if (sm) sm[i] = s;
             i += s.len_ops, ++chains;
+        } else if (match_fold_of_map(ops, n, i, fm)) {
+            steps[i] = MIMK_STEP_FOLD_OF_MAP, steps[i + 1] = MIMK_STEP_ABSORBED;
+            if (fm_out) fm_out[i] = fm;
+            i += 2, ++chains;
         } else {
             steps[i++] = MIMK_STEP_OP;
         }
@@ -196,7 +233,7 @@ extern "C" int mimk_program_classify(const mimk_mrp_desc* ops, int32_t n_ops, in
     if (n_ops < 0 || (n_ops > 0 && (!ops || !steps))) return MIMK_E_ARG;
     for (int i = 0; i < n_ops; ++i)
         if (!sane(ops[i])) return MIMK_E_ARG;
-    classify(ops, n_ops, steps, nullptr, nullptr);
+    classify(ops, n_ops, steps, nullptr, nullptr, nullptr);
     return MIMK_OK;
 }
 
@@ -209,13 +246,17 @@ extern "C" int mimk_program_run(const mimk_mrp_desc* ops, int32_t n_ops, void* s
     int32_t* steps = new int32_t[n_ops];
     Softmax* sm    = new Softmax[n_ops];
     Attention* at  = new Attention[n_ops];
-    classify(ops, n_ops, steps, sm, at);
+    FoldOfMap* fm  = new FoldOfMap[n_ops];
+    classify(ops, n_ops, steps, sm, at, fm);
     int st = MIMK_OK;
     for (int i = 0; i < n_ops && st == MIMK_OK; ++i) {
         switch (steps[i]) {
             case MIMK_STEP_ATTENTION: st = mimk_attn_fwd(&at[i].desc, stream); break;
             case MIMK_STEP_SOFTMAX:
                 st = mimk_softmax(sm[i].x, sm[i].y, sm[i].in_dtype, sm[i].out_dtype, sm[i].outer, sm[i].len, sm[i].inner, stream);
+                break;
+            case MIMK_STEP_FOLD_OF_MAP:
+                st = mimk_reduce_fused(fm[i].x, &fm[i].pre, fm[i].out, fm[i].dtype, fm[i].outer, fm[i].len, fm[i].inner, fm[i].monoid, stream);
                 break;
             case MIMK_STEP_OP: st = mimk_map_reduce_post(&ops[i], stream); break;
             default: break;  // absorbed into the chain before it
@@ -224,5 +265,6 @@ extern "C" int mimk_program_run(const mimk_mrp_desc* ops, int32_t n_ops, void* s
     delete[] steps;
     delete[] sm;
     delete[] at;
+    delete[] fm;
     return st;
 }

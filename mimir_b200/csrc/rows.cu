@@ -209,22 +209,83 @@ __global__ void softmax_strided_kernel(const TIn* __restrict__ x, TOut* __restri
 }
 
 // ---- reduce ------------------------------------------------------------------------------------
-template <class Op, class TIn, class TOut>
+// What a fold does to an element before combining it: nothing, or an inlined elementwise producer (mimk_producer).
+// `cell(o, i)` prepares what is constant along the folded axis of output cell (o, i): the second operand itself (y_mode 1),
+// or the address its elements start from (y_mode 0 and 2), from where they lie at the same stride as x's (a * inner).
+struct NoPre {
+    struct Cell {};
+    __device__ Cell cell(int64_t, int64_t) const { return Cell{}; }
+    __device__ float operator()(float v, const Cell&, int64_t) const { return v; }
+    __device__ float4 four(float4 v, const Cell&, int64_t) const { return v; }
+};
+// INNER / YMODE: the producer's first operator and the placement of its second operand fixed at compile time (the element
+// loop then holds no dispatch and no dead addressing), or -1 for the run-time form that takes any of them at a few times
+// the cost per element.
+template <class TIn, int INNER, int YMODE>
+struct MapPre {
+    int inner_op, outer_op, y_mode;
+    const TIn* y;
+    int64_t len, inner;
+    struct Cell {
+        const TIn* yp;
+        float yb;
+    };
+    static constexpr bool binary  = INNER < 0 || (INNER >= MIMK_OP_ADD && INNER <= MIMK_OP_SUBEXP);
+    __device__ int mode() const { return YMODE >= 0 ? YMODE : y_mode; }
+    __device__ bool per_element() const { return binary && (mode() == 0 || mode() == 2); }  // y read with every element
+    __device__ Cell cell(int64_t o, int64_t i) const {
+        Cell c{nullptr, 0.f};
+        if (!binary) return c;
+        if (mode() == 0) c.yp = y + o * len * inner + i;
+        else if (mode() == 2) c.yp = y + i;
+        else if (mode() == 1) c.yb = ldf(y, o * inner + i);
+        return c;
+    }
+    __device__ float apply(float v, float b) const {
+        float r;
+        switch (INNER) {
+            case MIMK_OP_ADD: r = v + b; break;
+            case MIMK_OP_SUB: r = v - b; break;
+            case MIMK_OP_MUL: r = v * b; break;
+            case MIMK_OP_SUBEXP: r = expf(v - b); break;
+            case MIMK_OP_RELU: r = fmaxf(0.f, v); break;
+            case MIMK_OP_EXP: r = expf(v); break;
+            case MIMK_OP_COPY: r = v; break;
+            case MIMK_OP_SQUARE: r = v * v; break;
+            case MIMK_OP_ABS: r = fabsf(v); break;
+            default: r = apply_op(inner_op, v, b); break;
+        }
+        return outer_op == MIMK_OP_COPY ? r : apply_op(outer_op, r, 0.f);
+    }
+    // element at offset `off` (= a * inner) from the cell's start
+    __device__ float operator()(float v, const Cell& c, int64_t off) const {
+        const float b = per_element() ? ldf(c.yp, off) : c.yb;
+        return apply(v, b);
+    }
+    // four consecutive elements of a row (inner == 1); the second operand's four come in one 128-bit load
+    __device__ float4 four(float4 v, const Cell& c, int64_t off) const {
+        float4 b = make_float4(c.yb, c.yb, c.yb, c.yb);
+        if (per_element()) b = load4(c.yp + off);
+        return make_float4(apply(v.x, b.x), apply(v.y, b.y), apply(v.z, b.z), apply(v.w, b.w));
+    }
+};
+template <class Op, class TIn, class TOut, class Pre>
 __global__ void __launch_bounds__(256) reduce_rows_kernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t rows,
-                                                         int64_t cols, int vec_ok) {
+                                                         int64_t cols, int vec_ok, const Pre pre) {
     __shared__ float red[32];
     Op op;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const TIn* xr = x + row * cols;
         float acc     = Op::ident();
+        const typename Pre::Cell cell = pre.cell(row, 0);
         if (vec_ok) {
             const int64_t nvec = cols >> 2;
             for (int64_t i = threadIdx.x; i < nvec; i += 256) {
-                float4 v = load4(xr + 4 * i);
-                acc      = op(acc, op(op(v.x, v.y), op(v.z, v.w)));
+                const float4 v = pre.four(load4(xr + 4 * i), cell, 4 * i);
+                acc            = op(acc, op(op(v.x, v.y), op(v.z, v.w)));
             }
         } else {
-            for (int64_t c = threadIdx.x; c < cols; c += 256) acc = op(acc, ldf(xr, c));
+            for (int64_t c = threadIdx.x; c < cols; c += 256) acc = op(acc, pre(ldf(xr, c), cell, c));
         }
         acc = block_reduce<256>(acc, red, op);
         if (threadIdx.x == 0) stf(out, row, acc);
@@ -233,9 +294,9 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const TIn* __restrict_
 
 // inner > 1: thread per (o, i) column; blockIdx.y splits the reduced axis into `gridDim.y` slices whose partial
 // results go to `partial` [slice, outer*inner] (or straight to `out` when there is a single slice).
-template <class Op, class TIn, class TDst>
+template <class Op, class TIn, class TDst, class Pre>
 __global__ void reduce_mid_kernel(const TIn* __restrict__ x, TDst* __restrict__ dst, int64_t outer, int64_t len,
-                                  int64_t inner, int64_t slice_len) {
+                                  int64_t inner, int64_t slice_len, const Pre pre) {
     Op op;
     const int64_t total = outer * inner;
     const int64_t a0    = int64_t(blockIdx.y) * slice_len;
@@ -244,7 +305,8 @@ __global__ void reduce_mid_kernel(const TIn* __restrict__ x, TDst* __restrict__ 
         const int64_t o = t / inner, i = t % inner;
         const TIn* p = x + o * len * inner + i;
         float acc    = Op::ident();
-        for (int64_t a = a0; a < a1; ++a) acc = op(acc, ldf(p, a * inner));
+        const typename Pre::Cell cell = pre.cell(o, i);
+        for (int64_t a = a0; a < a1; ++a) acc = op(acc, pre(ldf(p, a * inner), cell, a * inner));
         stf(dst, int64_t(blockIdx.y) * total + t, acc);
     }
 }
@@ -260,23 +322,6 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, TOut* 
 }
 
 // ---- elementwise -------------------------------------------------------------------------------
-__device__ __forceinline__ float apply_op(int op, float a, float b) {
-    switch (op) {
-        case MIMK_OP_ADD: return a + b;
-        case MIMK_OP_SUB: return a - b;
-        case MIMK_OP_MUL: return a * b;
-        case MIMK_OP_DIV: return a / b;
-        case MIMK_OP_MAX: return fmaxf(a, b);
-        case MIMK_OP_MIN: return fminf(a, b);
-        case MIMK_OP_SUBEXP: return expf(a - b);
-        case MIMK_OP_RELU: return fmaxf(0.f, a);
-        case MIMK_OP_TANH: return tanhf(a);
-        case MIMK_OP_EXP: return expf(a);
-        case MIMK_OP_SILU: return a / (1.f + expf(-a));
-        case MIMK_OP_NEG: return -a;
-        default: return a;
-    }
-}
 template <class TIn, class TOut>
 __global__ void map_kernel(int op, const TIn* __restrict__ x, const TIn* __restrict__ y, TOut* __restrict__ out,
                            int64_t outer, int64_t len, int64_t inner, int y_mode) {
@@ -403,25 +448,30 @@ ReducePlan reduce_plan(int64_t outer, int64_t len, int64_t inner, int sm_count) 
 // `partials(n, &ptr)` supplies room for n floats when the plan splits the axis: the cached allocation for mimk_reduce,
 // the array in the library image for mimk_reduce_static. Nothing there needs clearing: every partial the second kernel
 // reads is written by the first kernel of the same call.
-template <class Op, class TIn, class TOut, class Partials>
+inline bool pre_vec_ok(const NoPre&) { return true; }
+template <class TIn, int INNER, int YMODE>
+bool pre_vec_ok(const MapPre<TIn, INNER, YMODE>& p) {  // the second operand's 128-bit loads need its rows aligned too
+    return !MapPre<TIn, INNER, YMODE>::binary || (p.y_mode != 0 && p.y_mode != 2) || reinterpret_cast<uintptr_t>(p.y) % (4 * sizeof(TIn)) == 0;
+}
+template <class Op, class TIn, class TOut, class Partials, class Pre = NoPre>
 int reduce_impl(const TIn* x, TOut* out, int64_t outer, int64_t len, int64_t inner, cudaStream_t s, int sm_count,
-                Partials partials) {
+                Partials partials, Pre pre = Pre()) {
     if (inner == 1) {
-        const int vec_ok = (len % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(TIn))) == 0;
+        const int vec_ok = (len % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(TIn))) == 0 && pre_vec_ok(pre);
         int grid         = int(outer < int64_t(sm_count) * 8 ? outer : int64_t(sm_count) * 8);
-        reduce_rows_kernel<Op><<<grid, 256, 0, s>>>(x, out, outer, len, vec_ok);
+        reduce_rows_kernel<Op><<<grid, 256, 0, s>>>(x, out, outer, len, vec_ok, pre);
         return launch_status();
     }
     const int64_t total = outer * inner;
     const int threads   = 256;
     const ReducePlan p  = reduce_plan(outer, len, inner, sm_count);
     if (p.slices == 1) {
-        reduce_mid_kernel<Op><<<dim3(p.gx, 1), threads, 0, s>>>(x, out, outer, len, inner, len);
+        reduce_mid_kernel<Op><<<dim3(p.gx, 1), threads, 0, s>>>(x, out, outer, len, inner, len, pre);
         return launch_status();
     }
     float* scratch = nullptr;
     MIMK_TRY(partials(size_t(p.slices) * size_t(total), &scratch));
-    reduce_mid_kernel<Op><<<dim3(p.gx, p.slices), threads, 0, s>>>(x, scratch, outer, len, inner, p.slice_len);
+    reduce_mid_kernel<Op><<<dim3(p.gx, p.slices), threads, 0, s>>>(x, scratch, outer, len, inner, p.slice_len, pre);
     MIMK_TRY(launch_status());
     reduce_partials_kernel<Op><<<p.gx, threads, 0, s>>>(static_cast<const float*>(scratch), out, total, p.slices);
     return launch_status();
@@ -515,6 +565,72 @@ extern "C" int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, i
         case MIMK_MAX: return reduce_impl<MaxOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials());
         default: return reduce_impl<MinOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials());
     }
+}
+
+namespace mimk {
+namespace {
+template <class T, int INNER, int YMODE>
+int reduce_fused_inner(const T* x, const mimk_producer& pr, T* out, int64_t outer, int64_t len, int64_t inner, int monoid,
+                       cudaStream_t s, int sm_count) {
+    const MapPre<T, INNER, YMODE> pre{pr.inner_op, pr.outer_op, pr.y_mode, static_cast<const T*>(pr.y), len, inner};
+    switch (monoid) {
+        case MIMK_SUM: return reduce_impl<SumOp>(x, out, outer, len, inner, s, sm_count, CachedPartials(), pre);
+        case MIMK_MAX: return reduce_impl<MaxOp>(x, out, outer, len, inner, s, sm_count, CachedPartials(), pre);
+        default: return reduce_impl<MinOp>(x, out, outer, len, inner, s, sm_count, CachedPartials(), pre);
+    }
+}
+template <class T, int INNER>
+int reduce_fused_binary(const T* x, const mimk_producer& pr, T* out, int64_t outer, int64_t len, int64_t inner, int monoid,
+                        cudaStream_t s, int sm_count) {
+    switch (pr.y_mode) {
+        case 0: return reduce_fused_inner<T, INNER, 0>(x, pr, out, outer, len, inner, monoid, s, sm_count);
+        case 1: return reduce_fused_inner<T, INNER, 1>(x, pr, out, outer, len, inner, monoid, s, sm_count);
+        default: return reduce_fused_inner<T, INNER, 2>(x, pr, out, outer, len, inner, monoid, s, sm_count);
+    }
+}
+template <class T>
+int reduce_fused_typed(const T* x, const mimk_producer& pr, T* out, int64_t outer, int64_t len, int64_t inner, int monoid,
+                       cudaStream_t s, int sm_count) {
+#define MIMK_FUSED_BINARY(OP) case OP: return reduce_fused_binary<T, OP>(x, pr, out, outer, len, inner, monoid, s, sm_count);
+#define MIMK_FUSED_UNARY(OP) case OP: return reduce_fused_inner<T, OP, 3>(x, pr, out, outer, len, inner, monoid, s, sm_count);
+    switch (pr.inner_op) {
+        MIMK_FUSED_BINARY(MIMK_OP_ADD)
+        MIMK_FUSED_BINARY(MIMK_OP_SUB)
+        MIMK_FUSED_BINARY(MIMK_OP_MUL)
+        MIMK_FUSED_BINARY(MIMK_OP_SUBEXP)
+        MIMK_FUSED_UNARY(MIMK_OP_RELU)
+        MIMK_FUSED_UNARY(MIMK_OP_EXP)
+        MIMK_FUSED_UNARY(MIMK_OP_COPY)
+        MIMK_FUSED_UNARY(MIMK_OP_SQUARE)
+        MIMK_FUSED_UNARY(MIMK_OP_ABS)
+        default: return reduce_fused_inner<T, -1, -1>(x, pr, out, outer, len, inner, monoid, s, sm_count);
+    }
+#undef MIMK_FUSED_BINARY
+#undef MIMK_FUSED_UNARY
+}
+}  // namespace
+}  // namespace mimk
+
+extern "C" int mimk_reduce_fused(const void* x, const mimk_producer* pre, void* out, int dtype, int64_t outer, int64_t len,
+                                 int64_t inner, int monoid, void* stream) {
+    using namespace mimk;
+    if (!pre) return mimk_reduce(x, out, dtype, outer, len, inner, monoid, stream);
+    if (outer < 0 || len < 0 || inner < 0) return MIMK_E_ARG;
+    if (dtype != MIMK_F32 && dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    if (monoid < MIMK_SUM || monoid > MIMK_MIN) return MIMK_E_ARG;
+    const bool binary = op_is_binary(pre->inner_op);
+    if ((!binary && !op_is_unary(pre->inner_op)) || !op_is_unary(pre->outer_op)) return MIMK_E_ARG;
+    if (binary ? (pre->y_mode < 0 || pre->y_mode > 2) : pre->y_mode != 3) return MIMK_E_ARG;
+    int st          = MIMK_OK;
+    DeviceInfo* dev = device_info(&st);
+    if (!dev) return st;
+    if (outer * inner == 0) return MIMK_OK;
+    if (!out || (len > 0 && (!x || (binary && !pre->y)))) return MIMK_E_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == MIMK_BF16)
+        return reduce_fused_typed(static_cast<const __nv_bfloat16*>(x), *pre, static_cast<__nv_bfloat16*>(out), outer, len, inner, monoid, s,
+                                  dev->sm_count);
+    return reduce_fused_typed(static_cast<const float*>(x), *pre, static_cast<float*>(out), outer, len, inner, monoid, s, dev->sm_count);
 }
 
 extern "C" int mimk_reduce_plan(int64_t outer, int64_t len, int64_t inner, int sm_count, int64_t* partial_floats) {
@@ -621,7 +737,7 @@ int map_impl(int op, const TIn* x, const TIn* y, void* out, int out_dtype, int64
 extern "C" int mimk_map_t(int op, const void* x, const void* y, void* out, int in_dtype, int out_dtype, int64_t outer, int64_t len,
                           int64_t inner, int y_mode, void* stream) {
     if (outer < 0 || len < 0 || inner < 0 || y_mode < 0 || y_mode > 3) return MIMK_E_ARG;
-    const bool unary = op >= MIMK_OP_RELU && op <= MIMK_OP_COPY;
+    const bool unary = op_is_unary(op);
     const bool binary = op >= MIMK_OP_ADD && op <= MIMK_OP_SUBEXP;
     if (!unary && !binary) return MIMK_E_ARG;
     if (binary && y_mode == 3) return MIMK_E_ARG;

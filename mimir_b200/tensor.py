@@ -23,7 +23,8 @@ _POST = {None: L.POST_ID, "id": L.POST_ID, "bias": L.POST_BIAS, "bias_relu": L.P
          "bias_tanh": L.POST_BIAS_TANH, "relu": L.POST_RELU, "silu": L.POST_SILU, "add": L.POST_ADD_FULL}
 _BINOP = {"add": L.OP_ADD, "sub": L.OP_SUB, "mul": L.OP_MUL, "div": L.OP_DIV, "max": L.OP_MAX, "min": L.OP_MIN,
           "subexp": L.OP_SUBEXP}
-_UNOP = {"relu": L.OP_RELU, "tanh": L.OP_TANH, "exp": L.OP_EXP, "silu": L.OP_SILU, "neg": L.OP_NEG, "copy": L.OP_COPY}
+_UNOP = {"relu": L.OP_RELU, "tanh": L.OP_TANH, "exp": L.OP_EXP, "silu": L.OP_SILU, "neg": L.OP_NEG, "copy": L.OP_COPY,
+         "square": L.OP_SQUARE, "abs": L.OP_ABS}
 
 
 def _stream() -> int:
@@ -158,6 +159,38 @@ def reduce(monoid: str, ax: int, x: torch.Tensor) -> torch.Tensor:
     out = torch.empty(x.shape[:ax] + x.shape[ax + 1:], dtype=x.dtype, device=x.device)
     L.check(L.lib().mimk_reduce(x.data_ptr(), out.data_ptr(), _dt(x), outer, ln, inner, _MONOID[monoid], _stream()),
             "reduce")
+    return out
+
+
+def reduce_fused(monoid: str, ax: int, x: torch.Tensor, inner: str, y: torch.Tensor | None = None, outer: str = "copy") -> torch.Tensor:
+    """`reduce (g, init) ax` of an elementwise producer of x that is never written: every element v becomes
+    outer(inner(v, y)) as the fold reads it -- what `fuse_tensor` makes of a map feeding a reduce (phase/fuse.cpp:183-358).
+    `inner` is a binary operator name with `y` of x's shape, of x's shape without axis `ax` (binary_ax), or of x's trailing
+    axes from `ax` on; or a unary name with y = None. `outer` is a unary name."""
+    _dev(x)
+    _same_float(x)
+    x = x.contiguous()
+    ax, outer_n, ln, inner_n = _view3(x, ax)
+    pre = L.Producer()
+    pre.outer_op = _UNOP[outer]
+    if y is None:
+        pre.inner_op, pre.y_mode, pre.y = _UNOP[inner], 3, None
+    else:
+        _dev(y)
+        _same_float(x, y)
+        y = y.contiguous()
+        if tuple(y.shape) == tuple(x.shape):
+            pre.y_mode = 0
+        elif tuple(y.shape) == tuple(x.shape[:ax] + x.shape[ax + 1:]):
+            pre.y_mode = 1
+        elif tuple(y.shape) == tuple(x.shape[ax:]):
+            pre.y_mode = 2
+        else:
+            raise ValueError("reduce_fused: y must have x's shape, x's shape without axis ax, or x's axes from ax on")
+        pre.inner_op, pre.y = _BINOP[inner], y.data_ptr()
+    out = torch.empty(x.shape[:ax] + x.shape[ax + 1:], dtype=x.dtype, device=x.device)
+    L.check(L.lib().mimk_reduce_fused(x.data_ptr(), C.byref(pre), out.data_ptr(), _dt(x), outer_n, ln, inner_n, _MONOID[monoid],
+                                      _stream()), "reduce_fused")
     return out
 
 
@@ -434,7 +467,7 @@ def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_ma
 
 
 # ------------------------------------------------------------------------------------------------ programs
-STEPS = {0: "op", 1: "softmax", 2: "attention", 3: "absorbed"}
+STEPS = {0: "op", 1: "softmax", 2: "attention", 3: "absorbed", 4: "fold_of_map"}
 
 
 class Operand:
@@ -476,7 +509,8 @@ class Program:
         return arr
 
     def classify(self):
-        """How each operation would run: "op", "softmax" / "attention" (first operation of a fused chain), "absorbed"."""
+        """How each operation would run: "op", "softmax" / "attention" / "fold_of_map" (first operation of a fused
+        chain), "absorbed"."""
         steps = (C.c_int32 * max(len(self.descs), 1))()
         L.check(L.lib().mimk_program_classify(self._array(), len(self.descs), steps), "program_classify")
         return [STEPS[steps[i]] for i in range(len(self.descs))]

@@ -26,6 +26,14 @@ _DT2NP = {I32: np.int32, I64: np.int64, F32: np.float32, F64: np.float64, BF16: 
 F_ADD_I32, F_MULADD_I32, F_MIX_I32_I64, F_ADD_F32, F_MULADD_F32, F_FMAX_F32, F_SUBEXP_F32, F_DIV_F32 = range(8)
 F_ADD2_F32, F_FIRST_F32, F_MULADD_F64, F_ADD_F64, F_FMIN_F32, F_MUL2_F32, F_FIRST_I32 = range(8, 15)
 F_ADD_SUBEXP_F32, F_SUBEXP_DIV_F32 = 15, 16
+# fold(acc, outer(inner(u, v))) in f32 -- a combiner with an elementwise producer inlined (fuse.cpp:183-358).
+# fold: 0 add, 2 fmax, 3 fmin, 4 first; inner / outer: the elementwise op numbers of the interpreter (0 add .. 6 exp(u - v),
+# 16 relu .. 21 identity, 22 square, 23 abs)
+F_COMPOSED = 0x01000000
+
+
+def f_composed(fold: int, inner: int, outer: int = 21) -> int:
+    return F_COMPOSED | fold | (inner << 8) | (outer << 16)
 P_ID, P_CONV_ADD_I64, P_ADD_PLUS1_I32, P_BIAS_RELU_F32, P_BIAS_TANH_F32, P_BIAS_F32, P_F64_TO_F32 = range(7)
 
 

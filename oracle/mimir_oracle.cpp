@@ -113,6 +113,12 @@ enum {
     MO_F_FIRST_I32 = 14,
     MO_F_ADD_SUBEXP_F32 = 15,  // acc + exp(u - v): the sum fold of softmax with its producer inlined (fuse.cpp:225-245)
     MO_F_SUBEXP_DIV_F32 = 16,  // exp(u - v) / w: the divide with the exponential recomputed
+    // The general form of a combiner after fuse_map_reduce inlined an injective elementwise producer into the operand read
+    // (src/mim/plug/tensor/phase/fuse.cpp:183-358): id = MO_F_COMPOSED | fold | inner << 8 | outer << 16 computes
+    // fold(acc, outer(inner(u, v))) in f32, one rounding per operation. fold: 0 add, 2 fmax, 3 fmin, 4 first; inner / outer:
+    // 0 add, 1 sub, 2 mul, 3 div, 4 fmax, 5 fmin, 6 exp(u - v); 16 relu, 17 tanh, 18 exp, 19 x / (1 + exp(-x)), 20 neg,
+    // 21 identity, 22 square, 23 abs.
+    MO_F_COMPOSED = 0x01000000,
 };
 enum {
     MO_P_ID = 0,
@@ -124,8 +130,38 @@ enum {
     MO_P_F64_TO_F32 = 6,      // truth mode: narrow once at the end
 };
 
+static inline float elementwise(int op, float a, float b) {
+    switch (op) {
+        case 0: return a + b;
+        case 1: return a - b;
+        case 2: return a * b;
+        case 3: return a / b;
+        case 4: return std::fmax(a, b);
+        case 5: return std::fmin(a, b);
+        case 6: return std::exp(a - b);
+        case 16: return std::fmax(0.0f, a);
+        case 17: return std::tanh(a);
+        case 18: return std::exp(a);
+        case 19: return a / (1.0f + std::exp(-a));
+        case 20: return -a;
+        case 22: return a * a;
+        case 23: return std::fabs(a);
+        default: return a;
+    }
+}
 static inline Val comb(int id, Val acc, const Val* in) {
     Val r = acc;
+    if (id & MO_F_COMPOSED) {
+        volatile float inner = elementwise((id >> 8) & 0xff, in[0].f32, in[1].f32);  // one rounding per op: no contraction
+        volatile float v     = elementwise((id >> 16) & 0xff, inner, 0.0f);
+        switch (id & 0xff) {
+            case 0: r.f32 = acc.f32 + v; break;
+            case 2: r.f32 = std::fmax(acc.f32, v); break;
+            case 3: r.f32 = std::fmin(acc.f32, v); break;
+            default: r.f32 = v; break;
+        }
+        return r;
+    }
     switch (id) {
         case MO_F_ADD_I32: r.i32 = int32_t(uint32_t(acc.i32) + uint32_t(in[0].i32)); break;
         case MO_F_MULADD_I32: r.i32 = int32_t(uint32_t(acc.i32) + uint32_t(in[0].i32) * uint32_t(in[1].i32)); break;

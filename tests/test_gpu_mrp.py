@@ -363,3 +363,39 @@ def test_large_reshape_read_through_at_scale(T, L):
     got = T.map_reduce_post((600,), (600, 4096), L.F_ADD, 0.0, L.P_ID, T.proj_map(2, (0,)), [comp], [cu(x)])
     T.device_status()
     assert np.array_equal(got.cpu().numpy(), x.reshape(4096, 600).sum(0))
+
+
+def test_composed_combiners_small_and_large(T, L):
+    """fold(acc, outer(inner(a, b))) through the descriptor: the per-cell kernel on small instances (bit-equal to the
+    interpreter for exactly rounded operations), the fold kernels with the producer inlined on large ones."""
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((6, 7, 5)).astype(np.float32)
+    y = rng.standard_normal((6, 5)).astype(np.float32)
+    sub_sq = L.f_composed(L.F_ADD, L.OP_SUB, L.OP_SQUARE)
+    got = T.map_reduce_post((6, 5), (6, 5, 7), sub_sq, 0.0, L.P_ID, T.proj_map(3, (0, 1)),
+                            [T.proj_map(3, (0, 2, 1)), T.proj_map(3, (0, 1))], [cu(x), cu(y)])
+    want = mo.map_reduce_post((6, 5), (6, 5, 7), mo.f_composed(0, 1, 22), np.float32(0), mo.P_ID, T.proj_map(3, (0, 1)),
+                              [T.proj_map(3, (0, 2, 1)), T.proj_map(3, (0, 1))], [x, y])
+    assert np.allclose(got.cpu().numpy(), want, rtol=1e-6, atol=1e-6)
+    mabs = T.map_reduce_post((6, 5), (6, 5, 7), L.f_composed(L.F_MAX, L.OP_ABS), float("-inf"), L.P_ID, T.proj_map(3, (0, 1)),
+                             [T.proj_map(3, (0, 2, 1))], [cu(x)])
+    assert np.array_equal(mabs.cpu().numpy(), np.abs(x).max(axis=1))
+    # a map (no fold) with a producer chain: FIRST(relu(a * b))
+    e = T.map_reduce_post((6, 7, 5), (6, 7, 5), L.f_composed(L.F_FIRST, L.OP_MUL, L.OP_RELU), 0.0, L.P_ID, T.id_map(3),
+                          [T.id_map(3), T.proj_map(3, (0, 2))], [cu(x), cu(y)])
+    assert np.array_equal(e.cpu().numpy(), np.maximum(x * y[:, None, :], 0))
+    # integer accumulators take no composed combiner
+    xi = cu(np.arange(12, dtype=np.int32).reshape(3, 4))
+    with pytest.raises(RuntimeError):
+        T.map_reduce_post((3,), (3, 4), L.f_composed(L.F_ADD, L.OP_SQUARE), 0, L.P_ID, T.proj_map(2, (0,)), [T.id_map(2)], [xi],
+                          acc_dtype=torch.int32)
+    # large: routed to the fold kernel
+    X = rng.standard_normal((512, 4096)).astype(np.float32)
+    m = X.max(axis=1)
+    desc = dict(So=(512,), Sr=(512, 4096), init=0.0, post=L.P_ID, map_out=T.proj_map(2, (0,)))
+    assert T.mrp_route([512], [512, 4096], L.f_composed(L.F_ADD, L.OP_SUBEXP), 0.0, L.P_ID, T.proj_map(2, (0,)),
+                       [T.id_map(2), T.proj_map(2, (0,))], [[512, 4096], [512]], [torch.float32, torch.float32]) == "reduce"
+    den = T.map_reduce_post(desc["So"], desc["Sr"], L.f_composed(L.F_ADD, L.OP_SUBEXP), 0.0, L.P_ID, desc["map_out"],
+                            [T.id_map(2), T.proj_map(2, (0,))], [cu(X), cu(m)])
+    want = np.exp(X.astype(np.float64) - m[:, None]).sum(axis=1)
+    assert np.abs(den.cpu().numpy() - want).max() / np.abs(want).max() < 1e-5

@@ -129,3 +129,40 @@ def test_attention_program_at_scale_runs_the_tensor_core_kernel(TL):
     heads = [0, 5]
     want = mo.attention(bits(q), bits(k), bits(v), scale=1.0, causal=False, bf16=True, heads=heads)
     assert nerr(f64(o[heads]), want) <= TOL_BF16 and torch.isnan(s.float()).all()
+
+
+def test_centred_sum_as_a_program_of_a_map_and_folds(TL):
+    """A plain fold, then the map x + (-mean) (binary_ax) and the fold of its result: the map -> fold pair runs fused (the
+    tensor x - mean is never written: it stays NaN) and gives what the op-by-op run and numpy give."""
+    T, L = TL
+    x = randn((96, 700, 12), 41)
+    xn = x.cpu().numpy().astype(np.float64)
+    shape, red = list(x.shape), [96, 12]
+
+    def build(P, keep):
+        s = P.op(new(red), red + [700], L.F_ADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, (0, 2, 1))], [x])
+        d = P.op(new(shape), shape, L.F_ADD2, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.proj_map(3, (0, 2))], [x, keep["neg_mean"]])
+        keep["d"] = d
+        a = P.op(new(red), red + [700], L.F_ADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, (0, 2, 1))], [d])
+        return s, a
+
+    neg_mean = torch.from_numpy((-xn.mean(axis=1)).astype(np.float32)).cuda()
+    keep = {"neg_mean": neg_mean}
+    P = T.Program()
+    s, a = build(P, keep)
+    assert P.classify() == ["op", "fold_of_map", "absorbed"]
+    P.run()
+    T.device_status()
+    assert torch.isnan(keep["d"]).all()                       # the produced tensor was never written
+    want = (xn - xn.mean(axis=1, keepdims=True)).sum(axis=1)
+    assert np.abs(f64(a) - want).max() < 1e-3                  # sums of ~700 centred values: absolute tolerance
+    assert nerr(f64(s), xn.sum(axis=1)) < TOL_F32
+    # op by op gives the same numbers (other summation order inside the fold kernels: tolerance, not bits)
+    keep2 = {"neg_mean": neg_mean}
+    ops = T.Program()
+    s2, a2 = build(ops, keep2)
+    for dsc in ops.descs:
+        L.check(L.lib().mimk_map_reduce_post(dsc, None), "op by op")
+    torch.cuda.synchronize()
+    assert not torch.isnan(keep2["d"]).any()
+    assert np.abs(f64(a) - f64(a2)).max() < 1e-3

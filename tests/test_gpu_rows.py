@@ -193,3 +193,59 @@ def test_reduce_on_bf16_operands():
             want = x.double().sum(ax)
             assert s.dtype == torch.bfloat16
             assert ((s.double() - want).abs().max() / want.abs().max()).item() <= TOL_BF16
+
+
+@pytest.mark.parametrize("shape,ax", [((37, 1000), 1), ((64, 4096), 1), ((6, 300, 40), 1), ((2048, 96), 0), ((3, 5, 7), 2),
+                                      ((8, 4100, 24), 1)])
+def test_reduce_with_an_inlined_producer(T, shape, ax):
+    """Folds over produced values (phase/fuse.cpp:183-358): the produced tensor is never written."""
+    x = randn(shape, 5 + ax + shape[-1])
+    xn = x.cpu().numpy().astype(np.float64)
+    red_shape = tuple(s for i, s in enumerate(shape) if i != ax)
+    # sum of squares (RMSNorm's statistic), largest magnitude
+    assert nerr(f64(T.reduce_fused("sum", ax, x, "square")), (xn * xn).sum(axis=ax)) < TOL_F32
+    assert np.array_equal(T.reduce_fused("max", ax, x, "abs").cpu().numpy(), np.abs(x.cpu().numpy()).max(axis=ax))
+    # the softmax denominator: sum of exp(x - max), y broadcast along the folded axis
+    mx = T.reduce("max", ax, x)
+    den = T.reduce_fused("sum", ax, x, "subexp", mx)
+    want = np.exp(xn - np.expand_dims(xn.max(axis=ax), ax)).sum(axis=ax)
+    assert den.shape == red_shape and nerr(f64(den), want) < TOL_F32
+    # variance numerator: sum of (x - mean)^2
+    mean = randn(red_shape, 17)
+    got = T.reduce_fused("sum", ax, x, "sub", mean, outer="square")
+    want = ((xn - np.expand_dims(mean.cpu().numpy().astype(np.float64), ax)) ** 2).sum(axis=ax)
+    assert nerr(f64(got), want) < TOL_F32
+    # y of x's shape (a dot product along the axis), and y over the axes from the folded one on (weights)
+    y0 = randn(shape, 23)
+    assert nerr(f64(T.reduce_fused("sum", ax, x, "mul", y0)), (xn * y0.cpu().numpy().astype(np.float64)).sum(axis=ax)) < TOL_F32
+    w = randn(shape[ax:], 29)
+    assert nerr(f64(T.reduce_fused("sum", ax, x, "mul", w, outer="relu")),
+                np.maximum(xn * w.cpu().numpy().astype(np.float64), 0).sum(axis=ax)) < TOL_F32
+    # operators without a compile-time instance go through the run-time form: unary (no operand at all), binary in each placement
+    assert nerr(f64(T.reduce_fused("sum", ax, x, "tanh")), np.tanh(xn).sum(axis=ax)) < TOL_F32
+    assert nerr(f64(T.reduce_fused("max", ax, x, "neg", outer="silu")), ((-xn) / (1 + np.exp(xn))).max(axis=ax)) < TOL_F32
+    assert nerr(f64(T.reduce_fused("sum", ax, x, "max", y0)), np.maximum(xn, y0.cpu().numpy().astype(np.float64)).sum(axis=ax)) < TOL_F32
+    pos = uniform(red_shape, 31, 0.5, 2.0)
+    assert nerr(f64(T.reduce_fused("sum", ax, x, "div", pos)),
+                (xn / np.expand_dims(pos.cpu().numpy().astype(np.float64), ax)).sum(axis=ax)) < TOL_F32
+    assert nerr(f64(T.reduce_fused("min", ax, x, "min", w)), np.minimum(xn, w.cpu().numpy().astype(np.float64)).min(axis=ax)) < TOL_F32
+
+
+def test_reduce_with_an_inlined_producer_bf16_and_arguments(T):
+    from mimir_b200 import _lib as L
+    x = randn((300, 2048), 3).to(torch.bfloat16)
+    xn = x.float().cpu().numpy().astype(np.float64)
+    got = T.reduce_fused("sum", 1, x, "square")
+    assert got.dtype == torch.bfloat16 and nerr(f64(got.float()), (xn * xn).sum(axis=1)) < TOL_BF16
+    # the same fold as the composition that writes the produced tensor
+    two_pass = T.reduce("sum", 1, T.binary("mul", x.float(), x.float()))
+    assert nerr(f64(got.float()), f64(two_pass)) < TOL_BF16
+    # a binary producer needs its operand and a placement; a unary one takes none
+    pre = L.Producer()
+    pre.inner_op, pre.outer_op, pre.y_mode, pre.y = L.OP_SUB, L.OP_COPY, 3, None
+    xf = x.float()
+    out = torch.empty(300, device="cuda")
+    import ctypes as C
+    assert L.lib().mimk_reduce_fused(xf.data_ptr(), C.byref(pre), out.data_ptr(), L.F32, 300, 2048, 1, L.SUM, None) == 1  # MIMK_E_ARG
+    pre.inner_op, pre.y_mode = 99, 3
+    assert L.lib().mimk_reduce_fused(xf.data_ptr(), C.byref(pre), out.data_ptr(), L.F32, 300, 2048, 1, L.SUM, None) == 1

@@ -136,3 +136,59 @@ def test_reshape_maps_are_recognised_and_floordiv_maps_disqualify_the_rest(TL):
     a_map = T.AccessMap(T.proj_map(3, (0, 2)), div=[0, 0], mod=[0, 1024])
     assert T.mrp_route((1024, 1024), (1024, 1024, 1024), L.F_MULADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)),
                        [a_map, T.proj_map(3, (2, 1))], [(1024, 1024), (1024, 1024)], [F32, F32]) == "generic"
+
+
+def test_folds_with_an_inlined_producer(TL):
+    """fold(acc, outer(inner(a, b))): what fuse_map_reduce leaves of a map feeding a reduce (phase/fuse.cpp:183-358)."""
+    T, L = TL
+    shape = [64, 128, 256]
+    sq = L.f_composed(L.F_ADD, L.OP_SQUARE)                       # sum of squares: one input
+    sub_sq = L.f_composed(L.F_ADD, L.OP_SUB, L.OP_SQUARE)         # sum of (x - y)^2
+    max_abs = L.f_composed(L.F_MAX, L.OP_ABS)
+    for ax in range(3):
+        out = [s for i, s in enumerate(shape) if i != ax]
+        subs = [0, 1]
+        subs.insert(ax, 2)
+        xm = T.proj_map(3, subs)
+        assert T.mrp_route(out, out + [shape[ax]], sq, 0.0, L.P_ID, T.proj_map(3, [0, 1]), [xm], [shape], [F32]) == "reduce"
+        assert T.mrp_route(out, out + [shape[ax]], max_abs, NEG_INF, L.P_ID, T.proj_map(3, [0, 1]), [xm], [shape], [F32]) == "reduce"
+        # second operand of the producer: x's shape; x's shape without the folded axis; x's axes from the folded one on
+        assert T.mrp_route(out, out + [shape[ax]], sub_sq, 0.0, L.P_ID, T.proj_map(3, [0, 1]), [xm, xm], [shape, shape],
+                           [F32, F32]) == "reduce"
+        assert T.mrp_route(out, out + [shape[ax]], sub_sq, 0.0, L.P_ID, T.proj_map(3, [0, 1]), [xm, T.proj_map(3, [0, 1])],
+                           [shape, out], [F32, F32]) == "reduce"
+        assert T.mrp_route(out, out + [shape[ax]], sub_sq, 0.0, L.P_ID, T.proj_map(3, [0, 1]), [xm, T.proj_map(3, subs[ax:])],
+                           [shape, shape[ax:]], [F32, F32]) == "reduce"
+    # the softmax denominator, in its fixed and its general spelling
+    big = [1024, 2048]
+    for f in (L.F_ADD_SUBEXP, L.f_composed(L.F_ADD, L.OP_SUBEXP)):
+        assert T.mrp_route([1024], big, f, 0.0, L.P_ID, T.proj_map(2, [0]), [T.id_map(2), T.proj_map(2, [0])], [big, [1024]],
+                           [F32, F32]) == "reduce"
+    # not expressible on the fold kernels: a second operand over part of the leading axes only, mixed element types,
+    # a fold that does not start from its identity
+    assert T.mrp_route([64, 128], [64, 128, 256], sub_sq, 0.0, L.P_ID, T.proj_map(3, [0, 1]),
+                       [T.id_map(3), T.proj_map(3, [0])], [shape, [64]], [F32, F32]) == "generic"
+    assert T.mrp_route([1024], big, sub_sq, 0.0, L.P_ID, T.proj_map(2, [0]), [T.id_map(2), T.id_map(2)], [big, big],
+                       [F32, BF16]) == "generic"
+    assert T.mrp_route([1024], big, sq, 1.0, L.P_ID, T.proj_map(2, [0]), [T.id_map(2)], [big], [F32]) == "generic"
+
+
+def test_composed_combiners_in_the_oracle():
+    import numpy as np
+    import oracle as mo
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((5, 7, 3)).astype(np.float32)
+    m = x.max(axis=1)
+    proj = lambda n, subs: [[1 if l == s else 0 for l in range(n)] + [0] for s in subs]
+    got = mo.map_reduce_post((5, 3), (5, 3, 7), mo.f_composed(0, 22), np.float32(0), mo.P_ID, proj(3, (0, 1)), [proj(3, (0, 2, 1))], [x])
+    want = np.zeros((5, 3), np.float32)
+    for a in range(7):
+        want = want + x[:, a, :] * x[:, a, :]
+    assert np.array_equal(got, want)                              # ascending fold, one rounding per operation
+    den = mo.map_reduce_post((5, 3), (5, 3, 7), mo.f_composed(0, 6), np.float32(0), mo.P_ID, proj(3, (0, 1)),
+                             [proj(3, (0, 2, 1)), proj(3, (0, 1))], [x, m])
+    fixed = mo.map_reduce_post((5, 3), (5, 3, 7), mo.F_ADD_SUBEXP_F32, np.float32(0), mo.P_ID, proj(3, (0, 1)),
+                               [proj(3, (0, 2, 1)), proj(3, (0, 1))], [x, m])
+    assert np.array_equal(den, fixed)
+    mabs = mo.map_reduce_post((5, 3), (5, 3, 7), mo.f_composed(2, 23), np.float32(-np.inf), mo.P_ID, proj(3, (0, 1)), [proj(3, (0, 2, 1))], [x])
+    assert np.array_equal(mabs, np.abs(x).max(axis=1))

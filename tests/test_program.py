@@ -127,3 +127,48 @@ def test_attention_needs_the_whole_shape(TL):
     p = softmax_ops(T, L, P, mem, s, 0)
     matmul(T, L, P, mem, p, v, n, dh, n)
     assert "attention" not in P.classify() and "softmax" in P.classify()
+
+
+def test_a_map_feeding_one_fold_is_fused(TL):
+    """fuse_map_reduce on the list level (phase/fuse.cpp:183-358): the produced tensor is read by the fold alone."""
+    T, L = TL
+    mem, P = Mem(), T.Program()
+    shape, ax = [64, 300, 8], 1
+    red = [64, 8]
+    x, mean = mem.new(T, shape), mem.new(T, red)
+    # d = x - mean (binary_ax along axis 1); s = sum d along axis 1 ... a centred sum
+    d = P.op(mem.new(T, shape), shape, L.F_ADD2, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.proj_map(3, (0, 2))], [x, mean])
+    P.op(mem.new(T, red), red + [300], L.F_ADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, (0, 2, 1))], [d])
+    # unary map then a max fold along the last axis
+    a = P.op(mem.new(T, shape), shape, L.F_FIRST, 0.0, L.P_RELU, T.id_map(3), [T.id_map(3)], [x])
+    P.op(mem.new(T, [64, 300]), [64, 300, 8], L.F_MAX, float("-inf"), L.P_ID, T.proj_map(3, (0, 1)), [T.id_map(3)], [a])
+    # weights over the trailing axes from the folded one on
+    w = mem.new(T, [300, 8])
+    xw = P.op(mem.new(T, shape), shape, L.F_MUL2, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.proj_map(3, (1, 2))], [x, w])
+    P.op(mem.new(T, red), red + [300], L.F_ADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, (0, 2, 1))], [xw])
+    assert P.classify() == ["fold_of_map", "absorbed"] * 3
+
+
+def test_a_map_read_twice_or_broadcast_across_the_fold_is_not_fused(TL):
+    T, L = TL
+    mem, P = Mem(), T.Program()
+    shape, red = [64, 300, 8], [64, 8]
+    x, y = mem.new(T, shape), mem.new(T, [64, 300])
+    # the produced tensor has a second reader
+    sq = P.op(mem.new(T, shape), shape, L.F_MUL2, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.id_map(3)], [x, x])
+    P.op(mem.new(T, red), red + [300], L.F_ADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, (0, 2, 1))], [sq])
+    P.op(mem.new(T, shape), shape, L.F_FIRST, 0.0, L.P_RELU, T.id_map(3), [T.id_map(3)], [sq])
+    assert P.classify() == ["op", "op", "op"]
+    # y lacks the LAST axis while the fold runs over the middle one: no placement of the producer's operand fits
+    P2 = T.Program()
+    d = P2.op(mem.new(T, shape), shape, L.F_ADD2, 0.0, L.P_ID, T.id_map(3), [T.id_map(3), T.proj_map(3, (0, 1))], [x, y])
+    P2.op(mem.new(T, red), red + [300], L.F_ADD, 0.0, L.P_ID, T.proj_map(3, (0, 1)), [T.proj_map(3, (0, 2, 1))], [d])
+    assert P2.classify() == ["op", "op"]
+    # the exponential of an incomplete softmax chain still fuses with its sum
+    P3 = T.Program()
+    r = 2
+    xs = mem.new(T, [128, 512])
+    mx = P3.op(mem.new(T, [128]), [128, 512], L.F_MAX, float("-inf"), L.P_ID, T.proj_map(r, (0,)), [T.id_map(r)], [xs])
+    e = P3.op(mem.new(T, [128, 512]), [128, 512], L.F_SUBEXP, 0.0, L.P_ID, T.id_map(r), [T.id_map(r), T.proj_map(r, (0,))], [xs, mx])
+    P3.op(mem.new(T, [128]), [128, 512], L.F_ADD, 0.0, L.P_ID, T.proj_map(r, (0,)), [T.id_map(r)], [e])
+    assert P3.classify() == ["op", "fold_of_map", "absorbed"]
