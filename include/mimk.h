@@ -11,8 +11,9 @@
  *   - every call returns an int status (0 = ok) instead of aborting, so emitted code can pipe it to
  *     `mim_cu_check(int)` (src/mim/plug/nvptx/rt/mim_cuda_rt.c:16-21) exactly like a CUresult;
  *   - entry points that need scratch beyond their arguments (f32 contractions on the tensor cores, split-axis
- *     reductions, mimk_mlp_gated without `h`) share one cached per-device buffer: do not run two of them concurrently on
- *     different streams;
+ *     reductions, mimk_mlp_gated without `h`, composed attention, large scatters) take it from a cached buffer that belongs
+ *     to the stream of the call: calls on different streams never share one (up to 8 streams per device keep a buffer;
+ *     a ninth takes over the least recently used after a device-wide wait), calls on one stream are ordered by it;
  *   - nothing here falls back to the CPU: without a usable sm_100 device every compute call fails with
  *     MIMK_E_NO_DEVICE.
  */

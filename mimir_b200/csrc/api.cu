@@ -59,46 +59,44 @@ DeviceInfo* device_info(int* status) {
     return &d;
 }
 
-int get_scratch(size_t bytes, void** out) {
+namespace {
+int scratch_for(int kind, size_t bytes, void** out, cudaStream_t stream) {
     int st        = MIMK_OK;
     DeviceInfo* d = device_info(&st);
     if (!d) return st;
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (d->scratch_bytes < bytes) {
-        if (d->scratch) {
-            // work queued on any stream may still use the old buffer
-            MIMK_CUDA_TRY(cudaDeviceSynchronize());
-            MIMK_CUDA_TRY(cudaFree(d->scratch));
-            d->scratch       = nullptr;
-            d->scratch_bytes = 0;
-        }
-        size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-        MIMK_CUDA_TRY(cudaMalloc(&d->scratch, want));
-        d->scratch_bytes = want;
+    DeviceInfo::Scratch* slots = d->scratch[kind];
+    DeviceInfo::Scratch* e     = nullptr;
+    for (int i = 0; i < DeviceInfo::SCRATCH_SLOTS && !e; ++i)
+        if (slots[i].used && slots[i].stream == stream) e = &slots[i];
+    for (int i = 0; i < DeviceInfo::SCRATCH_SLOTS && !e; ++i)
+        if (!slots[i].used) e = &slots[i];
+    if (!e) {  // every slot belongs to another stream: take over the one used longest ago
+        e = &slots[0];
+        for (int i = 1; i < DeviceInfo::SCRATCH_SLOTS; ++i)
+            if (slots[i].last_use < e->last_use) e = &slots[i];
+        MIMK_CUDA_TRY(cudaDeviceSynchronize());  // its stream may still have work queued on the buffer
+        if (e->ptr) MIMK_CUDA_TRY(cudaFree(e->ptr));
+        *e = DeviceInfo::Scratch{};
     }
-    *out = d->scratch;
+    e->used = true, e->stream = stream, e->last_use = ++d->scratch_clock;
+    if (e->bytes < bytes) {
+        if (e->ptr) {
+            MIMK_CUDA_TRY(cudaDeviceSynchronize());  // queued work may still use the old buffer
+            MIMK_CUDA_TRY(cudaFree(e->ptr));
+            e->ptr = nullptr, e->bytes = 0;
+        }
+        const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+        MIMK_CUDA_TRY(cudaMalloc(&e->ptr, want));
+        e->bytes = want;
+    }
+    *out = e->ptr;
     return MIMK_OK;
 }
+}  // namespace
 
-int get_aux_scratch(size_t bytes, void** out) {
-    int st        = MIMK_OK;
-    DeviceInfo* d = device_info(&st);
-    if (!d) return st;
-    std::lock_guard<std::mutex> lock(g_mutex);
-    if (d->aux_bytes < bytes) {
-        if (d->aux) {
-            MIMK_CUDA_TRY(cudaDeviceSynchronize());  // work queued on any stream may still use the old buffer
-            MIMK_CUDA_TRY(cudaFree(d->aux));
-            d->aux       = nullptr;
-            d->aux_bytes = 0;
-        }
-        size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-        MIMK_CUDA_TRY(cudaMalloc(&d->aux, want));
-        d->aux_bytes = want;
-    }
-    *out = d->aux;
-    return MIMK_OK;
-}
+int get_scratch(size_t bytes, void** out, cudaStream_t stream) { return scratch_for(0, bytes, out, stream); }
+int get_aux_scratch(size_t bytes, void** out, cudaStream_t stream) { return scratch_for(1, bytes, out, stream); }
 
 }  // namespace mimk
 
@@ -271,7 +269,7 @@ extern "C" int mimk_mlp_gated(const mimk_mlp_desc* d, void* stream) {
     if (!d->x || !d->w1 || !d->w3 || !d->w2 || !d->y) return MIMK_E_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     void* h        = d->h;
-    if (!h) MIMK_TRY(get_scratch(size_t(d->m) * size_t(d->f) * 2, &h));
+    if (!h) MIMK_TRY(get_scratch(size_t(d->m) * size_t(d->f) * 2, &h, static_cast<cudaStream_t>(stream)));
     // stage 1: H = silu(X W1) * (X W3), both contractions in one kernel with two accumulators
     mimk_gemm_desc g1 = {};
     g1.batch = 1, g1.m = d->m, g1.n = d->f, g1.k = d->k;

@@ -131,7 +131,7 @@ int attn_composed(const mimk_attn_desc& d, cudaStream_t s) {
     if (group > 16) group = 16;  // the f32 tensor-core contraction takes batches of up to 16
     if (group > d.batch_heads) group = d.batch_heads;
     void* scratch = nullptr;
-    MIMK_TRY(get_aux_scratch(size_t(group * per_head) * (half ? 6 : 4), &scratch));
+    MIMK_TRY(get_aux_scratch(size_t(group * per_head) * (half ? 6 : 4), &scratch, s));
     float* S = static_cast<float*>(scratch);
     void* P  = half ? static_cast<void*>(S + group * per_head) : static_cast<void*>(S);  // bf16 P beside S, f32 P over S
     const uint8_t* q = static_cast<const uint8_t*>(d.q);

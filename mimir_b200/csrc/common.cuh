@@ -31,17 +31,28 @@ struct DeviceInfo {
     int cc_major = 0;
     int* status_dev = nullptr;   // device-visible alias of the pinned status word
     volatile int* status_host = nullptr;
-    void* scratch = nullptr;     // cached scratch buffer (grown on demand)
-    size_t scratch_bytes = 0;
-    void* aux = nullptr;         // a second cached buffer, for callers that run scratch-using entry points themselves
-    size_t aux_bytes = 0;
+    // Cached scratch buffers (grown on demand), one per stream that has asked for one: calls on different streams never
+    // share a buffer, calls on one stream are ordered by it. `kind` 0 is the general buffer, 1 the second one for callers
+    // that run scratch-using entry points themselves.
+    struct Scratch {
+        cudaStream_t stream = nullptr;
+        void* ptr           = nullptr;
+        size_t bytes        = 0;
+        unsigned long long last_use = 0;
+        bool used           = false;
+    };
+    static constexpr int SCRATCH_SLOTS = 8;
+    Scratch scratch[2][SCRATCH_SLOTS];
+    unsigned long long scratch_clock = 0;
 };
 // Per-device lazily created state; returns nullptr (and sets *status) when the device is unusable.
 DeviceInfo* device_info(int* status);
-// A scratch buffer of at least `bytes` on the current device, cached across calls (grows, never shrinks).
-int get_scratch(size_t bytes, void** out);
-// The second cached buffer (same growth rule); used by the composed f32 attention for its score matrix.
-int get_aux_scratch(size_t bytes, void** out);
+// A scratch buffer of at least `bytes` on the current device for work queued on `stream`, cached across calls (grows,
+// never shrinks). Up to DeviceInfo::SCRATCH_SLOTS streams keep a buffer of their own; one more evicts the least recently used
+// (after waiting for the device).
+int get_scratch(size_t bytes, void** out, cudaStream_t stream);
+// The second cached buffer (same rules); used by the composed f32 attention for its score matrix.
+int get_aux_scratch(size_t bytes, void** out, cudaStream_t stream);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t dtype_size(int dt) { return dt == MIMK_BF16 ? 2 : (dt == MIMK_I64 ? 8 : 4); }

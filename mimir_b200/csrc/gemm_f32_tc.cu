@@ -427,7 +427,7 @@ int gemm_f32_tc(const mimk_gemm_desc& d, cudaStream_t s) {
     const size_t a_elems = size_t(d.m) * kp, b_elems = size_t(d.n) * kp;
     const size_t a_bytes = (a_elems * 4 + 255) & ~size_t(255), b_bytes = (b_elems * 4 + 255) & ~size_t(255);
     void* scratch = nullptr;
-    MIMK_TRY(get_scratch(2 * a_bytes + 2 * b_bytes, &scratch));
+    MIMK_TRY(get_scratch(2 * a_bytes + 2 * b_bytes, &scratch, s));
     uint8_t* base = static_cast<uint8_t*>(scratch);
     float *a_hi = reinterpret_cast<float*>(base), *a_lo = reinterpret_cast<float*>(base + a_bytes);
     float *b_hi = reinterpret_cast<float*>(base + 2 * a_bytes), *b_lo = reinterpret_cast<float*>(base + 2 * a_bytes + b_bytes);

@@ -226,7 +226,7 @@ int scatter_any(const I* index, const T* upd, T* out, long long n_idx, long long
     // which touches the updated cells alone.
     if (n_idx >= 4096 && idx.ext[dim] > 4 && idx.ext[dim] < (int64_t(1) << 31) && n_src <= 8 * n_idx) {
         void* scratch = nullptr;
-        MIMK_TRY(get_scratch(size_t(n_src) * sizeof(int), &scratch));
+        MIMK_TRY(get_scratch(size_t(n_src) * sizeof(int), &scratch, s));
         int* winner = static_cast<int*>(scratch);
         MIMK_CUDA_TRY(cudaMemsetAsync(winner, 0xff, size_t(n_src) * sizeof(int), s));  // -1: no update names this cell
         const unsigned g = grid_for(dev, n_idx);

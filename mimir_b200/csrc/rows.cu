@@ -478,9 +478,10 @@ int reduce_impl(const TIn* x, TOut* out, int64_t outer, int64_t len, int64_t inn
 }
 
 struct CachedPartials {
+    cudaStream_t stream;
     int operator()(size_t n, float** out) const {
         void* p = nullptr;
-        MIMK_TRY(get_scratch(n * sizeof(float), &p));
+        MIMK_TRY(get_scratch(n * sizeof(float), &p, stream));
         *out = static_cast<float*>(p);
         return MIMK_OK;
     }
@@ -553,17 +554,17 @@ extern "C" int mimk_reduce(const void* x, void* out, int dtype, int64_t outer, i
         const __nv_bfloat16* xh = static_cast<const __nv_bfloat16*>(x);
         __nv_bfloat16* oh       = static_cast<__nv_bfloat16*>(out);
         switch (monoid) {
-            case MIMK_SUM: return reduce_impl<SumOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials());
-            case MIMK_MAX: return reduce_impl<MaxOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials());
-            default: return reduce_impl<MinOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials());
+            case MIMK_SUM: return reduce_impl<SumOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials{s});
+            case MIMK_MAX: return reduce_impl<MaxOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials{s});
+            default: return reduce_impl<MinOp>(xh, oh, outer, len, inner, s, dev->sm_count, CachedPartials{s});
         }
     }
     const float* xf = static_cast<const float*>(x);
     float* of       = static_cast<float*>(out);
     switch (monoid) {
-        case MIMK_SUM: return reduce_impl<SumOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials());
-        case MIMK_MAX: return reduce_impl<MaxOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials());
-        default: return reduce_impl<MinOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials());
+        case MIMK_SUM: return reduce_impl<SumOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials{s});
+        case MIMK_MAX: return reduce_impl<MaxOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials{s});
+        default: return reduce_impl<MinOp>(xf, of, outer, len, inner, s, dev->sm_count, CachedPartials{s});
     }
 }
 
@@ -574,9 +575,9 @@ int reduce_fused_inner(const T* x, const mimk_producer& pr, T* out, int64_t oute
                        cudaStream_t s, int sm_count) {
     const MapPre<T, INNER, YMODE> pre{pr.inner_op, pr.outer_op, pr.y_mode, static_cast<const T*>(pr.y), len, inner};
     switch (monoid) {
-        case MIMK_SUM: return reduce_impl<SumOp>(x, out, outer, len, inner, s, sm_count, CachedPartials(), pre);
-        case MIMK_MAX: return reduce_impl<MaxOp>(x, out, outer, len, inner, s, sm_count, CachedPartials(), pre);
-        default: return reduce_impl<MinOp>(x, out, outer, len, inner, s, sm_count, CachedPartials(), pre);
+        case MIMK_SUM: return reduce_impl<SumOp>(x, out, outer, len, inner, s, sm_count, CachedPartials{s}, pre);
+        case MIMK_MAX: return reduce_impl<MaxOp>(x, out, outer, len, inner, s, sm_count, CachedPartials{s}, pre);
+        default: return reduce_impl<MinOp>(x, out, outer, len, inner, s, sm_count, CachedPartials{s}, pre);
     }
 }
 template <class T, int INNER>

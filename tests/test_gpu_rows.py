@@ -249,3 +249,22 @@ def test_reduce_with_an_inlined_producer_bf16_and_arguments(T):
     assert L.lib().mimk_reduce_fused(xf.data_ptr(), C.byref(pre), out.data_ptr(), L.F32, 300, 2048, 1, L.SUM, None) == 1  # MIMK_E_ARG
     pre.inner_op, pre.y_mode = 99, 3
     assert L.lib().mimk_reduce_fused(xf.data_ptr(), C.byref(pre), out.data_ptr(), L.F32, 300, 2048, 1, L.SUM, None) == 1
+
+
+def test_scratch_using_calls_on_two_streams_do_not_share_a_buffer(T):
+    """Split-axis folds keep partial results in a cached buffer; that buffer belongs to the stream of the call, so the same
+    entry point may run on two streams at once."""
+    x1, x2 = randn((4, 60000, 24), 71), randn((4, 60000, 24), 72)        # few columns, long axis: the plan splits the axis
+    want1, want2 = T.reduce("sum", 1, x1).clone(), T.reduce("sum", 1, x2).clone()
+    torch.cuda.synchronize()
+    sa, sb = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for _ in range(20):
+        with torch.cuda.stream(sa):
+            a = T.reduce("sum", 1, x1)
+        with torch.cuda.stream(sb):
+            b = T.reduce("sum", 1, x2)
+        outs.append((a, b))
+    torch.cuda.synchronize()
+    for a, b in outs:
+        assert torch.equal(a, want1) and torch.equal(b, want2)
