@@ -43,7 +43,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="attn", choices=list(WORKLOADS))
-    ap.add_argument("--tp-gather", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--tp-gather", default="fused", choices=["fused", "nccl", "rows"],
                     help="mlp_tp: all-gather of H fused into the GEMM epilogue (peer stores) or a separate NCCL all-gather")
     ap.add_argument("--weak", action="store_true", help="under torchrun: every rank runs the whole stated problem")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-records of the other workloads")
@@ -488,10 +488,12 @@ class MlpTP(Mlp):  # noqa: D101
     @classmethod
     def config(cls, world, weak=False, gather=False, mode="fused"):
         return {"workload": cls.name, "l2": "weights and H larger than the 126 MB L2",
-                "tp_gather": (mode + (" (H slabs stored into every rank's H from the contraction's epilogue over NVLink)"
-                                      if mode == "fused" else " (separate NCCL all-gather of the H slabs)")) if world > 1 else "n/a",
-                "sharding": "W1/W3 column slabs, H all-gathered, W2 column slabs" +
-                            (", Y all-gathered too" if gather and world > 1 else " (Y stays sharded)")}
+                "tp_gather": (mode + {"fused": " (H slabs stored into every rank's H from the contraction's epilogue over NVLink)",
+                                      "nccl": " (separate NCCL all-gather of the H slabs)",
+                                      "rows": " (no gather of H: f32 partials of Y reduce-scattered over NCCL)"}[mode]) if world > 1 else "n/a",
+                "sharding": ("W1/W3 column slabs, W2 ROW slabs, Y row blocks after the reduce-scatter" if mode == "rows" and world > 1 else
+                             "W1/W3 column slabs, H all-gathered, W2 column slabs" +
+                             (", Y all-gathered too" if gather and world > 1 else " (Y stays sharded)"))}
 
     def setup(self):
         t = self.torch
@@ -504,7 +506,7 @@ class MlpTP(Mlp):  # noqa: D101
         self.x = x
         self.w1 = w1[:, r * self.fl:(r + 1) * self.fl].contiguous()
         self.w3 = w3[:, r * self.fl:(r + 1) * self.fl].contiguous()
-        self.w2 = w2[:, r * self.nl:(r + 1) * self.nl].contiguous()
+        self.w2 = (w2[r * self.fl:(r + 1) * self.fl, :] if self.mode == "rows" and W > 1 else w2[:, r * self.nl:(r + 1) * self.nl]).contiguous()
         del w1, w3, w2
         t.cuda.empty_cache()
         self.yg = self.hg = None
@@ -514,6 +516,8 @@ class MlpTP(Mlp):  # noqa: D101
                 self.yg = shard.GatheredMatrix(self.M, self.K)
         else:
             self.h_local = t.empty((self.M, self.fl), device="cuda", dtype=t.bfloat16)
+            if W > 1 and self.mode == "rows":
+                self.y_partial = t.empty((self.M, self.K), device="cuda", dtype=t.float32)
         self.units = self.dom_units = self.traffic_units = 3 * 2 * self.M * self.K * self.F // W     # this rank's share
 
     def step(self, ev=None):
@@ -523,6 +527,8 @@ class MlpTP(Mlp):  # noqa: D101
             self.y = self.T.mlp_gated(self.x, self.w1, self.w3, self.w2, h=self.h_local)
         elif self.mode == "fused":
             self.y = self.shard.tp_mlp_gated(self.x, self.w1, self.w3, self.w2, self.hg, gather="fused", y=self.yg)
+        elif self.mode == "rows":
+            self.y = self.shard.tp_mlp_gated_rows(self.x, self.w1, self.w3, self.w2, self.h_local, self.y_partial)
         else:
             self.y = self.shard.tp_mlp_gated_nccl(self.x, self.w1, self.w3, self.w2, self.h_local, gather_y=self.gather)
         if ev:
@@ -536,10 +542,18 @@ class MlpTP(Mlp):  # noqa: D101
         x, w1, w3, w2 = self.weights()
         rows = [1, self.M - 1]
         b = lambda v: bits_np(np, t, v)
-        want = mo.mlp_gated_truth(b(x[rows]), b(w1), b(w3), b(w2))
-        if not (self.gather and self.world > 1):
-            want = want[:, self.rank * self.nl:(self.rank + 1) * self.nl]
-        err = mo.normalised_error(self.y[rows].float().cpu().numpy(), want)
+        if self.mode == "rows" and self.world > 1:  # this rank holds rows [r M/W, (r+1) M/W) of the whole Y
+            per = self.M // self.world
+            mine = [1, per - 1]
+            rows = [self.rank * per + i for i in mine]
+            want = mo.mlp_gated_truth(b(x[rows]), b(w1), b(w3), b(w2))
+            got = self.y[mine]
+        else:
+            want = mo.mlp_gated_truth(b(x[rows]), b(w1), b(w3), b(w2))
+            if not (self.gather and self.world > 1):
+                want = want[:, self.rank * self.nl:(self.rank + 1) * self.nl]
+            got = self.y[rows]
+        err = mo.normalised_error(got.float().cpu().numpy(), want)
         checked = want.size
         if self.world > 1 and self.mode == "fused":
             # the gathered H on this rank against the one-GPU product of the whole operands: the same bits, whoever wrote them
@@ -855,7 +869,8 @@ def run_ours(args):
         else:
             plan = [("attn_weak", Attn, {"weak": True}),
                     ("gemm_cols", Gemm, {}), ("gemm_cols_gather", Gemm, {"gather": True}),
-                    ("mlp_tp_fused", MlpTP, {"mode": "fused"}), ("mlp_tp_nccl", MlpTP, {"mode": "nccl"})]
+                    ("mlp_tp_fused", MlpTP, {"mode": "fused"}), ("mlp_tp_nccl", MlpTP, {"mode": "nccl"}),
+                    ("mlp_tp_rows", MlpTP, {"mode": "rows"})]
         plan = [p for p in plan if not (p[1] is W and not p[2])]
         for name, cls, kw in plan:
             env.torch.cuda.empty_cache()

@@ -220,6 +220,45 @@ def tp_mlp_gated_nccl(x, w1_shard, w3_shard, w2_shard, h_local, gather_y: bool =
     return gather_columns(slab, slab.shape[1] * world)
 
 
+def tp_mlp_gated_rows(x, w1_shard, w3_shard, w2_rows, h_local, y_partial: "torch.Tensor | None" = None,
+                      out_dtype=None) -> torch.Tensor:
+    """The tensor-parallel gated MLP with W2 split by ROWS instead of columns: rank g owns columns [g F/G, (g+1) F/G) of
+    W1 / W3 and the matching rows of W2, so its slab of H never leaves the GPU; the second contraction gives an f32
+    partial of the WHOLE Y, and a reduce-scatter (NCCL) sums the partials and leaves rows [g M/G, (g+1) M/G) of Y on
+    rank g. Per rank it moves (G - 1) / G of M x N f32 instead of (G - 1) / G of M x F bf16 for the gather of H."""
+    from . import tensor as T
+    rank, world = _world()
+    gemm_gather_local(x, w1_shard, w3_shard, h_local)
+    m, n = x.shape[0], w2_rows.shape[1]
+    out_dtype = out_dtype or x.dtype
+    if world == 1:
+        return T.product_2d(h_local, w2_rows, out_dtype=out_dtype)
+    if m % world:
+        raise ValueError("tp_mlp_gated_rows: the row count must divide by the number of ranks")
+    if y_partial is None:
+        y_partial = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    _gemm_into(h_local, w2_rows, y_partial)
+    mine = torch.empty((m // world, n), dtype=torch.float32, device=x.device)
+    dist.reduce_scatter_tensor(mine, y_partial)
+    return mine if out_dtype == torch.float32 else T.unary("copy", mine, out_dtype=out_dtype)
+
+
+def _gemm_into(a, b, out):
+    """out = a b into a caller's buffer (f32 or bf16 result of bf16 operands)."""
+    import ctypes as C
+
+    from . import _lib as L
+    from .tensor import _b_layout, _dt, _stream
+    b_store, layout = _b_layout(b)
+    m, k = a.shape
+    n = b.shape[1]
+    d = L.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, m, n, k
+    d.a, d.b, d.c = a.data_ptr(), b_store.data_ptr(), out.data_ptr()
+    d.in_dtype, d.out_dtype, d.b_layout, d.post = _dt(a), _dt(out), layout, L.POST_ID
+    L.check(L.lib().mimk_gemm(C.byref(d), _stream()), "gemm_into")
+
+
 def gemm_gather_local(x, w1_shard, w3_shard, h_local):
     """Stage 1 of the tensor-parallel MLP into a LOCAL slab (for the variant that all-gathers with NCCL afterwards)."""
     import ctypes as C

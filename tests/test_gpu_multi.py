@@ -53,6 +53,15 @@ def _worker(rank, world, port, out_dir):
     wanty = mo.mlp_gated_truth(bits(x), bits(w1), bits(w3), bits(w2))[:, rank * nl:(rank + 1) * nl]
     assert mo.normalised_error(y.float().cpu().numpy(), wanty) <= 2e-2
 
+    # the same block with W2 split by rows: no gather of H, f32 partials of Y reduce-scattered; rank g ends with rows g M/G ..
+    h_loc = torch.empty((M, fl), dtype=torch.bfloat16, device="cuda")
+    yr = shard.tp_mlp_gated_rows(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), w3[:, rank * fl:(rank + 1) * fl].contiguous(),
+                                 w2[rank * fl:(rank + 1) * fl, :].contiguous(), h_loc)
+    T.device_status()
+    per = M // world
+    wantr = mo.mlp_gated_truth(bits(x), bits(w1), bits(w3), bits(w2))[rank * per:(rank + 1) * per]
+    assert yr.shape == (per, N) and mo.normalised_error(yr.float().cpu().numpy(), wantr) <= 2e-2
+
     # a slab large enough for the paired-SM kernel (>= 74 tiles of 256 x 256 per rank): its epilogue sends each piece with
     # one bulk store per destination. The product is checked bit for bit against the one-GPU product of the same operands.
     M, K, fl, nl = 2560, 256, 2048, 256
