@@ -111,15 +111,18 @@ class GatheredMatrix:
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.rows, self.cols = rows, cols
 
-    def barrier(self):
-        """Every rank's stores (issued before this call on the current stream) are complete on every rank afterwards."""
-        self.handle.barrier(channel=0, timeout_ms=20000)
+    def barrier(self, channel: int = 0):
+        """Every rank's stores (issued before this call on the current stream) are complete on every rank afterwards.
+        Barriers that may be in flight at the same time (on different streams) take different channels."""
+        self.handle.barrier(channel=channel, timeout_ms=20000)
 
 
-def gemm_gather(a: torch.Tensor, b: torch.Tensor, out: GatheredMatrix, col_off: int, *, gated_b2: torch.Tensor | None = None):
+def gemm_gather(a: torch.Tensor, b: torch.Tensor, out: GatheredMatrix, col_off: int, *, gated_b2: torch.Tensor | None = None,
+                row_off: int = 0):
     """This rank's column slab of `a . b` (or silu(a . b) * (a . gated_b2)) stored straight into every rank's copy of
-    `out` at columns [col_off, col_off + n): the all-gather happens in the contraction's epilogue.  `b` (and
-    `gated_b2`) may be transpose_2d views of [n, k] tensors.  Call `out.barrier()` before reading `out.local`."""
+    `out` at rows [row_off, row_off + m), columns [col_off, col_off + n): the all-gather happens in the contraction's
+    epilogue.  `b` (and `gated_b2`) may be transpose_2d views of [n, k] tensors.  Call `out.barrier()` before reading
+    `out.local`."""
     import ctypes as C
 
     from . import _lib as L
@@ -133,17 +136,18 @@ def gemm_gather(a: torch.Tensor, b: torch.Tensor, out: GatheredMatrix, col_off: 
             raise ValueError("both right operands must share one storage layout")
     m, k = a.shape
     n = b.shape[1]
-    if a.shape[1] != b.shape[0] or m != out.rows or col_off + n > out.cols:
+    if a.shape[1] != b.shape[0] or row_off < 0 or row_off + m > out.rows or col_off + n > out.cols:
         raise ValueError("contracting dims don't match")
+    at = row_off * out.cols * out.local.element_size()
     d = L.GemmDesc()
     d.batch, d.m, d.n, d.k = 1, m, n, k
-    d.a, d.b, d.c = a.data_ptr(), b_store.data_ptr(), out.local.data_ptr()
+    d.a, d.b, d.c = a.data_ptr(), b_store.data_ptr(), out.local.data_ptr() + at
     d.stride_c = m * n
     d.in_dtype, d.out_dtype, d.b_layout, d.post = _dt(a), _dt(out.local), layout, L.POST_ID
     g = L.GatherDst()
     g.n_dst = out.world
     for i, ptr in enumerate(out.ptrs):
-        g.dst[i] = ptr
+        g.dst[i] = ptr + at
     g.ldc, g.col_off = out.cols, col_off
     L.check(L.lib().mimk_gemm_gather(C.byref(d), b2_store.data_ptr() if b2_store is not None else None, C.byref(g),
                                      _stream()), "gemm_gather")
