@@ -207,7 +207,11 @@ enum {
     MIMK_OP_RELU = 16, MIMK_OP_TANH = 17, MIMK_OP_EXP = 18, MIMK_OP_SILU = 19, MIMK_OP_NEG = 20, MIMK_OP_COPY = 21,
     MIMK_OP_SQUARE = 22, MIMK_OP_ABS = 23,
 };
-/* out[o,a,i] = op(x[o,a,i], y[...]) over a [outer, len, inner] view of x (F32).
+/* An elementwise operator with a unary one applied to its result -- outer(inner(x, y)): one more level of producer
+ * inlining for elementwise consumers (relu(x + bias), tanh(x * y), |x - y| ...). inner: any MIMK_OP_*; outer: a unary one. */
+#define MIMK_OP_COMPOSED_BASE 0x10000
+#define MIMK_OP_COMPOSED(inner, outer) (MIMK_OP_COMPOSED_BASE | (inner) | ((outer) << 8))
+/* out[o,a,i] = op(x[o,a,i], y[...]) over a [outer, len, inner] view of x (F32); op may be a MIMK_OP_COMPOSED pair.
  * y_mode 0: y has x's shape (tensor.binary); 1: y is [outer, inner], broadcast along the middle axis
  * (binary_ax); 2: y is [len*inner], broadcast over `outer` (a bias row); 3: unary, y unused. */
 int mimk_map(int op, const void* x, const void* y, void* out, int out_dtype, int64_t outer, int64_t len,

@@ -79,6 +79,13 @@ class Producer(C.Structure):
 
 
 F_COMPOSED_BASE = 0x01000000
+OP_COMPOSED_BASE = 0x10000
+
+
+def op_composed(inner: int, outer: int) -> int:
+    """MIMK_OP_COMPOSED: the elementwise operator outer(inner(x, y))."""
+    return OP_COMPOSED_BASE | inner | (outer << 8)
+
 
 
 def f_composed(fold: int, inner: int, outer: int = OP_COPY) -> int:

@@ -77,6 +77,15 @@ bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status);
 // kernel): route MIMK_ROUTE_*, and the arguments of the specialised entry point that would take it.
 inline bool op_is_binary(int op) { return op >= MIMK_OP_ADD && op <= MIMK_OP_SUBEXP; }
 inline bool op_is_unary(int op) { return op >= MIMK_OP_RELU && op <= MIMK_OP_ABS; }  // COPY included
+// A (possibly composed) elementwise operator taken apart; false when it names an unknown part.
+inline bool decode_op(int op, int* inner, int* outer) {
+    *inner = op, *outer = MIMK_OP_COPY;
+    if (op & MIMK_OP_COMPOSED_BASE) {
+        if (op & ~0x1ffff) return false;
+        *inner = op & 0xff, *outer = (op >> 8) & 0xff;
+    }
+    return (op_is_binary(*inner) || op_is_unary(*inner)) && op_is_unary(*outer);
+}
 // A composed combiner taken apart; false when `comb` is not one or names an unknown part.
 inline bool decode_composed(int comb, int* fold, int* inner, int* outer) {
     if ((comb & ~0x00ffffff) != MIMK_F_COMPOSED_BASE) return false;
@@ -110,7 +119,7 @@ int attn_tc_pair(const mimk_attn_desc& d, cudaStream_t s);
 // ---- device side ----------------------------------------------------------------------------------
 #ifdef __CUDACC__
 // the scalar meaning of MIMK_OP_* (unary ones ignore b)
-__device__ __forceinline__ float apply_op(int op, float a, float b) {
+__device__ __forceinline__ float apply_op_plain(int op, float a, float b) {
     switch (op) {
         case MIMK_OP_ADD: return a + b;
         case MIMK_OP_SUB: return a - b;
@@ -128,6 +137,11 @@ __device__ __forceinline__ float apply_op(int op, float a, float b) {
         case MIMK_OP_ABS: return fabsf(a);
         default: return a;
     }
+}
+// ... and of a MIMK_OP_COMPOSED pair: outer(inner(a, b))
+__device__ __forceinline__ float apply_op(int op, float a, float b) {
+    if (op & MIMK_OP_COMPOSED_BASE) return apply_op_plain((op >> 8) & 0xff, apply_op_plain(op & 0xff, a, b), 0.f);
+    return apply_op_plain(op, a, b);
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

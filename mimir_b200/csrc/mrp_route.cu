@@ -197,6 +197,23 @@ bool plan_map(const mimk_mrp_desc& d, Plan& p) {
     for (int i = 0; i < d.nis; ++i)  // operands of one floating-point element type
         if ((d.in_dtype[i] != MIMK_F32 && d.in_dtype[i] != MIMK_BF16) || d.in_dtype[i] != d.in_dtype[0]) return false;
     int ax = 0;
+    // FIRST(outer(inner(a [, b]))): an elementwise operator with a unary one behind it
+    int c_fold = 0, c_inner = 0, c_outer = 0;
+    if (decode_composed(d.comb, &c_fold, &c_inner, &c_outer)) {
+        if (c_fold != MIMK_F_FIRST || d.post != MIMK_P_ID || d.nis != (op_is_binary(c_inner) ? 2 : 1)) return false;
+        if (broadcast_kind(d, 0, &ax) != 0) return false;
+        p.op = MIMK_OP_COMPOSED(c_inner, c_outer);
+        if (d.nis == 1) {
+            p.outer = 1, p.len = prod(d.sr, 0, d.ro), p.inner = 1, p.y_mode = 3;
+            return true;
+        }
+        switch (broadcast_kind(d, 1, &ax)) {
+            case 0: p.outer = 1, p.len = prod(d.sr, 0, d.ro), p.inner = 1, p.y_mode = 0; return true;
+            case 1: p.outer = prod(d.sr, 0, ax), p.len = d.sr[ax], p.inner = prod(d.sr, ax + 1, d.ro), p.y_mode = 1; return true;
+            case 2: p.outer = prod(d.sr, 0, ax), p.len = prod(d.sr, ax, d.ro), p.inner = 1, p.y_mode = 2; return true;
+            default: return false;
+        }
+    }
     if (d.nis == 1 && d.comb == MIMK_F_FIRST) {
         if (broadcast_kind(d, 0, &ax) != 0) return false;
         p.op = d.post == MIMK_P_ID ? MIMK_OP_COPY : d.post == MIMK_P_RELU ? MIMK_OP_RELU : d.post == MIMK_P_SILU ? MIMK_OP_SILU : -1;

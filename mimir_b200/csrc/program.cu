@@ -186,7 +186,9 @@ bool match_fold_of_map(const mimk_mrp_desc* ops, int n, int at, FoldOfMap& f) {
     const bool unary = pm.y_mode == 3;
     f.x = m.in[0], f.out = r.out, f.dtype = m.in_dtype[0], f.monoid = pf.monoid;
     f.outer = pf.outer, f.len = pf.len, f.inner = pf.inner;
-    f.pre.inner_op = pm.op, f.pre.outer_op = MIMK_OP_COPY, f.pre.y_mode = mode, f.pre.pad_ = 0;
+    int op_inner = 0, op_outer = 0;
+    if (!decode_op(pm.op, &op_inner, &op_outer)) return false;  // the map's operator may itself be a composed pair
+    f.pre.inner_op = op_inner, f.pre.outer_op = op_outer, f.pre.y_mode = mode, f.pre.pad_ = 0;
     f.pre.y = unary ? nullptr : m.in[1];
     return true;
 }

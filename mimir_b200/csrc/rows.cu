@@ -738,9 +738,9 @@ int map_impl(int op, const TIn* x, const TIn* y, void* out, int out_dtype, int64
 extern "C" int mimk_map_t(int op, const void* x, const void* y, void* out, int in_dtype, int out_dtype, int64_t outer, int64_t len,
                           int64_t inner, int y_mode, void* stream) {
     if (outer < 0 || len < 0 || inner < 0 || y_mode < 0 || y_mode > 3) return MIMK_E_ARG;
-    const bool unary = op_is_unary(op);
-    const bool binary = op >= MIMK_OP_ADD && op <= MIMK_OP_SUBEXP;
-    if (!unary && !binary) return MIMK_E_ARG;
+    int op_inner = 0, op_outer = 0;
+    if (!decode_op(op, &op_inner, &op_outer)) return MIMK_E_ARG;
+    const bool unary = op_is_unary(op_inner), binary = op_is_binary(op_inner);
     if (binary && y_mode == 3) return MIMK_E_ARG;
     if ((in_dtype != MIMK_F32 && in_dtype != MIMK_BF16) || (out_dtype != MIMK_F32 && out_dtype != MIMK_BF16)) return MIMK_E_DTYPE;
     int st          = MIMK_OK;

@@ -239,30 +239,36 @@ def _same_float(*ts):
     return dt
 
 
-def unary(op: str, x: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
+def _op(table, op: str, then) -> int:
+    """An operator name, optionally with a unary one applied to its result (`then`): MIMK_OP_COMPOSED."""
+    return table[op] if then is None else L.op_composed(table[op], _UNOP[then])
+
+
+def unary(op: str, x: torch.Tensor, *, out_dtype=None, then: str | None = None) -> torch.Tensor:
     _dev(x)
     _same_float(x)
     x = x.contiguous()
     out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
-    L.check(L.lib().mimk_map_t(_UNOP[op], x.data_ptr(), None, out.data_ptr(), _dt(x), _dt(out), 1, x.numel(), 1, 3, _stream()),
+    L.check(L.lib().mimk_map_t(_op(_UNOP, op, then), x.data_ptr(), None, out.data_ptr(), _dt(x), _dt(out), 1, x.numel(), 1, 3, _stream()),
             "unary")
     return out
 
 
-def binary(op: str, x: torch.Tensor, y: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
+def binary(op: str, x: torch.Tensor, y: torch.Tensor, *, out_dtype=None, then: str | None = None) -> torch.Tensor:
     _dev(x, y)
     _same_float(x, y)
     if x.shape != y.shape:
         raise ValueError("binary expects operands of one shape")
     x, y = x.contiguous(), y.contiguous()
     out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
-    L.check(L.lib().mimk_map_t(_BINOP[op], x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(x), _dt(out), 1, x.numel(), 1, 0,
+    L.check(L.lib().mimk_map_t(_op(_BINOP, op, then), x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(x), _dt(out), 1, x.numel(), 1, 0,
                                _stream()), "binary")
     return out
 
 
-def binary_ax(op: str, ax: int, x: torch.Tensor, y: torch.Tensor, *, out_dtype=None) -> torch.Tensor:
-    """`binary_ax app ax (x, y)`: y lacks axis `ax` of x and is broadcast along it."""
+def binary_ax(op: str, ax: int, x: torch.Tensor, y: torch.Tensor, *, out_dtype=None, then: str | None = None) -> torch.Tensor:
+    """`binary_ax app ax (x, y)`: y lacks axis `ax` of x and is broadcast along it. `then`: a unary operator applied to the
+    result in the same pass (a producer inlined into an elementwise consumer)."""
     _dev(x, y)
     _same_float(x, y)
     x, y = x.contiguous(), y.contiguous()
@@ -270,7 +276,7 @@ def binary_ax(op: str, ax: int, x: torch.Tensor, y: torch.Tensor, *, out_dtype=N
     if tuple(y.shape) != tuple(x.shape[:ax] + x.shape[ax + 1:]):
         raise ValueError("binary_ax: y must have x's shape without axis ax")
     out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
-    L.check(L.lib().mimk_map_t(_BINOP[op], x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(x), _dt(out), outer, ln, inner, 1,
+    L.check(L.lib().mimk_map_t(_op(_BINOP, op, then), x.data_ptr(), y.data_ptr(), out.data_ptr(), _dt(x), _dt(out), outer, ln, inner, 1,
                                _stream()), "binary_ax")
     return out
 

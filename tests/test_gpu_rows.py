@@ -268,3 +268,23 @@ def test_scratch_using_calls_on_two_streams_do_not_share_a_buffer(T):
     torch.cuda.synchronize()
     for a, b in outs:
         assert torch.equal(a, want1) and torch.equal(b, want2)
+
+
+def test_elementwise_operators_with_a_unary_one_behind_them(T):
+    """outer(inner(x, y)) in one pass: relu(x + bias), |x - y|, tanh(x * v) -- in every placement of the second operand."""
+    x, y = randn((37, 300, 8), 51), randn((37, 300, 8), 52)
+    xn, yn = x.cpu().numpy().astype(np.float64), y.cpu().numpy().astype(np.float64)
+    assert nerr(f64(T.binary("sub", x, y, then="abs")), np.abs(xn - yn)) < TOL_F32
+    v = randn((37, 8), 53)
+    vn = v.cpu().numpy().astype(np.float64)
+    assert nerr(f64(T.binary_ax("mul", 1, x, v, then="tanh")), np.tanh(xn * vn[:, None, :])) < TOL_F32
+    assert nerr(f64(T.unary("square", x, then="neg")), -(xn * xn)) < TOL_F32
+    big, bias = randn((512, 4096), 54), randn((512,), 55)
+    got = T.binary_ax("add", 1, big, bias, then="relu", out_dtype=torch.bfloat16)          # the 128-bit path, bf16 out
+    want = np.maximum(big.cpu().numpy().astype(np.float64) + bias.cpu().numpy().astype(np.float64)[:, None], 0)
+    assert got.dtype == torch.bfloat16 and nerr(f64(got.float()), want) < TOL_BF16
+    # the same through a descriptor: FIRST(relu(a + b)) with b broadcast along the last axis, routed to the map kernel
+    from mimir_b200 import _lib as L
+    d = T.map_reduce_post((512, 4096), (512, 4096), L.f_composed(L.F_FIRST, L.OP_ADD, L.OP_RELU), 0.0, L.P_ID, T.id_map(2),
+                          [T.id_map(2), T.proj_map(2, (0,))], [big, bias])
+    assert nerr(f64(d), want) < TOL_F32

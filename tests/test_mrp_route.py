@@ -192,3 +192,15 @@ def test_composed_combiners_in_the_oracle():
     assert np.array_equal(den, fixed)
     mabs = mo.map_reduce_post((5, 3), (5, 3, 7), mo.f_composed(2, 23), np.float32(-np.inf), mo.P_ID, proj(3, (0, 1)), [proj(3, (0, 2, 1))], [x])
     assert np.array_equal(mabs, np.abs(x).max(axis=1))
+
+
+def test_elementwise_operators_with_a_unary_one_behind_them(TL):
+    T, L = TL
+    big = [1024, 2048]
+    relu_add = L.f_composed(L.F_FIRST, L.OP_ADD, L.OP_RELU)
+    assert T.mrp_route(big, big, relu_add, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.proj_map(2, [1])], [big, [2048]], [F32, F32]) == "map"
+    assert T.mrp_route(big, big, relu_add, 0.0, L.P_ID, T.id_map(2), [T.id_map(2), T.id_map(2)], [big, big], [F32, F32]) == "map"
+    assert T.mrp_route(big, big, L.f_composed(L.F_FIRST, L.OP_SQUARE, L.OP_NEG), 0.0, L.P_ID, T.id_map(2), [T.id_map(2)], [big], [F32]) == "map"
+    # a transposed first operand is not an elementwise map
+    assert T.mrp_route([2048, 1024], [2048, 1024], relu_add, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0]), T.id_map(2)],
+                       [big, [2048, 1024]], [F32, F32]) == "generic"
