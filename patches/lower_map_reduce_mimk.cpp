@@ -84,6 +84,68 @@ std::optional<int> pool_monoid(const Lam* comb) {
     return {};
 }
 
+/// An elementwise operator of math over F32 as a MIMK_OP_* code, with its operands: binary `g (a, b)` or unary `u a`.
+struct ElemOp {
+    int op;
+    const Def* a;
+    const Def* b;  // nullptr for a unary operator
+};
+std::optional<ElemOp> elem_op(const Def* v) {
+    if (auto x = Axm::isa(math::arith::add, v)) return ElemOp{MIMK_OP_ADD, x->arg(2, 0), x->arg(2, 1)};
+    if (auto x = Axm::isa(math::arith::sub, v)) return ElemOp{MIMK_OP_SUB, x->arg(2, 0), x->arg(2, 1)};
+    if (auto x = Axm::isa(math::arith::mul, v)) {
+        if (x->arg(2, 0) == x->arg(2, 1)) return ElemOp{MIMK_OP_SQUARE, x->arg(2, 0), nullptr};
+        return ElemOp{MIMK_OP_MUL, x->arg(2, 0), x->arg(2, 1)};
+    }
+    if (auto x = Axm::isa(math::arith::div, v)) return ElemOp{MIMK_OP_DIV, x->arg(2, 0), x->arg(2, 1)};
+    if (auto x = Axm::isa(math::extrema::fmax, v)) return ElemOp{MIMK_OP_MAX, x->arg(2, 0), x->arg(2, 1)};
+    if (auto x = Axm::isa(math::extrema::fmin, v)) return ElemOp{MIMK_OP_MIN, x->arg(2, 0), x->arg(2, 1)};
+    if (auto x = Axm::isa(math::exp::exp, v)) {
+        if (auto d = Axm::isa(math::arith::sub, x->arg())) return ElemOp{MIMK_OP_SUBEXP, d->arg(2, 0), d->arg(2, 1)};
+        return ElemOp{MIMK_OP_EXP, x->arg(), nullptr};
+    }
+    if (auto x = Axm::isa(math::tri::tanh, v)) return ElemOp{MIMK_OP_TANH, x->arg(), nullptr};
+    if (auto x = Axm::isa(math::abs, v)) return ElemOp{MIMK_OP_ABS, x->arg(), nullptr};
+    if (auto x = Axm::isa(math::minus, v)) return ElemOp{MIMK_OP_NEG, x->arg(), nullptr};
+    return {};
+}
+
+/// What fuse_map_reduce leaves of a map feeding a fold (src/mim/plug/tensor/phase/fuse.cpp:183-358): the fold's combiner with
+/// the producer's body inlined, `acc, ins -> acc (+) u (g (ins#0, ins#1))` or `acc (+) g (...)` or `acc (+) u (ins#0)`.
+/// Yields (monoid, inner, outer) for mimk_reduce_fused / MIMK_F_COMPOSED; `nis` is the number of inputs the body reads.
+struct ProducedFold {
+    int monoid, inner, outer;
+};
+std::optional<ProducedFold> produced_fold(const Lam* comb, nat_t nis) {
+    auto v = returned_value(comb);
+    if (!v || !is_f32(v->type())) return {};
+    auto acc = comb->var(2, 0), ins = comb->var(2, 1);
+    int monoid = -1;
+    const Def* produced = nullptr;
+    auto split = [&](const App* app, int m) {
+        auto [a, b] = app->args<2>();
+        if (a == acc) monoid = m, produced = b;
+        else if (b == acc) monoid = m, produced = a;
+    };
+    if (auto x = Axm::isa(math::arith::add, v)) split(x, MIMK_SUM);
+    else if (auto x = Axm::isa(math::extrema::fmax, v)) split(x, MIMK_MAX);
+    else if (auto x = Axm::isa(math::extrema::fmin, v)) split(x, MIMK_MIN);
+    if (!produced) return {};
+    auto in = [&](nat_t i) { return nis == 1 ? ins : ins->proj(nis, i); };
+    auto outer = elem_op(produced);
+    if (!outer) return {};
+    // g (ins#0, ins#1), or u (ins#0)
+    if (outer->b ? (nis == 2 && outer->a == in(0) && outer->b == in(1)) : (nis == 1 && outer->a == in(0)))
+        return ProducedFold{monoid, outer->op, MIMK_OP_COPY};
+    // u (g (ins#0, ins#1)) or u (u' (ins#0))
+    if (outer->b) return {};
+    auto inner = elem_op(outer->a);
+    if (!inner) return {};
+    if (inner->b ? (nis == 2 && inner->a == in(0) && inner->b == in(1)) : (nis == 1 && inner->a == in(0)))
+        return ProducedFold{monoid, inner->op, outer->op};
+    return {};
+}
+
 /// post is btensor.id (returns its accumulator), or what fuse_epilogue sinks into the slot (fuse.cpp:408-534):
 /// `acc, b -> acc + b`, `fmax (0, acc + b)`, `tanh (acc + b)`, `fmax (0, acc)`. Yields MIMK_POST_*.
 std::optional<int> post_kind(const Lam* post, nat_t nps) {
@@ -248,6 +310,10 @@ const Def* LowerMapReduce::lower_map_reduce_post(const App* app) {
                 return call;
             }
         }
+    // 2b. the same fold with an elementwise producer inlined into its combiner (produced_fold): mimk_reduce_fused takes the
+    //     operator pair and the second input, placed as mimk_producer::y_mode says (its map is the fold's output loops ->
+    //     y_mode 1, the input's own map -> 0, the input's axes from the folded one on -> 2); the projections are probed exactly
+    //     as above. The call differs from case 2 only in the callee and in a `mimk_producer` built on the host stack.
     // 3. every other instance: one call of the generic launcher with the access maps flattened to coefficient matrices would go
     //    here (mimk_map_reduce_post takes a descriptor in memory; the maps' coefficients come from probing each map with unit
     //    markers and the zero vector, floordiv / rem results being read off the affine.semiop nodes). Until that emitter
