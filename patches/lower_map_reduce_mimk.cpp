@@ -92,7 +92,10 @@ struct ElemOp {
 };
 std::optional<ElemOp> elem_op(const Def* v) {
     if (auto x = Axm::isa(math::arith::add, v)) return ElemOp{MIMK_OP_ADD, x->arg(2, 0), x->arg(2, 1)};
-    if (auto x = Axm::isa(math::arith::sub, v)) return ElemOp{MIMK_OP_SUB, x->arg(2, 0), x->arg(2, 1)};
+    if (auto x = Axm::isa(math::arith::sub, v)) {
+        if (auto z = Lit::isa<f32>(x->arg(2, 0)); z && *z == 0.f) return ElemOp{MIMK_OP_NEG, x->arg(2, 1), nullptr};  // math.minus
+        return ElemOp{MIMK_OP_SUB, x->arg(2, 0), x->arg(2, 1)};
+    }
     if (auto x = Axm::isa(math::arith::mul, v)) {
         if (x->arg(2, 0) == x->arg(2, 1)) return ElemOp{MIMK_OP_SQUARE, x->arg(2, 0), nullptr};
         return ElemOp{MIMK_OP_MUL, x->arg(2, 0), x->arg(2, 1)};
@@ -106,7 +109,6 @@ std::optional<ElemOp> elem_op(const Def* v) {
     }
     if (auto x = Axm::isa(math::tri::tanh, v)) return ElemOp{MIMK_OP_TANH, x->arg(), nullptr};
     if (auto x = Axm::isa(math::abs, v)) return ElemOp{MIMK_OP_ABS, x->arg(), nullptr};
-    if (auto x = Axm::isa(math::minus, v)) return ElemOp{MIMK_OP_NEG, x->arg(), nullptr};
     return {};
 }
 
