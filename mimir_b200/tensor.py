@@ -640,6 +640,51 @@ def _mrp_into(out, Sr, f, init, post, map_out, maps, ins):
     return out
 
 
+# From this many multiply-adds on a floating-point convolution runs as a contraction on the tensor cores (patches gathered by
+# one copy operation, then product_2d); below it, and for integers, as ONE map_reduce_post on the per-cell kernel, which keeps
+# the reference's ascending fold per output cell bit for bit.
+CONV_CONTRACTION_MIN_WORK = 1 << 27
+_CONV_PATCH_BYTES = 1 << 30   # patches of at most this many bytes at a time (whole images per piece)
+
+
+def _conv_on_tensor_cores(dtype, n, cin, cout, kh, kw, oh, ow) -> bool:
+    k = cin * kh * kw
+    if dtype == torch.bfloat16:   # the bf16 contraction's alignment rules
+        ok = k % 8 == 0 and cout % 8 == 0
+    elif dtype == torch.float32:  # the 3xTF32 contraction wants at least one 128 x 128 tile
+        ok = cout >= 128 and cout % 4 == 0 and oh * ow >= 128
+    else:
+        return False
+    return ok and n * cout * oh * ow * k >= CONV_CONTRACTION_MIN_WORK
+
+
+def _conv_as_contraction(xp, w, n, cin, cout, kh, kw, oh, ow, stride, dilation) -> torch.Tensor:
+    """conv as patches x weights: P[(n, oh, ow), (ci, kh, kw)] = xp[n, ci, oh*s + kh*d, ow*s + kw*d] gathered by one copy
+    operation (the read map conv_impl builds, tensor.mim:1254-1282, with the reduction loops turned into axes), then
+    P . W^T on the contraction kernels with W read through transpose_2d, then the channel axis moved forward by the tiled
+    permutation copy."""
+    k = cin * kh * kw
+    esize = xp.element_size()
+    per_image = oh * ow * k * esize
+    step = max(1, min(n, _CONV_PATCH_BYTES // max(per_image, 1)))
+    w2 = w.contiguous().view(cout, k)
+    out = torch.empty((n, cout, oh, ow), dtype=xp.dtype, device=xp.device)
+    # loops: 0 n, 1 oh, 2 ow, 3 ci, 4 kh, 5 kw
+    mi = [[0] * 7 for _ in range(4)]
+    mi[0][0] = 1
+    mi[1][3] = 1
+    mi[2][1], mi[2][4] = stride[0], dilation[0]
+    mi[3][2], mi[3][5] = stride[1], dilation[1]
+    for n0 in range(0, n, step):
+        nb = min(step, n - n0)
+        shape = (nb, oh, ow, cin, kh, kw)
+        patches = map_reduce_post(shape, shape, L.F_FIRST, 0.0, L.P_ID, id_map(6), [mi], [xp[n0:n0 + nb].contiguous()],
+                                  acc_dtype=torch.float32, out_dtype=xp.dtype)
+        y = product_2d(patches.view(nb * oh * ow, k), transpose_2d(w2))          # [(n, oh, ow), cout]
+        out[n0:n0 + nb] = transpose(y.view(nb, oh, ow, cout), (0, 3, 1, 2))
+    return out
+
+
 def conv(x: torch.Tensor, w: torch.Tensor, stride=(1, 1), dilation=(1, 1), padding=(0, 0)) -> torch.Tensor:
     """`conv R (stride, dilation, padding) (input, weight)`: NCHW input, [Cout, Cin, KH, KW] weight (tensor.mim:434-438).
     Loop vector (n, co, oh, ow, ci, kh, kw); the input is read at (n, ci, oh*s + kh*d, ow*s + kw*d) of the padded tensor
@@ -652,6 +697,8 @@ def conv(x: torch.Tensor, w: torch.Tensor, stride=(1, 1), dilation=(1, 1), paddi
     xp = pad(x, (0, 0, padding[0], padding[1]), (0, 0, padding[0], padding[1])) if any(padding) else x
     oh = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
     ow = (wd + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    if _conv_on_tensor_cores(x.dtype, n, cin, cout, kh, kw, oh, ow):
+        return _conv_as_contraction(xp, w, n, cin, cout, kh, kw, oh, ow, stride, dilation)
     mi = [[0] * 8 for _ in range(4)]
     mi[0][0] = 1
     mi[1][4] = 1

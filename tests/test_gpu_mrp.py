@@ -399,3 +399,29 @@ def test_composed_combiners_small_and_large(T, L):
                             [T.id_map(2), T.proj_map(2, (0,))], [cu(X), cu(m)])
     want = np.exp(X.astype(np.float64) - m[:, None]).sum(axis=1)
     assert np.abs(den.cpu().numpy() - want).max() / np.abs(want).max() < 1e-5
+
+
+def test_large_convolutions_run_as_contractions(T, L):
+    """From 2^27 multiply-adds on, conv gathers its patches with one copy operation and contracts them with the weights on the
+    tensor cores (f32 as 3xTF32, bf16 directly); the result is held to the same tolerance as the per-cell kernel's."""
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((4, 64, 32, 32)).astype(np.float32)
+    w = (rng.standard_normal((128, 64, 3, 3)) * 0.05).astype(np.float32)
+    assert T._conv_on_tensor_cores(torch.float32, 4, 64, 128, 3, 3, 32, 32)
+    got = T.conv(cu(x), cu(w), padding=(1, 1))
+    want = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), padding=(1, 1)).numpy()
+    assert got.shape == want.shape and mo.normalised_error(got.cpu().numpy(), want) < 1e-5
+    # strided and dilated, bf16
+    xb = torch.from_numpy(rng.standard_normal((8, 64, 30, 29)).astype(np.float32)).to(torch.bfloat16)
+    wb = torch.from_numpy((rng.standard_normal((64, 64, 3, 3)) * 0.05).astype(np.float32)).to(torch.bfloat16)
+    gotb = T.conv(xb.cuda(), wb.cuda(), stride=(1, 1), dilation=(2, 1), padding=(2, 1))
+    wantb = torch.nn.functional.conv2d(xb.double(), wb.double(), dilation=(2, 1), padding=(2, 1)).numpy()
+    assert gotb.shape == wantb.shape and mo.normalised_error(gotb.float().cpu().numpy(), wantb) < 2e-2
+    # the per-cell kernel on the same f32 problem (threshold lifted) agrees
+    keep = T.CONV_CONTRACTION_MIN_WORK
+    try:
+        T.CONV_CONTRACTION_MIN_WORK = 1 << 62
+        ref = T.conv(cu(x[:1]), cu(w), padding=(1, 1))
+    finally:
+        T.CONV_CONTRACTION_MIN_WORK = keep
+    assert mo.normalised_error(got[:1].cpu().numpy(), ref.cpu().numpy().astype(np.float64)) < 1e-5
