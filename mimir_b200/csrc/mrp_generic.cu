@@ -163,6 +163,81 @@ __global__ void __launch_bounds__(256) mrp_generic_kernel(const __grid_constant_
     }
 }
 
+// The same walk for instances whose input maps carry no floordiv / rem -- all but the reshape family: every input's offset
+// is then ONE linear form of the loop vector (the host folds the row-major strides into the coefficients; in range was
+// proven there, so the wrap-around arithmetic of the coordinates never wraps), and the reduction loops are walked like an
+// odometer: an add per input and step instead of divisions and a matrix product. The fold order is unchanged (last loop
+// fastest), so the results are the same bits.
+struct LinearMaps {
+    long long base[MIMK_MRP_MAX_INPUTS];
+    long long lin[MIMK_MRP_MAX_INPUTS][MIMK_MRP_MAX_LOOPS];
+};
+__global__ void __launch_bounds__(256) mrp_linear_kernel(const __grid_constant__ mimk_mrp_desc d, const __grid_constant__ LinearMaps lm,
+                                                        long long n_out, long long n_red) {
+    for (long long o = blockIdx.x * (long long)blockDim.x + threadIdx.x; o < n_out; o += (long long)gridDim.x * blockDim.x) {
+        long long loop[MIMK_MRP_MAX_LOOPS];
+        long long rem = o;
+        for (int l = d.ro - 1; l >= 0; --l) {
+            loop[l] = rem % d.sr[l];
+            rem /= d.sr[l];
+        }
+        long long off[MIMK_MRP_MAX_INPUTS];
+        for (int i = 0; i < d.nis; ++i) {
+            off[i] = lm.base[i];
+            for (int l = 0; l < d.ro; ++l) off[i] += lm.lin[i][l] * loop[l];
+        }
+        long long cnt[MIMK_MRP_MAX_LOOPS];
+        for (int l = d.ro; l < d.rn; ++l) cnt[l] = 0;
+        Val acc;
+        acc.i = d.acc_dtype == MIMK_I32 ? (long long)(int)d.init_bits : d.init_bits;
+        acc.f = __int_as_float((int)d.init_bits);
+        for (long long r = 0; r < n_red; ++r) {
+            Val in[MIMK_MRP_MAX_INPUTS];
+            for (int i = 0; i < d.nis; ++i) in[i] = load_val(d.in[i], d.in_dtype[i], off[i]);
+            for (int i = d.nis; i < 3; ++i) in[i].i = 0, in[i].f = 0.f;
+            acc = combine(d.comb, d.acc_dtype, acc, in);
+            for (int l = d.rn - 1; l >= d.ro; --l) {  // next point of the reduction box
+                for (int i = 0; i < d.nis; ++i) off[i] += lm.lin[i][l];
+                if (++cnt[l] < d.sr[l]) break;
+                for (int i = 0; i < d.nis; ++i) off[i] -= lm.lin[i][l] * d.sr[l];
+                cnt[l] = 0;
+            }
+        }
+        for (int l = d.ro; l < d.rn; ++l) loop[l] = 0;
+        long long wc[MIMK_MRP_MAX_RANK];
+        for (int j = 0; j < d.ro; ++j) {
+            unsigned long long v = (unsigned long long)d.map_out.coef[j][d.rn];
+            for (int l = 0; l < d.rn; ++l) v += (unsigned long long)d.map_out.coef[j][l] * (unsigned long long)loop[l];
+            if (d.map_out.div[j] > 0) v /= (unsigned long long)d.map_out.div[j];
+            if (d.map_out.mod[j] > 0) v %= (unsigned long long)d.map_out.mod[j];
+            wc[j] = (long long)v;
+        }
+        Val p0;
+        p0.i = 0, p0.f = 0.f;
+        if (d.nps > 0) p0 = load_val(d.post_in[0], d.post_dtype[0], map_offset(d.post_map[0], d.ro, wc, d.post_shape[0]));
+        unsigned long long woff = 0;
+        for (int j = 0; j < d.ro; ++j) woff = woff * (unsigned long long)d.so[j] + (unsigned long long)wc[j];
+        store_post(d.post, d.acc_dtype, d.out_dtype, acc, p0, d.out, (long long)woff);
+    }
+}
+
+// Folds the row-major strides of every input into its map's coefficients; false when a map has a floordiv / rem.
+bool linear_maps(const mimk_mrp_desc& d, LinearMaps& lm) {
+    for (int i = 0; i < d.nis; ++i) {
+        const mimk_affine_map& m = d.in_map[i];
+        lm.base[i] = 0;
+        for (int l = 0; l < MIMK_MRP_MAX_LOOPS; ++l) lm.lin[i][l] = 0;
+        long long stride = 1;
+        for (int j = m.rows - 1; j >= 0; --j) {
+            if (m.div[j] > 0 || m.mod[j] > 0) return false;
+            lm.base[i] += m.coef[j][d.rn] * stride;
+            for (int l = 0; l < d.rn; ++l) lm.lin[i][l] += m.coef[j][l] * stride;
+            stride *= d.in_shape[i][j];
+        }
+    }
+    return true;
+}
+
 // Range of an access map over the box 0 <= loop[l] < bound[l]: every result coordinate must stay in [0, extent). The
 // linear form is bounded first, then the floordiv / rem are applied to the bounds.
 bool map_in_range(const mimk_affine_map& m, int n, const int64_t* bounds, const int64_t* shape) {
@@ -258,6 +333,10 @@ extern "C" int mimk_map_reduce_post(const mimk_mrp_desc* d, void* stream) {
     long long blocks = (n_out + 255) / 256;
     const long long cap = (long long)dev->sm_count * 8;
     if (blocks > cap) blocks = cap;
-    mrp_generic_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(*d, n_out, n_red);
+    LinearMaps lm;
+    if (n_red > 0 && linear_maps(*d, lm))
+        mrp_linear_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(*d, lm, n_out, n_red);
+    else
+        mrp_generic_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(*d, n_out, n_red);
     return launch_status();
 }
