@@ -176,10 +176,19 @@ __global__ void __launch_bounds__(256) mrp_linear_kernel(const __grid_constant__
                                                         long long n_out, long long n_red) {
     for (long long o = blockIdx.x * (long long)blockDim.x + threadIdx.x; o < n_out; o += (long long)gridDim.x * blockDim.x) {
         long long loop[MIMK_MRP_MAX_LOOPS];
-        long long rem = o;
-        for (int l = d.ro - 1; l >= 0; --l) {
-            loop[l] = rem % d.sr[l];
-            rem /= d.sr[l];
+        if (n_out < (1ll << 31)) {  // every extent then fits 32 bits too: a 32-bit division costs a fifth of a 64-bit one
+            unsigned rem = (unsigned)o;
+            for (int l = d.ro - 1; l >= 0; --l) {
+                const unsigned e = (unsigned)d.sr[l], q = rem / e;
+                loop[l] = rem - q * e;
+                rem     = q;
+            }
+        } else {
+            long long rem = o;
+            for (int l = d.ro - 1; l >= 0; --l) {
+                loop[l] = rem % d.sr[l];
+                rem /= d.sr[l];
+            }
         }
         long long off[MIMK_MRP_MAX_INPUTS];
         for (int i = 0; i < d.nis; ++i) {
