@@ -43,7 +43,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="attn", choices=list(WORKLOADS))
-    ap.add_argument("--tp-gather", default="fused", choices=["fused", "nccl", "rows"],
+    ap.add_argument("--tp-gather", default="fused", choices=["fused", "nccl", "rows", "rows_fused"],
                     help="mlp_tp: all-gather of H fused into the GEMM epilogue (peer stores) or a separate NCCL all-gather")
     ap.add_argument("--weak", action="store_true", help="under torchrun: every rank runs the whole stated problem")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-records of the other workloads")
@@ -490,8 +490,10 @@ class MlpTP(Mlp):  # noqa: D101
         return {"workload": cls.name, "l2": "weights and H larger than the 126 MB L2",
                 "tp_gather": (mode + {"fused": " (H slabs stored into every rank's H from the contraction's epilogue over NVLink)",
                                       "nccl": " (separate NCCL all-gather of the H slabs)",
-                                      "rows": " (no gather of H: f32 partials of Y reduce-scattered over NCCL)"}[mode]) if world > 1 else "n/a",
-                "sharding": ("W1/W3 column slabs, W2 ROW slabs, Y row blocks after the reduce-scatter" if mode == "rows" and world > 1 else
+                                      "rows": " (no gather of H: f32 partials of Y reduce-scattered over NCCL)",
+                                      "rows_fused": " (no gather of H: f32 partials of Y added into the owners' row blocks from the "
+                                                    "second contraction's epilogue, bulk reductions over NVLink)"}[mode]) if world > 1 else "n/a",
+                "sharding": ("W1/W3 column slabs, W2 ROW slabs, Y row blocks after the reduce-scatter" if mode.startswith("rows") and world > 1 else
                              "W1/W3 column slabs, H all-gathered, W2 column slabs" +
                              (", Y all-gathered too" if gather and world > 1 else " (Y stays sharded)"))}
 
@@ -506,7 +508,7 @@ class MlpTP(Mlp):  # noqa: D101
         self.x = x
         self.w1 = w1[:, r * self.fl:(r + 1) * self.fl].contiguous()
         self.w3 = w3[:, r * self.fl:(r + 1) * self.fl].contiguous()
-        self.w2 = (w2[r * self.fl:(r + 1) * self.fl, :] if self.mode == "rows" and W > 1 else w2[:, r * self.nl:(r + 1) * self.nl]).contiguous()
+        self.w2 = (w2[r * self.fl:(r + 1) * self.fl, :] if self.mode.startswith("rows") and W > 1 else w2[:, r * self.nl:(r + 1) * self.nl]).contiguous()
         del w1, w3, w2
         t.cuda.empty_cache()
         self.yg = self.hg = None
@@ -518,6 +520,8 @@ class MlpTP(Mlp):  # noqa: D101
             self.h_local = t.empty((self.M, self.fl), device="cuda", dtype=t.bfloat16)
             if W > 1 and self.mode == "rows":
                 self.y_partial = t.empty((self.M, self.K), device="cuda", dtype=t.float32)
+            if W > 1 and self.mode == "rows_fused":
+                self.acc = shard.GatheredMatrix(self.M // W, self.K, dtype=t.float32)
         self.units = self.dom_units = self.traffic_units = 3 * 2 * self.M * self.K * self.F // W     # this rank's share
 
     def step(self, ev=None):
@@ -529,6 +533,8 @@ class MlpTP(Mlp):  # noqa: D101
             self.y = self.shard.tp_mlp_gated(self.x, self.w1, self.w3, self.w2, self.hg, gather="fused", y=self.yg)
         elif self.mode == "rows":
             self.y = self.shard.tp_mlp_gated_rows(self.x, self.w1, self.w3, self.w2, self.h_local, self.y_partial)
+        elif self.mode == "rows_fused":
+            self.y = self.shard.tp_mlp_gated_rows_fused(self.x, self.w1, self.w3, self.w2, self.h_local, self.acc)
         else:
             self.y = self.shard.tp_mlp_gated_nccl(self.x, self.w1, self.w3, self.w2, self.h_local, gather_y=self.gather)
         if ev:
@@ -542,7 +548,7 @@ class MlpTP(Mlp):  # noqa: D101
         x, w1, w3, w2 = self.weights()
         rows = [1, self.M - 1]
         b = lambda v: bits_np(np, t, v)
-        if self.mode == "rows" and self.world > 1:  # this rank holds rows [r M/W, (r+1) M/W) of the whole Y
+        if self.mode.startswith("rows") and self.world > 1:  # this rank holds rows [r M/W, (r+1) M/W) of the whole Y
             per = self.M // self.world
             mine = [1, per - 1]
             rows = [self.rank * per + i for i in mine]
@@ -870,7 +876,7 @@ def run_ours(args):
             plan = [("attn_weak", Attn, {"weak": True}),
                     ("gemm_cols", Gemm, {}), ("gemm_cols_gather", Gemm, {"gather": True}),
                     ("mlp_tp_fused", MlpTP, {"mode": "fused"}), ("mlp_tp_nccl", MlpTP, {"mode": "nccl"}),
-                    ("mlp_tp_rows", MlpTP, {"mode": "rows"})]
+                    ("mlp_tp_rows", MlpTP, {"mode": "rows"}), ("mlp_tp_rows_fused", MlpTP, {"mode": "rows_fused"})]
         plan = [p for p in plan if not (p[1] is W and not p[2])]
         for name, cls, kw in plan:
             env.torch.cuda.empty_cache()

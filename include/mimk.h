@@ -119,11 +119,26 @@ int mimk_gemm(const mimk_gemm_desc* desc, void* stream);
 #define MIMK_MAX_GATHER 8
 typedef struct mimk_gather_dst {
     int32_t n_dst;
-    int32_t pad_;
+    int32_t first; /* mimk_gemm_reduce_scatter: the destination whose rows this GPU computes first; 0 otherwise */
     void* dst[MIMK_MAX_GATHER];
     int64_t ldc, col_off; /* in elements */
 } mimk_gather_dst;
 int mimk_gemm_gather(const mimk_gemm_desc* desc, const void* b2, const mimk_gather_dst* dsts, void* stream);
+/* A reduce-scatter fused into a contraction's epilogue: the counterpart of mimk_gemm_gather for a contraction whose K
+ * dimension is sharded (every GPU holds a K-slab of A and the matching rows of B, so its product is a PARTIAL of the whole
+ * [m, n] result). Row block t of the f32 result, rows [t rows_per_dst, (t + 1) rows_per_dst), is ADDED into dsts->dst[t],
+ * an f32 [rows_per_dst, ldc] accumulator on the GPU that owns those rows (this GPU's or a peer-mapped pointer), at column
+ * offset col_off: bulk reductions (cp.reduce.async.bulk.tensor, f32 add performed by the memory system at the
+ * destination) from the shared-memory staging tile, over NVLink for a peer, while the tensor cores work on the next
+ * tile -- no partial matrix is written to this GPU's memory and no separate collective follows.
+ * The caller zeroes every accumulator and orders that before any GPU's call (a barrier across ranks), and orders every
+ * GPU's call before the accumulators are read (another barrier). The order of the additions is not fixed, so the sum is
+ * reproducible only up to f32 rounding. Every GPU should start at a different destination (dsts->first, e.g. the rank after
+ * its own, so that its own rows come last): GPUs that walk the row blocks in the same order all send to one destination
+ * at a time and share that GPU's inbound link. bf16 operands, f32 result, batch = 1, no epilogue, m = n_dst * rows_per_dst,
+ * rows_per_dst a multiple of 32, ldc and col_off multiples of 4. No counterpart in the reference
+ * (src/mim/plug/nvptx/phase/nvptx.cpp:186-204: one device). */
+int mimk_gemm_reduce_scatter(const mimk_gemm_desc* desc, const mimk_gather_dst* dsts, int64_t rows_per_dst, void* stream);
 /* mimk_gemm whose left operand arrives as `panels` row-major [m, k / panels] matrices stored one after another -- panel g
  * holds columns [g k/panels, (g+1) k/panels) of A. That is the layout an all-gather of column slabs delivers (every
  * rank's [m, k/panels] slab, in rank order), so the contraction that consumes a gathered matrix reads it where the

@@ -23,7 +23,7 @@ ROWS_SOFTMAX, ROWS_RMSNORM, ROWS_SOFTMAX_RMSNORM = 0, 1, 2
 # every symbol include/mimk.h declares
 SYMBOLS = (
     "mimk_status_str", "mimk_abi_version", "mimk_last_cuda_error", "mimk_device_check", "mimk_device_status", "mimk_selftest_wait_expiry",
-    "mimk_gemm", "mimk_gemm_flat", "mimk_gemm_gather", "mimk_gemm_kpanels", "mimk_reduce", "mimk_reduce_fused", "mimk_reduce_plan", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map", "mimk_map_t",
+    "mimk_gemm", "mimk_gemm_flat", "mimk_gemm_gather", "mimk_gemm_reduce_scatter", "mimk_gemm_kpanels", "mimk_reduce", "mimk_reduce_fused", "mimk_reduce_plan", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map", "mimk_map_t",
     "mimk_splat", "mimk_select", "mimk_generate_affine", "mimk_gather", "mimk_scatter", "mimk_attn_fwd", "mimk_mlp_gated", "mimk_map_reduce_post", "mimk_mrp_classify", "mimk_program_classify", "mimk_program_run", "mimk_chain_order", "mimk_chain_cost",
     "mimk_host_rows", "mimk_host_rows_pair", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_map_reduce_post", "mimk_host_register",
     "mimk_host_unregister", "mimk_host_release",
@@ -54,7 +54,7 @@ class ChainSplit(C.Structure):
 
 
 class GatherDst(C.Structure):
-    _fields_ = [("n_dst", C.c_int32), ("pad_", C.c_int32), ("dst", C.c_void_p * 8), ("ldc", C.c_int64), ("col_off", C.c_int64)]
+    _fields_ = [("n_dst", C.c_int32), ("first", C.c_int32), ("dst", C.c_void_p * 8), ("ldc", C.c_int64), ("col_off", C.c_int64)]
 
 
 class AttnDesc(C.Structure):
@@ -135,6 +135,7 @@ def lib() -> C.CDLL:
         L.mimk_selftest_wait_expiry.argtypes = [i64, vp]
         L.mimk_gemm.argtypes = [C.POINTER(GemmDesc), vp]
         L.mimk_gemm_gather.argtypes = [C.POINTER(GemmDesc), vp, C.POINTER(GatherDst), vp]
+        L.mimk_gemm_reduce_scatter.argtypes = [C.POINTER(GemmDesc), C.POINTER(GatherDst), i64, vp]
         L.mimk_gemm_kpanels.argtypes = [C.POINTER(GemmDesc), i64, vp]
         L.mimk_gemm_flat.argtypes = [i64, i64, i64, vp, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp, vp]
         L.mimk_reduce.argtypes = [vp, vp, ci, i64, i64, i64, ci, vp]

@@ -207,6 +207,26 @@ extern "C" int mimk_gemm_gather(const mimk_gemm_desc* d, const void* b2, const m
     return gemm_tc_any(dd, static_cast<cudaStream_t>(stream), b2 ? 1 : 0, b2, g);
 }
 
+extern "C" int mimk_gemm_reduce_scatter(const mimk_gemm_desc* d, const mimk_gather_dst* g, int64_t rows_per_dst,
+                                       void* stream) {
+    MIMK_TRY(check_gemm(d));
+    if (!g || g->n_dst < 1 || g->n_dst > MIMK_MAX_GATHER || g->ldc < 0 || g->col_off < 0 || rows_per_dst < 1) return MIMK_E_ARG;
+    if (g->col_off + d->n > g->ldc || rows_per_dst * g->n_dst != d->m) return MIMK_E_SHAPE;
+    if (g->ldc % 4 != 0 || g->col_off % 4 != 0 || rows_per_dst % 32 != 0) return MIMK_E_ALIGN;  // 16-byte pieces, 32-row boxes
+    for (int t = 0; t < g->n_dst; ++t)
+        if (!g->dst[t] || !aligned16(g->dst[t])) return MIMK_E_ARG;
+    int st = MIMK_OK;
+    if (!device_info(&st)) return st;
+    if (d->batch != 1 || d->post_full || d->post_row || d->post != MIMK_POST_ID) return MIMK_E_UNSUPPORTED;
+    if (d->out_dtype != MIMK_F32 || d->in_dtype != MIMK_BF16) return MIMK_E_DTYPE;
+    if (d->n == 0) return MIMK_OK;
+    if (!d->a || !d->b) return MIMK_E_ARG;
+    mimk_gemm_desc dd = *d;
+    dd.c              = g->dst[0];  // only its alignment is looked at; the tiles go to g->dst[*]
+    if (!gemm_tc_supported(dd)) return MIMK_E_UNSUPPORTED;
+    return gemm_tc2(dd, static_cast<cudaStream_t>(stream), 0, nullptr, g, 1, rows_per_dst);
+}
+
 extern "C" int mimk_gemm_kpanels(const mimk_gemm_desc* d, int64_t panels, void* stream) {
     MIMK_TRY(check_gemm(d));
     if (panels < 1) return MIMK_E_ARG;

@@ -65,8 +65,9 @@ int gemm_tc_supported(const mimk_gemm_desc& d);
 int gemm_tc(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr,
             int64_t a_panels = 1);
 int gemm_tc2_supported(const mimk_gemm_desc& d, int gated);  // the paired-SM (cta_group::2) form
+// scatter_rows > 0 (gemm_tc2 only): rows [t scatter_rows, (t + 1) scatter_rows) of the f32 result are added into gather->dst[t]
 int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather = nullptr,
-             int64_t a_panels = 1);
+             int64_t a_panels = 1, int64_t scatter_rows = 0);
 int gemm_tc_any(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
                 const mimk_gather_dst* gather = nullptr, int64_t a_panels = 1);  // picks between the two
 int gemm_f32_tc_supported(const mimk_gemm_desc& d);  // f32 operands on the tensor cores (3xTF32)

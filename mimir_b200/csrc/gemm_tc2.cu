@@ -58,6 +58,10 @@ struct Params {
     void* dst[MIMK_MAX_GATHER];
     int n_dst;
     int64_t ldc, col_off;
+    // > 0: a reduce-scatter fused into the epilogue instead. Rows [t scatter_rows, (t + 1) scatter_rows) of the f32 result
+    // are ADDED into destination t (an [scatter_rows, N] matrix: this GPU's or a peer's accumulator) by bulk reductions.
+    int64_t scatter_rows;
+    int64_t tile_rot;  // row tile (of 256 rows) this GPU starts with
     const float* post_row;
     const void* post_full;
     int post;
@@ -117,13 +121,17 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
 
 // Bulk (TMA) store of a [32 rows x 128 bytes] shared-memory tile to a destination matrix; rows / columns beyond the
 // matrix are clipped by the tensor map. x (in elements) times the element size is a multiple of 128 bytes here.
-__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t& tm, int64_t& tn) {
+// `rot` rotates the order of the row tiles (0 for an ordinary call): with a fused reduce-scatter every GPU starts at a
+// different owner's rows, so that the GPUs do not all send to the same destination at the same time.
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t rot, int64_t& tm,
+                                            int64_t& tn) {
     const int64_t per_group = GROUP_M * tiles_n;
     const int64_t group     = tile / per_group;
     const int64_t first_m   = group * GROUP_M;
     const int64_t gsize     = (tiles_m - first_m) < GROUP_M ? (tiles_m - first_m) : GROUP_M;
     const int64_t in_group  = tile % per_group;
-    tm                      = first_m + in_group % gsize;
+    tm                      = first_m + in_group % gsize + rot;
+    tm                      = tm >= tiles_m ? tm - tiles_m : tm;
     tn                      = in_group / gsize;
 }
 
@@ -180,7 +188,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             bool ok = true;
             for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 int64_t tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                tile_coords(tile, tiles_m, tiles_n, p.tile_rot, tm, tn);
                 const int m0 = int(tm * 2 * BM) + int(rank) * BM;
                 const int n0 = int(tn * BN) + int(rank) * BH;
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -261,7 +269,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const TOut* post_full = static_cast<const TOut*>(p.post_full);
         for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
             int64_t tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            tile_coords(tile, tiles_m, tiles_n, p.tile_rot, tm, tn);
             const int64_t row0 = tm * 2 * BM + int64_t(rank) * BM + quarter * 32;
             const int64_t row  = row0 + lane;
             const int64_t n0   = tn * BN;
@@ -337,8 +345,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 fence_proxy_async_smem();  // the bulk store reads shared memory through the async proxy
                 __syncwarp();
                 if (lane == 0) {
-                    if (row0 < p.M && n0 + c0 < p.N)
-                        for (int t = 0; t < p.n_dst; ++t) tma_store_2d(&om.m[t], buf, int(n0 + c0), int(row0));
+                    if (row0 < p.M && n0 + c0 < p.N) {
+                        if (sizeof(TOut) == 4 && p.scatter_rows > 0) {
+                            const int64_t owner = row0 / p.scatter_rows;
+                            tma_reduce_add_2d(&om.m[owner], buf, int(n0 + c0), int(row0 - owner * p.scatter_rows));
+                        } else {
+                            for (int t = 0; t < p.n_dst; ++t) tma_store_2d(&om.m[t], buf, int(n0 + c0), int(row0));
+                        }
+                    }
                     bulk_commit();
                 }
             }
@@ -392,7 +406,7 @@ int gemm_tc2_supported(const mimk_gemm_desc& d, int gated) {
 }
 
 int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2, const mimk_gather_dst* gather,
-             int64_t a_panels) {
+             int64_t a_panels, int64_t scatter_rows) {
     int st          = MIMK_OK;
     DeviceInfo* dev = device_info(&st);
     if (!dev) return st;
@@ -422,7 +436,11 @@ int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
             p.n_dst = gather->n_dst;
             for (int t = 0; t < gather->n_dst; ++t) p.dst[t] = gather->dst[t];
             p.ldc = gather->ldc, p.col_off = gather->col_off;
+            if (scatter_rows > 0 && (gated || d.out_dtype != MIMK_F32 || scatter_rows % 32 != 0 ||
+                                     scatter_rows * gather->n_dst != d.m))
+                return MIMK_E_UNSUPPORTED;
         } else {
+            if (scatter_rows > 0) return MIMK_E_UNSUPPORTED;
             p.n_dst  = 1;
             p.dst[0] = static_cast<uint8_t*>(d.c) + size_t(b * d.stride_c) * out_size;
             p.ldc = d.n, p.col_off = 0;
@@ -431,11 +449,19 @@ int gemm_tc2(const mimk_gemm_desc& d, cudaStream_t s, int gated, const void* b2,
         p.post_full = d.post_full ? static_cast<const uint8_t*>(d.post_full) + size_t(b * d.stride_c) * out_size : nullptr;
         p.post      = d.post;
         p.status    = dev->status_dev;
-        // destination maps: [M, N] windows (row pitch ldc) starting at column col_off, boxes of 32 rows x 128 bytes
+        p.scatter_rows = scatter_rows;
+        p.tile_rot     = 0;
+        if (scatter_rows > 0) {
+            const int64_t tiles_m = (d.m + 2 * BM - 1) / (2 * BM);
+            p.tile_rot = ((int64_t(gather->first) % gather->n_dst) * scatter_rows / (2 * BM)) % tiles_m;
+        }
+        // destination maps: [M, N] windows (row pitch ldc) starting at column col_off, boxes of 32 rows x 128 bytes;
+        // [scatter_rows, N] windows when the row blocks are scattered
         OutMaps om;
         for (int t = 0; t < p.n_dst; ++t) {
             const uint8_t* base = static_cast<const uint8_t*>(p.dst[t]) + size_t(p.col_off) * out_size;
-            MIMK_TRY(make_tmap_2d(&om.m[t], d.out_dtype == MIMK_F32, base, uint64_t(d.n), uint64_t(d.m),
+            MIMK_TRY(make_tmap_2d(&om.m[t], d.out_dtype == MIMK_F32, base, uint64_t(d.n),
+                                  uint64_t(scatter_rows > 0 ? scatter_rows : d.m),
                                   uint64_t(p.ldc) * out_size, uint32_t(128 / out_size), 32));
         }
         for (int t = p.n_dst; t < MIMK_MAX_GATHER; ++t) om.m[t] = om.m[0];

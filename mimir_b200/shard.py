@@ -247,6 +247,52 @@ def tp_mlp_gated_rows(x, w1_shard, w3_shard, w2_rows, h_local, y_partial: "torch
     return mine if out_dtype == torch.float32 else T.unary("copy", mine, out_dtype=out_dtype)
 
 
+def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, acc: GatheredMatrix):
+    """This rank's PARTIAL of `a . b` (its K-slab of a, the matching rows of b) added into the owners' accumulators from
+    the contraction's epilogue: row block t of the [m, n] product goes to rank t's `acc` (an f32 GatheredMatrix of
+    [m / world, n] per rank) by bulk reductions over NVLink.  Every rank zeroes `acc.local` and calls `acc.barrier()`
+    before any rank makes this call, and `acc.barrier()` again before reading `acc.local`."""
+    import ctypes as C
+
+    from . import _lib as L
+    from .tensor import _b_layout, _dt, _stream
+    a = a.contiguous()
+    b_store, layout = _b_layout(b)
+    m, k = a.shape
+    n = b.shape[1]
+    if a.shape[1] != b.shape[0] or acc.local.dtype != torch.float32 or acc.rows * acc.world != m or acc.cols != n:
+        raise ValueError("gemm_reduce_scatter: acc must be an f32 [m / world, n] GatheredMatrix")
+    d = L.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, m, n, k
+    d.a, d.b, d.c = a.data_ptr(), b_store.data_ptr(), acc.local.data_ptr()
+    d.stride_c = m * n
+    d.in_dtype, d.out_dtype, d.b_layout, d.post = _dt(a), L.F32, layout, L.POST_ID
+    g = L.GatherDst()
+    g.n_dst = acc.world
+    for i, ptr in enumerate(acc.ptrs):
+        g.dst[i] = ptr
+    g.ldc, g.col_off = acc.cols, 0
+    g.first = (acc.rank + 1) % acc.world      # every rank starts at another owner's rows; its own come last
+    L.check(L.lib().mimk_gemm_reduce_scatter(C.byref(d), C.byref(g), acc.rows, _stream()), "gemm_reduce_scatter")
+
+
+def tp_mlp_gated_rows_fused(x, w1_shard, w3_shard, w2_rows, h_local, acc: GatheredMatrix, out_dtype=None) -> torch.Tensor:
+    """tp_mlp_gated_rows with the reduce-scatter fused into the second contraction's epilogue: no partial Y in this
+    GPU's memory and no separate collective; every 32 x 32 piece of the f32 partial is added into the owning rank's
+    accumulator `acc` (an f32 GatheredMatrix of [M / world, N]) straight from shared memory while the tensor cores work on
+    the next tile. Returns rows [g M/G, (g+1) M/G) of Y: a converted copy, or `acc.local` itself for f32 (valid until the
+    next call).  The sum's order is not fixed: results agree with the NCCL form up to f32 rounding."""
+    from . import tensor as T
+    rank, world = _world()
+    out_dtype = out_dtype or x.dtype
+    acc.local.zero_()
+    gemm_gather_local(x, w1_shard, w3_shard, h_local)
+    acc.barrier()                      # every accumulator is zero before anybody adds into it
+    gemm_reduce_scatter(h_local, w2_rows, acc)
+    acc.barrier()                      # every rank's pieces have landed
+    return acc.local if out_dtype == torch.float32 else T.unary("copy", acc.local, out_dtype=out_dtype)
+
+
 def _gemm_into(a, b, out):
     """out = a b into a caller's buffer (f32 or bf16 result of bf16 operands)."""
     import ctypes as C

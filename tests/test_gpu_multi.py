@@ -61,6 +61,15 @@ def _worker(rank, world, port, out_dir):
     per = M // world
     wantr = mo.mlp_gated_truth(bits(x), bits(w1), bits(w3), bits(w2))[rank * per:(rank + 1) * per]
     assert yr.shape == (per, N) and mo.normalised_error(yr.float().cpu().numpy(), wantr) <= 2e-2
+    # ... and with the reduce-scatter fused into the second contraction's epilogue (bulk reductions into the owners' row
+    # blocks): twice, the accumulators are reused
+    acc = shard.GatheredMatrix(per, N, dtype=torch.float32)
+    for _ in range(2):
+        yf = shard.tp_mlp_gated_rows_fused(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), w3[:, rank * fl:(rank + 1) * fl].contiguous(),
+                                           w2[rank * fl:(rank + 1) * fl, :].contiguous(), h_loc, acc)
+        T.device_status()
+        assert yf.shape == (per, N) and mo.normalised_error(yf.float().cpu().numpy(), wantr) <= 2e-2
+        assert mo.normalised_error(yf.float().cpu().numpy(), yr.float().cpu().numpy()) <= 1e-2
 
     # a slab large enough for the paired-SM kernel (>= 74 tiles of 256 x 256 per rank): its epilogue sends each piece with
     # one bulk store per destination. The product is checked bit for bit against the one-GPU product of the same operands.
@@ -83,6 +92,13 @@ def _worker(rank, world, port, out_dir):
     whole_y = T.mlp_gated(x, w1, w3, w2)
     whole = whole_y[:, rank * nl:(rank + 1) * nl].float().cpu().numpy()
     assert mo.normalised_error(y.float().cpu().numpy(), whole) <= 1e-2
+    # W2 by rows, reduce-scatter in the epilogue, at the size where every CTA pair has tiles of several owners
+    accl = shard.GatheredMatrix(M // world, N, dtype=torch.float32)
+    hl = torch.empty((M, fl), dtype=torch.bfloat16, device="cuda")
+    yf = shard.tp_mlp_gated_rows_fused(x, w1[:, rank * fl:(rank + 1) * fl].contiguous(), w3[:, rank * fl:(rank + 1) * fl].contiguous(),
+                                       w2[rank * fl:(rank + 1) * fl, :].contiguous(), hl, accl, out_dtype=torch.float32)
+    T.device_status()
+    assert mo.normalised_error(yf.cpu().numpy(), whole_y[rank * (M // world):(rank + 1) * (M // world)].float().cpu().numpy()) <= 1e-2
     # the output all-gather fused into the second contraction as well: the whole Y on every rank
     yg = shard.GatheredMatrix(M, N)
     for mode in ("fused", "nccl"):
