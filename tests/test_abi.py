@@ -67,6 +67,16 @@ def test_argument_validation_needs_no_device(lib):
     assert L.mimk_host_map_reduce_post(C.byref(m)) == 1
     assert L.mimk_mrp_classify(None) == 0
     assert L.mimk_chain_order(0, None, None, 0, 8, None, None) == 1
+    # the fused reduce-scatter: row blocks must tile the result exactly, in whole 32-row boxes
+    d = lib.GemmDesc()
+    d.batch, d.m, d.n, d.k = 1, 512, 256, 256
+    d.in_dtype, d.out_dtype, d.post = lib.BF16, lib.F32, lib.POST_ID
+    g = lib.GatherDst()
+    g.n_dst, g.ldc, g.col_off = 2, 256, 0
+    assert L.mimk_gemm_reduce_scatter(C.byref(d), None, 256, None) == 1
+    assert L.mimk_gemm_reduce_scatter(C.byref(d), C.byref(g), 128, None) == 2      # E_SHAPE: 2 x 128 rows != m
+    d.m = 80
+    assert L.mimk_gemm_reduce_scatter(C.byref(d), C.byref(g), 40, None) == 3       # E_ALIGN: not whole 32-row boxes
 
 
 def test_no_cpu_fallback_without_device(lib):
