@@ -583,8 +583,8 @@ class MatmulF32(Workload):
     key = "matmul_f32"
     name = "matmul f32 256^3 (config C1)"
     metric, unit, dtype, bound = "TFLOP/s (f32 matmul 256^3)", "TFLOP/s", "f32", "tensor"
-    kernel = "split_kernel+split_transpose_kernel+gemm_f32_tc_kernel<f32>"
-    launches_per_step = 3
+    kernel = "gemm_simt_small_kernel<0>"
+    launches_per_step = 1
     scaling = "weak"
     tol = 1e-5
 

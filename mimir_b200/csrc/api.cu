@@ -184,7 +184,7 @@ extern "C" int mimk_gemm(const mimk_gemm_desc* d, void* stream) {
         const char* e = getenv("MIMK_F32_TC");
         f32_tc        = (e && e[0] == '0') ? 0 : 1;
     }
-    if (f32_tc && gemm_f32_tc_supported(*d)) return gemm_f32_tc(*d, s);
+    if (f32_tc && gemm_f32_tc_supported(*d) && !gemm_simt_preferred(*d)) return gemm_f32_tc(*d, s);
     return gemm_simt(*d, s);
 }
 

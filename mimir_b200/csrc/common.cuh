@@ -59,6 +59,7 @@ inline size_t dtype_size(int dt) { return dt == MIMK_BF16 ? 2 : (dt == MIMK_I64 
 
 // kernels implemented in the other translation units
 int gemm_simt(const mimk_gemm_desc& d, cudaStream_t s);
+int gemm_simt_preferred(const mimk_gemm_desc& d);  // small f32 product: the 32 x 32-tile CUDA-core kernel beats 3xTF32
 int gemm_tc_supported(const mimk_gemm_desc& d);
 // a_panels > 1: A is given as that many row-major [m, k / a_panels] matrices one after another (the layout an all-gather
 // of column slabs delivers); k / a_panels must then be a multiple of 64

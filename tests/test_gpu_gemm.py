@@ -267,6 +267,24 @@ def test_paired_sm_gated_mlp(T):
     assert nerr(f64(y[rows]), want) <= TOL_BF16
 
 
+@pytest.mark.parametrize("nk", [False, True])
+@pytest.mark.parametrize("m,n,K", [(96, 80, 520), (32, 32, 4), (33, 100, 128), (256, 256, 256), (7, 260, 1028)])
+def test_small_f32_products_same_bits_on_either_cuda_core_kernel(T, m, n, K, nk):
+    # a small product runs on 32 x 32 tiles with K staged in chunks; a product with several hundred 64 x 64 tiles (and an
+    # N the tensor-core path does not take) runs on the 64 x 64 kernel. Both fold every cell in ascending k with one fma
+    # per step, so a corner of the large product equals the small product of the same rows and columns bit for bit.
+    M, N = 1280, 961
+    a = uniform((M, K), 500 + K)
+    b = uniform((N, K) if nk else (K, N), 501 + K)
+    big = T.product_2d(a, T.transpose_2d(b) if nk else b)
+    bs = b[:n].contiguous() if nk else b[:, :n].contiguous()
+    small = T.product_2d(a[:m].contiguous(), T.transpose_2d(bs) if nk else bs)
+    T.device_status()
+    assert torch.equal(small, big[:m, :n])
+    want = mo.gemm_truth(a[:m].cpu().numpy(), bs.cpu().numpy(), b_nk=nk)
+    assert nerr(f64(small), want) <= TOL_F32
+
+
 @pytest.mark.parametrize("M,N,K,nk", [(512, 512, 8192, True), (384, 640, 4100, False), (1024, 1024, 1024, False)])
 def test_f32_on_tensor_cores_keeps_f32_accuracy(T, M, N, K, nk):
     # large f32 contractions run as three TF32 products per term with K cut into chunks summed in f32: the error must
@@ -285,7 +303,7 @@ def test_f32_on_tensor_cores_non_finite_operands(T, nk):
     # inf / NaN operands (and a finite value whose TF32 head rounds up to inf) must give what the scalar ascending fold
     # gives -- +-inf where every product has one sign, NaN where inf meets 0 or -inf -- not the NaN a head/tail split of
     # inf would spread over the row
-    M, N, K = 256, 384, 512
+    M, N, K = 512, 512, 640                                 # 2^27 products and more go to the tensor cores
     a, b = uniform((M, K), 90), uniform((N, K) if nk else (K, N), 91)
     a[3, 5], a[10, 0], a[200, 17] = float("inf"), float("nan"), 3.4028e38
     a[77, 8] = float("-inf")
