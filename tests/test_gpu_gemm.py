@@ -326,6 +326,38 @@ def test_f32_on_tensor_cores_non_finite_operands(T, nk):
     assert fin[sub].all() and nerr(c[sub].astype(np.float64), truth[sub]) <= TOL_F32
 
 
+@pytest.mark.parametrize("nk", [False, True])
+def test_reduce_scatter_epilogue_on_one_gpu(T, nk):
+    """The contraction whose epilogue ADDS its f32 tiles into the owners' row blocks (bulk reductions), with every
+    "owner" a buffer of this GPU: four row blocks, two calls into accumulators that start from a known value."""
+    from mimir_b200 import shard
+
+    class Blocks:                       # the parts of a GatheredMatrix the call looks at, all on this GPU
+        def __init__(self, world, rows, cols):
+            self.all = [torch.full((rows, cols), 0.5, dtype=torch.float32, device="cuda") for _ in range(world)]
+            self.world, self.rank, self.rows, self.cols = world, 1, rows, cols
+            self.local, self.ptrs = self.all[1], [t.data_ptr() for t in self.all]
+
+    M, N, K, W = 1280, 520, 384, 4
+    a = randn((M, K), 410, dtype=torch.bfloat16)
+    b = randn((N, K) if nk else (K, N), 411, 0.05, dtype=torch.bfloat16)
+    bv = T.transpose_2d(b) if nk else b
+    acc = Blocks(W, M // W, N)
+    shard.gemm_reduce_scatter(a, bv, acc)
+    shard.gemm_reduce_scatter(a, bv, acc)
+    T.device_status()
+    got = torch.cat(acc.all)
+    whole = T.product_2d(a, bv, out_dtype=torch.float32)
+    # one contribution per call and cell, so the order of the additions is fixed here: (0.5 + c) + c up to the last bit of
+    # the product itself (the reference product may come from the one-CTA kernel)
+    assert float((got - ((whole + 0.5) + whole)).abs().max()) <= 1e-5
+    want = mo.gemm_truth(bits(a), bits(b), b_nk=nk, bf16=True, rows=[0, M - 1])
+    assert nerr(f64(got[[0, M - 1]] - 0.5) / 2, want) <= TOL_BF16
+    # malformed requests are refused before anything is launched
+    with pytest.raises(ValueError):
+        shard.gemm_reduce_scatter(a[:100], bv, acc)
+
+
 @pytest.mark.parametrize("M,G,kp,N", [(300, 4, 128, 264), (2560, 8, 256, 2048), (512, 2, 64, 8)])
 @pytest.mark.parametrize("nk", [False, True])
 def test_left_operand_as_k_panels(T, M, G, kp, N, nk):
