@@ -247,6 +247,175 @@ bool linear_maps(const mimk_mrp_desc& d, LinearMaps& lm) {
     return true;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The compiled form of the same walk, for the instances that matter in volume: floating-point windows (conv, conv_grouped,
+// pool), patch gathers, pads and strided copies -- same element type everywhere, f32 accumulator, no epilogue operand, no
+// floordiv / rem in any map, fewer than 2^31 cells. The host turns the descriptor into a plan: every operand's offset (the
+// result's too) as one linear form of the loop vector, output loops of extent 1 dropped and neighbours merged where every
+// form allows it (n and c of an NCHW pool become one loop), each remaining extent with the multiplier and shift that
+// replace its division (Granlund-Montgomery, exact below 2^31), at most three reduction loops. The kernel is then
+// straight-line: no local arrays, the combiner a template argument. Fold order per cell is unchanged (reduction loops in
+// order, last fastest), so the results are the same bits as the interpreting kernels'.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int WIN_OUT = 6, WIN_RED = 3;
+struct WindowPlan {
+    unsigned ext[WIN_OUT], mul[WIN_OUT], shift[WIN_OUT];  // output loops, unused ones in front with extent 1
+    long long lin[4][WIN_OUT];                            // offset step per loop: inputs 0..2, result
+    long long base[4];
+    int rext[WIN_RED];                                    // reduction loops, unused ones in front with extent 1
+    long long rlin[3][WIN_RED];
+    int nis, comb, post;
+    float init;
+};
+
+template <class T> __device__ __forceinline__ float win_ld(const T* p, long long off);
+template <> __device__ __forceinline__ float win_ld<float>(const float* p, long long off) { return __ldg(p + off); }
+template <> __device__ __forceinline__ float win_ld<__nv_bfloat16>(const __nv_bfloat16* p, long long off) {
+    return __bfloat162float(__ldg(p + off));
+}
+
+// COMB: one of MIMK_F_ADD / MULADD / MAX / MIN / FIRST, or -1 for "whatever the plan says" (any floating-point combiner).
+template <class T, int COMB>
+__global__ void __launch_bounds__(256) mrp_window_kernel(const T* __restrict__ in0, const T* __restrict__ in1,
+                                                        const T* __restrict__ in2, T* __restrict__ out,
+                                                        const __grid_constant__ WindowPlan p, unsigned n_out) {
+    const int comb = COMB >= 0 ? COMB : p.comb;
+    const int nis  = COMB == MIMK_F_MULADD ? 2 : (COMB >= 0 ? 1 : p.nis);
+    for (unsigned long long o64 = blockIdx.x * 256ull + threadIdx.x; o64 < n_out; o64 += gridDim.x * 256ull) {
+        unsigned rem = unsigned(o64);
+        long long o0 = p.base[0], o1 = p.base[1], o2 = p.base[2], oo = p.base[3];
+#pragma unroll
+        for (int l = WIN_OUT - 1; l >= 0; --l) {
+            const unsigned q   = p.ext[l] == 1 ? rem : (__umulhi(rem, p.mul[l]) >> p.shift[l]);
+            const long long ix = rem - q * p.ext[l];
+            rem                = q;
+            o0 += p.lin[0][l] * ix, o1 += p.lin[1][l] * ix, o2 += p.lin[2][l] * ix, oo += p.lin[3][l] * ix;
+        }
+        Val acc;
+        acc.i = 0, acc.f = p.init;
+        for (int r0 = 0; r0 < p.rext[0]; ++r0) {
+            for (int r1 = 0; r1 < p.rext[1]; ++r1) {
+                long long a0 = o0 + r0 * p.rlin[0][0] + r1 * p.rlin[0][1];
+                long long a1 = o1 + r0 * p.rlin[1][0] + r1 * p.rlin[1][1];
+                long long a2 = o2 + r0 * p.rlin[2][0] + r1 * p.rlin[2][1];
+#pragma unroll 4
+                for (int r2 = 0; r2 < p.rext[2]; ++r2) {
+                    Val in[3];
+                    in[0].i = in[1].i = in[2].i = 0;
+                    in[0].f = win_ld(in0, a0);
+                    in[1].f = nis > 1 ? win_ld(in1, a1) : 0.f;
+                    in[2].f = nis > 2 ? win_ld(in2, a2) : 0.f;
+                    acc     = combine(comb, MIMK_F32, acc, in);
+                    a0 += p.rlin[0][2], a1 += p.rlin[1][2], a2 += p.rlin[2][2];
+                }
+            }
+        }
+        float v = acc.f;
+        if (p.post == MIMK_P_RELU) v = fmaxf(0.f, v);
+        else if (p.post == MIMK_P_SILU) v = v / (1.f + expf(-v));
+        if (sizeof(T) == 2) reinterpret_cast<__nv_bfloat16*>(out)[oo] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float*>(out)[oo] = v;
+    }
+}
+
+// Builds the plan; false when the instance is outside what the compiled walk covers.
+bool window_plan(const mimk_mrp_desc& d, const LinearMaps& lm, long long n_out, WindowPlan& p) {
+    if (d.acc_dtype != MIMK_F32 || (d.out_dtype != MIMK_F32 && d.out_dtype != MIMK_BF16) || d.nps != 0) return false;
+    if (d.post != MIMK_P_ID && d.post != MIMK_P_RELU && d.post != MIMK_P_SILU) return false;
+    if (d.nis < 1 || d.nis > 3 || n_out >= (1ll << 31)) return false;
+    for (int i = 0; i < d.nis; ++i)
+        if (d.in_dtype[i] != d.out_dtype) return false;
+    // the result's offset as a linear form of the output loops
+    long long olin[MIMK_MRP_MAX_LOOPS] = {}, obase = 0, stride = 1;
+    for (int j = d.map_out.rows - 1; j >= 0; --j) {
+        if (d.map_out.div[j] > 0 || d.map_out.mod[j] > 0) return false;
+        obase += d.map_out.coef[j][d.rn] * stride;
+        for (int l = 0; l < d.ro; ++l) olin[l] += d.map_out.coef[j][l] * stride;
+        stride *= d.so[j];
+    }
+    // loops as (extent, step of every form), innermost last; drop extent 1, merge neighbours every form agrees on
+    struct Loop {
+        long long ext, lin[4];
+    };
+    auto compact = [&](int first, int last, bool with_out, Loop* out_loops, int cap) -> int {
+        int n = 0;
+        for (int l = first; l < last; ++l) {
+            if (d.sr[l] == 1) continue;
+            Loop cur;
+            cur.ext = d.sr[l];
+            for (int i = 0; i < 3; ++i) cur.lin[i] = i < d.nis ? lm.lin[i][l] : 0;
+            cur.lin[3] = with_out ? olin[l] : 0;
+            bool merged = false;
+            if (n > 0) {
+                Loop& prev = out_loops[n - 1];  // prev is the outer neighbour: prev.lin == cur.lin * cur.ext on every form
+                merged     = prev.ext * cur.ext < (1ll << 31);
+                for (int f = 0; f < 4 && merged; ++f) merged = prev.lin[f] == cur.lin[f] * cur.ext;
+                if (merged) {
+                    prev.ext *= cur.ext;
+                    for (int f = 0; f < 4; ++f) prev.lin[f] = cur.lin[f];
+                }
+            }
+            if (!merged) {
+                if (n == cap) return -1;
+                out_loops[n++] = cur;
+            }
+        }
+        return n;
+    };
+    Loop ol[WIN_OUT], rl[WIN_RED];
+    const int no = compact(0, d.ro, true, ol, WIN_OUT);
+    const int nr = compact(d.ro, d.rn, false, rl, WIN_RED);
+    if (no < 0 || nr < 0) return false;
+    for (int l = 0; l < WIN_OUT; ++l) {
+        const int src = l - (WIN_OUT - no);
+        const long long e = src >= 0 ? ol[src].ext : 1;
+        p.ext[l] = unsigned(e);
+        if (e == 1) {
+            p.mul[l] = 0, p.shift[l] = 0;
+        } else {
+            int sft = 0;
+            while ((1ll << sft) < e) ++sft;  // ceil(log2 e)
+            const unsigned __int128 one = 1;
+            p.mul[l]   = unsigned(((one << (31 + sft)) + e - 1) / e);  // below 2^32 for e >= 2; exact quotients for n < 2^31
+            p.shift[l] = unsigned(sft - 1);
+        }
+        for (int f = 0; f < 4; ++f) p.lin[f][l] = src >= 0 ? ol[src].lin[f] : 0;
+    }
+    for (int l = 0; l < WIN_RED; ++l) {
+        const int src = l - (WIN_RED - nr);
+        if (src >= 0 && rl[src].ext >= (1ll << 31)) return false;
+        p.rext[l] = src >= 0 ? int(rl[src].ext) : 1;
+        for (int i = 0; i < 3; ++i) p.rlin[i][l] = src >= 0 ? rl[src].lin[i] : 0;
+    }
+    for (int i = 0; i < 3; ++i) p.base[i] = i < d.nis ? lm.base[i] : 0;
+    p.base[3] = obase;
+    p.nis = d.nis, p.comb = d.comb, p.post = d.post;
+    const int bits = int(d.init_bits);
+    memcpy(&p.init, &bits, sizeof(float));
+    return true;
+}
+
+template <class T>
+void launch_window(const mimk_mrp_desc& d, const WindowPlan& p, unsigned blocks, unsigned n_out, cudaStream_t s) {
+    const T* a = static_cast<const T*>(d.in[0]);
+    const T* b = static_cast<const T*>(d.nis > 1 ? d.in[1] : d.in[0]);
+    const T* c = static_cast<const T*>(d.nis > 2 ? d.in[2] : d.in[0]);
+    T* o       = static_cast<T*>(d.out);
+    switch (d.comb) {
+        case MIMK_F_ADD: mrp_window_kernel<T, MIMK_F_ADD><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        case MIMK_F_MAX: mrp_window_kernel<T, MIMK_F_MAX><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        case MIMK_F_MIN: mrp_window_kernel<T, MIMK_F_MIN><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        case MIMK_F_FIRST: mrp_window_kernel<T, MIMK_F_FIRST><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        case MIMK_F_MULADD:
+            if (d.nis == 2) {
+                mrp_window_kernel<T, MIMK_F_MULADD><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out);
+                break;
+            }
+            [[fallthrough]];
+        default: mrp_window_kernel<T, -1><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+    }
+}
+
 // Range of an access map over the box 0 <= loop[l] < bound[l]: every result coordinate must stay in [0, extent). The
 // linear form is bounded first, then the floordiv / rem are applied to the bounds.
 bool map_in_range(const mimk_affine_map& m, int n, const int64_t* bounds, const int64_t* shape) {
@@ -343,7 +512,12 @@ extern "C" int mimk_map_reduce_post(const mimk_mrp_desc* d, void* stream) {
     const long long cap = (long long)dev->sm_count * 8;
     if (blocks > cap) blocks = cap;
     LinearMaps lm;
-    if (n_red > 0 && linear_maps(*d, lm))
+    WindowPlan wp;
+    const bool linear = n_red > 0 && linear_maps(*d, lm);
+    if (linear && window_plan(*d, lm, n_out, wp)) {
+        if (d->out_dtype == MIMK_F32) launch_window<float>(*d, wp, (unsigned)blocks, (unsigned)n_out, static_cast<cudaStream_t>(stream));
+        else launch_window<__nv_bfloat16>(*d, wp, (unsigned)blocks, (unsigned)n_out, static_cast<cudaStream_t>(stream));
+    } else if (linear)
         mrp_linear_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(*d, lm, n_out, n_red);
     else
         mrp_generic_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(*d, n_out, n_red);
