@@ -265,56 +265,88 @@ struct WindowPlan {
     int rext[WIN_RED];                                    // reduction loops, unused ones in front with extent 1
     long long rlin[3][WIN_RED];
     int nis, comb, post;
+    int first;  // first output loop in use
     float init;
 };
 
-template <class T> __device__ __forceinline__ float win_ld(const T* p, long long off);
-template <> __device__ __forceinline__ float win_ld<float>(const float* p, long long off) { return __ldg(p + off); }
-template <> __device__ __forceinline__ float win_ld<__nv_bfloat16>(const __nv_bfloat16* p, long long off) {
-    return __bfloat162float(__ldg(p + off));
+__device__ __forceinline__ size_t win_at(unsigned off) { return size_t(off); }
+__device__ __forceinline__ size_t win_at(long long off) { return size_t(off); }
+template <class T, class Off> __device__ __forceinline__ float win_ld(const T* p, Off off);
+template <> __device__ __forceinline__ float win_ld<float, unsigned>(const float* p, unsigned off) { return __ldg(p + win_at(off)); }
+template <> __device__ __forceinline__ float win_ld<float, long long>(const float* p, long long off) { return __ldg(p + win_at(off)); }
+template <> __device__ __forceinline__ float win_ld<__nv_bfloat16, unsigned>(const __nv_bfloat16* p, unsigned off) {
+    return __bfloat162float(__ldg(p + win_at(off)));
+}
+template <> __device__ __forceinline__ float win_ld<__nv_bfloat16, long long>(const __nv_bfloat16* p, long long off) {
+    return __bfloat162float(__ldg(p + win_at(off)));
 }
 
 // COMB: one of MIMK_F_ADD / MULADD / MAX / MIN / FIRST, or -1 for "whatever the plan says" (any floating-point combiner).
-template <class T, int COMB>
+// Off: unsigned when every operand has fewer than 2^31 elements -- offsets are then computed modulo 2^32, which is exact for
+// the in-range values the host has proven them to be, at a third of the instructions of 64-bit arithmetic.
+template <class T, int COMB, class Off, int CELLS>
 __global__ void __launch_bounds__(256) mrp_window_kernel(const T* __restrict__ in0, const T* __restrict__ in1,
                                                         const T* __restrict__ in2, T* __restrict__ out,
                                                         const __grid_constant__ WindowPlan p, unsigned n_out) {
     const int comb = COMB >= 0 ? COMB : p.comb;
     const int nis  = COMB == MIMK_F_MULADD ? 2 : (COMB >= 0 ? 1 : p.nis);
-    for (unsigned long long o64 = blockIdx.x * 256ull + threadIdx.x; o64 < n_out; o64 += gridDim.x * 256ull) {
-        unsigned rem = unsigned(o64);
-        long long o0 = p.base[0], o1 = p.base[1], o2 = p.base[2], oo = p.base[3];
+    // CELLS = 4 cells per thread and pass when there are enough cells to go round: a copy-like instance has one load per
+    // cell, and a thread with a single load in flight leaves the memory system idle -- 2048 threads x 4 bytes per SM is a
+    // quarter of what the bandwidth-latency product needs.
+    const unsigned long long step = gridDim.x * 256ull;
+    for (unsigned long long o64 = blockIdx.x * 256ull + threadIdx.x; o64 < n_out; o64 += step * CELLS) {
+        Off o0[CELLS], o1[CELLS], o2[CELLS], oo[CELLS];
+        bool live[CELLS];
 #pragma unroll
-        for (int l = WIN_OUT - 1; l >= 0; --l) {
-            const unsigned q   = p.ext[l] == 1 ? rem : (__umulhi(rem, p.mul[l]) >> p.shift[l]);
-            const long long ix = rem - q * p.ext[l];
-            rem                = q;
-            o0 += p.lin[0][l] * ix, o1 += p.lin[1][l] * ix, o2 += p.lin[2][l] * ix, oo += p.lin[3][l] * ix;
+        for (int c = 0; c < CELLS; ++c) {
+            const unsigned long long cell = o64 + c * step;
+            live[c]      = cell < n_out;
+            unsigned rem = unsigned(live[c] ? cell : o64);  // a cell past the end repeats the first one and is not stored
+            o0[c] = Off(p.base[0]), o1[c] = Off(p.base[1]), o2[c] = Off(p.base[2]), oo[c] = Off(p.base[3]);
+#pragma unroll
+            for (int l = WIN_OUT - 1; l >= 0; --l) {
+                if (l < p.first) break;  // the same for every thread
+                const unsigned q = __umulhi(rem, p.mul[l]) >> p.shift[l];
+                const Off ix     = Off(rem - q * p.ext[l]);
+                rem              = q;
+                o0[c] += Off(p.lin[0][l]) * ix, oo[c] += Off(p.lin[3][l]) * ix;
+                if (nis > 1) o1[c] += Off(p.lin[1][l]) * ix;
+                if (nis > 2) o2[c] += Off(p.lin[2][l]) * ix;
+            }
         }
-        Val acc;
-        acc.i = 0, acc.f = p.init;
+        Val acc[CELLS];
+#pragma unroll
+        for (int c = 0; c < CELLS; ++c) acc[c].i = 0, acc[c].f = p.init;
         for (int r0 = 0; r0 < p.rext[0]; ++r0) {
             for (int r1 = 0; r1 < p.rext[1]; ++r1) {
-                long long a0 = o0 + r0 * p.rlin[0][0] + r1 * p.rlin[0][1];
-                long long a1 = o1 + r0 * p.rlin[1][0] + r1 * p.rlin[1][1];
-                long long a2 = o2 + r0 * p.rlin[2][0] + r1 * p.rlin[2][1];
-#pragma unroll 4
+                Off r01[3];  // this row of the window, relative to the cell
+#pragma unroll
+                for (int i = 0; i < 3; ++i) r01[i] = Off(r0) * Off(p.rlin[i][0]) + Off(r1) * Off(p.rlin[i][1]);
+#pragma unroll 2
                 for (int r2 = 0; r2 < p.rext[2]; ++r2) {
-                    Val in[3];
-                    in[0].i = in[1].i = in[2].i = 0;
-                    in[0].f = win_ld(in0, a0);
-                    in[1].f = nis > 1 ? win_ld(in1, a1) : 0.f;
-                    in[2].f = nis > 2 ? win_ld(in2, a2) : 0.f;
-                    acc     = combine(comb, MIMK_F32, acc, in);
-                    a0 += p.rlin[0][2], a1 += p.rlin[1][2], a2 += p.rlin[2][2];
+#pragma unroll
+                    for (int c = 0; c < CELLS; ++c) {
+                        Val in[3];
+                        in[0].i = in[1].i = in[2].i = 0;
+                        in[0].f = win_ld(in0, Off(o0[c] + r01[0]));
+                        in[1].f = nis > 1 ? win_ld(in1, Off(o1[c] + r01[1])) : 0.f;
+                        in[2].f = nis > 2 ? win_ld(in2, Off(o2[c] + r01[2])) : 0.f;
+                        acc[c]  = combine(comb, MIMK_F32, acc[c], in);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 3; ++i) r01[i] += Off(p.rlin[i][2]);
                 }
             }
         }
-        float v = acc.f;
-        if (p.post == MIMK_P_RELU) v = fmaxf(0.f, v);
-        else if (p.post == MIMK_P_SILU) v = v / (1.f + expf(-v));
-        if (sizeof(T) == 2) reinterpret_cast<__nv_bfloat16*>(out)[oo] = __float2bfloat16_rn(v);
-        else reinterpret_cast<float*>(out)[oo] = v;
+#pragma unroll
+        for (int c = 0; c < CELLS; ++c) {
+            float v = acc[c].f;
+            if (p.post == MIMK_P_RELU) v = fmaxf(0.f, v);
+            else if (p.post == MIMK_P_SILU) v = v / (1.f + expf(-v));
+            if (!live[c]) continue;
+            if (sizeof(T) == 2) reinterpret_cast<__nv_bfloat16*>(out)[win_at(oo[c])] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float*>(out)[win_at(oo[c])] = v;
+        }
     }
 }
 
@@ -371,7 +403,7 @@ bool window_plan(const mimk_mrp_desc& d, const LinearMaps& lm, long long n_out, 
         const long long e = src >= 0 ? ol[src].ext : 1;
         p.ext[l] = unsigned(e);
         if (e == 1) {
-            p.mul[l] = 0, p.shift[l] = 0;
+            p.mul[l] = 0, p.shift[l] = 0;  // never looked at: loops before `first` are skipped
         } else {
             int sft = 0;
             while ((1ll << sft) < e) ++sft;  // ceil(log2 e)
@@ -389,30 +421,30 @@ bool window_plan(const mimk_mrp_desc& d, const LinearMaps& lm, long long n_out, 
     }
     for (int i = 0; i < 3; ++i) p.base[i] = i < d.nis ? lm.base[i] : 0;
     p.base[3] = obase;
-    p.nis = d.nis, p.comb = d.comb, p.post = d.post;
+    p.nis = d.nis, p.comb = d.comb, p.post = d.post, p.first = WIN_OUT - no;
     const int bits = int(d.init_bits);
     memcpy(&p.init, &bits, sizeof(float));
     return true;
 }
 
-template <class T>
+template <class T, class Off, int CELLS>
 void launch_window(const mimk_mrp_desc& d, const WindowPlan& p, unsigned blocks, unsigned n_out, cudaStream_t s) {
     const T* a = static_cast<const T*>(d.in[0]);
     const T* b = static_cast<const T*>(d.nis > 1 ? d.in[1] : d.in[0]);
     const T* c = static_cast<const T*>(d.nis > 2 ? d.in[2] : d.in[0]);
     T* o       = static_cast<T*>(d.out);
     switch (d.comb) {
-        case MIMK_F_ADD: mrp_window_kernel<T, MIMK_F_ADD><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
-        case MIMK_F_MAX: mrp_window_kernel<T, MIMK_F_MAX><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
-        case MIMK_F_MIN: mrp_window_kernel<T, MIMK_F_MIN><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
-        case MIMK_F_FIRST: mrp_window_kernel<T, MIMK_F_FIRST><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        case MIMK_F_ADD: mrp_window_kernel<T, MIMK_F_ADD, Off, CELLS><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        case MIMK_F_MAX: mrp_window_kernel<T, MIMK_F_MAX, Off, CELLS><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        case MIMK_F_MIN: mrp_window_kernel<T, MIMK_F_MIN, Off, CELLS><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        case MIMK_F_FIRST: mrp_window_kernel<T, MIMK_F_FIRST, Off, CELLS><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
         case MIMK_F_MULADD:
             if (d.nis == 2) {
-                mrp_window_kernel<T, MIMK_F_MULADD><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out);
+                mrp_window_kernel<T, MIMK_F_MULADD, Off, CELLS><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out);
                 break;
             }
             [[fallthrough]];
-        default: mrp_window_kernel<T, -1><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
+        default: mrp_window_kernel<T, -1, Off, 1><<<blocks, 256, 0, s>>>(a, b, c, o, p, n_out); break;
     }
 }
 
@@ -515,8 +547,26 @@ extern "C" int mimk_map_reduce_post(const mimk_mrp_desc* d, void* stream) {
     WindowPlan wp;
     const bool linear = n_red > 0 && linear_maps(*d, lm);
     if (linear && window_plan(*d, lm, n_out, wp)) {
-        if (d->out_dtype == MIMK_F32) launch_window<float>(*d, wp, (unsigned)blocks, (unsigned)n_out, static_cast<cudaStream_t>(stream));
-        else launch_window<__nv_bfloat16>(*d, wp, (unsigned)blocks, (unsigned)n_out, static_cast<cudaStream_t>(stream));
+        bool narrow = true;  // every operand below 2^31 elements: 32-bit offsets
+        long long cells = 1;
+        for (int j = 0; j < d->ro; ++j) cells *= d->so[j];
+        narrow = cells < (1ll << 31);
+        for (int i = 0; i < d->nis; ++i) {
+            cells = 1;
+            for (int j = 0; j < d->in_map[i].rows; ++j) cells *= d->in_shape[i][j];
+            narrow = narrow && cells < (1ll << 31);
+        }
+        const auto st = static_cast<cudaStream_t>(stream);
+        const unsigned nb = (unsigned)blocks, no = (unsigned)n_out;
+        const bool many = n_out >= cap * 256 * 8;  // every thread of a full grid gets at least two passes of four cells
+        const bool f32  = d->out_dtype == MIMK_F32;
+        if (many) {
+            if (f32) narrow ? launch_window<float, unsigned, 4>(*d, wp, nb, no, st) : launch_window<float, long long, 4>(*d, wp, nb, no, st);
+            else narrow ? launch_window<__nv_bfloat16, unsigned, 4>(*d, wp, nb, no, st) : launch_window<__nv_bfloat16, long long, 4>(*d, wp, nb, no, st);
+        } else {
+            if (f32) narrow ? launch_window<float, unsigned, 1>(*d, wp, nb, no, st) : launch_window<float, long long, 1>(*d, wp, nb, no, st);
+            else narrow ? launch_window<__nv_bfloat16, unsigned, 1>(*d, wp, nb, no, st) : launch_window<__nv_bfloat16, long long, 1>(*d, wp, nb, no, st);
+        }
     } else if (linear)
         mrp_linear_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(*d, lm, n_out, n_red);
     else
