@@ -425,3 +425,37 @@ def test_large_convolutions_run_as_contractions(T, L):
     finally:
         T.CONV_CONTRACTION_MIN_WORK = keep
     assert mo.normalised_error(got[:1].cpu().numpy(), ref.cpu().numpy().astype(np.float64)) < 1e-5
+
+
+def test_windows_at_scale_against_torch(T):
+    """pool / pad / depthwise conv / flip at sizes where the compiled per-cell walk takes four cells per thread and pass
+    (millions of cells), against torch's own operators on the same tensors."""
+    F = torch.nn.functional
+    g = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn((8, 64, 224, 224), generator=g, device="cuda")
+    assert torch.equal(T.pool("max", x, (2, 2)), F.max_pool2d(x, 2))
+    assert torch.equal(T.pool("max", x, (3, 3), (2, 2), (1, 1), (1, 1)), F.max_pool2d(x, 3, 2, 1))
+    assert torch.equal(T.pool("min", x, (2, 3), (2, 3)), -F.max_pool2d(-x, (2, 3)))
+    got, want = T.pool("sum", x, (3, 3), (1, 1)), F.avg_pool2d(x, 3, 1) * 9
+    assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+    assert torch.equal(T.pad(x, (0, 0, 1, 2), (0, 0, 3, 0), -1.5), F.pad(x, (2, 0, 1, 3), value=-1.5))
+    assert torch.equal(T.flip(x), torch.flip(x, (0, 1, 2, 3)))
+    xb = x.to(torch.bfloat16)
+    assert torch.equal(T.pool("max", xb, (2, 2)), F.max_pool2d(xb.float(), 2).to(torch.bfloat16))
+    xd = torch.randn((16, 128, 56, 56), generator=g, device="cuda")
+    wd = torch.randn((128, 1, 3, 3), generator=g, device="cuda")
+    got, want = T.conv_grouped(xd, wd, 128, padding=(1, 1)), F.conv2d(xd, wd, padding=1, groups=128)
+    assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+    T.device_status()
+
+
+def test_strided_slice_of_a_tensor_beyond_2_to_31_elements(T):
+    """An operand of more than 2^31 elements makes the compiled walk keep 64-bit offsets; fewer than 2^31 cells are written."""
+    rows, cols = (1 << 20) + 2, 2048
+    x = torch.empty((rows, cols), dtype=torch.bfloat16, device="cuda")
+    # distinct-looking finite values: hashed bit patterns with the top exponent bit cleared (no inf / NaN, whose payload a
+    # copy through f32 need not keep)
+    x.view(torch.int16).copy_(((torch.arange(rows * cols, device="cuda", dtype=torch.int64) * 2654435761 >> 7) & 0xBFFF).to(torch.int16).view(rows, cols))
+    y = T.slice_(x, (1, 0), (2, 1), ((rows - 1) // 2, cols))
+    T.device_status()
+    assert torch.equal(y.view(torch.int16), x[1::2][: (rows - 1) // 2].view(torch.int16))
