@@ -651,8 +651,8 @@ def _conv_on_tensor_cores(dtype, n, cin, cout, kh, kw, oh, ow) -> bool:
     k = cin * kh * kw
     if dtype == torch.bfloat16:   # the bf16 contraction's alignment rules
         ok = k % 8 == 0 and cout % 8 == 0
-    elif dtype == torch.float32:  # the 3xTF32 contraction wants at least one 128 x 128 tile
-        ok = cout >= 128 and cout % 4 == 0 and oh * ow >= 128
+    elif dtype == torch.float32:  # the 3xTF32 contraction wants at least one 128 x 128 tile: fewer filters are padded with zeros
+        ok = cout >= 16 and n * oh * ow >= 128
     else:
         return False
     return ok and n * cout * oh * ow * k >= CONV_CONTRACTION_MIN_WORK
@@ -668,6 +668,12 @@ def _conv_as_contraction(xp, w, n, cin, cout, kh, kw, oh, ow, stride, dilation) 
     per_image = oh * ow * k * esize
     step = max(1, min(n, _CONV_PATCH_BYTES // max(per_image, 1)))
     w2 = w.contiguous().view(cout, k)
+    cpad = cout
+    if xp.dtype == torch.float32 and (cout < 128 or cout % 4):
+        # rows of zeros up to one tile of filters (a multiple of 4 beyond it): at most twice the tensor-core work, still
+        # far ahead of the per-cell kernel; the zero filters' columns of the product are dropped below
+        cpad = max(128, (cout + 3) // 4 * 4)
+        w2 = torch.cat([w2, torch.zeros((cpad - cout, k), dtype=w2.dtype, device=w2.device)])
     out = torch.empty((n, cout, oh, ow), dtype=xp.dtype, device=xp.device)
     # loops: 0 n, 1 oh, 2 ow, 3 ci, 4 kh, 5 kw
     mi = [[0] * 7 for _ in range(4)]
@@ -680,7 +686,9 @@ def _conv_as_contraction(xp, w, n, cin, cout, kh, kw, oh, ow, stride, dilation) 
         shape = (nb, oh, ow, cin, kh, kw)
         patches = map_reduce_post(shape, shape, L.F_FIRST, 0.0, L.P_ID, id_map(6), [mi], [xp[n0:n0 + nb].contiguous()],
                                   acc_dtype=torch.float32, out_dtype=xp.dtype)
-        y = product_2d(patches.view(nb * oh * ow, k), transpose_2d(w2))          # [(n, oh, ow), cout]
+        y = product_2d(patches.view(nb * oh * ow, k), transpose_2d(w2))          # [(n, oh, ow), cout (+ zero filters)]
+        if cpad != cout:
+            y = y[:, :cout].contiguous()
         out[n0:n0 + nb] = transpose(y.view(nb, oh, ow, cout), (0, 3, 1, 2))
     return out
 

@@ -411,6 +411,13 @@ def test_large_convolutions_run_as_contractions(T, L):
     got = T.conv(cu(x), cu(w), padding=(1, 1))
     want = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), padding=(1, 1)).numpy()
     assert got.shape == want.shape and mo.normalised_error(got.cpu().numpy(), want) < 1e-5
+    # fewer filters than one tensor-core tile (and not a multiple of 4): zero filters fill the tile and are dropped again
+    w3 = (rng.standard_normal((30, 64, 3, 3)) * 0.05).astype(np.float32)
+    x3 = rng.standard_normal((16, 64, 64, 64)).astype(np.float32)
+    assert T._conv_on_tensor_cores(torch.float32, 16, 64, 30, 3, 3, 32, 32)
+    got3 = T.conv(cu(x3), cu(w3), stride=(2, 2), padding=(1, 1))
+    want3 = torch.nn.functional.conv2d(torch.from_numpy(x3).double(), torch.from_numpy(w3).double(), stride=2, padding=1).numpy()
+    assert got3.shape == want3.shape and mo.normalised_error(got3.cpu().numpy(), want3) < 1e-5
     # strided and dilated, bf16
     xb = torch.from_numpy(rng.standard_normal((8, 64, 30, 29)).astype(np.float32)).to(torch.bfloat16)
     wb = torch.from_numpy((rng.standard_normal((64, 64, 3, 3)) * 0.05).astype(np.float32)).to(torch.bfloat16)
