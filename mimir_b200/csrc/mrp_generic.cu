@@ -266,6 +266,10 @@ struct WindowPlan {
     long long rlin[3][WIN_RED];
     int nis, comb, post;
     int first;  // first output loop in use
+    // The outermost loop in use cut into four equal parts (when its extent allows): a thread's four cells then share every
+    // loop index but that one, their offsets differ by `quarter_step`, and one decomposition serves all four.
+    int split;
+    long long quarter_step[4];
     float init;
 };
 
@@ -294,13 +298,21 @@ __global__ void __launch_bounds__(256) mrp_window_kernel(const T* __restrict__ i
     // cell, and a thread with a single load in flight leaves the memory system idle -- 2048 threads x 4 bytes per SM is a
     // quarter of what the bandwidth-latency product needs.
     const unsigned long long step = gridDim.x * 256ull;
-    for (unsigned long long o64 = blockIdx.x * 256ull + threadIdx.x; o64 < n_out; o64 += step * CELLS) {
+    const bool split               = CELLS == 4 && p.split;  // the same for every thread
+    const unsigned long long limit = split ? n_out / 4 : n_out;
+    for (unsigned long long o64 = blockIdx.x * 256ull + threadIdx.x; o64 < limit; o64 += split ? step : step * CELLS) {
         Off o0[CELLS], o1[CELLS], o2[CELLS], oo[CELLS];
         bool live[CELLS];
 #pragma unroll
         for (int c = 0; c < CELLS; ++c) {
+            if (split && c > 0) {  // cell c = cell 0 with the outermost index moved on by c quarters of its extent
+                live[c] = true;
+                o0[c] = o0[0] + Off(c) * Off(p.quarter_step[0]), o1[c] = o1[0] + Off(c) * Off(p.quarter_step[1]);
+                o2[c] = o2[0] + Off(c) * Off(p.quarter_step[2]), oo[c] = oo[0] + Off(c) * Off(p.quarter_step[3]);
+                continue;
+            }
             const unsigned long long cell = o64 + c * step;
-            live[c]      = cell < n_out;
+            live[c]      = cell < limit;
             unsigned rem = unsigned(live[c] ? cell : o64);  // a cell past the end repeats the first one and is not stored
             o0[c] = Off(p.base[0]), o1[c] = Off(p.base[1]), o2[c] = Off(p.base[2]), oo[c] = Off(p.base[3]);
 #pragma unroll
@@ -422,6 +434,8 @@ bool window_plan(const mimk_mrp_desc& d, const LinearMaps& lm, long long n_out, 
     for (int i = 0; i < 3; ++i) p.base[i] = i < d.nis ? lm.base[i] : 0;
     p.base[3] = obase;
     p.nis = d.nis, p.comb = d.comb, p.post = d.post, p.first = WIN_OUT - no;
+    p.split = no > 0 && ol[0].ext % 4 == 0;
+    for (int f = 0; f < 4; ++f) p.quarter_step[f] = p.split ? ol[0].lin[f] * (ol[0].ext / 4) : 0;
     const int bits = int(d.init_bits);
     memcpy(&p.init, &bits, sizeof(float));
     return true;
