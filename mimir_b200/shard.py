@@ -285,6 +285,9 @@ def tp_mlp_gated_rows_fused(x, w1_shard, w3_shard, w2_rows, h_local, acc: Gather
     from . import tensor as T
     rank, world = _world()
     out_dtype = out_dtype or x.dtype
+    if world == 1:
+        gemm_gather_local(x, w1_shard, w3_shard, h_local)
+        return T.product_2d(h_local, w2_rows, out_dtype=out_dtype)
     acc.local.zero_()
     gemm_gather_local(x, w1_shard, w3_shard, h_local)
     acc.barrier()                      # every accumulator is zero before anybody adds into it
