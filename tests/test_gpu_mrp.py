@@ -459,10 +459,12 @@ def test_windows_at_scale_against_torch(T):
 def test_strided_slice_of_a_tensor_beyond_2_to_31_elements(T):
     """An operand of more than 2^31 elements makes the compiled walk keep 64-bit offsets; fewer than 2^31 cells are written."""
     rows, cols = (1 << 20) + 2, 2048
-    x = torch.empty((rows, cols), dtype=torch.bfloat16, device="cuda")
-    # distinct-looking finite values: hashed bit patterns with the top exponent bit cleared (no inf / NaN, whose payload a
-    # copy through f32 need not keep)
-    x.view(torch.int16).copy_(((torch.arange(rows * cols, device="cuda", dtype=torch.int64) * 2654435761 >> 7) & 0xBFFF).to(torch.int16).view(rows, cols))
+    # distinct-looking finite values built in 16-bit arithmetic (no 64-bit temporaries of 2^31 elements): a pattern of row and
+    # column with the top exponent bit cleared -- no inf / NaN, whose payload a copy through f32 need not keep
+    r16 = torch.arange(rows, device="cuda", dtype=torch.int32).to(torch.int16)[:, None]
+    c16 = torch.arange(cols, device="cuda", dtype=torch.int32).to(torch.int16)[None, :]
+    x = ((r16 * 251 + c16 * 7) & -16385).view(torch.bfloat16)
+    assert x.shape == (rows, cols) and x.numel() > (1 << 31)
     y = T.slice_(x, (1, 0), (2, 1), ((rows - 1) // 2, cols))
     T.device_status()
     assert torch.equal(y.view(torch.int16), x[1::2][: (rows - 1) // 2].view(torch.int16))
