@@ -383,6 +383,17 @@ int mimk_map_reduce_post(const mimk_mrp_desc* desc, void* stream);
  * Pure host logic: needs no device. No counterpart in the reference, whose GPU lowering has the one kernel shape. */
 enum { MIMK_ROUTE_GENERIC = 0, MIMK_ROUTE_GEMM = 1, MIMK_ROUTE_REDUCE = 2, MIMK_ROUTE_MAP = 3, MIMK_ROUTE_PERMUTE = 4, MIMK_ROUTE_COPY = 5 };
 int mimk_mrp_classify(const mimk_mrp_desc* desc);
+/* Which per-cell kernel an instance that stays on MIMK_ROUTE_GENERIC runs on -- all three keep the reference's kernel shape
+ * (one thread per output cell, the reduction loops folded in order: lower_map_reduce.cpp:198-260) and give the same bits:
+ *   INTERPRETED  maps, combiner and epilogue read as data; the only one that takes floordiv / rem in an input map
+ *   LINEAR       every input's offset one linear form of the loop vector, the reduction box walked like an odometer
+ *   COMPILED     the linear forms in straight-line code with the combiner fixed at compile time: floating-point instances
+ *                with one element type throughout, no epilogue operand, fewer than 2^31 cells, and -- after loops of extent
+ *                1 are dropped and neighbours merged where every operand's form allows it (n and c of an NCHW pool become
+ *                one loop) -- at most 6 output and 3 reduction loops. `loops`, if not NULL, receives those two counts.
+ * conv / conv_grouped / pool / pad / strided copies of tensor.mim:434-451, 499-504 land on COMPILED. Pure host logic. */
+enum { MIMK_CELL_INTERPRETED = 0, MIMK_CELL_LINEAR = 1, MIMK_CELL_COMPILED = 2 };
+int mimk_mrp_cell_kernel(const mimk_mrp_desc* desc, int32_t* loops);
 
 /* ---- programs: a list of map_reduce_post operations -----------------------------------------------------------
  * `ops` are executed in order; an input (or epilogue input) whose pointer equals the `out` of an earlier operation reads

@@ -24,7 +24,7 @@ ROWS_SOFTMAX, ROWS_RMSNORM, ROWS_SOFTMAX_RMSNORM = 0, 1, 2
 SYMBOLS = (
     "mimk_status_str", "mimk_abi_version", "mimk_last_cuda_error", "mimk_device_check", "mimk_device_status", "mimk_selftest_wait_expiry",
     "mimk_gemm", "mimk_gemm_flat", "mimk_gemm_gather", "mimk_gemm_reduce_scatter", "mimk_gemm_kpanels", "mimk_reduce", "mimk_reduce_fused", "mimk_reduce_plan", "mimk_reduce_static", "mimk_softmax", "mimk_rmsnorm", "mimk_softmax_rmsnorm", "mimk_map", "mimk_map_t",
-    "mimk_splat", "mimk_select", "mimk_generate_affine", "mimk_gather", "mimk_scatter", "mimk_attn_fwd", "mimk_mlp_gated", "mimk_map_reduce_post", "mimk_mrp_classify", "mimk_program_classify", "mimk_program_run", "mimk_chain_order", "mimk_chain_cost",
+    "mimk_splat", "mimk_select", "mimk_generate_affine", "mimk_gather", "mimk_scatter", "mimk_attn_fwd", "mimk_mlp_gated", "mimk_map_reduce_post", "mimk_mrp_classify", "mimk_mrp_cell_kernel", "mimk_program_classify", "mimk_program_run", "mimk_chain_order", "mimk_chain_cost",
     "mimk_host_rows", "mimk_host_rows_pair", "mimk_host_gemm", "mimk_host_attn_fwd", "mimk_host_mlp_gated", "mimk_host_map_reduce_post", "mimk_host_register",
     "mimk_host_unregister", "mimk_host_release",
 )
@@ -158,6 +158,7 @@ def lib() -> C.CDLL:
         L.mimk_mlp_gated.argtypes = [C.POINTER(MlpDesc), vp]
         L.mimk_map_reduce_post.argtypes = [C.POINTER(MrpDesc), vp]
         L.mimk_mrp_classify.argtypes = [C.POINTER(MrpDesc)]
+        L.mimk_mrp_cell_kernel.argtypes = [C.POINTER(MrpDesc), C.POINTER(C.c_int32)]
         L.mimk_chain_order.argtypes = [C.c_int32, C.POINTER(i64), C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.POINTER(ChainSplit), C.POINTER(C.c_double)]
         L.mimk_chain_cost.argtypes = [C.c_int32, C.POINTER(i64), C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.POINTER(ChainSplit), C.c_int32, C.POINTER(C.c_double)]
         L.mimk_host_rows.argtypes = [ci, vp, vp, vp, ci, ci, i64, i64, cf]

@@ -266,6 +266,7 @@ struct WindowPlan {
     long long rlin[3][WIN_RED];
     int nis, comb, post;
     int first;  // first output loop in use
+    int n_red_loops;  // reduction loops in use (for mimk_mrp_cell_kernel; the kernel walks all three slots)
     // The outermost loop in use cut into four equal parts (when its extent allows): a thread's four cells then share every
     // loop index but that one, their offsets differ by `quarter_step`, and one decomposition serves all four.
     int split;
@@ -434,6 +435,7 @@ bool window_plan(const mimk_mrp_desc& d, const LinearMaps& lm, long long n_out, 
     for (int i = 0; i < 3; ++i) p.base[i] = i < d.nis ? lm.base[i] : 0;
     p.base[3] = obase;
     p.nis = d.nis, p.comb = d.comb, p.post = d.post, p.first = WIN_OUT - no;
+    p.n_red_loops = nr;
     p.split = no > 0 && ol[0].ext % 4 == 0;
     for (int f = 0; f < 4; ++f) p.quarter_step[f] = p.split ? ol[0].lin[f] * (ol[0].ext / 4) : 0;
     const int bits = int(d.init_bits);
@@ -494,6 +496,23 @@ bool dtype_ok(int dt) { return dt == MIMK_F32 || dt == MIMK_BF16 || dt == MIMK_I
 }  // namespace mimk
 
 using namespace mimk;
+
+extern "C" int mimk_mrp_cell_kernel(const mimk_mrp_desc* d, int32_t* loops) {
+    if (loops) loops[0] = loops[1] = 0;
+    if (!d || d->ro < 0 || d->rn < d->ro || d->rn > MIMK_MRP_MAX_LOOPS || d->ro > MIMK_MRP_MAX_RANK) return MIMK_CELL_INTERPRETED;
+    if (d->nis < 0 || d->nis > MIMK_MRP_MAX_INPUTS || d->map_out.rows != d->ro) return MIMK_CELL_INTERPRETED;
+    long long n_out = 1, n_red = 1;
+    for (int l = 0; l < d->rn; ++l) {
+        if (d->sr[l] < 0) return MIMK_CELL_INTERPRETED;
+        (l < d->ro ? n_out : n_red) *= d->sr[l];
+    }
+    LinearMaps lm;
+    WindowPlan wp;
+    if (n_red <= 0 || !linear_maps(*d, lm)) return MIMK_CELL_INTERPRETED;
+    if (!window_plan(*d, lm, n_out, wp)) return MIMK_CELL_LINEAR;
+    if (loops) loops[0] = WIN_OUT - wp.first, loops[1] = wp.n_red_loops;
+    return MIMK_CELL_COMPILED;
+}
 
 extern "C" int mimk_map_reduce_post(const mimk_mrp_desc* d, void* stream) {
     if (!d) return MIMK_E_ARG;

@@ -448,6 +448,21 @@ def mrp_route(So, Sr, f: int, init, post: int, map_out, maps, in_shapes, in_dtyp
     return ROUTES[L.lib().mimk_mrp_classify(C.byref(d))]
 
 
+CELL_KERNELS = {0: "interpreted", 1: "linear", 2: "compiled"}
+
+
+def mrp_cell_kernel(So, Sr, f: int, init, post: int, map_out, maps, in_shapes, in_dtypes, *, acc_dtype=torch.float32,
+                    out_dtype=None):
+    """Which per-cell kernel an instance that stays on the "generic" route runs on, and for "compiled" how many output and
+    reduction loops are left after merging: ("compiled", 3, 2) for an NCHW pool. Host logic (mimk_mrp_cell_kernel)."""
+    So, Sr = [int(v) for v in So], [int(v) for v in Sr]
+    d = _mrp_desc(So, Sr, f, init, post, map_out, maps, [(0, dt, tuple(sh)) for sh, dt in zip(in_shapes, in_dtypes)], (), [],
+                  acc_dtype, out_dtype or acc_dtype, 0)
+    loops = (C.c_int32 * 2)()
+    kind = L.lib().mimk_mrp_cell_kernel(C.byref(d), loops)
+    return CELL_KERNELS[kind], int(loops[0]), int(loops[1])
+
+
 def map_reduce_post(So, Sr, f: int, init, post: int, map_out, maps, ins, post_maps=(), post_ins=(), *,
                     acc_dtype=None, out_dtype=None) -> torch.Tensor:
     """`map_reduce_post` itself (tensor.mim:159-169): combiner / epilogue by id (mimir_b200._lib.F_*, P_*), access

@@ -204,3 +204,59 @@ def test_elementwise_operators_with_a_unary_one_behind_them(TL):
     # a transposed first operand is not an elementwise map
     assert T.mrp_route([2048, 1024], [2048, 1024], relu_add, 0.0, L.P_ID, T.id_map(2), [T.proj_map(2, [1, 0]), T.id_map(2)],
                        [big, [2048, 1024]], [F32, F32]) == "generic"
+
+
+def _pool_maps(T, stride, dilation):
+    mi = [[0] * 7 for _ in range(4)]
+    mi[0][0] = mi[1][1] = 1
+    mi[2][2], mi[2][4] = stride[0], dilation[0]
+    mi[3][3], mi[3][5] = stride[1], dilation[1]
+    return mi
+
+
+def test_which_per_cell_kernel_runs_a_generic_instance(TL):
+    """The compiled walk takes floating-point windows / gathers / pads after dropping extent-1 loops and merging the
+    neighbours every operand's linear form agrees on; integers and floordiv / rem maps stay on the interpreting kernels."""
+    T, L = TL
+    # NCHW max pool 2x2 / 2 whose windows tile the rows exactly (32 = 2 * 16): n, c and oh merge -- every operand's form steps
+    # extent(inner) * step(inner) per outer index -- and ow stays apart (two columns per step, rows 32 apart)
+    shape_in, so = [8, 16, 32, 32], [8, 16, 16, 16]
+    pool = lambda dt, **kw: T.mrp_cell_kernel(so, so + [2, 2], L.F_MAX, NEG_INF, L.P_ID, T.proj_map(6, (0, 1, 2, 3)),
+                                             [_pool_maps(T, (2, 2), (1, 1))], [shape_in], [dt], **kw)
+    assert pool(F32) == ("compiled", 2, 2)
+    assert pool(BF16, out_dtype=BF16) == ("compiled", 2, 2)
+    assert pool(BF16) == ("linear", 0, 0)                                   # bf16 in, f32 out: not one element type
+    # 3x3 / 2 over 33 rows: 16 windows do not tile 33 rows, so oh no longer merges with c; n and c still do
+    so3 = [8, 16, 16, 16]
+    assert T.mrp_cell_kernel(so3, so3 + [3, 3], L.F_MAX, NEG_INF, L.P_ID, T.proj_map(6, (0, 1, 2, 3)),
+                             [_pool_maps(T, (2, 2), (1, 1))], [[8, 16, 33, 33]], [F32]) == ("compiled", 3, 2)
+    # a 1x1 "window": the reduction loops have extent 1 and vanish; stride 1 then lets oh and ow merge with everything
+    one = T.mrp_cell_kernel(shape_in, shape_in + [1, 1], L.F_MAX, NEG_INF, L.P_ID, T.proj_map(6, (0, 1, 2, 3)),
+                            [_pool_maps(T, (1, 1), (1, 1))], [shape_in], [F32])
+    assert one == ("compiled", 1, 0)
+    # conv, loops (n, co, oh, ow | ci, kh, kw): nothing merges on the output side (x ignores co, w ignores n, oh, ow);
+    # kh and kw walk w contiguously but x with a row pitch, so only the weights would merge them
+    n, cin, cout, h, kh = 2, 8, 16, 12, 3
+    mi = [[0] * 8 for _ in range(4)]
+    mi[0][0], mi[1][4] = 1, 1
+    mi[2][2], mi[2][5] = 1, 1
+    mi[3][3], mi[3][6] = 1, 1
+    oh = h - kh + 1
+    conv = T.mrp_cell_kernel([n, cout, oh, oh], [n, cout, oh, oh, cin, kh, kh], L.F_MULADD, 0.0, L.P_ID, T.proj_map(7, (0, 1, 2, 3)),
+                             [mi, T.proj_map(7, (1, 4, 5, 6))], [[n, cin, h, h], [cout, cin, kh, kh]], [F32, F32])
+    assert conv == ("compiled", 4, 3)
+    # the same convolution on integers keeps the interpreting walk (linear form: no floordiv / rem)
+    convi = T.mrp_cell_kernel([n, cout, oh, oh], [n, cout, oh, oh, cin, kh, kh], L.F_MULADD, 0, L.P_ID, T.proj_map(7, (0, 1, 2, 3)),
+                              [mi, T.proj_map(7, (1, 4, 5, 6))], [[n, cin, h, h], [cout, cin, kh, kh]], [I32, I32], acc_dtype=I32)
+    assert convi == ("linear", 0, 0)
+    # pad: the result is written through o + lo; rows of the padded result are longer than x's, so h and w stay apart
+    mo = [[0] * 5 for _ in range(4)]
+    for d_ in range(4):
+        mo[d_][d_] = 1
+    mo[2][4], mo[3][4] = 1, 2
+    pad = T.mrp_cell_kernel([8, 16, 35, 34], shape_in, L.F_FIRST, 0.0, L.P_ID, mo, [T.id_map(4)], [shape_in], [F32])
+    assert pad == ("compiled", 3, 0)
+    # a read through reshape_map (floordiv / rem) is interpreted
+    rm = T.reshape_map([6, 4], [24])
+    resh = T.mrp_cell_kernel([24], [24], L.F_FIRST, 0.0, L.P_ID, T.id_map(1), [rm], [[6, 4]], [F32])
+    assert resh[0] == "interpreted"
