@@ -1,6 +1,9 @@
 // UNVERIFIED -- not compiled anywhere: the reference's toolchain is absent where this was written (see patches/README.md).
-// Every helper has a body, written against the reference's headers as read; names that could not be checked against a
-// build (math::isa_f, math::tri::tanh, World::externals()[sym], the CPS wrapper of mim_cu_check) are the first things to fix.
+// Every helper has a body, written against the reference's headers as read. Every World / Def / Lam / Axm member it calls was
+// looked up there (math::isa_f: include/mim/plug/math/math.h:55; math::tri::tanh: src/mim/plug/math/math.mim:126;
+// World::Externals::operator[](Sym): include/mim/world.h:195; Def::externalize: include/mim/def.h:570; World::mut_con,
+// type_i32, lit_i32: include/mim/world.h:427, 637, 586; Lam::ret_var: include/mim/lam.h:136) -- their existence and arity,
+// not their behaviour. What no header shows is the CPS wrapper of mim_cu_check assumed below: the first thing to fix.
 //
 // Drop-in body for mim::plug::gpu::phase::LowerMapReduce::lower_map_reduce_post
 // (src/mim/plug/gpu/phase/lower_map_reduce.cpp:317-395 in MimIR). It keeps that function's structure -- decode with
