@@ -221,6 +221,9 @@ enum {
     /* unary (y operand ignored) */
     MIMK_OP_RELU = 16, MIMK_OP_TANH = 17, MIMK_OP_EXP = 18, MIMK_OP_SILU = 19, MIMK_OP_NEG = 20, MIMK_OP_COPY = 21,
     MIMK_OP_SQUARE = 22, MIMK_OP_ABS = 23,
+    /* the rest of math.mim's unary operators over F that tensor programs apply elementwise: rt.sq (math.mim:147), rrt =
+     * 1 / rt.sq (:297-298), exp.log / exp.exp2 / exp.log2 (:167-169), slf = 1 / (1 + exp(-x)) (:283-284) */
+    MIMK_OP_SQRT = 24, MIMK_OP_RSQRT = 25, MIMK_OP_LOG = 26, MIMK_OP_EXP2 = 27, MIMK_OP_LOG2 = 28, MIMK_OP_SIGMOID = 29,
 };
 /* An elementwise operator with a unary one applied to its result -- outer(inner(x, y)): one more level of producer
  * inlining for elementwise consumers (relu(x + bias), tanh(x * y), |x - y| ...). inner: any MIMK_OP_*; outer: a unary one. */

@@ -17,6 +17,7 @@ POST_ID, POST_BIAS, POST_BIAS_RELU, POST_BIAS_TANH, POST_RELU, POST_SILU, POST_A
 B_KN, B_NK = 0, 1
 OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MAX, OP_MIN, OP_SUBEXP = range(7)
 OP_RELU, OP_TANH, OP_EXP, OP_SILU, OP_NEG, OP_COPY, OP_SQUARE, OP_ABS = range(16, 24)
+OP_SQRT, OP_RSQRT, OP_LOG, OP_EXP2, OP_LOG2, OP_SIGMOID = range(24, 30)
 E_DEVICE_WAIT = 7
 ROWS_SOFTMAX, ROWS_RMSNORM, ROWS_SOFTMAX_RMSNORM = 0, 1, 2
 

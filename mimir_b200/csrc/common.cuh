@@ -78,7 +78,7 @@ bool mrp_try_route(const mimk_mrp_desc& d, void* stream, int* status);
 // What a descriptor's access maps spell, whatever its size (the router itself leaves small instances on the per-cell
 // kernel): route MIMK_ROUTE_*, and the arguments of the specialised entry point that would take it.
 inline bool op_is_binary(int op) { return op >= MIMK_OP_ADD && op <= MIMK_OP_SUBEXP; }
-inline bool op_is_unary(int op) { return op >= MIMK_OP_RELU && op <= MIMK_OP_ABS; }  // COPY included
+inline bool op_is_unary(int op) { return op >= MIMK_OP_RELU && op <= MIMK_OP_SIGMOID; }  // COPY included
 // A (possibly composed) elementwise operator taken apart; false when it names an unknown part.
 inline bool decode_op(int op, int* inner, int* outer) {
     *inner = op, *outer = MIMK_OP_COPY;
@@ -137,6 +137,12 @@ __device__ __forceinline__ float apply_op_plain(int op, float a, float b) {
         case MIMK_OP_NEG: return -a;
         case MIMK_OP_SQUARE: return a * a;
         case MIMK_OP_ABS: return fabsf(a);
+        case MIMK_OP_SQRT: return sqrtf(a);
+        case MIMK_OP_RSQRT: return 1.f / sqrtf(a);  // math.rrt is a division by rt.sq, not an approximation
+        case MIMK_OP_LOG: return logf(a);
+        case MIMK_OP_EXP2: return exp2f(a);
+        case MIMK_OP_LOG2: return log2f(a);
+        case MIMK_OP_SIGMOID: return 1.f / (1.f + expf(-a));
         default: return a;
     }
 }

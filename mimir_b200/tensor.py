@@ -24,7 +24,8 @@ _POST = {None: L.POST_ID, "id": L.POST_ID, "bias": L.POST_BIAS, "bias_relu": L.P
 _BINOP = {"add": L.OP_ADD, "sub": L.OP_SUB, "mul": L.OP_MUL, "div": L.OP_DIV, "max": L.OP_MAX, "min": L.OP_MIN,
           "subexp": L.OP_SUBEXP}
 _UNOP = {"relu": L.OP_RELU, "tanh": L.OP_TANH, "exp": L.OP_EXP, "silu": L.OP_SILU, "neg": L.OP_NEG, "copy": L.OP_COPY,
-         "square": L.OP_SQUARE, "abs": L.OP_ABS}
+         "square": L.OP_SQUARE, "abs": L.OP_ABS, "sqrt": L.OP_SQRT, "rsqrt": L.OP_RSQRT, "log": L.OP_LOG, "exp2": L.OP_EXP2,
+         "log2": L.OP_LOG2, "sigmoid": L.OP_SIGMOID}
 
 
 def _stream() -> int:

@@ -117,7 +117,8 @@ enum {
     // (src/mim/plug/tensor/phase/fuse.cpp:183-358): id = MO_F_COMPOSED | fold | inner << 8 | outer << 16 computes
     // fold(acc, outer(inner(u, v))) in f32, one rounding per operation. fold: 0 add, 2 fmax, 3 fmin, 4 first; inner / outer:
     // 0 add, 1 sub, 2 mul, 3 div, 4 fmax, 5 fmin, 6 exp(u - v); 16 relu, 17 tanh, 18 exp, 19 x / (1 + exp(-x)), 20 neg,
-    // 21 identity, 22 square, 23 abs.
+    // 21 identity, 22 square, 23 abs, 24 sqrt, 25 1 / sqrt, 26 log, 27 exp2, 28 log2, 29 1 / (1 + exp(-x))
+    // (math.mim:147, 297-298, 167-169, 283-284).
     MO_F_COMPOSED = 0x01000000,
 };
 enum {
@@ -146,6 +147,12 @@ static inline float elementwise(int op, float a, float b) {
         case 20: return -a;
         case 22: return a * a;
         case 23: return std::fabs(a);
+        case 24: return std::sqrt(a);
+        case 25: return 1.0f / std::sqrt(a);
+        case 26: return std::log(a);
+        case 27: return std::exp2(a);
+        case 28: return std::log2(a);
+        case 29: return 1.0f / (1.0f + std::exp(-a));
         default: return a;
     }
 }

@@ -103,7 +103,22 @@ std::optional<ElemOp> elem_op(const Def* v) {
         if (x->arg(2, 0) == x->arg(2, 1)) return ElemOp{MIMK_OP_SQUARE, x->arg(2, 0), nullptr};
         return ElemOp{MIMK_OP_MUL, x->arg(2, 0), x->arg(2, 1)};
     }
-    if (auto x = Axm::isa(math::arith::div, v)) return ElemOp{MIMK_OP_DIV, x->arg(2, 0), x->arg(2, 1)};
+    if (auto x = Axm::isa(math::arith::div, v)) {
+        // math.rrt and math.slf are lams over a division by then (math.mim:283-284, 297-298): 1 / rt.sq x, 1 / (1 + exp (0 - x))
+        if (auto one = Lit::isa<f32>(x->arg(2, 0)); one && *one == 1.f) {
+            if (auto r = Axm::isa(math::rt::sq, x->arg(2, 1))) return ElemOp{MIMK_OP_RSQRT, r->arg(), nullptr};
+            if (auto s = Axm::isa(math::arith::add, x->arg(2, 1)))
+                if (auto l = Lit::isa<f32>(s->arg(2, 0)); l && *l == 1.f)
+                    if (auto e = Axm::isa(math::exp::exp, s->arg(2, 1)))
+                        if (auto n = Axm::isa(math::arith::sub, e->arg()))
+                            if (auto z = Lit::isa<f32>(n->arg(2, 0)); z && *z == 0.f) return ElemOp{MIMK_OP_SIGMOID, n->arg(2, 1), nullptr};
+        }
+        return ElemOp{MIMK_OP_DIV, x->arg(2, 0), x->arg(2, 1)};
+    }
+    if (auto x = Axm::isa(math::rt::sq, v)) return ElemOp{MIMK_OP_SQRT, x->arg(), nullptr};
+    if (auto x = Axm::isa(math::exp::log, v)) return ElemOp{MIMK_OP_LOG, x->arg(), nullptr};
+    if (auto x = Axm::isa(math::exp::exp2, v)) return ElemOp{MIMK_OP_EXP2, x->arg(), nullptr};
+    if (auto x = Axm::isa(math::exp::log2, v)) return ElemOp{MIMK_OP_LOG2, x->arg(), nullptr};
     if (auto x = Axm::isa(math::extrema::fmax, v)) return ElemOp{MIMK_OP_MAX, x->arg(2, 0), x->arg(2, 1)};
     if (auto x = Axm::isa(math::extrema::fmin, v)) return ElemOp{MIMK_OP_MIN, x->arg(2, 0), x->arg(2, 1)};
     if (auto x = Axm::isa(math::exp::exp, v)) {

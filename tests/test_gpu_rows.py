@@ -279,6 +279,16 @@ def test_elementwise_operators_with_a_unary_one_behind_them(T):
     vn = v.cpu().numpy().astype(np.float64)
     assert nerr(f64(T.binary_ax("mul", 1, x, v, then="tanh")), np.tanh(xn * vn[:, None, :])) < TOL_F32
     assert nerr(f64(T.unary("square", x, then="neg")), -(xn * xn)) < TOL_F32
+    # the rest of math.mim's unary operators, alone, behind a binary one, and inlined into a fold
+    pos = np.abs(xn) + 0.5
+    xp = T.unary("abs", x, then=None)
+    xp = T.binary("add", xp, torch.full_like(xp, 0.5))
+    for name, fn in (("sqrt", np.sqrt), ("rsqrt", lambda v: 1 / np.sqrt(v)), ("log", np.log), ("log2", np.log2)):
+        assert nerr(f64(T.unary(name, xp)), fn(pos)) < TOL_F32
+    assert nerr(f64(T.unary("exp2", x)), np.exp2(xn)) < TOL_F32
+    assert nerr(f64(T.unary("sigmoid", x)), 1 / (1 + np.exp(-xn))) < TOL_F32
+    assert nerr(f64(T.binary("mul", x, x, then="sqrt")), np.abs(xn)) < TOL_F32                       # sqrt(x * x)
+    assert nerr(f64(T.reduce_fused("sum", 1, xp, "log")), np.log(pos).sum(axis=1)) < TOL_F32          # a sum of logarithms
     big, bias = randn((512, 4096), 54), randn((512,), 55)
     got = T.binary_ax("add", 1, big, bias, then="relu", out_dtype=torch.bfloat16)          # the 128-bit path, bf16 out
     want = np.maximum(big.cpu().numpy().astype(np.float64) + bias.cpu().numpy().astype(np.float64)[:, None], 0)

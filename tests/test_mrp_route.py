@@ -192,6 +192,14 @@ def test_composed_combiners_in_the_oracle():
     assert np.array_equal(den, fixed)
     mabs = mo.map_reduce_post((5, 3), (5, 3, 7), mo.f_composed(2, 23), np.float32(-np.inf), mo.P_ID, proj(3, (0, 1)), [proj(3, (0, 2, 1))], [x])
     assert np.array_equal(mabs, np.abs(x).max(axis=1))
+    # the rest of math.mim's unary operators (sqrt, 1 / sqrt, log, exp2, log2, logistic), each behind |x| + 1 or alone
+    p = (np.abs(x) + np.float32(1)).astype(np.float32)
+    for code, fn in ((24, np.sqrt), (25, lambda v: np.float32(1) / np.sqrt(v)), (26, np.log), (28, np.log2)):
+        got = mo.map_reduce_post((5, 7, 3), (5, 7, 3), mo.f_composed(4, code), np.float32(0), mo.P_ID, proj(3, (0, 1, 2)), [proj(3, (0, 1, 2))], [p])
+        assert np.allclose(got, fn(p).astype(np.float32), rtol=2e-7, atol=0)
+    for code, fn in ((27, np.exp2), (29, lambda v: np.float32(1) / (np.float32(1) + np.exp(-v)))):
+        got = mo.map_reduce_post((5, 7, 3), (5, 7, 3), mo.f_composed(4, code), np.float32(0), mo.P_ID, proj(3, (0, 1, 2)), [proj(3, (0, 1, 2))], [x])
+        assert np.allclose(got, fn(x).astype(np.float32), rtol=2e-7, atol=0)
 
 
 def test_elementwise_operators_with_a_unary_one_behind_them(TL):
