@@ -268,3 +268,40 @@ def test_which_per_cell_kernel_runs_a_generic_instance(TL):
     rm = T.reshape_map([6, 4], [24])
     resh = T.mrp_cell_kernel([24], [24], L.F_FIRST, 0.0, L.P_ID, T.id_map(1), [rm], [[6, 4]], [F32])
     assert resh[0] == "interpreted"
+
+
+def test_loop_merging_of_the_compiled_walk_on_copies_and_grouped_windows(TL):
+    T, L = TL
+    # flip: every axis reversed -- x's steps are the negated row-major strides, so all four loops still merge into one
+    s = [4, 6, 10, 12]
+    fm = [[0] * 5 for _ in range(4)]
+    for d_ in range(4):
+        fm[d_][d_], fm[d_][4] = -1, s[d_] - 1
+    assert T.mrp_cell_kernel(s, s, L.F_FIRST, 0.0, L.P_ID, T.id_map(4), [fm], [s], [F32]) == ("compiled", 1, 0)
+    # rows 1, 3, 5, ... of a matrix: rows and columns stay apart (x steps two rows where the result steps one)
+    sm = [[2, 0, 1], [0, 1, 0]]
+    assert T.mrp_cell_kernel([8, 32], [8, 32], L.F_FIRST, 0.0, L.P_ID, T.id_map(2), [sm], [[17, 32]], [F32]) == ("compiled", 2, 0)
+    # the patch gather of a convolution run as a contraction: (n, oh, ow, ci, kh, kw) -> six loops, none of them mergeable
+    # (3x3 windows over 12 columns: neither the rows of windows nor the windows of a row tile x)
+    n, cin, h, kh = 2, 8, 12, 3
+    oh = h - kh + 1
+    mi = [[0] * 7 for _ in range(4)]
+    mi[0][0], mi[1][3] = 1, 1
+    mi[2][1], mi[2][4] = 1, 1
+    mi[3][2], mi[3][5] = 1, 1
+    shape = [n, oh, oh, cin, kh, kh]
+    assert T.mrp_cell_kernel(shape, shape, L.F_FIRST, 0.0, L.P_ID, T.id_map(6), [mi], [[n, cin, h, h]], [F32]) == ("compiled", 6, 0)
+    # grouped convolution, loops (n, g, co, oh, ow | ci, kh, kw) over x viewed [n, g, ci, H, W] and w viewed [g, co, ci, kh, kw]
+    g, co, ci = 4, 2, 3
+    mx = [[0] * 9 for _ in range(5)]
+    mx[0][0], mx[1][1], mx[2][5] = 1, 1, 1
+    mx[3][3], mx[3][6] = 1, 1
+    mx[4][4], mx[4][7] = 1, 1
+    so = [n, g, co, oh, oh]
+    got = T.mrp_cell_kernel(so, so + [ci, kh, kh], L.F_MULADD, 0.0, L.P_ID, T.proj_map(8, (0, 1, 2, 3, 4)),
+                            [mx, T.proj_map(8, (1, 2, 5, 6, 7))], [[n, g, ci, h, h], [g, co, ci, kh, kh]], [F32, F32])
+    assert got == ("compiled", 5, 3)
+    # four reduction loops that do not merge: beyond the compiled walk's three, the interpreting linear walk takes it
+    m4 = [[0, 2, 0, 0, 0, 0], [0, 0, 2, 0, 0, 0], [0, 0, 0, 2, 0, 0], [0, 0, 0, 0, 2, 0]]
+    got = T.mrp_cell_kernel([5], [5, 2, 2, 2, 2], L.F_ADD, 0.0, L.P_ID, T.proj_map(5, (0,)), [m4], [[3, 3, 3, 3]], [F32])
+    assert got == ("linear", 0, 0)
